@@ -1,0 +1,275 @@
+"""CPU oracle: numpy restatement of the reference's CPU (LLVM) backend for the LLM decode path.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the product package imports this module; it is
+the checker used by ``tests/``, by ``__graft_entry__.smoke()`` and by the
+``cpu_baseline`` / ``--impl reference`` legs of ``bench.py``.
+
+Parity status: the reference itself (Rust + LLVM 18 + OpenBLAS) cannot be built in this
+environment, so the restatement is pinned against the reference's own golden vectors
+(``models/test/single_op/*`` of the reference, converted by ``tests/golden/make_golden.py``)
+and against the ``tiny-llama-random`` greedy ids of
+``crates/llm/tests/tinyllama_random.rs:23-24``.  M=1 int8 decode beyond the 3x8 toy fixture
+is pinned by restatement only.
+
+Every function names the reference code it follows (paths relative to the reference root).
+All arithmetic is float32 unless stated; bf16 values travel as uint16 bit patterns or as
+float32 arrays that are exactly representable in bf16.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+# --------------------------------------------------------------------------------------
+# storage conversions
+# --------------------------------------------------------------------------------------
+
+
+def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    """bf16 bit pattern -> f32 by a 16-bit left shift (src/codegen/cpu/translator.rs:162-172)."""
+    return (np.asarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits_rne(x: np.ndarray) -> np.ndarray:
+    """f32 -> bf16 bits, round to nearest even, no NaN special case
+    (src/codegen/cpu/translator.rs:174-204: bias = 0x7FFF + ((bits >> 16) & 1))."""
+    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    bias = ((bits >> 16) & 1) + np.uint32(0x7FFF)
+    return ((bits + bias) >> 16).astype(np.uint16)
+
+
+def f32_to_bf16_bits_trunc(x: np.ndarray) -> np.ndarray:
+    """f64/f32 host tensor -> bf16 bits by truncation, the conversion applied to graph inputs
+    and initializers (src/session.rs:171-175: ``(x as f32).to_bits() >> 16``)."""
+    bits = np.asarray(x, dtype=np.float64).astype(np.float32).view(np.uint32)
+    return (bits >> 16).astype(np.uint16)
+
+
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    """f32 -> nearest bf16, returned as f32 (a kernel's bf16 store followed by a reload)."""
+    return bf16_bits_to_f32(f32_to_bf16_bits_rne(x))
+
+
+def round_f16(x: np.ndarray) -> np.ndarray:
+    """f32 -> nearest fp16 -> f32.  fp16 is an extension: the reference has no fp16 tensor type
+    (src/tensor/types.rs:278-282); store points are the same as for bf16."""
+    return np.asarray(x, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+
+def store_round(x: np.ndarray, dtype: str) -> np.ndarray:
+    """Model one kernel's output store in storage dtype ``dtype`` ('f32' | 'bf16' | 'f16')."""
+    x = np.asarray(x, dtype=np.float32)
+    if dtype == "f32":
+        return x
+    if dtype == "bf16":
+        return round_bf16(x)
+    if dtype == "f16":
+        return round_f16(x)
+    raise ValueError(dtype)
+
+
+# --------------------------------------------------------------------------------------
+# DequantizeLinear / DequantMatMul
+# --------------------------------------------------------------------------------------
+
+
+def dequantize_linear(x: np.ndarray, scale: np.ndarray, axis: int = 0) -> np.ndarray:
+    """out = f32(x) * scale[axis_idx]  (src/codegen/cpu/translator.rs:206-282)."""
+    shape = [1] * x.ndim
+    shape[axis] = x.shape[axis]
+    return x.astype(np.float32) * np.asarray(scale, dtype=np.float32).reshape(shape)
+
+
+def dequant_matmul_variant_a(act: np.ndarray, wq: np.ndarray, scale: np.ndarray) -> np.ndarray:
+    """M=1 fused decode loop: out[n] = scale[n] * sum_k f32(act[k]) * f32(wq[n,k])
+    (src/codegen/cpu/translator.rs:3208-3313; same formula as the CUDA GEMV,
+    src/codegen/cuda/cpp/dequant_gemv.cuh:11-59).  act [M,K] f32, wq [N,K] int8, scale [N]."""
+    acc = act.astype(np.float32) @ wq.astype(np.float32).T
+    return acc * np.asarray(scale, dtype=np.float32)[None, :]
+
+
+def dequant_matmul_variant_b(act: np.ndarray, wq: np.ndarray, scale: np.ndarray) -> np.ndarray:
+    """Tensor-core tile of the reference: the weight is dequantised and ROUNDED TO BF16 before
+    the product, f32 accumulate (src/codegen/cuda/cpp/dequant_matmul_wmma.cuh:65-76,87-192).
+    The reference's dequant_matmul_MxNxK golden outputs equal this variant after the bf16 store."""
+    w = round_bf16(wq.astype(np.float32) * np.asarray(scale, dtype=np.float32)[:, None])
+    return act.astype(np.float32) @ w.T
+
+
+def dequant_matmul_variant_c(act: np.ndarray, wq: np.ndarray, scale: np.ndarray) -> np.ndarray:
+    """CPU M>1 path: dequantise W to an f32 workspace (scale[n]*f32(w)), then sgemm(A, B^T)
+    (src/codegen/cpu/translator.rs:3042-3111).  The BLAS summation order is unspecified."""
+    w = dequantize_linear(wq, scale, 0)
+    return act.astype(np.float32) @ w.T
+
+
+def dequant_matmul(act: np.ndarray, wq: np.ndarray, scale: np.ndarray) -> np.ndarray:
+    """Reference CPU dispatch (src/codegen/cpu/translator.rs:3045-3049): M == 1 -> variant A,
+    otherwise variant C.  ``act`` may have leading dims; they are flattened to M."""
+    k = wq.shape[1]
+    a2 = act.reshape(-1, k)
+    out = dequant_matmul_variant_a(a2, wq, scale) if a2.shape[0] == 1 else dequant_matmul_variant_c(a2, wq, scale)
+    return out.reshape(act.shape[:-1] + (wq.shape[0],))
+
+
+# --------------------------------------------------------------------------------------
+# Attention / KV cache
+# --------------------------------------------------------------------------------------
+
+
+def attention(q, k, v, scale, active_seq_kv=None, is_causal=False, mask=None, k_scale=None, v_scale=None):
+    """Streaming-softmax attention exactly as the CPU kernel orders it
+    (src/codegen/cpu/translator.rs:4440-5008).
+
+    q [B,Hq,Sq,D], k/v [B,Hkv,Sk,D] (float, or int8 with per-token scales [B,Hkv,Sk]).
+    kv head = q head // (Hq/Hkv).  k_bound = min(active, causal cap, Sk) where the causal cap of
+    query row sq is (active - Sq) + sq + 1.  Per kv row: qk = (q.k)[*k_scale]*scale [+mask];
+    m' = max(m, qk); f = exp(m-m'); e = exp(qk-m'); s = s*f+e; o = o*f + e[*v_scale]*v; out = o/s.
+    The loop over kv rows is vectorised over (b, h, sq) here; the recurrence itself is kept.
+    """
+    q = np.asarray(q, dtype=np.float32)
+    b, hq, sq, d = q.shape
+    hkv, sk = k.shape[1], k.shape[2]
+    group = hq // hkv
+    active = sk if active_seq_kv is None else int(active_seq_kv)
+    kf = np.repeat(np.asarray(k).astype(np.float32), group, axis=1)
+    vf = np.repeat(np.asarray(v).astype(np.float32), group, axis=1)
+    ks = None if k_scale is None else np.repeat(np.asarray(k_scale, dtype=np.float32), group, axis=1)
+    vs = None if v_scale is None else np.repeat(np.asarray(v_scale, dtype=np.float32), group, axis=1)
+    bounds = np.full((sq,), active, dtype=np.int64)
+    if is_causal:
+        past = active - sq
+        bounds = np.minimum(bounds, past + np.arange(sq) + 1)
+    bounds = np.minimum(bounds, sk)
+    m = np.full((b, hq, sq), -np.inf, dtype=np.float32)
+    s = np.zeros((b, hq, sq), dtype=np.float32)
+    o = np.zeros((b, hq, sq, d), dtype=np.float32)
+    fscale = np.float32(scale)
+    for r in range(int(bounds.max()) if sq else 0):
+        live = (r < bounds)[None, None, :]
+        qk = np.einsum("bhsd,bhd->bhs", q, kf[:, :, r, :]).astype(np.float32)
+        if ks is not None:
+            qk = qk * ks[:, :, r][:, :, None]
+        qk = qk * fscale
+        if mask is not None:
+            qk = qk + np.broadcast_to(mask, (b, hq, sq, sk))[..., r].astype(np.float32)
+        m_new = np.where(live, np.maximum(m, qk), m)
+        with np.errstate(invalid="ignore"):
+            f = np.where(live, np.exp(m - m_new), np.float32(1)).astype(np.float32)
+            e = np.where(live, np.exp(qk - m_new), np.float32(0)).astype(np.float32)
+        s = s * f + e
+        e_eff = e if vs is None else e * vs[:, :, r][:, :, None]
+        o = o * f[..., None] + e_eff[..., None] * vf[:, :, r, :][:, :, None, :]
+        m = m_new
+    with np.errstate(invalid="ignore", divide="ignore"):
+        return (o / s[..., None]).astype(np.float32)
+
+
+def attention_softmax_f64(q, k, v, scale, active):
+    """Plain two-pass softmax attention in float64: the in-test reference the engine's own KV
+    session test uses (tests/session_state.rs:122-150)."""
+    q = np.asarray(q, dtype=np.float64)
+    b, hq, sq, d = q.shape
+    group = hq // k.shape[1]
+    kf = np.repeat(np.asarray(k, dtype=np.float64), group, axis=1)[:, :, :active]
+    vf = np.repeat(np.asarray(v, dtype=np.float64), group, axis=1)[:, :, :active]
+    logits = np.einsum("bhsd,bhkd->bhsk", q, kf) * scale
+    logits -= logits.max(axis=-1, keepdims=True)
+    p = np.exp(logits)
+    p /= p.sum(axis=-1, keepdims=True)
+    return np.einsum("bhsk,bhkd->bhsd", p, vf)
+
+
+def ring_phys_index(rank: int, ring_sink: int, ring_window: int, ring_start: int) -> int:
+    """Logical kv rank -> physical cache row for the sink+ring layout
+    (src/codegen/cuda/cpp/common.cuh:55-60).  ring_window == 0 means plain contiguous."""
+    if ring_window == 0 or rank < ring_sink:
+        return rank
+    return ring_sink + (ring_start + (rank - ring_sink)) % ring_window
+
+
+def kv_cache_update(cache: np.ndarray, new: np.ndarray, offset: int) -> np.ndarray:
+    """In place: cache[b,h,offset+t,:] = new[b,h,t,:] (src/codegen/cpu/translator.rs:4374-4424;
+    CUDA src/codegen/cuda/cpp/kvcache_update.cuh:6-26).  No bounds check in the reference."""
+    t = new.shape[2]
+    cache[:, :, offset:offset + t, :] = new
+    return cache
+
+
+# --------------------------------------------------------------------------------------
+# glue ops
+# --------------------------------------------------------------------------------------
+
+
+def rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    """y = x * (1/sqrt(mean(x^2)+eps)) * w over the last axis, f32
+    (src/codegen/cpu/translator.rs:5896-6027; src/codegen/cuda/cpp/rms_norm.cuh:9-59)."""
+    x = np.asarray(x, dtype=np.float32)
+    ms = (x * x).sum(axis=-1, keepdims=True, dtype=np.float32) / np.float32(x.shape[-1])
+    inv = np.float32(1.0) / np.sqrt(ms + np.float32(eps), dtype=np.float32)
+    return (x * inv) * np.asarray(w, dtype=np.float32)
+
+
+def rope_table(max_seq: int, head_dim: int, base: float, dtype: str):
+    """cos/sin tables [max_seq, head_dim]: angle = p * inv_freq[j % (D/2)],
+    inv_freq[i] = 1/base^(2i/D), computed in f64 (crates/llm/src/builder.rs:359-393, ``base`` is
+    an f32 widened to f64) and then converted like any initializer: f64 -> f32 (nearest) ->
+    bf16 by TRUNCATION (src/session.rs:171-175).  For 'f32' storage only the f64->f32 step applies;
+    'f16' (extension) rounds to nearest."""
+    half = head_dim // 2
+    base64 = float(np.float32(base))
+    inv_freq = np.array([1.0 / math.pow(base64, 2.0 * i / head_dim) for i in range(half)], dtype=np.float64)
+    ang = np.arange(max_seq, dtype=np.float64)[:, None] * inv_freq[np.arange(head_dim) % half][None, :]
+    cos, sin = np.cos(ang), np.sin(ang)
+    if dtype == "bf16":
+        return bf16_bits_to_f32(f32_to_bf16_bits_trunc(cos)), bf16_bits_to_f32(f32_to_bf16_bits_trunc(sin))
+    if dtype == "f16":
+        return round_f16(cos.astype(np.float32)), round_f16(sin.astype(np.float32))
+    return cos.astype(np.float32), sin.astype(np.float32)
+
+
+def rope(x: np.ndarray, cos_rows: np.ndarray, sin_rows: np.ndarray) -> np.ndarray:
+    """Half-split rotation out = x*cos + concat(-x_high, x_low)*sin
+    (crates/llm/src/builder.rs:402-438; fused form src/codegen/cuda/cpp/rope.cuh:19-46).
+    x [..., S, D]; cos_rows/sin_rows [S, D] are the table rows already gathered by position."""
+    x = np.asarray(x, dtype=np.float32)
+    half = x.shape[-1] // 2
+    rot = np.concatenate([-x[..., half:], x[..., :half]], axis=-1)
+    return x * cos_rows.astype(np.float32) + rot * sin_rows.astype(np.float32)
+
+
+def swish_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """SwiGLU inner product: (g / (1 + exp(-g))) * u in f32
+    (src/codegen/cuda/kernel.rs:763; CPU src/codegen/cpu/translator.rs:459-476,994-1001)."""
+    g = np.asarray(gate, dtype=np.float32)
+    with np.errstate(over="ignore"):
+        return (g / (np.float32(1) + np.exp(-g, dtype=np.float32))) * np.asarray(up, dtype=np.float32)
+
+
+def argmax_last(logits: np.ndarray) -> int:
+    """Greedy pick with the reference's tie rule: ``max_by(partial_cmp)`` returns the LAST index
+    among equal maxima (crates/llm/src/session.rs:683-690)."""
+    logits = np.asarray(logits).ravel()
+    return int(len(logits) - 1 - np.argmax(logits[::-1]))
+
+
+# --------------------------------------------------------------------------------------
+# quantizer
+# --------------------------------------------------------------------------------------
+
+
+def quantize_per_channel(w: np.ndarray):
+    """int8 per-output-channel quantizer (crates/llm/src/quantize.rs:124-169): scale = max|row|/127
+    (zero row -> 1.0); q = clamp(round_half_away(x / scale), -128, 127) using the f32 scale; the
+    stored scale is then rounded to bf16 (RNE, NaN -> 0x7FC0).  Returns (int8 [N,K], bf16 bits [N])."""
+    w = np.asarray(w, dtype=np.float32)
+    rows = w.reshape(w.shape[0], -1)
+    max_abs = np.abs(rows).max(axis=1)
+    scale = np.where(max_abs == 0, np.float32(1.0), max_abs / np.float32(127.0)).astype(np.float32)
+    ratio = rows / scale[:, None]
+    rounded = np.sign(ratio) * np.floor(np.abs(ratio) + np.float32(0.5))  # f32::round = half away from zero
+    q = np.clip(rounded, -128, 127).astype(np.int8).reshape(w.shape)
+    bits = f32_to_bf16_bits_rne(scale)
+    bits = np.where(np.isnan(scale), np.uint16(0x7FC0), bits)
+    return q, bits

@@ -1,0 +1,149 @@
+"""Pins the CPU oracle (numpy and C) against the reference's own golden vectors (CPU only)."""
+import numpy as np
+import pytest
+
+from conftest import eq_with_epsilon
+from oracle import c_oracle, ref_ops as R
+from oracle.ref_model import LlamaConfig, OracleLlama
+
+DQMM = ["dequant_matmul", "dequant_matmul_16x16x16", "dequant_matmul_16x32x32", "dequant_matmul_32x32x64",
+        "dequant_matmul_64x64x128", "dequant_matmul_128x128x64", "dequant_matmul_24x48x40",
+        "dequant_matmul_17x17x17", "dequant_matmul_50x50x50", "dequant_matmul_80x96x96"]
+
+
+@pytest.mark.parametrize("name", DQMM)
+def test_dequant_matmul_goldens(single_op, name):
+    """Reference tolerance for these fixtures is 1e-1 'Either' (tests/single_op.rs:1201-1231).  The CPU
+    dispatch (variants A/C) must meet it; the tensor-core variant B reproduces the stored bf16 bits."""
+    fx = single_op(name)
+    act, wq, scale = fx.inputs
+    k = wq.shape[1]
+    a = R.bf16_bits_to_f32(act).reshape(-1, k)
+    s = R.bf16_bits_to_f32(scale)
+    want = R.bf16_bits_to_f32(fx.outputs[0]).reshape(a.shape[0], -1)
+    for fn in (R.dequant_matmul_variant_a, R.dequant_matmul_variant_c, R.dequant_matmul):
+        ok, md = eq_with_epsilon(R.round_bf16(fn(a, wq, s)), want, 1e-1)
+        assert ok, (fn.__name__, md)
+    got_b = R.f32_to_bf16_bits_rne(R.dequant_matmul_variant_b(a, wq, s))
+    mism = int((got_b != fx.outputs[0].reshape(got_b.shape)).sum())
+    assert mism <= max(1, got_b.size // 200), f"variant B differs from golden bits in {mism}/{got_b.size}"
+    # C oracle, bf16 storage in/out
+    c_out = c_oracle.dequant_matmul_fused(act.reshape(-1, k), wq, scale)
+    ok, md = eq_with_epsilon(R.bf16_bits_to_f32(c_out), want, 1e-1)
+    assert ok, md
+    c_out = c_oracle.dequant_matmul_workspace(act.reshape(-1, k), wq, scale)
+    ok, md = eq_with_epsilon(R.bf16_bits_to_f32(c_out), want, 1e-1)
+    assert ok, md
+
+
+@pytest.mark.parametrize("name,n_in", [("attention_decode", 3), ("attention_decode_gqa", 3),
+                                       ("attention_decode_runtime_kv", 4), ("attention_causal", 3),
+                                       ("attention_no_causal", 3), ("attention_causal_large", 3)])
+def test_attention_goldens(single_op, name, n_in):
+    """Reference tolerance 1e-4 'Either' (tests/single_op.rs:906-985)."""
+    fx = single_op(name)
+    q, k, v = fx.inputs[:3]
+    active = int(fx.inputs[3]) if n_in == 4 else None
+    causal = bool(fx.attr("is_causal", 0))
+    scale = fx.attr("scale")
+    got = R.attention(q, k, v, scale, active, causal)
+    ok, md = eq_with_epsilon(got, fx.outputs[0], 1e-4)
+    assert ok, md
+    got_c = c_oracle.attention(q, k, v, scale, active, causal)
+    ok, md = eq_with_epsilon(got_c, fx.outputs[0], 1e-4)
+    assert ok, md
+
+
+def test_kv_cache_update_golden(single_op):
+    """Fixture graph is KVCacheUpdate followed by Sigmoid (tests/single_op.rs:951-957, eps 1e-5)."""
+    fx = single_op("kv_cache_update")
+    cache, new, offset = fx.inputs
+    upd = R.kv_cache_update(cache.copy(), new, int(offset))
+    ok, md = eq_with_epsilon(1.0 / (1.0 + np.exp(-upd.astype(np.float64))), fx.outputs[0], 1e-5)
+    assert ok, md
+    upd_c = c_oracle.kv_cache_update(cache.copy(), new, int(offset))
+    assert np.array_equal(upd, upd_c)
+
+
+def test_dequantize_linear_golden(single_op):
+    fx = single_op("dequantize_linear")
+    x, scale = fx.inputs
+    got = R.round_bf16(R.dequantize_linear(x, R.bf16_bits_to_f32(scale), fx.attr("axis", 0)))
+    ok, md = eq_with_epsilon(got, R.bf16_bits_to_f32(fx.outputs[0]), 1e-2)
+    assert ok, md
+
+
+def test_swish_golden(single_op):
+    fx = single_op("swish")
+    x = fx.inputs[0].astype(np.float32)
+    got = R.swish_mul(x, np.ones_like(x))
+    ok, md = eq_with_epsilon(got, fx.outputs[0], 1e-5)
+    assert ok, md
+
+
+def test_session_state_attention_reference():
+    """Streaming softmax == the two-pass f64 softmax the reference's KV session test checks against
+    (tests/session_state.rs:122-229): 3 decode steps appending to a zero-initialised cache."""
+    B, H, S_MAX, D = 1, 2, 8, 4
+    kc = np.zeros((B, H, S_MAX, D), np.float32)
+    vc = np.zeros((B, H, S_MAX, D), np.float32)
+
+    def data(step, kind):
+        i = np.arange(B * H * D, dtype=np.float64)
+        return np.clip(np.sin(i * 0.31 + step * 1.7 + kind * 2.4) * 0.5, -1, 1).astype(np.float32).reshape(B, H, 1, D)
+
+    for step in range(3):
+        q, k, v = data(step, 0), data(step, 1), data(step, 2)
+        R.kv_cache_update(kc, k, step)
+        R.kv_cache_update(vc, v, step)
+        got = R.attention(q, kc, vc, 1.0 / np.sqrt(D), step + 1)
+        want = R.attention_softmax_f64(q, kc, vc, 1.0 / np.sqrt(D), step + 1)
+        ok, md = eq_with_epsilon(got, want, 1e-4)
+        assert ok, md
+    assert not kc[:, :, 3:].any()
+
+
+def test_quantizer_known_answers():
+    """crates/llm/tests/quantize.rs:101-166 of the reference."""
+    w = np.array([[127.0, -127.0, 0.0, 64.0], [2.0, -1.0, 0.0, 0.5], [0, 0, 0, 0]], dtype=np.float32)
+    q, sbits = R.quantize_per_channel(w)
+    s = R.bf16_bits_to_f32(sbits)
+    assert np.allclose(s, [1.0, 2.0 / 127.0, 1.0], atol=1e-3)
+    assert q[0].tolist() == [127, -127, 0, 64]
+    assert q[1].tolist() == [127, -64, 0, 32]     # -63.5 and 31.75 round half away / to nearest
+    assert q[2].tolist() == [0, 0, 0, 0]
+    assert np.abs(q.astype(np.float32) * s[:, None] - w).max() < 0.02
+
+
+def test_argmax_takes_last_maximum():
+    assert R.argmax_last(np.array([1.0, 5.0, 5.0, 2.0])) == 2
+    assert R.argmax_last(np.array([7.0])) == 0
+
+
+def test_rope_table_truncates_to_bf16():
+    cos, sin = R.rope_table(8, 4, 10000.0, "bf16")
+    exact = np.cos(np.arange(8.0)[:, None] * np.array([1.0, 0.01, 1.0, 0.01])[None, :]).astype(np.float32)
+    bits = exact.view(np.uint32) >> 16
+    assert np.array_equal(R.f32_to_bf16_bits_rne(cos), bits.astype(np.uint16))
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("prefill_len", [None, 4])
+def test_tiny_llama_random_greedy_ids(tiny_llama, dtype, prefill_len):
+    """End-to-end pin: prompt "Hello" -> the 8 greedy ids of crates/llm/tests/tinyllama_random.rs:23-24,
+    for f32 and bf16 storage, token-by-token and through chunked prefill (:79-147)."""
+    cfg, weights, prompt, _, expected = tiny_llama
+    model = OracleLlama(LlamaConfig.from_hf(cfg), weights, dtype, max_seq_len=32)
+    got = model.generate(prompt, len(expected), prefill_len)
+    assert got[0].tolist() == expected.tolist()
+
+
+def test_tiny_llama_prefill_matches_decode_only_multi_turn(tiny_llama):
+    """crates/llm/tests/tinyllama_random.rs:84-142: two turns, prefill(4) vs decode-only give the same ids."""
+    cfg, weights, p1, p2, _ = tiny_llama
+    c = LlamaConfig.from_hf(cfg)
+    a = OracleLlama(c, weights, "f32", 32)
+    ref = a.generate(p1, 1)[0].tolist() + a.generate(p2, 3)[0].tolist()
+    b = OracleLlama(c, weights, "f32", 32)
+    got = b.generate(p1, 1, 4)[0].tolist() + b.generate(p2, 3, 4)[0].tolist()
+    assert ref == got
