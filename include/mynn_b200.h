@@ -1,0 +1,178 @@
+/*
+ * mynn_b200 — C ABI of the B200 (sm_100a) decode-path library.
+ *
+ * Drop-in boundary for the LLM decode hot path of kcvlex/my-nn-engine: the int8 weight-only
+ * DequantMatMul and GQA decode attention over the KV cache, the small operators between them, the
+ * tensor-parallel all-reduce, and a whole-step entry with the exact model_init / model /
+ * model_destroy signatures the engine's CUDA session resolves from its generated library.
+ *
+ * Conventions
+ *   - Every function returns 0 on success and a negative MYNN_E_* code otherwise; it never calls
+ *     exit() and never traps the device (the engine's generated code exits the process on any CUDA
+ *     error, src/codegen/cuda/cpp/common.cuh:7-43).  mynn_b200_last_error() gives the text.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream).  Launchers only enqueue.
+ *   - All tensor pointers are DEVICE pointers unless a parameter is documented as host memory.
+ *   - dtype codes: MYNN_F32 / MYNN_BF16 / MYNN_F16.  bf16 and f32 are the engine's float storage types
+ *     (src/tensor/types.rs:278-282); f16 is an extension with the same store points.
+ *   - There is no CPU fallback: without a CUDA device every launcher returns MYNN_E_CUDA.
+ *   - Thread safety: calls on distinct streams/states may run concurrently; a model state is
+ *     single-caller, as the engine serialises runs with its CUDA_LOCK (src/session/cuda.rs:36-40).
+ */
+#ifndef MYNN_B200_H_
+#define MYNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { MYNN_F32 = 0, MYNN_BF16 = 1, MYNN_F16 = 2 };
+enum { MYNN_OK = 0, MYNN_E_ARG = -1, MYNN_E_CUDA = -2, MYNN_E_UNSUPPORTED = -3, MYNN_E_COMM = -4, MYNN_E_STATE = -5 };
+/* weight layouts of DequantMatMul: [N,K] with per-row scale (axis 0, what DequantGemmFusion produces)
+ * or [K,N] with per-column scale (axis 1, the unfused DequantizeLinear -> MatMul graph). */
+enum { MYNN_W_NK = 0, MYNN_W_KN = 1 };
+
+const char *mynn_b200_last_error(void);
+/* Library/ABI version and the SM architecture the kernels were compiled for (100 for sm_100a). */
+int mynn_b200_abi_version(void);
+int mynn_b200_compiled_arch(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * DequantMatMul: out[m,n] = scale[n] * sum_k act[m,k] * wq[n,k]   (f32 accumulate, out in scale dtype)
+ * Replaces: Operator::DequantMatMul (src/graph/operator.rs:240-244) and its three CUDA kernels chosen in
+ * src/codegen/cuda.rs:1518-1652 (dequant_gemv.cuh:11-59, dequant_matmul_wmma.cuh:87-192,
+ * dequant_matmul.cuh:13-51); argument order follows the generated launch (out, act, wq, scale, M, N, K).
+ * act [M,K] act_dtype; wq int8 [N,K] (MYNN_W_NK) or [K,N] (MYNN_W_KN); scale [N] and out [M,N] out_dtype.
+ * Any M >= 0, N, K accepted (M == 0 is a no-op); shapes with K % 64 == 0 and N % 16 == 0 take the streaming
+ * tensor-core kernel, others a generic kernel. */
+int mynn_b200_dequant_matmul(void *stream, void *out, const void *act, const int8_t *wq, const void *scale, int M,
+                             int N, int K, int act_dtype, int out_dtype, int w_layout);
+
+/* Same product followed by a fused epilogue used by the decoder step (no counterpart kernel in the engine,
+ * which runs these as separate elementwise launches, src/codegen/cuda/kernel.rs:723-950):
+ *   residual != NULL : out = round(residual + round(product))      (two store points kept)
+ * wq must be [N,K]. */
+int mynn_b200_dequant_matmul_residual(void *stream, void *out, const void *act, const int8_t *wq, const void *scale,
+                                      const void *residual, int M, int N, int K, int dtype);
+
+/* ---------------------------------------------------------------------------------------------
+ * Attention (decode and generic).  out = softmax(scale * Q K^T [causal]) V with GQA.
+ * Replaces: Operator::Attention (src/graph/operator.rs:193-197), CUDA dispatch src/codegen/cuda.rs:1194-1403,
+ * kernels attention_decode (cpp/attention.cuh:495-606) and attention / attention_tc (:50-489).
+ * q [B,Hq,Sq,D], k/v [B,Hkv,cache_seq_len,D] contiguous, out [B,Hq,Sq,D], all `dtype`.
+ * active_seq_kv: valid kv rows.  If active_seq_kv_dev != NULL the value is read on the device from that int32
+ * (so a captured graph can be replayed as the sequence grows) and the host value is only an upper bound used
+ * for grid sizing.  workspace: device scratch of at least mynn_b200_attention_workspace_bytes(); it may be
+ * NULL when Sq > 1 or when the generic kernel is taken (D not 64/128, f32, or group size > 8). */
+size_t mynn_b200_attention_workspace_bytes(int B, int Hq, int Hkv, int D, int cache_seq_len);
+int mynn_b200_attention(void *stream, void *out, const void *q, const void *k, const void *v, float scale, int B,
+                        int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
+                        const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
+                        size_t workspace_bytes);
+
+/* KVCacheUpdate: cache[bh, offset+t, :] = new[bh, t, :] in place.
+ * Replaces: kvcache_update (cpp/kvcache_update.cuh:6-26, dispatch src/codegen/cuda.rs:2176-2228).
+ * Unlike the engine (no bounds check) rows that would land past cache_seq_len are rejected with MYNN_E_ARG when
+ * the offset is given on the host, and skipped on the device when offset_dev is used. */
+int mynn_b200_kv_cache_update(void *stream, void *cache, const void *new_kv, int BH, int cache_seq_len,
+                              int new_seq_len, int D, int offset, const int32_t *offset_dev, int dtype);
+
+/* RMSNorm over the last axis: y = x * rsqrt(mean(x^2) + eps) * w.  Replaces rms_norm (cpp/rms_norm.cuh:9-59). */
+int mynn_b200_rms_norm(void *stream, void *out, const void *x, const void *weight, float eps, int rows, int D,
+                       int dtype);
+/* out = round(a + b); y = RMSNorm(out).  Two store points of the engine's schedule in one launch. */
+int mynn_b200_add_rms_norm(void *stream, void *sum_out, void *norm_out, const void *a, const void *b,
+                           const void *weight, float eps, int rows, int D, int dtype);
+
+/* Half-split RoPE with per-token position gather.  x, out [outer, seq_len, D]; cos/sin tables [max_pos, D];
+ * position int64 [seq_len] on the device.  Replaces rope (cpp/rope.cuh:19-46). */
+int mynn_b200_rope(void *stream, void *out, const void *x, const void *cos_table, const void *sin_table,
+                   const int64_t *position, int outer, int seq_len, int D, int dtype);
+
+/* out = (gate / (1 + exp(-gate))) * up, f32 math.  Replaces the generated Swish*Mul elementwise group
+ * (src/codegen/cuda/kernel.rs:763). */
+int mynn_b200_swish_mul(void *stream, void *out, const void *gate, const void *up, int64_t n, int dtype);
+/* out = a + b (residual add, a standalone kernel in the engine's schedule). */
+int mynn_b200_add(void *stream, void *out, const void *a, const void *b, int64_t n, int dtype);
+
+/* Gather(DequantizeLinear(table int8 [V,H], scale [V]), ids): out[i,:] = round(table[ids[i],:] * scale[ids[i]]).
+ * Replaces dequantize_linear + gather_axis0_kernel (cpp/dequantize.cuh, cpp/gather.cuh), which dequantise the
+ * whole table every step (crates/llm/src/decoder.rs:828-835); only the gathered rows are touched here. */
+int mynn_b200_embed_gather_dequant(void *stream, void *out, const int8_t *table, const void *scale,
+                                   const int64_t *ids, int n_ids, int H, int V, int dtype);
+
+/* Greedy pick per row with the engine's tie rule (last index among equal maxima,
+ * crates/llm/src/session.rs:683-690).  logits [rows, V]; out_idx int32 [rows] on the device. */
+int mynn_b200_argmax_last(void *stream, int32_t *out_idx, const void *logits, int rows, int V, int dtype);
+
+/* ---------------------------------------------------------------------------------------------
+ * Tensor-parallel communicator.  Replaces trait Communicator {rank, world_size, all_reduce, barrier}
+ * (crates/comm/src/lib.rs:32-38), the process-global slot of src/collective.rs:1-20 and the CPU helper
+ * mynn_all_reduce(dst, src, num_elements, dtype) (src/codegen/cpu/kernels/all_reduce.rs:14-33).
+ * One process per GPU.  unique_id is the 128-byte NCCL id created on rank 0 by mynn_b200_comm_unique_id and
+ * distributed by the host (torch.distributed, a file, a socket ...). */
+int mynn_b200_comm_unique_id(void *id_out_128_bytes);
+int mynn_b200_comm_init(const void *unique_id_128_bytes, int rank, int world_size);
+int mynn_b200_comm_rank(void);
+int mynn_b200_comm_world_size(void);
+int mynn_b200_all_reduce(void *stream, void *dst, const void *src, int64_t num_elements, int dtype);
+int mynn_b200_comm_barrier(void *stream);
+int mynn_b200_comm_destroy(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Whole decode step.  Replaces the generated library's entry points resolved by SessionCUDA
+ * (src/session/cuda.rs:53-56,323-335; generated in src/codegen/cuda.rs:2727-2745):
+ *     void *model_init(void **initializer, void **session_state);
+ *     void  model(void *state, void **output, void **input);
+ *     void  model_destroy(void *state);
+ * The generated library is specialised per model at code-generation time; this one is specialised by a
+ * configuration call made once before model_init.  Ownership is the engine's: the host owns weights
+ * (initializer[i], device pointers) and KV buffers (session_state[i], device, zeroed by the host); the library
+ * owns activations, streams and graphs.  input[i] / output[i] are HOST pointers in storage dtype.
+ *
+ * initializer order (tp shard of each):
+ *   0 embed int8 [V,H], 1 embed scale [V], then per layer l (base 2+16*l):
+ *   +0 input_layernorm [H], +1..+2 q (wq, scale), +3..+4 k, +5..+6 v, +7..+8 o, +9 post_attention_layernorm,
+ *   +10..+11 gate, +12..+13 up, +14..+15 down; then final norm [H], lm_head wq, lm_head scale, cos table, sin table
+ *   ([max_seq_len, head_dim]).
+ * session_state order: per layer K cache then V cache, each [batch, n_kv_heads/tp, max_seq_len, head_dim].
+ * input: 0 input_ids int64 [batch,1]; 1 position_id int64 [1]; 2 past_len int64 []; 3 active_seq_kv int64 []
+ *        (crates/llm/src/session.rs:508-537).
+ * output: 0 logits [batch,1,vocab] storage dtype (output_mode 0) or int32 next-token ids [batch] (output_mode 1,
+ *         on-device last-max argmax). */
+typedef struct mynn_b200_model_config {
+    int32_t n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_seq_len, batch;
+    int32_t dtype;       /* MYNN_BF16 or MYNN_F16 */
+    int32_t output_mode; /* 0 logits, 1 token ids */
+    int32_t tp_rank, tp_world;
+    int32_t use_graph;   /* capture the step in a CUDA graph and replay it */
+    int32_t max_prefill; /* largest T accepted by mynn_b200_model_prefill (0 = decode only) */
+    float rms_eps;
+} mynn_b200_model_config;
+
+int mynn_b200_model_configure(const mynn_b200_model_config *cfg);
+void *model_init(void **initializer, void **session_state);
+void model(void *state, void **output, void **input);
+void model_destroy(void *state);
+/* Status of the last model_init / model call (they return void to keep the engine's signatures). */
+int mynn_b200_model_status(void);
+/* Device-resident variant of model(): ids and outputs stay on the device, no host synchronisation.
+ * ids_dev int64 [batch]; past_len is advanced by the caller.  out_dev as output[0] of model(). */
+int mynn_b200_model_step_device(void *state, void *stream, const int64_t *ids_dev, int past_len, void *out_dev);
+/* Prefill of T tokens per sequence starting at cache row past_len: the engine's prefill graph
+ * (crates/llm/src/session.rs:426-480) without its padding rows.  ids_host int64 [batch, T] (host memory); out_host
+ * receives what model() would return for the last position.  T <= max_prefill. */
+int mynn_b200_model_prefill(void *state, const int64_t *ids_host, int T, int past_len, void *out_host);
+/* Kernels launched by this library since load (monotonic). */
+int64_t mynn_b200_launch_count(void);
+
+/* Pinned host allocations, as the engine's common.cu exports (src/codegen/cuda/cpp/common.cu:4-13). */
+void *alloc_pinned(size_t bytes);
+void free_pinned(void *p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MYNN_B200_H_ */

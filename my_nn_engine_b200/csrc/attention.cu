@@ -1,0 +1,430 @@
+// GQA attention over the KV cache for sm_100a.
+//
+// Decode (one query token per sequence) is bound by reading K and V once from HBM.  The decode kernel
+//   * assigns one CTA to (kv-row split, kv head, batch) so that all query heads of a GQA group share a single
+//     pass over their KV head (the engine's kernel re-reads the KV head once per query head and walks the rows
+//     serially, src/codegen/cuda/cpp/attention.cuh:495-606);
+//   * lets each of its 4 warps take 16-row tiles and pull K and V straight from global memory into registers
+//     with 128-bit loads laid out as mma.m16n8k16 B fragments: the head-dim index (for QK^T) and the kv-row
+//     pairing (for PV) are permuted so that no shared-memory transpose is needed;
+//   * computes S = Q K^T and O += P V on the tensor cores with f32 accumulation and an online softmax in f32.
+//     The A tile has 16 rows but a group has at most 8 heads: rows 0-7 carry the high 16-bit part of P and rows
+//     8-15 the rounding remainder, so P enters the product with ~16 significant bits;
+//   * merges the warps through shared memory, and the splits through a small global workspace where the last
+//     CTA to arrive (atomic ticket, no spinning) combines the partial results and writes the output.
+// Everything else (f32 tensors, head dims other than 64/128, groups larger than 8, more than one query row,
+// causal masks) goes to a generic one-warp-per-query-row kernel that follows the CPU recurrence literally.
+#include <type_traits>
+
+#include "common.cuh"
+#include "ops_internal.cuh"
+
+namespace mynn {
+
+constexpr int kAttnWarps = 4;
+constexpr int kMaxSplits = 64;
+
+__device__ __forceinline__ uint4 ldg_16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void mma_kv(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    if constexpr (std::is_same<T, __half>::value) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// pack hi parts of (x, y) into one 32-bit register and the rounding remainders into another
+template <typename T>
+__device__ __forceinline__ void split_pack(float x, float y, uint32_t &hi, uint32_t &lo) {
+    const T xh = from_f32<T>(x), yh = from_f32<T>(y);
+    const T xl = from_f32<T>(x - to_f32<T>(xh)), yl = from_f32<T>(y - to_f32<T>(yh));
+    hi = (uint32_t)reinterpret_cast<const uint16_t &>(xh) | ((uint32_t)reinterpret_cast<const uint16_t &>(yh) << 16);
+    lo = (uint32_t)reinterpret_cast<const uint16_t &>(xl) | ((uint32_t)reinterpret_cast<const uint16_t &>(yl) << 16);
+}
+
+struct DecodeParams {
+    void *out;
+    const void *q, *k, *v;
+    float scale;
+    int Hq, Hkv, G, cache_seq;
+    int active_host;
+    const int32_t *active_dev;
+    int splits;
+    float *ws_o;    // [B*Hkv][splits][8][D]
+    float *ws_ml;   // [B*Hkv][splits][8][2]
+    unsigned *ws_ticket;  // [B*Hkv], zero before first use; the combining CTA re-zeroes it
+};
+
+// grid (splits, Hkv, B), block 128.
+template <typename T, int D>
+__global__ void __launch_bounds__(kAttnWarps * 32, 3) attention_decode_kernel(const DecodeParams p) {
+    constexpr int KS = D / 16;   // k16 steps of QK^T
+    constexpr int NTO = D / 8;   // n8 tiles of the output
+    constexpr int KCH = D / 32;  // 16-byte K chunks per lane per row
+    constexpr int VH = D / 64;   // 16-byte V chunks per lane per row
+    __shared__ float sm_o[kAttnWarps][8][D];
+    __shared__ float sm_m[kAttnWarps][8], sm_l[kAttnWarps][8];
+    __shared__ unsigned sm_last;
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int G = p.G;
+    int active = p.active_dev ? *p.active_dev : p.active_host;
+    active = max(0, min(active, p.cache_seq));
+    const int rows_per_split = (((active + p.splits - 1) / p.splits) + 15) & ~15;
+    const int row_beg = split * rows_per_split;
+    const int row_end = min(row_beg + rows_per_split, active);
+
+    const T *kbase = reinterpret_cast<const T *>(p.k) + (size_t)(b * p.Hkv + kvh) * p.cache_seq * D;
+    const T *vbase = reinterpret_cast<const T *>(p.v) + (size_t)(b * p.Hkv + kvh) * p.cache_seq * D;
+
+    // Q fragments of head g (zero for padding rows g >= G)
+    uint32_t qa0[KS], qa2[KS];
+    {
+        const T *qrow = reinterpret_cast<const T *>(p.q) + (size_t)(b * p.Hq + kvh * G + min(g, G - 1)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            const int d0 = 8 * (t + 4 * (ks >> 1)) + 4 * (ks & 1);
+            uint2 w = *reinterpret_cast<const uint2 *>(qrow + d0);
+            qa0[ks] = g < G ? w.x : 0u;
+            qa2[ks] = g < G ? w.y : 0u;
+        }
+    }
+
+    float o[NTO][4];
+#pragma unroll
+    for (int j = 0; j < NTO; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[j][i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    for (int base = row_beg + 16 * warp; base < row_end; base += 16 * kAttnWarps) {
+        const int last = row_end - 1;
+        // ---- issue all loads of this tile ----
+        uint4 kr[2][KCH], vr[4][VH];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            const T *kp = kbase + (size_t)min(base + 8 * nt + g, last) * D + 8 * t;
+#pragma unroll
+            for (int i = 0; i < KCH; i++) kr[nt][i] = ldg_16(kp + 32 * i);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int row = base + 2 * t + (r & 1) + 8 * (r >> 1);
+            const T *vp = vbase + (size_t)min(row, last) * D + 8 * g;
+#pragma unroll
+            for (int h = 0; h < VH; h++) vr[r][h] = ldg_16(vp + 64 * h);
+        }
+        // ---- S = Q K^T ----
+        float s[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+            for (int i = 0; i < KCH; i++) {
+                mma_kv<T>(s[nt], qa0[2 * i], 0u, qa2[2 * i], 0u, kr[nt][i].x, kr[nt][i].y);
+                mma_kv<T>(s[nt], qa0[2 * i + 1], 0u, qa2[2 * i + 1], 0u, kr[nt][i].z, kr[nt][i].w);
+            }
+        }
+        // ---- online softmax for head g: this lane holds kv rows base + 8nt + 2t + {0,1} ----
+        float pv[2][2];
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int row = base + 8 * nt + 2 * t + e;
+                pv[nt][e] = row < row_end ? s[nt][e] * p.scale : -INFINITY;
+                tmax = fmaxf(tmax, pv[nt][e]);
+            }
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        const float m_new = fmaxf(m_run, tmax);  // finite: the tile has at least one valid row
+        const float alpha = __expf(m_run - m_new);
+        float psum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                pv[nt][e] = __expf(pv[nt][e] - m_new);
+                psum += pv[nt][e];
+            }
+        l_run = l_run * alpha + psum;  // per-lane partial; lanes of a group are summed at the end
+        m_run = m_new;
+        uint32_t pa0, pa1, pa2, pa3;
+        split_pack<T>(pv[0][0], pv[0][1], pa0, pa1);
+        split_pack<T>(pv[1][0], pv[1][1], pa2, pa3);
+        // ---- O = O * alpha + P V ----
+#pragma unroll
+        for (int h = 0; h < VH; h++) {
+            const uint32_t r0[4] = {vr[0][h].x, vr[0][h].y, vr[0][h].z, vr[0][h].w};
+            const uint32_t r1[4] = {vr[1][h].x, vr[1][h].y, vr[1][h].z, vr[1][h].w};
+            const uint32_t r2[4] = {vr[2][h].x, vr[2][h].y, vr[2][h].z, vr[2][h].w};
+            const uint32_t r3[4] = {vr[3][h].x, vr[3][h].y, vr[3][h].z, vr[3][h].w};
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(r0[j >> 1], r1[j >> 1], sel);
+                const uint32_t b1 = __byte_perm(r2[j >> 1], r3[j >> 1], sel);
+                float(&acc)[4] = o[8 * h + j];
+                acc[0] *= alpha;
+                acc[1] *= alpha;
+                acc[2] *= alpha;
+                acc[3] *= alpha;
+                mma_kv<T>(acc, pa0, pa1, pa2, pa3, b0, b1);
+            }
+        }
+    }
+
+    // ---- merge the warps of this CTA ----
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (t == 0) {
+        sm_m[warp][g] = m_run;
+        sm_l[warp][g] = l_run;
+    }
+#pragma unroll
+    for (int h = 0; h < VH; h++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float(&acc)[4] = o[8 * h + j];
+            // accumulator column x of tile (h, j) is head-dim index 64h + 8x + j; rows g and g+8 are the two parts of P
+            sm_o[warp][g][64 * h + 8 * (2 * t) + j] = acc[0] + acc[2];
+            sm_o[warp][g][64 * h + 8 * (2 * t + 1) + j] = acc[1] + acc[3];
+        }
+    __syncthreads();
+
+    const size_t pair = (size_t)b * p.Hkv + kvh;
+    T *outp = reinterpret_cast<T *>(p.out) + (size_t)(b * p.Hq + kvh * G) * D;
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+        const int hd = idx / D, d = idx - hd * D;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; w++) mx = fmaxf(mx, sm_m[w][hd]);
+        float L = 0.f, O = 0.f;
+        if (mx > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < kAttnWarps; w++) {
+                const float f = __expf(sm_m[w][hd] - mx);
+                L += sm_l[w][hd] * f;
+                O += sm_o[w][hd][d] * f;
+            }
+        }
+        if (p.splits == 1) {
+            outp[(size_t)hd * D + d] = from_f32<T>(O / L);
+        } else {
+            const size_t slot = (pair * p.splits + split) * 8 + hd;
+            p.ws_o[slot * D + d] = O;
+            if (d == 0) {
+                p.ws_ml[slot * 2] = mx;
+                p.ws_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+    if (p.splits == 1) return;
+
+    // ---- last CTA of this (batch, kv head) combines the splits ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) sm_last = (atomicAdd(&p.ws_ticket[pair], 1u) == (unsigned)(p.splits - 1)) ? 1u : 0u;
+    __syncthreads();
+    if (!sm_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+        const int hd = idx / D, d = idx - hd * D;
+        float mx = -INFINITY;
+        for (int sp = 0; sp < p.splits; sp++) mx = fmaxf(mx, __ldcg(&p.ws_ml[((pair * p.splits + sp) * 8 + hd) * 2]));
+        float L = 0.f, O = 0.f;
+        for (int sp = 0; sp < p.splits; sp++) {
+            const size_t slot = (pair * p.splits + sp) * 8 + hd;
+            const float ms = __ldcg(&p.ws_ml[slot * 2]);
+            if (ms == -INFINITY) continue;
+            const float f = __expf(ms - mx);
+            L += __ldcg(&p.ws_ml[slot * 2 + 1]) * f;
+            O += __ldcg(&p.ws_o[slot * D + d]) * f;
+        }
+        outp[(size_t)hd * D + d] = from_f32<T>(O / L);
+    }
+    if (threadIdx.x == 0) p.ws_ticket[pair] = 0u;
+}
+
+// Generic attention: one warp per (b, h, sq) query row, the CPU kernel's recurrence row by row
+// (m' = max(m, qk); f = exp(m - m'); e = exp(qk - m'); s = s f + e; o = o f + e v; out = o / s).
+template <typename T, int MAXE>
+__global__ void attention_generic_kernel(T *out, const T *q, const T *k, const T *v, float scale, int B, int Hq,
+                                         int Hkv, int Sq, int Sk, int D, int active_host, const int32_t *active_dev,
+                                         int is_causal, int out_bshd) {
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)B * Hq * Sq) return;
+    const int sq = (int)(wid % Sq);
+    const long long bh = wid / Sq;
+    const int h = (int)(bh % Hq), b = (int)(bh / Hq);
+    const int kvh = h / (Hq / Hkv);
+    const int active = active_dev ? *active_dev : active_host;
+    int bound = active;
+    if (is_causal) bound = min(bound, active - Sq + sq + 1);
+    bound = min(bound, Sk);
+    const T *qp = q + (size_t)wid * D;
+    const T *kp = k + (size_t)(b * Hkv + kvh) * Sk * D;
+    const T *vp = v + (size_t)(b * Hkv + kvh) * Sk * D;
+    float qr[MAXE], o[MAXE];
+#pragma unroll
+    for (int e = 0; e < MAXE; e++) {
+        const int d = lane + 32 * e;
+        qr[e] = d < D ? to_f32<T>(qp[d]) : 0.f;
+        o[e] = 0.f;
+    }
+    float m = -INFINITY, s = 0.f;
+    for (int r = 0; r < bound; r++) {
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < MAXE; e++) {
+            const int d = lane + 32 * e;
+            if (d < D) dot += qr[e] * to_f32<T>(kp[(size_t)r * D + d]);
+        }
+        const float qk = warp_sum(dot) * scale;
+        const float m_new = fmaxf(m, qk);
+        const float f = expf(m - m_new), ev = expf(qk - m_new);
+        s = s * f + ev;
+#pragma unroll
+        for (int e = 0; e < MAXE; e++) {
+            const int d = lane + 32 * e;
+            if (d < D) o[e] = o[e] * f + ev * to_f32<T>(vp[(size_t)r * D + d]);
+        }
+        m = m_new;
+    }
+#pragma unroll
+    for (int e = 0; e < MAXE; e++) {
+        const int d = lane + 32 * e;
+        const size_t orow = out_bshd ? ((size_t)b * Sq + sq) * Hq + h : (size_t)wid;
+        if (d < D) out[orow * D + d] = from_f32<T>(o[e] / s);
+    }
+}
+
+static int decode_splits(int B, int Hkv, int rows_bound) {
+    const int pairs = B * Hkv;
+    int want = (3 * 148 + pairs - 1) / pairs;             // about three CTAs per SM
+    int cap = rows_bound / (16 * kAttnWarps);              // at least one tile per warp and split
+    int s = want < cap ? want : cap;
+    if (s < 1) s = 1;
+    if (s > kMaxSplits) s = kMaxSplits;
+    return s;
+}
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace mynn
+
+using namespace mynn;
+
+extern "C" size_t mynn_b200_attention_workspace_bytes(int B, int Hq, int Hkv, int D, int cache_seq_len) {
+    if (B <= 0 || Hkv <= 0 || D <= 0) return 0;
+    const size_t pairs = (size_t)B * Hkv;
+    const size_t tickets = align_up(pairs * sizeof(unsigned), 256);
+    const size_t ml = align_up(pairs * kMaxSplits * 8 * 2 * sizeof(float), 256);
+    const size_t o = pairs * kMaxSplits * 8 * (size_t)D * sizeof(float);
+    (void)Hq;
+    (void)cache_seq_len;
+    return tickets + ml + o;
+}
+
+template <typename T>
+static int launch_generic(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
+                          int Hq, int Hkv, int Sq, int Sk, int D, int active, const int32_t *active_dev, int causal,
+                          int out_bshd) {
+    const long long rows = (long long)B * Hq * Sq;
+    const unsigned blocks = (unsigned)((rows * 32 + 127) / 128);
+#define GEN(MAXE)                                                                                                     \
+    attention_generic_kernel<T, MAXE><<<blocks, 128, 0, st>>>((T *)out, (const T *)q, (const T *)k, (const T *)v, scale, B, \
+                                                             Hq, Hkv, Sq, Sk, D, active, active_dev, causal, out_bshd)
+    if (D <= 32) GEN(1);
+    else if (D <= 64) GEN(2);
+    else if (D <= 128) GEN(4);
+    else if (D <= 256) GEN(8);
+    else if (D <= 512) GEN(16);
+    else return fail(MYNN_E_UNSUPPORTED, "attention: head dim %d > 512", D);
+#undef GEN
+    MYNN_LAUNCH_OK("attention_generic_kernel");
+    return MYNN_OK;
+}
+
+template <typename T, int D>
+static int launch_decode(cudaStream_t st, const DecodeParams &p, int B) {
+    attention_decode_kernel<T, D><<<dim3(p.splits, p.Hkv, B), kAttnWarps * 32, 0, st>>>(p);
+    MYNN_LAUNCH_OK("attention_decode_kernel");
+    return MYNN_OK;
+}
+
+extern "C" int mynn_b200_attention(void *stream, void *out, const void *q, const void *k, const void *v, float scale,
+                                   int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
+                                   const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
+                                   size_t workspace_bytes) {
+    return mynn::launch_attention((cudaStream_t)stream, out, q, k, v, scale, B, Hq, Hkv, Sq, D, cache_seq_len,
+                                  active_seq_kv, active_seq_kv_dev, is_causal, dtype, workspace, workspace_bytes, 0);
+}
+
+int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
+                           int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
+                           const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
+                           size_t workspace_bytes, int out_bshd) {
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || Sq < 0 || D <= 0 || cache_seq_len < 0 || active_seq_kv < 0)
+        return fail(MYNN_E_ARG, "attention: bad shape");
+    if (Hq % Hkv != 0) return fail(MYNN_E_ARG, "attention: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
+    if (!dtype_ok(dtype)) return fail(MYNN_E_ARG, "attention: bad dtype %d", dtype);
+    if (B == 0 || Sq == 0) return MYNN_OK;
+    if (!out || !q || !k || !v) return fail(MYNN_E_ARG, "attention: null pointer");
+    const int G = Hq / Hkv;
+    const bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % 16) == 0;
+    const bool fast = Sq == 1 && (D == 64 || D == 128) && G <= 8 && dtype != MYNN_F32 && aligned;
+    if (!fast) {
+        if (dtype == MYNN_F32) return launch_generic<float>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, active_seq_kv_dev, is_causal, out_bshd);
+        if (dtype == MYNN_BF16) return launch_generic<__nv_bfloat16>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, active_seq_kv_dev, is_causal, out_bshd);
+        return launch_generic<__half>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, active_seq_kv_dev, is_causal, out_bshd);
+    }
+    // decode: is_causal with one query row means bound = min(active, active - 1 + 0 + 1) = active, no extra mask
+    DecodeParams p;
+    p.out = out;
+    p.q = q;
+    p.k = k;
+    p.v = v;
+    p.scale = scale;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.G = G;
+    p.cache_seq = cache_seq_len;
+    p.active_host = active_seq_kv;
+    p.active_dev = active_seq_kv_dev;
+    const int rows_bound = active_seq_kv_dev ? cache_seq_len : (active_seq_kv < cache_seq_len ? active_seq_kv : cache_seq_len);
+    p.splits = decode_splits(B, Hkv, rows_bound);
+    p.ws_o = nullptr;
+    p.ws_ml = nullptr;
+    p.ws_ticket = nullptr;
+    if (p.splits > 1) {
+        const size_t need = mynn_b200_attention_workspace_bytes(B, Hq, Hkv, D, cache_seq_len);
+        if (!workspace || workspace_bytes < need)
+            return fail(MYNN_E_ARG, "attention: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+        const size_t pairs = (size_t)B * Hkv;
+        char *w = (char *)workspace;
+        p.ws_ticket = (unsigned *)w;
+        w += align_up(pairs * sizeof(unsigned), 256);
+        p.ws_ml = (float *)w;
+        w += align_up(pairs * kMaxSplits * 8 * 2 * sizeof(float), 256);
+        p.ws_o = (float *)w;
+    }
+    if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B) : launch_decode<__nv_bfloat16, 128>(st, p, B);
+    return D == 64 ? launch_decode<__half, 64>(st, p, B) : launch_decode<__half, 128>(st, p, B);
+}

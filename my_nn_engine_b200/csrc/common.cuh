@@ -1,0 +1,96 @@
+// Shared helpers for the sm_100a decode-path kernels: status/error plumbing, storage-dtype
+// conversions and small warp utilities.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/mynn_b200.h"
+
+namespace mynn {
+
+// ---- host-side status ----------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+extern std::atomic<long long> g_launches;
+
+inline int fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+inline int fail(int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    set_error("%s", buf);
+    return code;
+}
+
+#define MYNN_CUDA_OK(expr)                                                                                 \
+    do {                                                                                                   \
+        cudaError_t e__ = (expr);                                                                          \
+        if (e__ != cudaSuccess)                                                                            \
+            return mynn::fail(MYNN_E_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, \
+                              __LINE__);                                                                   \
+    } while (0)
+
+// Call after every kernel launch: counts it and turns a launch error into a status code.
+#define MYNN_LAUNCH_OK(name)                                                                          \
+    do {                                                                                              \
+        mynn::g_launches.fetch_add(1, std::memory_order_relaxed);                                     \
+        cudaError_t e__ = cudaGetLastError();                                                         \
+        if (e__ != cudaSuccess)                                                                       \
+            return mynn::fail(MYNN_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e__)); \
+    } while (0)
+
+inline size_t dtype_size(int dt) { return dt == MYNN_F32 ? 4 : 2; }
+inline bool dtype_ok(int dt) { return dt == MYNN_F32 || dt == MYNN_BF16 || dt == MYNN_F16; }
+
+// ---- device-side storage conversions ---------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// One store point: round to storage dtype and come back to f32.
+template <typename T>
+__device__ __forceinline__ float round_store(float v) { return to_f32<T>(from_f32<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Dispatch a launcher template over the three storage dtypes.
+#define MYNN_DISPATCH_DTYPE(dt, T, ...)                       \
+    switch (dt) {                                             \
+        case MYNN_F32: { using T = float; __VA_ARGS__; } break;          \
+        case MYNN_BF16: { using T = __nv_bfloat16; __VA_ARGS__; } break; \
+        case MYNN_F16: { using T = __half; __VA_ARGS__; } break;         \
+        default: return mynn::fail(MYNN_E_ARG, "bad dtype %d", dt);      \
+    }
+
+}  // namespace mynn

@@ -1,0 +1,441 @@
+// DequantMatMul for the decode path on sm_100a:  out[m,n] = scale[n] * sum_k act[m,k] * wq[n,k].
+//
+// The decode step is bound by streaming the int8 weights from HBM once.  The streaming kernel
+//   * gives each warp 16 weight rows and lets it pull them straight from global memory into registers with
+//     128-bit loads (two rows x 16 bytes per lane per 64-wide k step), one whole 256-wide k stage ahead of
+//     the math, so that every lane keeps eight 16-byte loads in flight;
+//   * converts int8 -> bf16 (or fp16) in registers with byte-permute bit tricks (exact: |w| <= 128 fits the
+//     8-bit significand), and feeds them as the A operand of mma.m16n8k16 with f32 accumulation;
+//   * stages the few activation rows (M <= 32, the batch) through shared memory with cp.async double
+//     buffering, shared by the 8 warps (128 weight rows) of the CTA; they are the B operand;
+//   * splits K over a thread-block cluster and reduces the partial sums through distributed shared memory
+//     in a fixed order (deterministic), then applies the per-row scale, an optional residual add, and stores.
+// Because a dot product is invariant under a permutation of k, the k index inside each 64-wide step is
+// permuted so that the 16 contiguous bytes one lane loads are exactly its A fragments of four MMAs.
+//
+// f32 activations (the engine's f32 graphs) are split into three bf16 terms (hi + mid + lo = 24 significant
+// bits) that occupy three B columns, so the tensor-core product stays f32-accurate.
+//
+// Shapes outside the fast path (K % 64 != 0, N % 16 != 0, M > 32, [K,N] weight layout) use a plain generic
+// kernel: correct for every shape the engine's tests use, not tuned.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace mynn {
+
+constexpr int kWarps = 8;            // warps per CTA
+constexpr int kRowsPerCta = 16 * kWarps;
+constexpr int kStageK = 256;         // k values per activation stage (4 MMA k64 steps)
+constexpr int kActPad = 8;           // bf16 elements of row padding (16 B): conflict-free 16-byte fragment reads
+constexpr int kActStride = kStageK + kActPad;
+
+__device__ __forceinline__ uint4 ld_stream_16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+// 4 int8 (one 32-bit word) -> 4 x 16-bit floats as two packed pairs {b0,b1} and {b2,b3}.
+template <bool F16>
+__device__ __forceinline__ void cvt_s8x4(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    if constexpr (F16) {
+        // 0x6400 | (b ^ 0x80) is fp16(1024 + b + 128); subtracting 1152 gives b exactly.
+        uint32_t p0 = __byte_perm(w, 0x64646464u, 0x4140) ^ 0x00800080u;
+        uint32_t p1 = __byte_perm(w, 0x64646464u, 0x4342) ^ 0x00800080u;
+        const uint32_t bias = 0x64806480u;
+        asm("sub.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(p0), "r"(bias));
+        asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(p1), "r"(bias));
+    } else {
+        // 0x4300 | (b & 0x7f) is bf16(128 + (b & 0x7f)); the subtrahend 0x4300 | (b & 0x80) is 128 for b >= 0
+        // and 256 for b < 0, so the difference is the signed byte exactly.
+        uint32_t p0 = __byte_perm(w, 0x43434343u, 0x4140);
+        uint32_t p1 = __byte_perm(w, 0x43434343u, 0x4342);
+        uint32_t y0 = p0 & 0xFF7FFF7Fu, c0 = p0 & 0xFF80FF80u;
+        uint32_t y1 = p1 & 0xFF7FFF7Fu, c1 = p1 & 0xFF80FF80u;
+        asm("sub.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(y0), "r"(c0));
+        asm("sub.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(y1), "r"(c1));
+    }
+}
+
+template <bool F16>
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    if constexpr (F16) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+template <typename ActT>
+struct ActTraits {
+    static constexpr bool kF16 = false;
+    static constexpr int kColsPerRow = 1;
+};
+template <>
+struct ActTraits<__half> {
+    static constexpr bool kF16 = true;
+    static constexpr int kColsPerRow = 1;
+};
+template <>
+struct ActTraits<float> {
+    static constexpr bool kF16 = false;
+    static constexpr int kColsPerRow = 3;  // hi / mid / lo bf16 terms
+};
+
+// Stage `klen` (multiple of 64, <= kStageK) activation columns starting at k0 into buf[col][k].
+template <typename ActT, int NT>
+__device__ __forceinline__ void stage_act(uint16_t *buf, const ActT *act, int M, int K, int k0, int klen) {
+    if constexpr (sizeof(ActT) == 2) {
+        const int chunks_per_row = klen >> 3;  // 16-byte chunks
+        for (int i = threadIdx.x; i < M * chunks_per_row; i += blockDim.x) {
+            int m = i / chunks_per_row, c = i - m * chunks_per_row;
+            cp_async_16(buf + m * kActStride + c * 8, act + (size_t)m * K + k0 + c * 8);
+        }
+    } else {
+        const int quads_per_row = klen >> 2;
+        for (int i = threadIdx.x; i < M * quads_per_row; i += blockDim.x) {
+            int m = i / quads_per_row, c = i - m * quads_per_row;
+            float4 v = *reinterpret_cast<const float4 *>(act + (size_t)m * K + k0 + c * 4);
+            float x[4] = {v.x, v.y, v.z, v.w};
+            uint16_t h[4], md[4], l[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                __nv_bfloat16 bh = __float2bfloat16_rn(x[j]);
+                float r1 = x[j] - __bfloat162float(bh);
+                __nv_bfloat16 bm = __float2bfloat16_rn(r1);
+                float r2 = r1 - __bfloat162float(bm);
+                __nv_bfloat16 bl = __float2bfloat16_rn(r2);
+                h[j] = __bfloat16_as_ushort(bh);
+                md[j] = __bfloat16_as_ushort(bm);
+                l[j] = __bfloat16_as_ushort(bl);
+            }
+            uint16_t *d = buf + (3 * m) * kActStride + c * 4;
+            *reinterpret_cast<uint2 *>(d) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+            *reinterpret_cast<uint2 *>(d + kActStride) = make_uint2(md[0] | (md[1] << 16), md[2] | (md[3] << 16));
+            *reinterpret_cast<uint2 *>(d + 2 * kActStride) = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+        }
+    }
+}
+
+// grid (row tiles of 128, S) with cluster (1, S, 1): CTA (x, y) accumulates rows [128x, 128x+128) over the y-th
+// contiguous share of the K/64 steps; the cluster then reduces over y.
+template <typename ActT, typename OutT, int NT>
+__global__ void __launch_bounds__(kWarps * 32)
+dequant_gemm_stream_kernel(OutT *out, const ActT *__restrict__ act, const int8_t *__restrict__ wq,
+                           const OutT *__restrict__ scale, const OutT *resid, int M, int N, int K) {
+    constexpr bool F16 = ActTraits<ActT>::kF16;
+    constexpr int CPR = ActTraits<ActT>::kColsPerRow;
+    constexpr int COLS = 8 * NT;
+    __shared__ __align__(16) uint16_t act_s[2][COLS * kActStride];
+    static_assert(sizeof(act_s) >= kRowsPerCta * (COLS + 1) * sizeof(float), "reduction buffer aliases act_s");
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int S = gridDim.y, rank = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+    // this CTA's share of the k64 steps
+    const int steps = K >> 6;
+    const int q = steps / S, rem = steps - q * S;
+    const int step_beg = rank * q + min(rank, rem);
+    const int nsteps = q + (rank < rem ? 1 : 0);
+    const int kbeg = step_beg << 6;
+    const int nstages = (nsteps + 3) >> 2;
+
+    const int row0 = blockIdx.x * kRowsPerCta + warp * 16;
+    const bool warp_active = row0 < N;  // N % 16 == 0, so a warp's 16 rows are all in or all out
+    const int8_t *w0 = wq + (size_t)(row0 + g) * K + kbeg + 16 * t;
+    const int8_t *w1 = w0 + (size_t)8 * K;
+
+    // zero the unused activation columns of both buffers once: they stay zero for the whole kernel
+    {
+        const int used = M * CPR, chunks = kActStride / 8;
+        for (int i = threadIdx.x; i < 2 * (COLS - used) * chunks; i += blockDim.x) {
+            const int b = i / ((COLS - used) * chunks), r = i - b * (COLS - used) * chunks;
+            reinterpret_cast<uint4 *>(&act_s[b][(used + r / chunks) * kActStride])[r % chunks] = make_uint4(0, 0, 0, 0);
+        }
+    }
+    __syncthreads();
+
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[j][i] = 0.f;
+
+    uint4 wcur[4][2], wnext[4][2];
+    auto load_weights = [&](uint4(&dst)[4][2], int stage) {
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            int st = stage * 4 + s;
+            if (warp_active && st < nsteps) {
+                dst[s][0] = ld_stream_16(w0 + (size_t)st * 64);
+                dst[s][1] = ld_stream_16(w1 + (size_t)st * 64);
+            } else {
+                dst[s][0] = make_uint4(0, 0, 0, 0);
+                dst[s][1] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    if (nstages > 0) {
+        load_weights(wcur, 0);
+        stage_act<ActT, NT>(act_s[0], act, M, K, kbeg, min(4, nsteps) * 64);
+        cp_async_commit();
+    }
+    for (int stage = 0; stage < nstages; stage++) {
+        const int buf = stage & 1;
+        if (stage + 1 < nstages) {
+            load_weights(wnext, stage + 1);
+            stage_act<ActT, NT>(act_s[buf ^ 1], act, M, K, kbeg + (stage + 1) * kStageK,
+                                min(4, nsteps - (stage + 1) * 4) * 64);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int steps_here = min(4, nsteps - stage * 4);
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            if (s < steps_here) {
+                // B fragments: 16 consecutive k values of column (8j + g), starting at 64 s + 16 t
+                uint4 b[NT][2];
+#pragma unroll
+                for (int j = 0; j < NT; j++) {
+                    const uint16_t *p = &act_s[buf][(8 * j + g) * kActStride + 64 * s + 16 * t];
+                    b[j][0] = *reinterpret_cast<const uint4 *>(p);
+                    b[j][1] = *reinterpret_cast<const uint4 *>(p + 8);
+                }
+                const uint32_t wa[4] = {wcur[s][0].x, wcur[s][0].y, wcur[s][0].z, wcur[s][0].w};
+                const uint32_t wb[4] = {wcur[s][1].x, wcur[s][1].y, wcur[s][1].z, wcur[s][1].w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {  // MMA i covers bytes 4i..4i+3 of each lane's 16
+                    uint32_t a0, a2, a1, a3;
+                    cvt_s8x4<F16>(wa[i], a0, a2);
+                    cvt_s8x4<F16>(wb[i], a1, a3);
+#pragma unroll
+                    for (int j = 0; j < NT; j++) {
+                        const uint32_t *bw = reinterpret_cast<const uint32_t *>(&b[j][i >> 1]);
+                        mma_16816<F16>(acc[j], a0, a1, a2, a3, bw[(i & 1) * 2], bw[(i & 1) * 2 + 1]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            wcur[s][0] = wnext[s][0];
+            wcur[s][1] = wnext[s][1];
+        }
+    }
+
+    // ---- cluster reduction through distributed shared memory ----
+    float *red = reinterpret_cast<float *>(&act_s[0][0]);  // [128][COLS + 1]
+    constexpr int RS = COLS + 1;
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        red[(warp * 16 + g) * RS + 8 * j + 2 * t] = acc[j][0];
+        red[(warp * 16 + g) * RS + 8 * j + 2 * t + 1] = acc[j][1];
+        red[(warp * 16 + g + 8) * RS + 8 * j + 2 * t] = acc[j][2];
+        red[(warp * 16 + g + 8) * RS + 8 * j + 2 * t + 1] = acc[j][3];
+    }
+    cluster.sync();
+    {
+        // rank r finishes rows [r * rows_per_rank, ...) of the 128-row tile
+        const int rows_per_rank = (kRowsPerCta + S - 1) / S;
+        const int rbeg = rank * rows_per_rank;
+        const int rcnt = max(0, min(rows_per_rank, kRowsPerCta - rbeg));
+        for (int idx = threadIdx.x; idx < rcnt * M; idx += blockDim.x) {
+            const int m = idx / rcnt, r = rbeg + (idx - m * rcnt);
+            const int n = blockIdx.x * kRowsPerCta + r;
+            if (n >= N) continue;
+            // issue the (independent) remote reads together, then add in rank order
+            float part[8];
+#pragma unroll
+            for (int rr = 0; rr < 8; rr++) {
+                part[rr] = 0.f;
+                if (rr < S) {
+                    const float *remote = cluster.map_shared_rank(red, rr);
+#pragma unroll
+                    for (int c = 0; c < CPR; c++) part[rr] += remote[r * RS + CPR * m + c];
+                }
+            }
+            float sum = 0.f;
+#pragma unroll
+            for (int rr = 0; rr < 8; rr++) sum += part[rr];
+            float v = sum * to_f32<OutT>(scale[n]);
+            if (resid != nullptr) v = round_store<OutT>(v) + to_f32<OutT>(resid[(size_t)m * N + n]);
+            out[(size_t)m * N + n] = from_f32<OutT>(v);
+        }
+    }
+    cluster.sync();  // keep shared memory alive until every peer has read it
+}
+
+// Generic kernel: one warp per output element, any shape and either weight layout (element strides given).
+template <typename ActT, typename OutT>
+__global__ void dequant_matmul_generic_kernel(OutT *out, const ActT *act, const int8_t *wq, const OutT *scale,
+                                              const OutT *resid, int M, int N, int K, long long w_stride_n,
+                                              long long w_stride_k) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M * N) return;
+    const int m = warp / N, n = warp - m * N;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32)
+        acc += to_f32<ActT>(act[(size_t)m * K + k]) * (float)wq[n * w_stride_n + k * w_stride_k];
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        float v = acc * to_f32<OutT>(scale[n]);
+        if (resid != nullptr) v = round_store<OutT>(v) + to_f32<OutT>(resid[(size_t)m * N + n]);
+        out[(size_t)m * N + n] = from_f32<OutT>(v);
+    }
+}
+
+// [K,N] layout (per-column scale): each thread owns 4 adjacent columns, the block's y dimension splits K and the
+// partial sums meet in shared memory.  Reads of W are coalesced along N.
+template <typename ActT, typename OutT>
+__global__ void __launch_bounds__(256)
+dequant_gemv_kn_kernel(OutT *out, const ActT *act, const int8_t *wq, const OutT *scale, int N, int K) {
+    __shared__ float part[8][128];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int n0 = blockIdx.x * 128 + tx * 4;
+    const int m = blockIdx.y;
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    if (n0 < N) {
+        for (int k = ty; k < K; k += 8) {
+            const char4 w = *reinterpret_cast<const char4 *>(wq + (size_t)k * N + n0);
+            const float x = to_f32<ActT>(act[(size_t)m * K + k]);
+            a[0] += x * (float)w.x;
+            a[1] += x * (float)w.y;
+            a[2] += x * (float)w.z;
+            a[3] += x * (float)w.w;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) part[ty][tx * 4 + i] = a[i];
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        const int n = blockIdx.x * 128 + threadIdx.x;
+        if (n < N) {
+            float s = 0.f;
+#pragma unroll
+            for (int y = 0; y < 8; y++) s += part[y][threadIdx.x];
+            out[(size_t)m * N + n] = from_f32<OutT>(s * to_f32<OutT>(scale[n]));
+        }
+    }
+}
+
+static int pick_ksplit(int row_tiles, int steps) {
+    // Every CTA pays a fixed prologue and a cluster reduction, so split K only until there is about one CTA per
+    // SM (148), keep at least 8 k64 steps (two stages) per CTA, and stay within the portable cluster size of 8.
+    int s = 1;
+    while (s < 8 && row_tiles * s < 148 && steps / (s * 2) >= 8) s *= 2;
+    return s;
+}
+
+template <typename ActT, typename OutT, int NT>
+static int launch_stream(cudaStream_t st, OutT *out, const ActT *act, const int8_t *wq, const OutT *scale,
+                         const OutT *resid, int M, int N, int K, int ksplit_override) {
+    const int row_tiles = (N + kRowsPerCta - 1) / kRowsPerCta;
+    int S = ksplit_override > 0 ? ksplit_override : pick_ksplit(row_tiles, K / 64);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(row_tiles, S, 1);
+    cfg.blockDim = dim3(kWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = S;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MYNN_CUDA_OK(cudaLaunchKernelEx(&cfg, dequant_gemm_stream_kernel<ActT, OutT, NT>, out, act, wq, scale, resid, M, N, K));
+    MYNN_LAUNCH_OK("dequant_gemm_stream_kernel");
+    return MYNN_OK;
+}
+
+int g_ksplit_override = 0;  // test/tuning hook, see mynn_b200_debug_set_ksplit
+
+template <typename ActT, typename OutT>
+static int dequant_matmul_typed(cudaStream_t st, OutT *out, const ActT *act, const int8_t *wq, const OutT *scale,
+                                const OutT *resid, int M, int N, int K, int w_layout) {
+    constexpr int CPR = ActTraits<ActT>::kColsPerRow;
+    const bool aligned = ((uintptr_t)wq % 16 == 0) && ((uintptr_t)act % 16 == 0);
+    if (w_layout == MYNN_W_NK && K % 64 == 0 && N % 16 == 0 && M * CPR <= 32 && aligned) {
+        const int cols = M * CPR;
+        if (cols <= 8) return launch_stream<ActT, OutT, 1>(st, out, act, wq, scale, resid, M, N, K, g_ksplit_override);
+        if (cols <= 16) return launch_stream<ActT, OutT, 2>(st, out, act, wq, scale, resid, M, N, K, g_ksplit_override);
+        return launch_stream<ActT, OutT, 4>(st, out, act, wq, scale, resid, M, N, K, g_ksplit_override);
+    }
+    if (w_layout == MYNN_W_KN && N % 4 == 0 && ((uintptr_t)wq % 4 == 0) && resid == nullptr) {
+        dequant_gemv_kn_kernel<ActT, OutT><<<dim3((N + 127) / 128, M), 256, 0, st>>>(out, act, wq, scale, N, K);
+        MYNN_LAUNCH_OK("dequant_gemv_kn_kernel");
+        return MYNN_OK;
+    }
+    const long long sn = w_layout == MYNN_W_NK ? K : 1, sk = w_layout == MYNN_W_NK ? 1 : N;
+    const long long warps = (long long)M * N;
+    const int blocks = (int)((warps * 32 + 255) / 256);
+    dequant_matmul_generic_kernel<ActT, OutT><<<blocks, 256, 0, st>>>(out, act, wq, scale, resid, M, N, K, sn, sk);
+    MYNN_LAUNCH_OK("dequant_matmul_generic_kernel");
+    return MYNN_OK;
+}
+
+static int dequant_matmul_dispatch(void *stream, void *out, const void *act, const int8_t *wq, const void *scale,
+                                   const void *resid, int M, int N, int K, int act_dtype, int out_dtype,
+                                   int w_layout) {
+    if (M < 0 || N < 0 || K < 0) return fail(MYNN_E_ARG, "dequant_matmul: negative dimension (M=%d N=%d K=%d)", M, N, K);
+    if (w_layout != MYNN_W_NK && w_layout != MYNN_W_KN) return fail(MYNN_E_ARG, "dequant_matmul: bad weight layout %d", w_layout);
+    if (!dtype_ok(act_dtype) || !dtype_ok(out_dtype)) return fail(MYNN_E_ARG, "dequant_matmul: bad dtype");
+    if (M == 0 || N == 0) return MYNN_OK;
+    if (!out || !wq || !scale || (!act && K > 0)) return fail(MYNN_E_ARG, "dequant_matmul: null pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+#define CASE(AD, AT, OD, OT)                                                                                        \
+    if (act_dtype == AD && out_dtype == OD)                                                                         \
+        return dequant_matmul_typed<AT, OT>(st, (OT *)out, (const AT *)act, wq, (const OT *)scale, (const OT *)resid, \
+                                            M, N, K, w_layout);
+    CASE(MYNN_BF16, __nv_bfloat16, MYNN_BF16, __nv_bfloat16)
+    CASE(MYNN_F16, __half, MYNN_F16, __half)
+    CASE(MYNN_F32, float, MYNN_F32, float)
+    CASE(MYNN_BF16, __nv_bfloat16, MYNN_F32, float)
+    CASE(MYNN_F32, float, MYNN_BF16, __nv_bfloat16)
+#undef CASE
+    return fail(MYNN_E_UNSUPPORTED, "dequant_matmul: act dtype %d with out dtype %d is not supported", act_dtype, out_dtype);
+}
+
+}  // namespace mynn
+
+extern "C" int mynn_b200_dequant_matmul(void *stream, void *out, const void *act, const int8_t *wq, const void *scale,
+                                        int M, int N, int K, int act_dtype, int out_dtype, int w_layout) {
+    return mynn::dequant_matmul_dispatch(stream, out, act, wq, scale, nullptr, M, N, K, act_dtype, out_dtype, w_layout);
+}
+
+extern "C" int mynn_b200_dequant_matmul_residual(void *stream, void *out, const void *act, const int8_t *wq,
+                                                 const void *scale, const void *residual, int M, int N, int K,
+                                                 int dtype) {
+    return mynn::dequant_matmul_dispatch(stream, out, act, wq, scale, residual, M, N, K, dtype, dtype, MYNN_W_NK);
+}
+
+// Tuning hook (not part of the engine-facing ABI): force the cluster K split of the streaming kernel; 0 = automatic.
+extern "C" int mynn_b200_debug_set_ksplit(int s) {
+    if (s != 0 && s != 1 && s != 2 && s != 4 && s != 8) return mynn::fail(MYNN_E_ARG, "ksplit must be 0,1,2,4,8");
+    mynn::g_ksplit_override = s;
+    return MYNN_OK;
+}

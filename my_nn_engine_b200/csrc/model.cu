@@ -1,0 +1,424 @@
+// Whole decoder step behind the engine's generated-library entry points (model_init / model / model_destroy).
+//
+// The engine generates one CUDA library per model and resolves those three symbols from it; the decoder DAG it
+// generates for a Llama-family model is fixed (crates/llm/src/decoder.rs:203-537,731-865), so here it is written
+// once and specialised by mynn_b200_model_configure().  Per layer the step launches
+//     RMSNorm -> QKV DequantMatMul (one launch when the three weights are adjacent in memory) -> RoPE + KV append
+//     -> GQA decode attention -> O DequantMatMul (+ residual) -> RMSNorm -> gate/up DequantMatMul -> Swish*Mul
+//     -> down DequantMatMul (+ residual)
+// on ONE stream (the DAG is a chain; the engine's 16-stream plan only adds event traffic) and captures the whole
+// step in a CUDA graph that is replayed every token: sequence position, KV offset and active length live in
+// device scalars, so the graph never changes.  Activations live in one arena sized at init; weights and KV
+// caches belong to the host, as in the engine.  Every rounding point of the engine's schedule is kept (one
+// rounding per kernel output), so greedy tokens can be compared with the CPU oracle.
+//
+// Tensor parallel (tp_world > 1): q/k/v/gate/up/lm_head shards are column-parallel (rows of wq), o/down are
+// row-parallel (columns of wq) and produce f32 partial sums that are all-reduced and then rounded once and added
+// to the residual, fused with the following RMSNorm.
+#include <cstring>
+#include <vector>
+
+#include "comm.cuh"
+#include "common.cuh"
+#include "ops_internal.cuh"
+
+namespace mynn {
+
+struct LayerW {
+    const void *ln1, *ln2;
+    const int8_t *wq, *wk, *wv, *wo, *wg, *wu, *wd;
+    const void *sq, *sk, *sv, *so, *sg, *su, *sd;
+    void *kc, *vc;
+    bool qkv_fused, gu_fused;
+};
+
+struct Model {
+    mynn_b200_model_config c;
+    int Hq, Hkv, ffn, vocab_l;  // per-rank sizes
+    int max_rows;               // batch * max(1, max_prefill)
+    std::vector<LayerW> layers;
+    const int8_t *embed;
+    const void *embed_scale, *final_norm, *lm_scale, *cos_t, *sin_t;
+    const int8_t *lm_w;
+    // device buffers
+    char *arena = nullptr;
+    // step inputs, contiguous so that one host-to-device copy delivers them: {past, active, pos0, ids[rows]}
+    int32_t *past_dev, *active_dev;
+    int64_t *pos0_dev, *ids_dev;
+    int64_t *pos_dev;  // positions of a prefill chunk
+    int32_t *tok_dev;
+    char *h_in = nullptr;  // pinned mirror of the input block
+    void *x, *n, *qkv, *q_rot, *attn, *gu, *h, *last_x, *logits, *logits_full;
+    float *part, *pairs, *pairs_all;
+    void *attn_ws;
+    size_t attn_ws_bytes;
+    cudaStream_t stream = nullptr;
+    cudaGraphExec_t graph_exec = nullptr;
+};
+
+static mynn_b200_model_config g_cfg;
+static bool g_cfg_set = false;
+static int g_status = MYNN_OK;
+
+static size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+
+#define RC(expr)            \
+    do {                    \
+        int rc__ = (expr);  \
+        if (rc__) return rc__; \
+    } while (0)
+
+// DequantMatMul over any number of rows: the streaming kernel takes up to 32 rows per pass.
+static int gemm(cudaStream_t st, const Model &m, void *out, const void *act, const int8_t *w, const void *scale,
+                const void *resid, int M, int N, int K, int out_dtype) {
+    const int dt = m.c.dtype;
+    const size_t esz = dtype_size(dt), osz = dtype_size(out_dtype);
+    for (int m0 = 0; m0 < M; m0 += 32) {
+        const int mm = M - m0 < 32 ? M - m0 : 32;
+        char *o = (char *)out + (size_t)m0 * N * osz;
+        const char *a = (const char *)act + (size_t)m0 * K * esz;
+        if (resid) {
+            RC(mynn_b200_dequant_matmul_residual(st, o, a, w, scale, (const char *)resid + (size_t)m0 * N * osz, mm, N, K, dt));
+        } else {
+            RC(mynn_b200_dequant_matmul(st, o, a, w, scale, mm, N, K, dt, out_dtype, MYNN_W_NK));
+        }
+    }
+    return MYNN_OK;
+}
+
+// Enqueue one forward pass over S tokens per sequence (S == 1: decode).  Inputs are the device buffers
+// ids_dev [B*S], pos_dev [S], past_dev, active_dev.  Leaves logits (and token ids) in device buffers.
+static int enqueue_forward(Model &m, cudaStream_t st, int S) {
+    const mynn_b200_model_config &c = m.c;
+    const int B = c.batch, H = c.hidden, D = c.head_dim, dt = c.dtype;
+    const int M = B * S;
+    const int tp = c.tp_world;
+    const size_t esz = dtype_size(dt);
+    const int Nq = m.Hq * D, Nkv = m.Hkv * D;
+    const float attn_scale = 1.0f / sqrtf((float)D);
+
+    RC(mynn_b200_embed_gather_dequant(st, m.x, m.embed, m.embed_scale, m.ids_dev, M, H, c.vocab, dt));
+    RC(mynn_b200_rms_norm(st, m.n, m.x, m.layers[0].ln1, c.rms_eps, M, H, dt));
+    for (int l = 0; l < c.n_layers; l++) {
+        const LayerW &L = m.layers[l];
+        // --- attention block ---
+        char *qb = (char *)m.qkv;
+        long long qs, ks, vs;
+        const char *kb, *vb;
+        if (L.qkv_fused) {
+            const int Nt = Nq + 2 * Nkv;
+            RC(gemm(st, m, qb, m.n, L.wq, L.sq, nullptr, M, Nt, H, dt));
+            qs = ks = vs = Nt;
+            kb = qb + (size_t)Nq * esz;
+            vb = qb + (size_t)(Nq + Nkv) * esz;
+        } else {
+            char *k_ = qb + (size_t)M * Nq * esz, *v_ = k_ + (size_t)M * Nkv * esz;
+            RC(gemm(st, m, qb, m.n, L.wq, L.sq, nullptr, M, Nq, H, dt));
+            RC(gemm(st, m, k_, m.n, L.wk, L.sk, nullptr, M, Nkv, H, dt));
+            RC(gemm(st, m, v_, m.n, L.wv, L.sv, nullptr, M, Nkv, H, dt));
+            qs = Nq;
+            ks = vs = Nkv;
+            kb = k_;
+            vb = v_;
+        }
+        RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t, S == 1 ? m.pos0_dev : m.pos_dev, B, S,
+                                 m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
+        RC(launch_attention(st, m.attn, m.q_rot, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
+                            c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
+        if (tp == 1) {
+            RC(gemm(st, m, m.x, m.attn, L.wo, L.so, m.x, M, H, Nq, dt));  // x = round(x + round(o))
+            RC(mynn_b200_rms_norm(st, m.n, m.x, L.ln2, c.rms_eps, M, H, dt));
+        } else {
+            RC(gemm(st, m, m.part, m.attn, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
+            RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
+            RC(launch_add_f32_rms_norm(st, dt, m.x, m.n, m.x, m.part, L.ln2, c.rms_eps, M, H));
+        }
+        // --- MLP block ---
+        if (L.gu_fused) {
+            RC(gemm(st, m, m.gu, m.n, L.wg, L.sg, nullptr, M, 2 * m.ffn, H, dt));
+            RC(launch_swiglu_strided(st, dt, m.h, m.gu, (char *)m.gu + (size_t)m.ffn * esz, M, m.ffn, 2LL * m.ffn));
+        } else {
+            char *u_ = (char *)m.gu + (size_t)M * m.ffn * esz;
+            RC(gemm(st, m, m.gu, m.n, L.wg, L.sg, nullptr, M, m.ffn, H, dt));
+            RC(gemm(st, m, u_, m.n, L.wu, L.su, nullptr, M, m.ffn, H, dt));
+            RC(launch_swiglu_strided(st, dt, m.h, m.gu, u_, M, m.ffn, m.ffn));
+        }
+        const bool last = l + 1 == c.n_layers;
+        const void *next_norm = last ? nullptr : m.layers[l + 1].ln1;
+        if (tp == 1) {
+            RC(gemm(st, m, m.x, m.h, L.wd, L.sd, m.x, M, H, m.ffn, dt));
+            if (!last) RC(mynn_b200_rms_norm(st, m.n, m.x, next_norm, c.rms_eps, M, H, dt));
+        } else {
+            RC(gemm(st, m, m.part, m.h, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
+            RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
+            RC(launch_add_f32_rms_norm(st, dt, m.x, last ? nullptr : m.n, m.x, m.part, next_norm, c.rms_eps, M, H));
+        }
+    }
+    // --- head: only the last token of each sequence is needed ---
+    const void *xl = m.x;
+    if (S > 1) {
+        MYNN_CUDA_OK(cudaMemcpy2DAsync(m.last_x, (size_t)H * esz, (const char *)m.x + (size_t)(S - 1) * H * esz,
+                                       (size_t)S * H * esz, (size_t)H * esz, B, cudaMemcpyDeviceToDevice, st));
+        xl = m.last_x;
+    }
+    RC(mynn_b200_rms_norm(st, m.n, xl, m.final_norm, c.rms_eps, B, H, dt));
+    RC(gemm(st, m, m.logits, m.n, m.lm_w, m.lm_scale, nullptr, B, m.vocab_l, H, dt));
+    if (c.output_mode == 1) {
+        if (tp == 1) {
+            RC(mynn_b200_argmax_last(st, m.tok_dev, m.logits, B, m.vocab_l, dt));
+        } else {
+            RC(launch_argmax_pairs(st, dt, m.pairs, m.logits, B, m.vocab_l, c.tp_rank * m.vocab_l));
+            RC(comm_all_gather(st, m.pairs_all, m.pairs, (size_t)B * 2 * sizeof(float)));
+            RC(launch_argmax_merge(st, m.tok_dev, m.pairs_all, B, tp));
+        }
+        if (S == 1) RC(launch_tok_feedback(st, m.ids_dev, m.tok_dev, B));  // next step may reuse the resident ids
+    } else if (tp > 1) {
+        RC(comm_all_gather(st, m.logits_full, m.logits, (size_t)B * m.vocab_l * esz));
+    }
+    return MYNN_OK;
+}
+
+static int model_create(Model **out, void **initializer, void **session_state) {
+    if (!g_cfg_set) return fail(MYNN_E_STATE, "model_init: call mynn_b200_model_configure first");
+    if (!initializer || !session_state) return fail(MYNN_E_ARG, "model_init: null pointer table");
+    Model *m = new Model();
+    m->c = g_cfg;
+    const mynn_b200_model_config &c = m->c;
+    const int tp = c.tp_world;
+    m->Hq = c.n_heads / tp;
+    m->Hkv = c.n_kv_heads / tp;
+    m->ffn = c.ffn / tp;
+    m->vocab_l = c.vocab / tp;
+    const int prefill = c.max_prefill > 0 ? c.max_prefill : 1;
+    m->max_rows = c.batch * prefill;
+    const size_t esz = dtype_size(c.dtype);
+    const int D = c.head_dim, H = c.hidden;
+
+    int i = 0;
+    m->embed = (const int8_t *)initializer[i++];
+    m->embed_scale = initializer[i++];
+    m->layers.resize(c.n_layers);
+    for (int l = 0; l < c.n_layers; l++) {
+        LayerW &L = m->layers[l];
+        L.ln1 = initializer[i++];
+        L.wq = (const int8_t *)initializer[i++]; L.sq = initializer[i++];
+        L.wk = (const int8_t *)initializer[i++]; L.sk = initializer[i++];
+        L.wv = (const int8_t *)initializer[i++]; L.sv = initializer[i++];
+        L.wo = (const int8_t *)initializer[i++]; L.so = initializer[i++];
+        L.ln2 = initializer[i++];
+        L.wg = (const int8_t *)initializer[i++]; L.sg = initializer[i++];
+        L.wu = (const int8_t *)initializer[i++]; L.su = initializer[i++];
+        L.wd = (const int8_t *)initializer[i++]; L.sd = initializer[i++];
+        L.kc = session_state[2 * l];
+        L.vc = session_state[2 * l + 1];
+        const size_t nq = (size_t)m->Hq * D, nkv = (size_t)m->Hkv * D;
+        L.qkv_fused = L.wk == L.wq + nq * H && L.wv == L.wk + nkv * H &&
+                      (const char *)L.sk == (const char *)L.sq + nq * esz &&
+                      (const char *)L.sv == (const char *)L.sk + nkv * esz;
+        L.gu_fused = L.wu == L.wg + (size_t)m->ffn * H && (const char *)L.su == (const char *)L.sg + (size_t)m->ffn * esz;
+    }
+    m->final_norm = initializer[i++];
+    m->lm_w = (const int8_t *)initializer[i++];
+    m->lm_scale = initializer[i++];
+    m->cos_t = initializer[i++];
+    m->sin_t = initializer[i++];
+    for (int j = 0; j < i; j++)
+        if (!initializer[j]) {
+            delete m;
+            return fail(MYNN_E_ARG, "model_init: initializer %d is null", j);
+        }
+
+    // ---- activation arena ----
+    const size_t R = m->max_rows;
+    const size_t nqkv = (size_t)(m->Hq + 2 * m->Hkv) * D;
+    m->attn_ws_bytes = mynn_b200_attention_workspace_bytes(c.batch, m->Hq, m->Hkv, D, c.max_seq_len);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += up256(bytes); return o; };
+    const size_t o_in = take(16 + R * 8), o_pos = take((size_t)prefill * 8), o_tok = take((size_t)c.batch * 4), o_x = take(R * H * esz), o_n = take(R * H * esz),
+                 o_qkv = take(R * nqkv * esz), o_qrot = take(R * m->Hq * D * esz), o_attn = take(R * m->Hq * D * esz),
+                 o_gu = take(R * 2 * m->ffn * esz), o_h = take(R * m->ffn * esz), o_last = take((size_t)c.batch * H * esz),
+                 o_logits = take((size_t)c.batch * m->vocab_l * esz),
+                 o_full = take(tp > 1 ? (size_t)c.batch * c.vocab * esz : 0), o_part = take(tp > 1 ? R * H * 4 : 0),
+                 o_pairs = take((size_t)c.batch * 8), o_pairs_all = take((size_t)c.batch * 8 * tp),
+                 o_ws = take(m->attn_ws_bytes);
+    cudaError_t e = cudaMalloc(&m->arena, off);
+    if (e != cudaSuccess) {
+        delete m;
+        return fail(MYNN_E_CUDA, "model_init: cudaMalloc(%zu) failed: %s", off, cudaGetErrorString(e));
+    }
+    cudaMemset(m->arena, 0, off);
+    char *a = m->arena;
+    m->past_dev = (int32_t *)(a + o_in);
+    m->active_dev = (int32_t *)(a + o_in + 4);
+    m->pos0_dev = (int64_t *)(a + o_in + 8);
+    m->ids_dev = (int64_t *)(a + o_in + 16);
+    m->pos_dev = (int64_t *)(a + o_pos);
+    m->tok_dev = (int32_t *)(a + o_tok);
+    m->x = a + o_x; m->n = a + o_n; m->qkv = a + o_qkv; m->q_rot = a + o_qrot; m->attn = a + o_attn;
+    m->gu = a + o_gu; m->h = a + o_h; m->last_x = a + o_last; m->logits = a + o_logits;
+    m->logits_full = a + o_full; m->part = (float *)(a + o_part); m->pairs = (float *)(a + o_pairs);
+    m->pairs_all = (float *)(a + o_pairs_all); m->attn_ws = a + o_ws;
+    e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMallocHost((void **)&m->h_in, 16 + R * 8);
+    if (e != cudaSuccess) {
+        cudaFree(m->arena);
+        delete m;
+        return fail(MYNN_E_CUDA, "model_init: stream / pinned buffer creation failed: %s", cudaGetErrorString(e));
+    }
+    *out = m;
+    return MYNN_OK;
+}
+
+// Run the decode step from device-resident inputs already in ids_dev/pos_dev/past_dev/active_dev.
+static int run_decode(Model &m, cudaStream_t st) {
+    if (!m.c.use_graph) return enqueue_forward(m, st, 1);
+    if (!m.graph_exec) {
+        cudaGraph_t graph = nullptr;
+        MYNN_CUDA_OK(cudaStreamBeginCapture(m.stream, cudaStreamCaptureModeThreadLocal));
+        int rc = enqueue_forward(m, m.stream, 1);
+        cudaError_t e = cudaStreamEndCapture(m.stream, &graph);
+        if (rc) {
+            if (graph) cudaGraphDestroy(graph);
+            return rc;
+        }
+        if (e != cudaSuccess) return fail(MYNN_E_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+        e = cudaGraphInstantiate(&m.graph_exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) return fail(MYNN_E_CUDA, "graph instantiation failed: %s", cudaGetErrorString(e));
+    }
+    MYNN_CUDA_OK(cudaGraphLaunch(m.graph_exec, st));
+    return MYNN_OK;
+}
+
+static const void *result_ptr(const Model &m, size_t *bytes) {
+    if (m.c.output_mode == 1) {
+        *bytes = (size_t)m.c.batch * 4;
+        return m.tok_dev;
+    }
+    *bytes = (size_t)m.c.batch * m.c.vocab * dtype_size(m.c.dtype);
+    return m.c.tp_world > 1 ? m.logits_full : m.logits;
+}
+
+// tp > 1 logits arrive as [rank][batch][vocab/tp]; reorder on the host side of the copy.
+static int copy_result_to_host(Model &m, void *dst) {
+    size_t bytes;
+    const void *src = result_ptr(m, &bytes);
+    if (m.c.output_mode == 0 && m.c.tp_world > 1) {
+        const size_t row = (size_t)m.vocab_l * dtype_size(m.c.dtype);
+        for (int r = 0; r < m.c.tp_world; r++)
+            MYNN_CUDA_OK(cudaMemcpy2DAsync((char *)dst + r * row, row * m.c.tp_world, (const char *)src + (size_t)r * m.c.batch * row,
+                                           row, row, m.c.batch, cudaMemcpyDeviceToHost, m.stream));
+    } else {
+        MYNN_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, m.stream));
+    }
+    MYNN_CUDA_OK(cudaStreamSynchronize(m.stream));
+    return MYNN_OK;
+}
+
+static int model_run(Model &m, void **output, void **input) {
+    if (!output || !input || !output[0] || !input[0] || !input[1] || !input[2] || !input[3])
+        return fail(MYNN_E_ARG, "model: null input/output pointer");
+    const int64_t past = *(const int64_t *)input[2], active = *(const int64_t *)input[3];
+    if (past < 0 || past >= m.c.max_seq_len || active < 0 || active > m.c.max_seq_len)
+        return fail(MYNN_E_ARG, "model: past_len %lld / active_seq_kv %lld outside the %d-row cache", (long long)past,
+                    (long long)active, m.c.max_seq_len);
+    cudaStream_t st = m.stream;
+    // one pinned block, one copy: {past, active, position, ids}
+    ((int32_t *)m.h_in)[0] = (int32_t)past;
+    ((int32_t *)m.h_in)[1] = (int32_t)active;
+    memcpy(m.h_in + 8, input[1], 8);
+    memcpy(m.h_in + 16, input[0], (size_t)m.c.batch * 8);
+    MYNN_CUDA_OK(cudaMemcpyAsync(m.past_dev, m.h_in, 16 + (size_t)m.c.batch * 8, cudaMemcpyHostToDevice, st));
+    RC(run_decode(m, st));
+    return copy_result_to_host(m, output[0]);
+}
+
+}  // namespace mynn
+
+using namespace mynn;
+
+extern "C" int mynn_b200_model_configure(const mynn_b200_model_config *cfg) {
+    if (!cfg) return fail(MYNN_E_ARG, "model_configure: null config");
+    const mynn_b200_model_config &c = *cfg;
+    if (c.n_layers <= 0 || c.hidden <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.head_dim <= 0 || c.ffn <= 0 ||
+        c.vocab <= 0 || c.max_seq_len <= 0 || c.batch <= 0)
+        return fail(MYNN_E_ARG, "model_configure: non-positive dimension");
+    if (c.dtype != MYNN_BF16 && c.dtype != MYNN_F16 && c.dtype != MYNN_F32) return fail(MYNN_E_ARG, "model_configure: bad dtype %d", c.dtype);
+    if (c.tp_world < 1 || c.tp_rank < 0 || c.tp_rank >= c.tp_world) return fail(MYNN_E_ARG, "model_configure: bad tp rank %d/%d", c.tp_rank, c.tp_world);
+    if (c.n_heads % c.n_kv_heads) return fail(MYNN_E_ARG, "model_configure: heads %d not a multiple of kv heads %d", c.n_heads, c.n_kv_heads);
+    if (c.n_kv_heads % c.tp_world || c.ffn % c.tp_world || c.vocab % c.tp_world)
+        return fail(MYNN_E_ARG, "model_configure: kv heads / ffn / vocab must divide by tp_world=%d", c.tp_world);
+    if (c.tp_world > 1 && (comm_world() != c.tp_world || comm_rank() != c.tp_rank))
+        return fail(MYNN_E_STATE, "model_configure: communicator is rank %d of %d, config says %d of %d", comm_rank(), comm_world(), c.tp_rank, c.tp_world);
+    if (c.head_dim & 1) return fail(MYNN_E_ARG, "model_configure: odd head_dim");
+    g_cfg = c;
+    g_cfg_set = true;
+    return MYNN_OK;
+}
+
+extern "C" void *model_init(void **initializer, void **session_state) {
+    Model *m = nullptr;
+    g_status = model_create(&m, initializer, session_state);
+    return m;
+}
+
+extern "C" void model(void *state, void **output, void **input) {
+    if (!state) {
+        g_status = fail(MYNN_E_STATE, "model: null state");
+        return;
+    }
+    g_status = model_run(*(Model *)state, output, input);
+}
+
+extern "C" void model_destroy(void *state) {
+    if (!state) return;
+    Model *m = (Model *)state;
+    if (m->stream) cudaStreamSynchronize(m->stream);
+    if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+    if (m->stream) cudaStreamDestroy(m->stream);
+    if (m->arena) cudaFree(m->arena);
+    if (m->h_in) cudaFreeHost(m->h_in);
+    delete m;
+}
+
+extern "C" int mynn_b200_model_status(void) { return g_status; }
+
+extern "C" int mynn_b200_model_step_device(void *state, void *stream, const int64_t *ids_dev, int past_len, void *out_dev) {
+    if (!state) return fail(MYNN_E_STATE, "model_step_device: null state");
+    Model &m = *(Model *)state;
+    if (past_len < 0 || past_len >= m.c.max_seq_len) return fail(MYNN_E_ARG, "model_step_device: past_len %d outside the cache", past_len);
+    cudaStream_t st = stream ? (cudaStream_t)stream : m.stream;
+    // The 16-byte header is passed by value through a pageable copy (staged by the runtime before it returns).
+    struct { int32_t past, active; int64_t pos; } hdr = {past_len, past_len + 1, (int64_t)past_len};
+    if (ids_dev) MYNN_CUDA_OK(cudaMemcpyAsync(m.ids_dev, ids_dev, (size_t)m.c.batch * 8, cudaMemcpyDeviceToDevice, st));
+    MYNN_CUDA_OK(cudaMemcpyAsync(m.past_dev, &hdr, 16, cudaMemcpyHostToDevice, st));
+    RC(run_decode(m, st));
+    if (out_dev) {
+        size_t bytes;
+        const void *src = result_ptr(m, &bytes);
+        MYNN_CUDA_OK(cudaMemcpyAsync(out_dev, src, bytes, cudaMemcpyDeviceToDevice, st));
+    }
+    return MYNN_OK;
+}
+
+// Prefill of T tokens per sequence starting at cache row past_len (the engine's prefill graph,
+// crates/llm/src/session.rs:426-480, without the padding rows): ids_host int64 [batch, T]; out_host receives the
+// logits / token ids of the last position, as model() does.  T <= max_prefill.
+extern "C" int mynn_b200_model_prefill(void *state, const int64_t *ids_host, int T, int past_len, void *out_host) {
+    if (!state) return fail(MYNN_E_STATE, "model_prefill: null state");
+    Model &m = *(Model *)state;
+    const int cap = m.c.max_prefill > 0 ? m.c.max_prefill : 1;
+    if (T <= 0 || T > cap) return fail(MYNN_E_ARG, "model_prefill: %d tokens, capacity %d", T, cap);
+    if (past_len < 0 || past_len + T > m.c.max_seq_len) return fail(MYNN_E_ARG, "model_prefill: rows [%d, %d) outside the %d-row cache", past_len, past_len + T, m.c.max_seq_len);
+    if (!ids_host || !out_host) return fail(MYNN_E_ARG, "model_prefill: null pointer");
+    cudaStream_t st = m.stream;
+    std::vector<int64_t> pos(T);
+    for (int i = 0; i < T; i++) pos[i] = past_len + i;
+    struct { int32_t past, active; int64_t pos; } hdr = {past_len, past_len + T, (int64_t)past_len};
+    MYNN_CUDA_OK(cudaMemcpyAsync(m.ids_dev, ids_host, (size_t)m.c.batch * T * 8, cudaMemcpyHostToDevice, st));
+    MYNN_CUDA_OK(cudaMemcpyAsync(m.pos_dev, pos.data(), (size_t)T * 8, cudaMemcpyHostToDevice, st));
+    MYNN_CUDA_OK(cudaMemcpyAsync(m.past_dev, &hdr, 16, cudaMemcpyHostToDevice, st));
+    MYNN_CUDA_OK(cudaStreamSynchronize(st));  // the sources above are short-lived host memory
+    RC(enqueue_forward(m, st, T));
+    return copy_result_to_host(m, out_host);
+}

@@ -1,0 +1,40 @@
+// Launchers shared between translation units that are not part of the public C ABI: the fused forms the
+// decoder step uses on top of the operator-level entry points.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mynn {
+
+// RoPE(q), RoPE(k) and the KV append of one step in a single launch.
+// q/k/v: [B*S rows] with row strides (elements) q_stride/k_stride/v_stride, heads contiguous inside a row.
+// positions int64 [S] (device) select the cos/sin rows; K and V rows go to cache row (*past_len_dev + s).
+// q_out [B, Hq, S, D].
+int launch_rope_kv_append(cudaStream_t st, int dtype, void *q_out, void *k_cache, void *v_cache, const void *q,
+                          const void *k, const void *v, long long q_stride, long long k_stride, long long v_stride,
+                          const void *cos_t, const void *sin_t, const int64_t *positions, int B, int S, int Hq,
+                          int Hkv, int D, int cache_seq, const int32_t *past_len_dev);
+
+// out[m, f] = swish(gate[m, f]) * up[m, f] with gate/up rows `in_stride` elements apart.
+int launch_swiglu_strided(cudaStream_t st, int dtype, void *out, const void *gate, const void *up, int M, int F,
+                          long long in_stride);
+
+// sum = round(a + round(b_f32)); norm = RMSNorm(sum) (norm_out/weight may be null to skip the norm).
+int launch_add_f32_rms_norm(cudaStream_t st, int dtype, void *sum_out, void *norm_out, const void *a, const float *b,
+                            const void *weight, float eps, int rows, int D);
+
+// Attention with a choice of output layout: out_bshd != 0 writes [B, Sq, Hq, D] instead of [B, Hq, Sq, D].
+int launch_attention(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
+                     int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
+                     const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
+                     size_t workspace_bytes, int out_bshd);
+
+// Per-row (max value, last index of the maximum) of a logits shard, and the merge over tensor-parallel shards.
+int launch_argmax_pairs(cudaStream_t st, int dtype, float *pairs /*[rows][2]*/, const void *logits, int rows, int V,
+                        int index_offset);
+int launch_argmax_merge(cudaStream_t st, int32_t *out_idx, const float *pairs /*[world][rows][2]*/, int rows, int world);
+
+// ids[i] = tok[i]: feeds the greedy tokens back as the next step's input ids without leaving the device.
+int launch_tok_feedback(cudaStream_t st, int64_t *ids, const int32_t *tok, int n);
+
+}  // namespace mynn

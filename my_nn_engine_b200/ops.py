@@ -1,0 +1,172 @@
+"""Operator-level host API: the engine's decode-path operators over torch CUDA tensors.
+
+Each function mirrors one operator of the engine's graph (same operand order and meaning as the ``Operator``
+variants and ``args::*`` slots in src/graph/operator.rs of the engine) and forwards raw device pointers to the
+C ABI.  torch is used only for device memory and streams.  Nothing here computes on the CPU: inputs must be CUDA
+tensors and the call raises otherwise.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ffi
+
+_DT = {torch.float32: ffi.F32, torch.bfloat16: ffi.BF16, torch.float16: ffi.F16}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("mynn_b200 operators need CUDA tensors (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError("mynn_b200 operators need contiguous tensors")
+    return t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dequant_matmul(act, wq, scale, axis: int = 0, out=None):
+    """``DequantMatMul{axis}(act, wq, scale)``: act [..., K]; wq int8 [N, K] (axis 0) or [K, N] (axis 1);
+    scale [N].  Output dtype = scale dtype (src/transform/shape.rs:326-345)."""
+    if wq.dtype != torch.int8:
+        raise TypeError("wq must be int8")
+    if axis not in (0, 1):
+        raise ValueError("axis must be 0 or 1")
+    n, k = (wq.shape[0], wq.shape[1]) if axis == 0 else (wq.shape[1], wq.shape[0])
+    if act.shape[-1] != k or scale.numel() != n:
+        raise ValueError(f"shape mismatch: act {tuple(act.shape)}, wq {tuple(wq.shape)}, scale {tuple(scale.shape)}")
+    m = act.numel() // k if k else 0
+    if out is None:
+        out = torch.empty(act.shape[:-1] + (n,), dtype=scale.dtype, device=act.device)
+    ffi.check(ffi.lib().mynn_b200_dequant_matmul(_stream(), _ptr(out), _ptr(act), _ptr(wq), _ptr(scale), m, n, k,
+                                                 _dt(act), _dt(scale), ffi.W_NK if axis == 0 else ffi.W_KN))
+    return out
+
+
+def dequant_matmul_residual(act, wq, scale, residual, out=None):
+    """round(residual + round(DequantMatMul(act, wq, scale))); ``out`` may alias ``residual``."""
+    n, k = wq.shape
+    m = act.numel() // k
+    if out is None:
+        out = torch.empty_like(residual)
+    ffi.check(ffi.lib().mynn_b200_dequant_matmul_residual(_stream(), _ptr(out), _ptr(act), _ptr(wq), _ptr(scale),
+                                                          _ptr(residual), m, n, k, _dt(act)))
+    return out
+
+
+_workspaces: dict = {}
+
+
+def attention_workspace(b, hq, hkv, d, cache_seq_len, device):
+    """Zero-initialised scratch for the split-KV decode kernel, cached per shape and device."""
+    need = ffi.lib().mynn_b200_attention_workspace_bytes(b, hq, hkv, d, cache_seq_len)
+    key = (b, hkv, d, str(device))
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def attention(q, k, v, scale: float, active_seq_kv=None, is_causal: bool = False, out=None, workspace=None):
+    """``Attention{is_causal, scale}``: q [B,Hq,Sq,D]; k, v [B,Hkv,cache_seq_len,D]; ``active_seq_kv`` is an int
+    (host scalar, as the engine passes it) or an int32 CUDA tensor (read on the device); None = all rows."""
+    b, hq, sq, d = q.shape
+    hkv, sk = k.shape[1], k.shape[2]
+    if out is None:
+        out = torch.empty_like(q)
+    dev_ptr, host_val = None, sk
+    if isinstance(active_seq_kv, torch.Tensor):
+        if active_seq_kv.dtype != torch.int32:
+            raise TypeError("device active_seq_kv must be int32")
+        dev_ptr = _ptr(active_seq_kv)
+    elif active_seq_kv is not None:
+        host_val = int(active_seq_kv)
+    if workspace is None:
+        workspace = attention_workspace(b, hq, hkv, d, sk, q.device)
+    ffi.check(ffi.lib().mynn_b200_attention(_stream(), _ptr(out), _ptr(q), _ptr(k), _ptr(v), float(scale), b, hq, hkv,
+                                            sq, d, sk, host_val, dev_ptr, int(is_causal), _dt(q), _ptr(workspace),
+                                            workspace.numel()))
+    return out
+
+
+def kv_cache_update(cache, new, offset):
+    """``KVCacheUpdate``: cache[b,h,offset+t,:] = new[b,h,t,:] in place; offset int or int32 CUDA tensor."""
+    bh = cache.shape[0] * cache.shape[1]
+    dev_ptr, host_val = None, 0
+    if isinstance(offset, torch.Tensor):
+        dev_ptr = _ptr(offset)
+    else:
+        host_val = int(offset)
+    ffi.check(ffi.lib().mynn_b200_kv_cache_update(_stream(), _ptr(cache), _ptr(new), bh, cache.shape[2], new.shape[2],
+                                                  cache.shape[3], host_val, dev_ptr, _dt(cache)))
+    return cache
+
+
+def rms_norm(x, weight, eps: float, out=None):
+    d = x.shape[-1]
+    if out is None:
+        out = torch.empty_like(x)
+    ffi.check(ffi.lib().mynn_b200_rms_norm(_stream(), _ptr(out), _ptr(x), _ptr(weight), float(eps), x.numel() // d, d, _dt(x)))
+    return out
+
+
+def add_rms_norm(a, b, weight, eps: float):
+    """Returns (round(a + b), RMSNorm of it)."""
+    d = a.shape[-1]
+    s, n = torch.empty_like(a), torch.empty_like(a)
+    ffi.check(ffi.lib().mynn_b200_add_rms_norm(_stream(), _ptr(s), _ptr(n), _ptr(a), _ptr(b), _ptr(weight), float(eps),
+                                               a.numel() // d, d, _dt(a)))
+    return s, n
+
+
+def rope(x, cos_table, sin_table, position, out=None):
+    """Fused RoPE: x [..., S, D]; tables [max_pos, D]; position int64 CUDA tensor [S]."""
+    s, d = x.shape[-2], x.shape[-1]
+    if out is None:
+        out = torch.empty_like(x)
+    ffi.check(ffi.lib().mynn_b200_rope(_stream(), _ptr(out), _ptr(x), _ptr(cos_table), _ptr(sin_table), _ptr(position),
+                                       x.numel() // (s * d) if s * d else 0, s, d, _dt(x)))
+    return out
+
+
+def swish_mul(gate, up, out=None):
+    if out is None:
+        out = torch.empty_like(gate)
+    ffi.check(ffi.lib().mynn_b200_swish_mul(_stream(), _ptr(out), _ptr(gate), _ptr(up), gate.numel(), _dt(gate)))
+    return out
+
+
+def add(a, b, out=None):
+    if out is None:
+        out = torch.empty_like(a)
+    ffi.check(ffi.lib().mynn_b200_add(_stream(), _ptr(out), _ptr(a), _ptr(b), a.numel(), _dt(a)))
+    return out
+
+
+def embed_gather_dequant(table, scale, ids):
+    """Gather(DequantizeLinear(table, scale, axis=0), ids): table int8 [V,H]; scale [V]; ids int64 CUDA tensor."""
+    v, h = table.shape
+    out = torch.empty(tuple(ids.shape) + (h,), dtype=scale.dtype, device=table.device)
+    ffi.check(ffi.lib().mynn_b200_embed_gather_dequant(_stream(), _ptr(out), _ptr(table), _ptr(scale), _ptr(ids),
+                                                       ids.numel(), h, v, _dt(scale)))
+    return out
+
+
+def argmax_last(logits):
+    """Per-row greedy pick, last index among equal maxima; returns int32 CUDA tensor [rows]."""
+    v = logits.shape[-1]
+    rows = logits.numel() // v
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    ffi.check(ffi.lib().mynn_b200_argmax_last(_stream(), _ptr(out), _ptr(logits), rows, v, _dt(logits)))
+    return out

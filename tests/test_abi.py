@@ -1,0 +1,72 @@
+"""CPU-only checks of the C-ABI boundary: the library loads, exports every symbol the header declares, and
+rejects bad arguments with a status code and message (no compute calls are made without a GPU)."""
+import os
+import re
+
+import pytest
+
+from my_nn_engine_b200 import ffi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "mynn_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\(", text)
+    return sorted({n for n in names if n.startswith("mynn_b200_") or n in ("model_init", "model", "model_destroy", "alloc_pinned", "free_pinned")})
+
+
+def test_header_symbols_are_exported_and_bound():
+    lib = ffi.lib()
+    syms = declared_symbols()
+    assert len(syms) >= 30
+    for name in syms:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+        assert name in ffi.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(ffi.SIGNATURES) == set(syms)
+
+
+def test_version_and_arch():
+    assert ffi.lib().mynn_b200_abi_version() == 1
+    assert ffi.lib().mynn_b200_compiled_arch() == 100
+
+
+def test_argument_errors_return_status_not_exit():
+    lib = ffi.lib()
+    assert lib.mynn_b200_rms_norm(None, None, None, None, 1e-5, -1, 4, ffi.BF16) == ffi.E_ARG
+    assert "rms_norm" in ffi.last_error()
+    assert lib.mynn_b200_dequant_matmul(None, None, None, None, None, 1, 16, 64, 7, ffi.BF16, ffi.W_NK) == ffi.E_ARG
+    assert lib.mynn_b200_dequant_matmul(None, None, None, None, None, 1, 16, 64, ffi.BF16, ffi.BF16, 5) == ffi.E_ARG
+    assert lib.mynn_b200_attention(None, None, None, None, None, 1.0, 1, 3, 2, 1, 64, 8, 8, None, 0, ffi.BF16, None, 0) == ffi.E_ARG
+    assert "multiple" in ffi.last_error()
+    assert lib.mynn_b200_kv_cache_update(None, None, None, 1, -1, 1, 4, 0, None, ffi.BF16) == ffi.E_ARG
+    # empty problems are accepted without touching a device
+    assert lib.mynn_b200_dequant_matmul(None, None, None, None, None, 0, 16, 64, ffi.BF16, ffi.BF16, ffi.W_NK) == ffi.OK
+    assert lib.mynn_b200_swish_mul(None, None, None, None, 0, ffi.BF16) == ffi.OK
+
+
+def test_model_configure_validation():
+    lib = ffi.lib()
+    cfg = ffi.ModelConfig(n_layers=2, hidden=64, n_heads=4, n_kv_heads=3, head_dim=16, ffn=128, vocab=100,
+                          max_seq_len=32, batch=1, dtype=ffi.BF16, output_mode=0, tp_rank=0, tp_world=1, use_graph=0,
+                          max_prefill=0, rms_eps=1e-5)
+    assert lib.mynn_b200_model_configure(cfg) == ffi.E_ARG  # 4 heads not a multiple of 3 kv heads
+    cfg.n_kv_heads = 2
+    assert lib.mynn_b200_model_configure(cfg) == ffi.OK
+    cfg.tp_world = 2  # no communicator of that size
+    assert lib.mynn_b200_model_configure(cfg) == ffi.E_STATE
+    with pytest.raises(ffi.MynnError):
+        ffi.check(lib.mynn_b200_model_configure(None))
+
+
+def test_communicator_identity_world():
+    """world_size 1 needs no NCCL and behaves as the identity (mirrors crates/comm/src/uds.rs:258-316 of the
+    reference: world_size=1 identity); bad ranks are rejected."""
+    lib = ffi.lib()
+    assert lib.mynn_b200_comm_init(None, 0, 0) == ffi.E_ARG
+    assert lib.mynn_b200_comm_init(None, 2, 2) == ffi.E_ARG
+    assert lib.mynn_b200_comm_init(None, 0, 1) == ffi.OK
+    assert lib.mynn_b200_comm_rank() == 0 and lib.mynn_b200_comm_world_size() == 1
+    assert lib.mynn_b200_all_reduce(None, None, None, -1, ffi.F32) == ffi.E_ARG
+    assert lib.mynn_b200_comm_destroy() == ffi.OK

@@ -1,0 +1,96 @@
+"""Decode-loop semantics on the host (CPU only), mirroring the reference's mock-model tests
+(crates/llm/tests/mock_decode.rs): the 'model' is a logit table indexed by past_len."""
+import pytest
+
+from my_nn_engine_b200.session import GenerateOptions, LlmSession, PromptTooLong, argmax_last
+
+SEQUENCE = [1, 2, 3, 4, 5, 0, 1, 2, 3, 4, 5, 0, 1, 2, 3, 4]  # fixtures/mock_decode/expected_sequence.json
+VOCAB = ["<unk>", "a", "b", "c", "d", "e"]
+
+
+class WordTokenizer:
+    def encode(self, text):
+        return [VOCAB.index(w) if w in VOCAB else 0 for w in text.split()]
+
+    def decode(self, ids):
+        return " ".join(VOCAB[i] for i in ids)
+
+
+def make_session(prefill_len=None, max_seq_len=16):
+    calls = []
+
+    def step(token, past_len):
+        calls.append(("step", token, past_len))
+        return SEQUENCE[past_len]
+
+    def prefill(ids, past_len):
+        calls.append(("prefill", tuple(ids), past_len))
+        return SEQUENCE[past_len + len(ids) - 1]
+
+    s = LlmSession(step, max_seq_len, eos_token_id=999, prefill=prefill if prefill_len else None,
+                   prefill_len=prefill_len, tokenizer=WordTokenizer())
+    return s, calls
+
+
+def test_generate_ids_follows_logit_table():
+    s, _ = make_session()
+    assert s.generate_ids("a b c", 5) == [3, 4, 5, 0, 1]
+
+
+def test_generate_decodes_to_text():
+    s, _ = make_session()
+    assert s.generate("a b c", 5) == "c d e <unk> a"
+
+
+def test_past_len_tracks_decode_steps_and_reset():
+    s, _ = make_session()
+    assert s.past_len() == 0
+    s.generate_ids("a b c", 5)
+    assert s.past_len() == 7
+    s.reset()
+    assert s.past_len() == 0
+
+
+def test_empty_prompt_returns_no_tokens():
+    s, calls = make_session()
+    assert s.generate_ids("", 5) == [] and not calls
+
+
+def test_stop_string_truncates_and_rewinds_past_len():
+    s, _ = make_session()
+    opts = GenerateOptions(max_new_tokens=5, stop_strings=["<unk>"])
+    assert s.generate("a b c", opts=opts) == "c d e"
+    s2, _ = make_session()
+    ids = s2.generate_ids("a b c", opts=opts)
+    assert s2.past_len() == 2 + len(ids)
+
+
+def test_eos_stops_generation():
+    s = LlmSession(lambda tok, past: 7, 16, eos_token_id=7)
+    assert s.generate_ids([1, 2], 5) == [7]
+
+
+def test_prompt_too_long_and_cache_limit():
+    s, _ = make_session(max_seq_len=4)
+    with pytest.raises(PromptTooLong):
+        s.generate_ids("a b c d e", 3)
+    s, _ = make_session(max_seq_len=4)
+    assert len(s.generate_ids("a b c", 10)) == 2  # rows 0..3 only: 3 prompt steps + 1 more
+
+
+def test_chunked_prefill_matches_decode_only():
+    a, _ = make_session()
+    b, calls = make_session(prefill_len=2)
+    assert a.generate_ids("a b c", 4) == b.generate_ids("a b c", 4)
+    assert calls[0] == ("prefill", (1, 2), 0) and calls[1] == ("prefill", (3,), 2)
+    assert a.past_len() == b.past_len()
+    # prefill pads to a multiple of prefill_len when checking capacity
+    c, _ = make_session(prefill_len=4, max_seq_len=6)
+    with pytest.raises(PromptTooLong):
+        c.generate_ids("a b c d e", 1)
+
+
+def test_argmax_last_tie_rule():
+    assert argmax_last([1.0, 5.0, 5.0, 2.0]) == 2
+    with pytest.raises(ValueError):
+        argmax_last([1.0, float("nan")])
