@@ -217,7 +217,8 @@ def run_gpu_arm(args, cfg):
         t[:, :, :CONTEXT].copy_(torch.randn(t[:, :, :CONTEXT].shape, generator=g, device=dev, dtype=torch.float32) * 0.5)
     ids0 = torch.randint(0, cfg["vocab_size"], (BATCH,), device=dev, dtype=torch.int64,
                          generator=torch.Generator(device=dev).manual_seed(7))
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream(device=dev)  # a real stream handle: the library treats NULL as the model's own stream
+    torch.cuda.set_stream(stream)
 
     def barrier():
         if world > 1:

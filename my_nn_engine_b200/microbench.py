@@ -1,0 +1,137 @@
+"""Per-kernel timing of the decode path against the HBM roofline.
+
+    python -m my_nn_engine_b200.microbench gemm --m 32 --n 28672 --k 4096 [--dtype bf16] [--ksplit 0] [--copies 8]
+    python -m my_nn_engine_b200.microbench attn --b 16 --hq 32 --hkv 8 --d 128 --len 4096
+    python -m my_nn_engine_b200.microbench suite
+
+Every launch reads a different copy of its weights / KV (copies x size > L2) and the launches are replayed from one
+CUDA graph, so the time is device time of HBM-fed kernels without host launch gaps.  Algorithmic bytes:
+GEMM  N*K + N*sizeof(scale) + M*K*sizeof(act) + M*N*sizeof(out);  attention  2*B*Hkv*L*D*2 + Q + out.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import ffi, ops
+
+_DT = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
+
+
+def _peak():
+    try:
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        return float(json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def _time_graph(fns, reps=3):
+    """fns: list of callables launching one kernel each; returns microseconds per launch."""
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for f in fns[:2]:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        best = 1e30
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            g.replay()
+            e1.record(s)
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) * 1e3 / len(fns))
+    return best
+
+
+def gemm(m, n, k, dtype="bf16", ksplit=0, copies=None, quiet=False):
+    td = _DT[dtype]
+    copies = copies or max(3, int(600e6 // (n * k)) + 1)
+    ws = [torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda") for _ in range(copies)]
+    sc = (torch.rand(n, device="cuda") * 0.018 + 0.002).to(td)
+    act = torch.randn(m, k, device="cuda").to(td)
+    out = torch.empty(m, n, device="cuda", dtype=td)
+    ffi.check(ffi.lib().mynn_b200_debug_set_ksplit(ksplit))
+    us = _time_graph([(lambda w=w: ops.dequant_matmul(act, w, sc, out=out)) for w in ws])
+    ffi.lib().mynn_b200_debug_set_ksplit(0)
+    esz = act.element_size()
+    alg = n * k + n * esz + m * k * esz + m * n * esz
+    res = {"kernel": "dequant_matmul", "m": m, "n": n, "k": k, "dtype": dtype, "ksplit": ksplit, "us": us,
+           "GBps": alg / us / 1e3, "frac_of_measured_peak": alg / us / 1e3 / _peak(), "algorithmic_bytes": alg}
+    if not quiet:
+        print(json.dumps(res), flush=True)
+    return res
+
+
+def attn(b, hq, hkv, d, length, dtype="bf16", copies=None, quiet=False):
+    td = _DT[dtype]
+    kv_bytes = 2 * b * hkv * length * d * 2
+    copies = copies or max(3, int(600e6 // kv_bytes) + 1)
+    ks = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(copies)]
+    vs = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(copies)]
+    q = torch.randn(b, hq, 1, d, device="cuda").to(td)
+    out = torch.empty_like(q)
+    ws = ops.attention_workspace(b, hq, hkv, d, length, q.device)
+    us = _time_graph([(lambda k=k, v=v: ops.attention(q, k, v, 1 / np.sqrt(d), length, out=out, workspace=ws))
+                      for k, v in zip(ks, vs)])
+    alg = kv_bytes + 2 * q.numel() * 2
+    res = {"kernel": "attention_decode", "b": b, "hq": hq, "hkv": hkv, "d": d, "len": length, "dtype": dtype, "us": us,
+           "GBps": alg / us / 1e3, "frac_of_measured_peak": alg / us / 1e3 / _peak(), "algorithmic_bytes": alg}
+    if not quiet:
+        print(json.dumps(res), flush=True)
+    return res
+
+
+def suite():
+    """The shapes of the benchmark configurations: Llama-3-8B and TinyLlama projections at batch 1 and 32, the
+    config-1 GEMV, and the decode-attention microbenchmark."""
+    for m in (1, 32):
+        for n, k in [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128256, 4096)]:
+            gemm(m, n, k)
+    for n, k in [(5632, 2048), (2560, 2048), (2048, 2048), (11264, 2048), (2048, 5632), (32000, 2048)]:
+        gemm(1, n, k)
+    attn(16, 32, 8, 128, 4096)
+    attn(32, 32, 8, 128, 2048)
+    attn(1, 32, 4, 64, 256)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=32)
+    g.add_argument("--n", type=int, default=28672)
+    g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--dtype", default="bf16")
+    g.add_argument("--ksplit", type=int, default=0)
+    g.add_argument("--copies", type=int, default=None)
+    a = sub.add_parser("attn")
+    a.add_argument("--b", type=int, default=16)
+    a.add_argument("--hq", type=int, default=32)
+    a.add_argument("--hkv", type=int, default=8)
+    a.add_argument("--d", type=int, default=128)
+    a.add_argument("--len", type=int, default=4096)
+    a.add_argument("--dtype", default="bf16")
+    a.add_argument("--copies", type=int, default=None)
+    sub.add_parser("suite")
+    args = ap.parse_args()
+    if args.cmd == "gemm":
+        gemm(args.m, args.n, args.k, args.dtype, args.ksplit, args.copies)
+    elif args.cmd == "attn":
+        attn(args.b, args.hq, args.hkv, args.d, args.len, args.dtype, args.copies)
+    else:
+        suite()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,8 +1,10 @@
 """GPU parity tests, model level: the whole decoder step behind model_init / model / model_destroy against the CPU
 oracle on the same seeded int8 checkpoints.  Greedy tokens are compared teacher-forced (the device model is fed the
 oracle's token each step, so one flipped near-tie cannot cascade): every step must pick the oracle's token unless the
-oracle's own top-2 logits are closer than the storage dtype can resolve, and the logits must agree to 1e-2 of their
-scale."""
+oracle's own top-2 logits are closer than the storage dtype can resolve.  Each kernel meets the 1e-2 bound on its
+own (operator tests); the logits at the end of the stack carry the rounding noise of every bf16/fp16 store in between
+(the two sides round differently whenever their f32 sums differ in the last bit), so the end-to-end bound is a few
+storage ulps of the logit scale: 3e-2 for bf16, 1e-2 for fp16, 1e-4 for f32."""
 import numpy as np
 import pytest
 import torch
@@ -71,7 +73,7 @@ def run_parity(cfg, state, dtype, batch, steps, max_seq, prompt_len, prefill_len
     assert np.abs(kc[:, :, :past] - oracle.k_cache[0][:, :, :past]).max() <= 8 * ulp * np.abs(oracle.k_cache[0]).max()
     assert not kc[:, :, past:].any()
     model.close()
-    assert worst <= 1e-2, worst
+    assert worst <= {"bf16": 3e-2, "f16": 1e-2, "f32": 1e-4}[dtype], worst
     return worst, flips
 
 
