@@ -40,22 +40,35 @@ int mynn_b200_abi_version(void);
 int mynn_b200_compiled_arch(void);
 
 /* ---------------------------------------------------------------------------------------------
- * DequantMatMul: out[m,n] = scale[n] * sum_k act[m,k] * wq[n,k]   (f32 accumulate, out in scale dtype)
- * Replaces: Operator::DequantMatMul (src/graph/operator.rs:240-244) and its three CUDA kernels chosen in
- * src/codegen/cuda.rs:1518-1652 (dequant_gemv.cuh:11-59, dequant_matmul_wmma.cuh:87-192,
- * dequant_matmul.cuh:13-51); argument order follows the generated launch (out, act, wq, scale, M, N, K).
+ * DequantMatMul: out[m,n] = scale[n] * sum_k act[m,k] * wq[n,k]   (out in scale dtype)
+ * Replaces: Operator::DequantMatMul (src/graph/operator.rs:240-244; operand slots LHS, RHS, SCALE, WORKSPACE at
+ * :1109-1113) and its three CUDA kernels chosen in src/codegen/cuda.rs:1518-1652 (dequant_gemv.cuh:11-59,
+ * dequant_matmul_wmma.cuh:87-192, dequant_matmul.cuh:13-51); argument order follows the generated launch
+ * (out, act, wq, scale, M, N, K) with the operator's workspace slot last.
  * act [M,K] act_dtype; wq int8 [N,K] (MYNN_W_NK) or [K,N] (MYNN_W_KN); scale [N] and out [M,N] out_dtype.
- * Any M >= 0, N, K accepted (M == 0 is a no-op); shapes with K % 64 == 0 and N % 16 == 0 take the streaming
- * tensor-core kernel, others a generic kernel. */
+ * Any M >= 0, N, K is accepted (M == 0 is a no-op).
+ * workspace: device scratch of mynn_b200_dequant_matmul_workspace_bytes(M, N, K) bytes, 256-byte aligned and ZEROED
+ * before its first use (its first word is a status flag, see mynn_b200_dequant_matmul_check).  With a workspace,
+ * [N,K] problems of up to 32 rows with K % 16 == 0 run on the tcgen05 int8 tensor-core kernel (exact int32
+ * accumulation of 23-bit fixed-point activations).  With workspace == NULL, or for other shapes, kernels that need no
+ * scratch are used (mma.sync streaming kernel for K % 64 == 0, N % 16 == 0, M <= 32; a generic kernel otherwise).
+ * Calls that share a workspace must be ordered on one stream. */
+size_t mynn_b200_dequant_matmul_workspace_bytes(int M, int N, int K);
 int mynn_b200_dequant_matmul(void *stream, void *out, const void *act, const int8_t *wq, const void *scale, int M,
-                             int N, int K, int act_dtype, int out_dtype, int w_layout);
+                             int N, int K, int act_dtype, int out_dtype, int w_layout, void *workspace,
+                             size_t workspace_bytes);
 
 /* Same product followed by a fused epilogue used by the decoder step (no counterpart kernel in the engine,
  * which runs these as separate elementwise launches, src/codegen/cuda/kernel.rs:723-950):
- *   residual != NULL : out = round(residual + round(product))      (two store points kept)
+ *   out = round(residual + round(product))      (two store points kept; out may alias residual)
  * wq must be [N,K]. */
 int mynn_b200_dequant_matmul_residual(void *stream, void *out, const void *act, const int8_t *wq, const void *scale,
-                                      const void *residual, int M, int N, int K, int dtype);
+                                      const void *residual, int M, int N, int K, int dtype, void *workspace,
+                                      size_t workspace_bytes);
+
+/* Synchronises the stream and reads the workspace status word: MYNN_E_CUDA if a bounded pipeline wait inside the
+ * tcgen05 kernel expired (the outputs of that call are then invalid), MYNN_OK otherwise. */
+int mynn_b200_dequant_matmul_check(void *stream, const void *workspace);
 
 /* ---------------------------------------------------------------------------------------------
  * Attention (decode and generic).  out = softmax(scale * Q K^T [causal]) V with GQA.
@@ -149,6 +162,7 @@ typedef struct mynn_b200_model_config {
     int32_t tp_rank, tp_world;
     int32_t use_graph;   /* capture the step in a CUDA graph and replay it */
     int32_t max_prefill; /* largest T accepted by mynn_b200_model_prefill (0 = decode only) */
+    int32_t use_tensor_gemm; /* 1: DequantMatMul on the tcgen05 int8 kernel (needs scratch); 0: mma.sync streaming kernel */
     float rms_eps;
 } mynn_b200_model_config;
 

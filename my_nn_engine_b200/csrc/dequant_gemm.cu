@@ -21,6 +21,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "i8_gemm.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -400,13 +401,16 @@ static int dequant_matmul_typed(cudaStream_t st, OutT *out, const ActT *act, con
 
 static int dequant_matmul_dispatch(void *stream, void *out, const void *act, const int8_t *wq, const void *scale,
                                    const void *resid, int M, int N, int K, int act_dtype, int out_dtype,
-                                   int w_layout) {
+                                   int w_layout, void *workspace, size_t workspace_bytes) {
     if (M < 0 || N < 0 || K < 0) return fail(MYNN_E_ARG, "dequant_matmul: negative dimension (M=%d N=%d K=%d)", M, N, K);
     if (w_layout != MYNN_W_NK && w_layout != MYNN_W_KN) return fail(MYNN_E_ARG, "dequant_matmul: bad weight layout %d", w_layout);
     if (!dtype_ok(act_dtype) || !dtype_ok(out_dtype)) return fail(MYNN_E_ARG, "dequant_matmul: bad dtype");
     if (M == 0 || N == 0) return MYNN_OK;
     if (!out || !wq || !scale || (!act && K > 0)) return fail(MYNN_E_ARG, "dequant_matmul: null pointer");
     cudaStream_t st = (cudaStream_t)stream;
+    // With scratch memory the tcgen05 int8 kernel takes every [N,K] problem of up to 32 rows.
+    if (workspace && w_layout == MYNN_W_NK && i8_gemm_supported(M, N, K, wq, act_dtype, out_dtype))
+        return i8_gemm_launch(st, out, act, wq, scale, resid, M, N, K, act_dtype, out_dtype, workspace, workspace_bytes);
 #define CASE(AD, AT, OD, OT)                                                                                        \
     if (act_dtype == AD && out_dtype == OD)                                                                         \
         return dequant_matmul_typed<AT, OT>(st, (OT *)out, (const AT *)act, wq, (const OT *)scale, (const OT *)resid, \
@@ -422,20 +426,40 @@ static int dequant_matmul_dispatch(void *stream, void *out, const void *act, con
 
 }  // namespace mynn
 
+extern "C" size_t mynn_b200_dequant_matmul_workspace_bytes(int M, int N, int K) {
+    (void)N;
+    return mynn::i8_gemm_workspace_bytes(M < mynn::kI8MaxRows ? M : mynn::kI8MaxRows, K);
+}
+
 extern "C" int mynn_b200_dequant_matmul(void *stream, void *out, const void *act, const int8_t *wq, const void *scale,
-                                        int M, int N, int K, int act_dtype, int out_dtype, int w_layout) {
-    return mynn::dequant_matmul_dispatch(stream, out, act, wq, scale, nullptr, M, N, K, act_dtype, out_dtype, w_layout);
+                                        int M, int N, int K, int act_dtype, int out_dtype, int w_layout,
+                                        void *workspace, size_t workspace_bytes) {
+    return mynn::dequant_matmul_dispatch(stream, out, act, wq, scale, nullptr, M, N, K, act_dtype, out_dtype, w_layout,
+                                         workspace, workspace_bytes);
 }
 
 extern "C" int mynn_b200_dequant_matmul_residual(void *stream, void *out, const void *act, const int8_t *wq,
                                                  const void *scale, const void *residual, int M, int N, int K,
-                                                 int dtype) {
-    return mynn::dequant_matmul_dispatch(stream, out, act, wq, scale, residual, M, N, K, dtype, dtype, MYNN_W_NK);
+                                                 int dtype, void *workspace, size_t workspace_bytes) {
+    return mynn::dequant_matmul_dispatch(stream, out, act, wq, scale, residual, M, N, K, dtype, dtype, MYNN_W_NK,
+                                         workspace, workspace_bytes);
+}
+
+// Reads the status word of a DequantMatMul workspace after synchronising the stream: non-zero means a pipeline
+// wait inside the tcgen05 kernel ran out of time and the outputs of that call are invalid.
+extern "C" int mynn_b200_dequant_matmul_check(void *stream, const void *workspace) {
+    if (!workspace) return MYNN_OK;
+    int status = 0;
+    MYNN_CUDA_OK(cudaMemcpyAsync(&status, workspace, sizeof status, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    MYNN_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+    if (status) return mynn::fail(MYNN_E_CUDA, "dequant_matmul: pipeline wait %d timed out inside the tcgen05 kernel", status);
+    return MYNN_OK;
 }
 
 // Tuning hook (not part of the engine-facing ABI): force the cluster K split of the streaming kernel; 0 = automatic.
 extern "C" int mynn_b200_debug_set_ksplit(int s) {
     if (s != 0 && s != 1 && s != 2 && s != 4 && s != 8) return mynn::fail(MYNN_E_ARG, "ksplit must be 0,1,2,4,8");
     mynn::g_ksplit_override = s;
+    mynn::g_i8_split_override = s;
     return MYNN_OK;
 }

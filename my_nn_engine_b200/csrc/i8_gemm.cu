@@ -1,0 +1,550 @@
+// Weight-streaming DequantMatMul on the 5th-generation tensor cores (tcgen05, kind::i8) for small batches.
+//
+//   out[m,n] = scale[n] * sum_k act[m,k] * wq[n,k],   M*3 <= 96 rows of activations (decode batches up to 32)
+//
+// Decode is bound by reading the int8 weights from HBM once.  Converting int8 to bf16 in registers and feeding
+// mma.sync costs more issue slots and legacy-MMA throughput than the memory system leaves time for at batch 32, so
+// this kernel removes all per-weight work from the SM's instruction stream:
+//
+//   * A tiny pre-pass rewrites each activation row as a fixed-point number with a per-row power-of-two scale and
+//     splits it into three signed 8-bit digits ("limbs"): act = 2^(e-22) * (l0 + 256 l1 + 65536 l2) where the row
+//     maximum is below 2^e.  A bf16 element within 2^-14 of its row maximum is represented EXACTLY; smaller ones are
+//     rounded to 2^-23 of the maximum.
+//   * The product then is three int8 x int8 dot products accumulated exactly in int32 (tcgen05.mma kind::i8): the
+//     weight bytes go from HBM to shared memory by TMA (128-byte swizzled tiles, 3-stage mbarrier pipeline) and
+//     from shared memory straight into the tensor core; no thread ever touches a weight.
+//   * Accumulators live in TMEM (one lane per weight row, one column per (activation row, limb)); the epilogue reads
+//     them with tcgen05.ld, recombines the limbs in f32, applies the activation-row and weight-row scales, the
+//     optional residual add, and stores.
+//   * K can be split over a thread-block cluster; the int32 partial sums are reduced through distributed shared
+//     memory.  Integer addition is associative, so the result does not depend on the split.
+//
+// Roles inside a CTA (192 threads): warp 0 = TMA producer (one elected lane), warp 1 = MMA issuer (one elected
+// lane) and TMEM allocator, warps 2-5 = epilogue (TMEM lane quadrant = warp index mod 4).
+// Every mbarrier wait is bounded: on expiry the kernel records an error code in `status`, skips the remaining work,
+// still releases TMEM and reaches every cluster barrier, and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "i8_gemm.cuh"
+
+namespace mynn {
+
+constexpr int kTileRows = 128;   // weight rows per CTA (UMMA M)
+constexpr int kBlockK = 128;     // int8 k values per pipeline stage = one 128-byte swizzle row
+constexpr int kStages = 3;
+constexpr int kGemmThreads = 192;
+constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // a wait gives up after 2 s
+
+// ---- PTX wrappers ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait on a phase parity.  Returns false when the time budget is spent or another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const int *abort_flag) {
+    const uint32_t addr = smem_u32(bar);
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((i & 63) == 63) {
+            if (*(volatile const int *)abort_flag) return false;
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitBudgetNs) return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ int ld_dsmem_s32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    int v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, written by TMA with the 128-byte
+// swizzle: 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1, layout type SWIZZLE_128B.
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);       // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                            // leading byte offset: unused for swizzled K-major tiles
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                            // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+struct I8GemmParams {
+    void *out;
+    const void *scale, *resid;
+    const float *ascale;  // [M] activation row scales 2^(e-22)
+    int M, N, K;
+    int *status;          // device int, set non-zero on a timed-out wait
+};
+
+// grid (ceil(N/128), S), cluster (1, S, 1).  NC = activation columns (3 limbs x rows, padded to 16).
+template <typename OutT, int NC>
+__global__ void __launch_bounds__(kGemmThreads, 2)
+i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                      const I8GemmParams p) {
+    constexpr uint32_t kWBytes = kTileRows * kBlockK, kABytes = NC * kBlockK;
+    constexpr uint32_t kStageBytes = kWBytes + ((kABytes + 1023) / 1024) * 1024;
+    constexpr uint32_t kTmemCols = NC <= 32 ? 32 : (NC <= 64 ? 64 : 128);
+    static_assert(kStages * kStageBytes >= NC * kTileRows * 4, "reduction buffer aliases the stage buffers");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzled tiles need 1024-byte alignment
+    __shared__ uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = gridDim.y;
+    const int rank = S > 1 ? (int)cluster_ctarank() : 0;
+    const int row0 = blockIdx.x * kTileRows;
+    // this CTA's contiguous share of the k blocks
+    const int kblocks = (p.K + kBlockK - 1) / kBlockK;
+    const int q = kblocks / S, rem = kblocks - q * S;
+    const int kb_beg = rank * q + min(rank, rem);
+    const int nkb = q + (rank < rem ? 1 : 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            // The weights do not depend on the preceding kernel: start streaming them at once, and only then wait
+            // (programmatic dependent launch) for the grid that writes the activation limbs.
+            const int pre = min(nkb, kStages);
+            for (int i = 0; i < pre; i++) {
+                mbar_expect_tx(&full_bar[i], kWBytes + kABytes);
+                tma_load_2d(smem + i * kStageBytes, &map_w, (kb_beg + i) * kBlockK, row0, &full_bar[i]);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int i = 0; i < pre; i++)
+                tma_load_2d(smem + i * kStageBytes + kWBytes, &map_a, (kb_beg + i) * kBlockK, 0, &full_bar[i]);
+            for (int i = pre; i < nkb; i++) {
+                const int s = i % kStages, it = i / kStages;
+                if (!mbar_wait(&empty_bar[s], (it - 1) & 1, &abort_flag)) {
+                    atomicExch(&abort_flag, 1);
+                    atomicExch(p.status, 1);
+                    break;
+                }
+                uint8_t *st = smem + s * kStageBytes;
+                mbar_expect_tx(&full_bar[s], kWBytes + kABytes);
+                tma_load_2d(st, &map_w, (kb_beg + i) * kBlockK, row0, &full_bar[s]);
+                tma_load_2d(st + kWBytes, &map_a, (kb_beg + i) * kBlockK, 0, &full_bar[s]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // instruction descriptor: D = S32, A = B = signed int8, both K-major, N = NC, M = 128
+            constexpr uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NC >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; i++) {
+                const int s = i % kStages, it = i / kStages;
+                if (!mbar_wait(&full_bar[s], it & 1, &abort_flag)) {
+                    atomicExch(&abort_flag, 1);
+                    atomicExch(p.status, 2);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+                const uint64_t adesc = make_kmajor_sw128_desc(a_addr), bdesc = make_kmajor_sw128_desc(a_addr + kWBytes);
+#pragma unroll
+                for (int k = 0; k < kBlockK / 32; k++)  // 32 bytes of k per instruction: advance the start address
+                    umma_i8(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (i | k) ? 1u : 0u);
+                umma_commit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
+            }
+            umma_commit(&accum_bar);  // accumulators complete (also fires when nothing was issued)
+        }
+        __syncwarp();
+    }
+
+    // ---------------- epilogue: warps 2..5 own TMEM lane quadrants (warp & 3) ----------------
+    int *red = reinterpret_cast<int *>(smem);  // [NC][128] int32, aliases the stage buffers once the MMAs are done
+    uint32_t acc[NC];
+    const int quad = warp & 3;
+    const int r_local = quad * 32 + lane;
+    bool have_acc = false;
+    if (warp >= 2) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // row scales and the residual come from earlier grids
+        const bool ok = mbar_wait(&accum_bar, 0, &abort_flag);
+        if (!ok) {
+            atomicExch(&abort_flag, 1);
+            atomicExch(p.status, 3);
+        }
+        tc_fence_after();
+        if (ok && nkb > 0 && !*(volatile int *)&abort_flag) {
+#pragma unroll
+            for (int c = 0; c < NC / 16; c++) {
+                uint32_t v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + c * 16, v);
+#pragma unroll
+                for (int j = 0; j < 16; j++) acc[c * 16 + j] = v[j];
+            }
+            tmem_ld_wait();
+            have_acc = true;
+        }
+        if (!have_acc) {
+#pragma unroll
+            for (int c = 0; c < NC; c++) acc[c] = 0u;
+        }
+    }
+
+    auto finalize = [&](int r, int m, int s0, int s1, int s2) {
+        const int n = row0 + r;
+        if (n >= p.N) return;
+        const float dot = ((float)s2 * 65536.0f + (float)s1 * 256.0f + (float)s0) * p.ascale[m];
+        float v = dot * to_f32<OutT>(reinterpret_cast<const OutT *>(p.scale)[n]);
+        if (p.resid) v = round_store<OutT>(v) + to_f32<OutT>(reinterpret_cast<const OutT *>(p.resid)[(size_t)m * p.N + n]);
+        reinterpret_cast<OutT *>(p.out)[(size_t)m * p.N + n] = from_f32<OutT>(v);
+    };
+
+    if (S == 1) {
+        if (warp >= 2) {
+#pragma unroll
+            for (int m = 0; m < NC / 3; m++)
+                if (m < p.M) finalize(r_local, m, (int)acc[3 * m], (int)acc[3 * m + 1], (int)acc[3 * m + 2]);
+        }
+    } else {
+        // all MMAs of this CTA have completed (accum_bar), so the stage buffers can hold the partial sums
+        if (warp >= 2) {
+#pragma unroll
+            for (int c = 0; c < NC; c++) red[c * kTileRows + r_local] = (int)acc[c];
+        }
+        cluster_sync_all();
+        if (warp >= 2) {
+            const int rows_per = kTileRows / S;  // S is 2, 4 or 8
+            const int t = threadIdx.x - 64;      // 0..127
+            const int r = rank * rows_per + (t % rows_per);
+            for (int m = t / rows_per; m < p.M; m += kTileRows / rows_per) {
+                // issue all (independent) remote reads first, then add
+                int part[3][8];
+#pragma unroll
+                for (int l = 0; l < 3; l++) {
+                    const uint32_t a = smem_u32(&red[(3 * m + l) * kTileRows + r]);
+#pragma unroll
+                    for (int rr = 0; rr < 8; rr++) part[l][rr] = rr < S ? ld_dsmem_s32(a, (uint32_t)rr) : 0;
+                }
+                int s[3] = {0, 0, 0};
+#pragma unroll
+                for (int l = 0; l < 3; l++)
+#pragma unroll
+                    for (int rr = 0; rr < 8; rr++) s[l] += part[l][rr];
+                finalize(r, m, s[0], s[1], s[2]);
+            }
+        }
+        cluster_sync_all();  // peers may still be reading this CTA's shared memory
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---- activation pre-pass: rows -> three int8 limbs + power-of-two row scale -----------------------------------
+// limbs [(3m + l)][K] int8 (row stride K); with max |row| < 2^e the row is scaled by 2^(22-e), so |A| < 2^22, and
+// ascale[m] = 2^(e-22).
+template <typename ActT>
+__global__ void __launch_bounds__(256) act_to_limbs_kernel(int8_t *limbs, float *ascale, const ActT *act, int K) {
+    constexpr int kMaxPer = 16;  // 4-element groups held per thread: rows up to 256 * 4 * 16 = 16384 stay in registers
+    __shared__ float wmax[8];
+    __shared__ float s_scale;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMM may begin streaming its weights
+    const int m = blockIdx.x;
+    const ActT *row = act + (size_t)m * K;
+    const int groups = K >> 2;  // K % 16 == 0
+    float v[kMaxPer][4];
+    float mx = 0.f;
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < kMaxPer; j++) {
+        const int gi = threadIdx.x + j * 256;
+        if (gi < groups) {
+            if constexpr (sizeof(ActT) == 2) {
+                const uint2 raw = *reinterpret_cast<const uint2 *>(row + 4 * gi);
+                const ActT *e = reinterpret_cast<const ActT *>(&raw);
+#pragma unroll
+                for (int i = 0; i < 4; i++) v[j][i] = to_f32<ActT>(e[i]);
+            } else {
+                const float4 raw = *reinterpret_cast<const float4 *>(row + 4 * gi);
+                v[j][0] = raw.x; v[j][1] = raw.y; v[j][2] = raw.z; v[j][3] = raw.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                bad |= !(fabsf(v[j][i]) <= 3.0e38f);
+                mx = fmaxf(mx, fabsf(v[j][i]));
+            }
+        }
+    }
+    for (int gi = threadIdx.x + kMaxPer * 256; gi < groups; gi += 256)  // rows longer than 16384: second read below
+        for (int i = 0; i < 4; i++) {
+            const float a = to_f32<ActT>(row[4 * gi + i]);
+            bad |= !(fabsf(a) <= 3.0e38f);
+            mx = fmaxf(mx, fabsf(a));
+        }
+    mx = warp_max(mx);
+    const unsigned anybad = __syncthreads_or(bad);
+    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < 8; i++) t = fmaxf(t, wmax[i]);
+        int e = 0;
+        if (t > 0.f) frexpf(t, &e);  // t = f * 2^e, f in [0.5, 1): t < 2^e
+        s_scale = t > 0.f ? ldexpf(1.0f, 22 - e) : 1.0f;  // |a| * s_scale < 2^22
+    }
+    __syncthreads();
+    const float sc = s_scale;
+    if (threadIdx.x == 0) ascale[m] = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc;  // non-finite input -> NaN outputs
+    int8_t *l0 = limbs + (size_t)(3 * m) * K, *l1 = l0 + K, *l2 = l1 + K;
+    auto split4 = [&](const float (&x)[4], int gi) {
+        uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int A = anybad ? 0 : __float2int_rn(x[i] * sc);
+            const int d0 = (int)(int8_t)(A & 0xFF);
+            A = (A - d0) >> 8;
+            const int d1 = (int)(int8_t)(A & 0xFF);
+            A = (A - d1) >> 8;
+            w0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
+            w1 |= (uint32_t)(d1 & 0xFF) << (8 * i);
+            w2 |= (uint32_t)(A & 0xFF) << (8 * i);
+        }
+        reinterpret_cast<uint32_t *>(l0)[gi] = w0;
+        reinterpret_cast<uint32_t *>(l1)[gi] = w1;
+        reinterpret_cast<uint32_t *>(l2)[gi] = w2;
+    };
+#pragma unroll
+    for (int j = 0; j < kMaxPer; j++) {
+        const int gi = threadIdx.x + j * 256;
+        if (gi < groups) split4(v[j], gi);
+    }
+    for (int gi = threadIdx.x + kMaxPer * 256; gi < groups; gi += 256) {
+        float x[4];
+        for (int i = 0; i < 4; i++) x[i] = to_f32<ActT>(row[4 * gi + i]);
+        split4(x, gi);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2D int8 tensor [rows][cols] (row stride = ld bytes), box = box_rows x 128 bytes, 128-byte swizzle, zero fill.
+static int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(MYNN_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld};
+    cuuint32_t box[2] = {(cuuint32_t)kBlockK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MYNN_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return MYNN_OK;
+}
+
+static int nc_for(int M) {
+    const int c = 3 * M;
+    return c <= 16 ? 16 : c <= 32 ? 32 : c <= 48 ? 48 : c <= 64 ? 64 : 96;
+}
+
+size_t i8_gemm_workspace_bytes(int M, int K) {
+    if (M <= 0 || M > kI8MaxRows || K <= 0) return 0;
+    return 256 /* status word */ + 256 /* row scales */ + ((size_t)nc_for(M) * K + 255) / 256 * 256;
+}
+
+bool i8_gemm_supported(int M, int N, int K, const void *wq, int act_dtype, int out_dtype) {
+    (void)act_dtype;
+    return M >= 1 && M <= kI8MaxRows && K % 16 == 0 && K >= 16 && N >= 1 && ((uintptr_t)wq % 16) == 0 &&
+           (out_dtype == MYNN_BF16 || out_dtype == MYNN_F16 || out_dtype == MYNN_F32) && encode_fn() != nullptr;
+}
+
+static int pick_split(int row_tiles, int kblocks) {
+    // Few row tiles cannot pull the full HBM bandwidth (one SM streams ~100 GB/s), so split K over a cluster of
+    // 2, 4 or 8 until there are about 120 CTAs, keeping at least 8 k blocks (128 KB of weights) per CTA.
+    int s = 1;
+    while (s < 8 && row_tiles * s < 120 && kblocks / (s * 2) >= 8) s *= 2;
+    return s;
+}
+
+int g_i8_split_override = 0;
+
+template <typename OutT, int NC>
+static int launch_i8(cudaStream_t st, const CUtensorMap &mw, const CUtensorMap &ma, const I8GemmParams &p, int S) {
+    constexpr uint32_t kStageBytes = kTileRows * kBlockK + ((NC * kBlockK + 1023) / 1024) * 1024;
+    const size_t smem = (size_t)kStages * kStageBytes + 1024;
+    auto kern = i8_stream_gemm_kernel<OutT, NC>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.N + kTileRows - 1) / kTileRows, S, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = S;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while the limb pre-pass still runs
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    MYNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mw, ma, p));
+    MYNN_LAUNCH_OK("i8_stream_gemm_kernel");
+    return MYNN_OK;
+}
+
+int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
+                   int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes) {
+    const size_t need = i8_gemm_workspace_bytes(M, K);
+    if (!workspace || workspace_bytes < need)
+        return fail(MYNN_E_ARG, "dequant_matmul: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+    if ((uintptr_t)workspace % 256) return fail(MYNN_E_ARG, "dequant_matmul: workspace must be 256-byte aligned");
+    const int NC = nc_for(M);
+    int *status = (int *)workspace;
+    float *ascale = (float *)((char *)workspace + 256);
+    int8_t *limbs = (int8_t *)workspace + 512;  // rows 3M..NC-1 are padding: whatever they hold only reaches
+                                                 // accumulator columns that are never read
+    switch (act_dtype) {
+        case MYNN_BF16: act_to_limbs_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(limbs, ascale, (const __nv_bfloat16 *)act, K); break;
+        case MYNN_F16: act_to_limbs_kernel<__half><<<M, 256, 0, st>>>(limbs, ascale, (const __half *)act, K); break;
+        case MYNN_F32: act_to_limbs_kernel<float><<<M, 256, 0, st>>>(limbs, ascale, (const float *)act, K); break;
+        default: return fail(MYNN_E_ARG, "dequant_matmul: bad activation dtype %d", act_dtype);
+    }
+    MYNN_LAUNCH_OK("act_to_limbs_kernel");
+    CUtensorMap mw, ma;
+    int rc = make_map(&mw, wq, (uint64_t)N, (uint64_t)K, (uint64_t)K, kTileRows);
+    if (rc) return rc;
+    rc = make_map(&ma, limbs, (uint64_t)NC, (uint64_t)K, (uint64_t)K, (uint32_t)NC);
+    if (rc) return rc;
+    I8GemmParams p;
+    p.out = out;
+    p.scale = scale;
+    p.resid = resid;
+    p.ascale = ascale;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.status = status;
+    const int row_tiles = (N + kTileRows - 1) / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
+    const int S = g_i8_split_override > 0 ? g_i8_split_override : pick_split(row_tiles, kblocks);
+#define GO(OT, NCV) return launch_i8<OT, NCV>(st, mw, ma, p, S)
+#define BY_NC(OT)                \
+    switch (NC) {                \
+        case 16: GO(OT, 16);     \
+        case 32: GO(OT, 32);     \
+        case 48: GO(OT, 48);     \
+        case 64: GO(OT, 64);     \
+        default: GO(OT, 96);     \
+    }
+    if (out_dtype == MYNN_BF16) BY_NC(__nv_bfloat16)
+    if (out_dtype == MYNN_F16) BY_NC(__half)
+    BY_NC(float)
+#undef BY_NC
+#undef GO
+}
+
+}  // namespace mynn

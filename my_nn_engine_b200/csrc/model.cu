@@ -15,6 +15,7 @@
 // Tensor parallel (tp_world > 1): q/k/v/gate/up/lm_head shards are column-parallel (rows of wq), o/down are
 // row-parallel (columns of wq) and produce f32 partial sums that are all-reduced and then rounded once and added
 // to the residual, fused with the following RMSNorm.
+#include <algorithm>
 #include <cstring>
 #include <vector>
 
@@ -50,8 +51,8 @@ struct Model {
     char *h_in = nullptr;  // pinned mirror of the input block
     void *x, *n, *qkv, *q_rot, *attn, *gu, *h, *last_x, *logits, *logits_full;
     float *part, *pairs, *pairs_all;
-    void *attn_ws;
-    size_t attn_ws_bytes;
+    void *attn_ws, *gemm_ws;
+    size_t attn_ws_bytes, gemm_ws_bytes;
     cudaStream_t stream = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
 };
@@ -78,9 +79,10 @@ static int gemm(cudaStream_t st, const Model &m, void *out, const void *act, con
         char *o = (char *)out + (size_t)m0 * N * osz;
         const char *a = (const char *)act + (size_t)m0 * K * esz;
         if (resid) {
-            RC(mynn_b200_dequant_matmul_residual(st, o, a, w, scale, (const char *)resid + (size_t)m0 * N * osz, mm, N, K, dt));
+            RC(mynn_b200_dequant_matmul_residual(st, o, a, w, scale, (const char *)resid + (size_t)m0 * N * osz, mm, N, K, dt,
+                                                 m.gemm_ws, m.gemm_ws_bytes));
         } else {
-            RC(mynn_b200_dequant_matmul(st, o, a, w, scale, mm, N, K, dt, out_dtype, MYNN_W_NK));
+            RC(mynn_b200_dequant_matmul(st, o, a, w, scale, mm, N, K, dt, out_dtype, MYNN_W_NK, m.gemm_ws, m.gemm_ws_bytes));
         }
     }
     return MYNN_OK;
@@ -232,6 +234,10 @@ static int model_create(Model **out, void **initializer, void **session_state) {
     const size_t R = m->max_rows;
     const size_t nqkv = (size_t)(m->Hq + 2 * m->Hkv) * D;
     m->attn_ws_bytes = mynn_b200_attention_workspace_bytes(c.batch, m->Hq, m->Hkv, D, c.max_seq_len);
+    {
+        const int kmax = std::max(std::max(H, m->ffn), m->Hq * D);
+        m->gemm_ws_bytes = c.use_tensor_gemm ? mynn_b200_dequant_matmul_workspace_bytes(32, 0, kmax) : 0;
+    }
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += up256(bytes); return o; };
     const size_t o_in = take(16 + R * 8), o_pos = take((size_t)prefill * 8), o_tok = take((size_t)c.batch * 4), o_x = take(R * H * esz), o_n = take(R * H * esz),
@@ -240,7 +246,7 @@ static int model_create(Model **out, void **initializer, void **session_state) {
                  o_logits = take((size_t)c.batch * m->vocab_l * esz),
                  o_full = take(tp > 1 ? (size_t)c.batch * c.vocab * esz : 0), o_part = take(tp > 1 ? R * H * 4 : 0),
                  o_pairs = take((size_t)c.batch * 8), o_pairs_all = take((size_t)c.batch * 8 * tp),
-                 o_ws = take(m->attn_ws_bytes);
+                 o_ws = take(m->attn_ws_bytes), o_gws = take(m->gemm_ws_bytes);
     cudaError_t e = cudaMalloc(&m->arena, off);
     if (e != cudaSuccess) {
         delete m;
@@ -258,6 +264,7 @@ static int model_create(Model **out, void **initializer, void **session_state) {
     m->gu = a + o_gu; m->h = a + o_h; m->last_x = a + o_last; m->logits = a + o_logits;
     m->logits_full = a + o_full; m->part = (float *)(a + o_part); m->pairs = (float *)(a + o_pairs);
     m->pairs_all = (float *)(a + o_pairs_all); m->attn_ws = a + o_ws;
+    m->gemm_ws = m->gemm_ws_bytes ? a + o_gws : nullptr;
     e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMallocHost((void **)&m->h_in, 16 + R * 8);
     if (e != cudaSuccess) {
@@ -312,6 +319,7 @@ static int copy_result_to_host(Model &m, void *dst) {
         MYNN_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, m.stream));
     }
     MYNN_CUDA_OK(cudaStreamSynchronize(m.stream));
+    if (m.gemm_ws) RC(mynn_b200_dequant_matmul_check(m.stream, m.gemm_ws));
     return MYNN_OK;
 }
 

@@ -75,7 +75,7 @@ class DecoderModel:
 
     def __init__(self, cfg: dict, state: dict, dtype: str = "bf16", max_seq_len: int = 256, batch: int = 1,
                  tp_rank: int = 0, tp_world: int = 1, output: str = "logits", use_graph: bool = True,
-                 max_prefill: int = 0, device=None):
+                 max_prefill: int = 0, device=None, tensor_gemm: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("DecoderModel needs a CUDA device: the decode path has no CPU implementation")
         self.lib = ffi.lib()
@@ -160,7 +160,8 @@ class DecoderModel:
         c = ffi.ModelConfig(n_layers=self.n_layers, hidden=h, n_heads=self.n_heads, n_kv_heads=self.n_kv,
                             head_dim=self.head_dim, ffn=self.ffn, vocab=self.vocab, max_seq_len=max_seq_len, batch=batch,
                             dtype=_FFI_DT[dtype], output_mode=1 if output == "ids" else 0, tp_rank=r, tp_world=G,
-                            use_graph=int(use_graph), max_prefill=max_prefill, rms_eps=cfg["rms_norm_eps"])
+                            use_graph=int(use_graph), max_prefill=max_prefill, use_tensor_gemm=int(tensor_gemm),
+                            rms_eps=cfg["rms_norm_eps"])
         ffi.check(self.lib.mynn_b200_model_configure(ctypes.byref(c)))
         self._init_arr = (ctypes.c_void_p * len(init))(*init)
         self._state_arr = (ctypes.c_void_p * len(states))(*states)

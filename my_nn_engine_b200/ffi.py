@@ -28,7 +28,7 @@ class ModelConfig(ctypes.Structure):
 
     _fields_ = [(n, c_int32) for n in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab",
                                        "max_seq_len", "batch", "dtype", "output_mode", "tp_rank", "tp_world",
-                                       "use_graph", "max_prefill")] + [("rms_eps", c_float)]
+                                       "use_graph", "max_prefill", "use_tensor_gemm")] + [("rms_eps", c_float)]
 
 
 # name -> (restype, argtypes); every symbol declared in include/mynn_b200.h
@@ -36,8 +36,10 @@ SIGNATURES = {
     "mynn_b200_last_error": (c_char_p, []),
     "mynn_b200_abi_version": (c_int, []),
     "mynn_b200_compiled_arch": (c_int, []),
-    "mynn_b200_dequant_matmul": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int]),
-    "mynn_b200_dequant_matmul_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int]),
+    "mynn_b200_dequant_matmul_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "mynn_b200_dequant_matmul": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t]),
+    "mynn_b200_dequant_matmul_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t]),
+    "mynn_b200_dequant_matmul_check": (c_int, [c_void_p, c_void_p]),
     "mynn_b200_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "mynn_b200_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_size_t]),
     "mynn_b200_kv_cache_update": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int]),

@@ -54,7 +54,7 @@ def _time_graph(fns, reps=3):
     return best
 
 
-def gemm(m, n, k, dtype="bf16", ksplit=0, copies=None, quiet=False):
+def gemm(m, n, k, dtype="bf16", ksplit=0, copies=None, quiet=False, kernel="tcgen05_i8"):
     td = _DT[dtype]
     copies = copies or max(3, int(600e6 // (n * k)) + 1)
     ws = [torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda") for _ in range(copies)]
@@ -62,11 +62,12 @@ def gemm(m, n, k, dtype="bf16", ksplit=0, copies=None, quiet=False):
     act = torch.randn(m, k, device="cuda").to(td)
     out = torch.empty(m, n, device="cuda", dtype=td)
     ffi.check(ffi.lib().mynn_b200_debug_set_ksplit(ksplit))
-    us = _time_graph([(lambda w=w: ops.dequant_matmul(act, w, sc, out=out)) for w in ws])
+    wsp = ops.dequant_matmul_workspace(m, n, k, act.device) if kernel == "tcgen05_i8" else None
+    us = _time_graph([(lambda w=w: ops.dequant_matmul(act, w, sc, out=out, workspace=wsp)) for w in ws])
     ffi.lib().mynn_b200_debug_set_ksplit(0)
     esz = act.element_size()
     alg = n * k + n * esz + m * k * esz + m * n * esz
-    res = {"kernel": "dequant_matmul", "m": m, "n": n, "k": k, "dtype": dtype, "ksplit": ksplit, "us": us,
+    res = {"kernel": "dequant_matmul/" + kernel, "m": m, "n": n, "k": k, "dtype": dtype, "ksplit": ksplit, "us": us,
            "GBps": alg / us / 1e3, "frac_of_measured_peak": alg / us / 1e3 / _peak(), "algorithmic_bytes": alg}
     if not quiet:
         print(json.dumps(res), flush=True)
@@ -115,6 +116,7 @@ def main():
     g.add_argument("--dtype", default="bf16")
     g.add_argument("--ksplit", type=int, default=0)
     g.add_argument("--copies", type=int, default=None)
+    g.add_argument("--kernel", default="tcgen05_i8", choices=["tcgen05_i8", "mma_sync"])
     a = sub.add_parser("attn")
     a.add_argument("--b", type=int, default=16)
     a.add_argument("--hq", type=int, default=32)
@@ -126,7 +128,7 @@ def main():
     sub.add_parser("suite")
     args = ap.parse_args()
     if args.cmd == "gemm":
-        gemm(args.m, args.n, args.k, args.dtype, args.ksplit, args.copies)
+        gemm(args.m, args.n, args.k, args.dtype, args.ksplit, args.copies, kernel=args.kernel)
     elif args.cmd == "attn":
         attn(args.b, args.hq, args.hkv, args.d, args.len, args.dtype, args.copies)
     else:

@@ -35,9 +35,29 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def dequant_matmul(act, wq, scale, axis: int = 0, out=None):
-    """``DequantMatMul{axis}(act, wq, scale)``: act [..., K]; wq int8 [N, K] (axis 0) or [K, N] (axis 1);
-    scale [N].  Output dtype = scale dtype (src/transform/shape.rs:326-345)."""
+_gemm_ws: dict = {}
+
+
+def dequant_matmul_workspace(m, n, k, device):
+    """Zero-initialised scratch for DequantMatMul (the operator's WORKSPACE slot), cached per device and stream."""
+    need = ffi.lib().mynn_b200_dequant_matmul_workspace_bytes(m, n, k)
+    key = (str(device), torch.cuda.current_stream().cuda_stream)
+    ws = _gemm_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 512), dtype=torch.uint8, device=device)
+        _gemm_ws[key] = ws
+    return ws
+
+
+def check_workspace(ws):
+    """Raise if a bounded wait inside the tcgen05 kernel expired during an earlier call that used ``ws``."""
+    ffi.check(ffi.lib().mynn_b200_dequant_matmul_check(_stream(), _ptr(ws)))
+
+
+def dequant_matmul(act, wq, scale, axis: int = 0, out=None, workspace="auto"):
+    """``DequantMatMul{axis}(act, wq, scale[, workspace])``: act [..., K]; wq int8 [N, K] (axis 0) or [K, N] (axis 1);
+    scale [N].  Output dtype = scale dtype (src/transform/shape.rs:326-345).  workspace: 'auto' (a cached scratch
+    buffer), None (use only the kernels that need no scratch) or a zeroed uint8 CUDA tensor."""
     if wq.dtype != torch.int8:
         raise TypeError("wq must be int8")
     if axis not in (0, 1):
@@ -48,19 +68,25 @@ def dequant_matmul(act, wq, scale, axis: int = 0, out=None):
     m = act.numel() // k if k else 0
     if out is None:
         out = torch.empty(act.shape[:-1] + (n,), dtype=scale.dtype, device=act.device)
+    if isinstance(workspace, str):
+        workspace = dequant_matmul_workspace(m, n, k, act.device) if axis == 0 and m > 0 else None
     ffi.check(ffi.lib().mynn_b200_dequant_matmul(_stream(), _ptr(out), _ptr(act), _ptr(wq), _ptr(scale), m, n, k,
-                                                 _dt(act), _dt(scale), ffi.W_NK if axis == 0 else ffi.W_KN))
+                                                 _dt(act), _dt(scale), ffi.W_NK if axis == 0 else ffi.W_KN,
+                                                 _ptr(workspace), 0 if workspace is None else workspace.numel()))
     return out
 
 
-def dequant_matmul_residual(act, wq, scale, residual, out=None):
+def dequant_matmul_residual(act, wq, scale, residual, out=None, workspace="auto"):
     """round(residual + round(DequantMatMul(act, wq, scale))); ``out`` may alias ``residual``."""
     n, k = wq.shape
     m = act.numel() // k
     if out is None:
         out = torch.empty_like(residual)
+    if isinstance(workspace, str):
+        workspace = dequant_matmul_workspace(m, n, k, act.device)
     ffi.check(ffi.lib().mynn_b200_dequant_matmul_residual(_stream(), _ptr(out), _ptr(act), _ptr(wq), _ptr(scale),
-                                                          _ptr(residual), m, n, k, _dt(act)))
+                                                          _ptr(residual), m, n, k, _dt(act), _ptr(workspace),
+                                                          0 if workspace is None else workspace.numel()))
     return out
 
 

@@ -36,13 +36,13 @@ def test_argument_errors_return_status_not_exit():
     lib = ffi.lib()
     assert lib.mynn_b200_rms_norm(None, None, None, None, 1e-5, -1, 4, ffi.BF16) == ffi.E_ARG
     assert "rms_norm" in ffi.last_error()
-    assert lib.mynn_b200_dequant_matmul(None, None, None, None, None, 1, 16, 64, 7, ffi.BF16, ffi.W_NK) == ffi.E_ARG
-    assert lib.mynn_b200_dequant_matmul(None, None, None, None, None, 1, 16, 64, ffi.BF16, ffi.BF16, 5) == ffi.E_ARG
+    assert lib.mynn_b200_dequant_matmul(None, None, None, None, None, 1, 16, 64, 7, ffi.BF16, ffi.W_NK, None, 0) == ffi.E_ARG
+    assert lib.mynn_b200_dequant_matmul(None, None, None, None, None, 1, 16, 64, ffi.BF16, ffi.BF16, 5, None, 0) == ffi.E_ARG
     assert lib.mynn_b200_attention(None, None, None, None, None, 1.0, 1, 3, 2, 1, 64, 8, 8, None, 0, ffi.BF16, None, 0) == ffi.E_ARG
     assert "multiple" in ffi.last_error()
     assert lib.mynn_b200_kv_cache_update(None, None, None, 1, -1, 1, 4, 0, None, ffi.BF16) == ffi.E_ARG
     # empty problems are accepted without touching a device
-    assert lib.mynn_b200_dequant_matmul(None, None, None, None, None, 0, 16, 64, ffi.BF16, ffi.BF16, ffi.W_NK) == ffi.OK
+    assert lib.mynn_b200_dequant_matmul(None, None, None, None, None, 0, 16, 64, ffi.BF16, ffi.BF16, ffi.W_NK, None, 0) == ffi.OK
     assert lib.mynn_b200_swish_mul(None, None, None, None, 0, ffi.BF16) == ffi.OK
 
 
@@ -50,7 +50,7 @@ def test_model_configure_validation():
     lib = ffi.lib()
     cfg = ffi.ModelConfig(n_layers=2, hidden=64, n_heads=4, n_kv_heads=3, head_dim=16, ffn=128, vocab=100,
                           max_seq_len=32, batch=1, dtype=ffi.BF16, output_mode=0, tp_rank=0, tp_world=1, use_graph=0,
-                          max_prefill=0, rms_eps=1e-5)
+                          max_prefill=0, use_tensor_gemm=1, rms_eps=1e-5)
     assert lib.mynn_b200_model_configure(cfg) == ffi.E_ARG  # 4 heads not a multiple of 3 kv heads
     cfg.n_kv_heads = 2
     assert lib.mynn_b200_model_configure(cfg) == ffi.OK

@@ -54,18 +54,23 @@ def test_dequant_matmul_goldens(single_op, name):
     assert ok, md
 
 
+@pytest.mark.parametrize("path", ["tcgen05_i8", "mma_sync"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("m,n,k", [(1, 5632, 2048), (1, 2048, 5632), (2, 256, 2048), (3, 1024, 4096), (8, 512, 1024),
                                    (9, 512, 1024), (16, 4096, 4096), (17, 2048, 512), (32, 6144, 4096), (32, 4096, 14336),
                                    (32, 1008, 448), (1, 16, 64), (5, 144, 192), (40, 256, 512)])
-def test_dequant_matmul_vs_oracle(dtype, m, n, k):
-    if dtype == torch.float32 and m * 3 > 32:
-        pytest.skip("f32 activations use the streaming kernel up to 10 rows")
+def test_dequant_matmul_vs_oracle(path, dtype, m, n, k):
+    """Both DequantMatMul kernels against the oracle: the tcgen05 int8 kernel (workspace given) and the mma.sync
+    streaming kernel (no workspace).  Shapes outside a kernel's fast path exercise the generic kernel."""
+    if path == "mma_sync" and dtype == torch.float32 and m * 3 > 32:
+        pytest.skip("f32 activations use the mma.sync streaming kernel up to 10 rows")
     rng = np.random.default_rng(m * 1000003 + n * 101 + k)
     wq = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
     scale = torch.from_numpy(rng.uniform(0.002, 0.02, size=n).astype(np.float32)).to(dtype)
     act = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype)
-    out = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda())
+    out = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda(), workspace="auto" if path == "tcgen05_i8" else None)
+    if path == "tcgen05_i8":
+        ops.check_workspace(ops.dequant_matmul_workspace(m, n, k, "cuda"))
     want = R.dequant_matmul(act.float().numpy(), wq, scale.float().numpy())
     tol = 1e-2 if dtype != torch.float32 else 1e-5
     assert rel_err(to_np(out), want) <= tol
@@ -74,20 +79,26 @@ def test_dequant_matmul_vs_oracle(dtype, m, n, k):
         assert np.abs(to_np(out) - w).max() <= np.abs(w).max() * 2.0 ** -7
 
 
+@pytest.mark.parametrize("path", ["tcgen05_i8", "mma_sync"])
 @pytest.mark.parametrize("ksplit", [1, 2, 4, 8])
-def test_dequant_matmul_cluster_splits_agree(ksplit):
-    """Every cluster K-split gives the oracle's result; the reduction order is fixed, so repeated calls are bit-equal."""
+def test_dequant_matmul_cluster_splits_agree(ksplit, path):
+    """Every cluster K-split gives the oracle's result; the reduction order is fixed, so repeated calls are bit-equal.
+    The int8 kernel accumulates exact integers, so its result is also identical across splits."""
     from my_nn_engine_b200 import ffi
     rng = np.random.default_rng(7)
     wq = rng.integers(-127, 128, size=(400, 2048), dtype=np.int8)
     scale = torch.from_numpy(rng.uniform(0.002, 0.02, size=400).astype(np.float32)).bfloat16()
     act = torch.from_numpy(rng.standard_normal((32, 2048)).astype(np.float32)).bfloat16()
+    ws = "auto" if path == "tcgen05_i8" else None
+    ref1 = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda(), workspace=ws) if ksplit > 1 else None
     ffi.check(ffi.lib().mynn_b200_debug_set_ksplit(ksplit))
     try:
-        a = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda())
-        b = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda())
+        a = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda(), workspace=ws)
+        b = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda(), workspace=ws)
     finally:
         ffi.lib().mynn_b200_debug_set_ksplit(0)
+    if path == "tcgen05_i8" and ref1 is not None:
+        assert torch.equal(a, ref1)
     want = R.dequant_matmul(act.float().numpy(), wq, scale.float().numpy())
     assert rel_err(to_np(a), want) <= 1e-2
     assert torch.equal(a, b)
@@ -102,9 +113,10 @@ def test_dequant_matmul_config1_both_layouts():
     act = rng.standard_normal((1, 2048)).astype(np.float32)
     want = R.dequant_matmul_variant_a(act, np.ascontiguousarray(w_kn.T), scale)
     out_kn = ops.dequant_matmul(dev(act), dev(w_kn), dev(scale), axis=1)
-    out_nk = ops.dequant_matmul(dev(act), dev(np.ascontiguousarray(w_kn.T)), dev(scale), axis=0)
+    w_nk = dev(np.ascontiguousarray(w_kn.T))
     assert rel_err(to_np(out_kn), want) <= 1e-5
-    assert rel_err(to_np(out_nk), want) <= 1e-5
+    assert rel_err(to_np(ops.dequant_matmul(dev(act), w_nk, dev(scale), axis=0)), want) <= 1e-5
+    assert rel_err(to_np(ops.dequant_matmul(dev(act), w_nk, dev(scale), axis=0, workspace=None)), want) <= 1e-5
 
 
 def test_weight_bytes_and_scale_indexing_bit_exact():
@@ -117,8 +129,9 @@ def test_weight_bytes_and_scale_indexing_bit_exact():
     for k0 in [0, 1, 15, 16, 63, 64, 255, 256, 300, 511]:
         act = np.zeros((1, k), np.float32)
         act[0, k0] = 1.0
-        out = to_np(ops.dequant_matmul(dev(act), dev(wq), dev(scale)))
-        assert np.array_equal(out[0], scale * wq[:, k0].astype(np.float32)), k0
+        for ws in ("auto", None):
+            out = to_np(ops.dequant_matmul(dev(act), dev(wq), dev(scale), workspace=ws))
+            assert np.array_equal(out[0], scale * wq[:, k0].astype(np.float32)), (k0, ws)
 
 
 def test_dequant_matmul_residual_epilogue():
@@ -127,10 +140,30 @@ def test_dequant_matmul_residual_epilogue():
     scale = torch.from_numpy(rng.uniform(0.002, 0.02, size=512).astype(np.float32)).bfloat16()
     act = torch.from_numpy(rng.standard_normal((4, 1024)).astype(np.float32)).bfloat16()
     res = torch.from_numpy(rng.standard_normal((4, 512)).astype(np.float32)).bfloat16()
-    out = ops.dequant_matmul_residual(act.cuda(), dev(wq), scale.cuda(), res.cuda())
     prod = R.round_bf16(R.dequant_matmul(act.float().numpy(), wq, scale.float().numpy()))
     want = R.round_bf16(prod + res.float().numpy())
-    assert np.abs(to_np(out) - want).max() <= np.abs(want).max() * 2.0 ** -6
+    for ws in ("auto", None):
+        out = ops.dequant_matmul_residual(act.cuda(), dev(wq), scale.cuda(), res.cuda(), workspace=ws)
+        assert np.abs(to_np(out) - want).max() <= np.abs(want).max() * 2.0 ** -6
+
+
+def test_int8_kernel_handles_outliers_zero_rows_and_non_finite_inputs():
+    """The fixed-point activation split keeps its accuracy with a 1e4x outlier in a row, passes all-zero rows
+    through, and turns a row holding Inf/NaN into NaN outputs (what f32 arithmetic would give) without touching the
+    other rows."""
+    rng = np.random.default_rng(13)
+    wq = rng.integers(-127, 128, size=(256, 1024), dtype=np.int8)
+    scale = rng.uniform(0.002, 0.02, 256).astype(np.float32)
+    act = rng.standard_normal((4, 1024)).astype(np.float32)
+    act[0, 7] = 1.0e4
+    act[1] = 0.0
+    act[2, 100] = np.inf
+    out = to_np(ops.dequant_matmul(dev(act), dev(wq), dev(scale)))
+    want = R.dequant_matmul_variant_a(act[[0, 1, 3]], wq, scale)
+    assert rel_err(out[0], want[0]) <= 1e-5
+    assert not out[1].any()
+    assert np.isnan(out[2]).all()
+    assert rel_err(out[3], want[2]) <= 1e-5
 
 
 @pytest.mark.parametrize("name,n_in", [("attention_decode", 3), ("attention_decode_gqa", 3),
