@@ -4,9 +4,11 @@
 //   * assigns one CTA to (kv-row split, kv head, batch) so that all query heads of a GQA group share a single
 //     pass over their KV head (the engine's kernel re-reads the KV head once per query head and walks the rows
 //     serially, src/codegen/cuda/cpp/attention.cuh:495-606);
-//   * lets each of its 4 warps take 16-row tiles and pull K and V straight from global memory into registers
-//     with 128-bit loads laid out as mma.m16n8k16 B fragments: the head-dim index (for QK^T) and the kv-row
-//     pairing (for PV) are permuted so that no shared-memory transpose is needed;
+//   * lets each of its 4 warps take 16-row tiles whose K and V bytes every lane fetches in 16-byte pieces laid out
+//     as mma.m16n8k16 B fragments: the head-dim index (for QK^T) and the kv-row pairing (for PV) are permuted so
+//     that no shared-memory transpose is needed.  The pieces travel through a private per-lane ring in shared
+//     memory filled by cp.async three tiles deep, so each warp keeps 16 KB of HBM reads in flight while it
+//     computes (a lane only ever reads back what it copied itself: no barriers, no bank conflicts);
 //   * computes S = Q K^T and O += P V on the tensor cores with f32 accumulation and an online softmax in f32.
 //     The A tile has 16 rows but a group has at most 8 heads: rows 0-7 carry the high 16-bit part of P and rows
 //     8-15 the rounding remainder, so P enters the product with ~16 significant bits;
@@ -23,6 +25,7 @@ namespace mynn {
 
 constexpr int kAttnWarps = 4;
 constexpr int kMaxSplits = 64;
+constexpr int kKvDepth = 3;  // tiles in the per-lane cp.async ring
 
 __device__ __forceinline__ uint4 ldg_16(const void *p) {
     uint4 v;
@@ -31,6 +34,14 @@ __device__ __forceinline__ uint4 ldg_16(const void *p) {
                  : "l"(p));
     return v;
 }
+
+__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <typename T>
 __device__ __forceinline__ void mma_kv(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -70,7 +81,7 @@ struct DecodeParams {
 
 // grid (splits, Hkv, B), block 128.
 template <typename T, int D>
-__global__ void __launch_bounds__(kAttnWarps * 32, 3) attention_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_decode_kernel(const DecodeParams p) {
     constexpr int KS = D / 16;   // k16 steps of QK^T
     constexpr int NTO = D / 8;   // n8 tiles of the output
     constexpr int KCH = D / 32;  // 16-byte K chunks per lane per row
@@ -111,22 +122,48 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 3) attention_decode_kernel(co
         for (int i = 0; i < 4; i++) o[j][i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
 
-    for (int base = row_beg + 16 * warp; base < row_end; base += 16 * kAttnWarps) {
-        const int last = row_end - 1;
-        // ---- issue all loads of this tile ----
-        uint4 kr[2][KCH], vr[4][VH];
+    // per-lane ring: chunk j of stage s of this warp lives at ring[((warp*kKvDepth + s)*CH + j)*32 + lane]
+    constexpr int CH = 2 * KCH + 4 * VH;
+    extern __shared__ uint4 kv_ring[];
+    uint4 *my_ring = kv_ring + (size_t)warp * kKvDepth * CH * 32 + lane;
+    const int last = row_end - 1;
+    auto issue_tile = [&](int base, int stage) {
+        if (base < row_end) {
+            uint4 *dst = my_ring + (size_t)stage * CH * 32;
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++) {
-            const T *kp = kbase + (size_t)min(base + 8 * nt + g, last) * D + 8 * t;
+            for (int nt = 0; nt < 2; nt++) {
+                const T *kp = kbase + (size_t)min(base + 8 * nt + g, last) * D + 8 * t;
 #pragma unroll
-            for (int i = 0; i < KCH; i++) kr[nt][i] = ldg_16(kp + 32 * i);
+                for (int i = 0; i < KCH; i++) cp_async_16(dst + (nt * KCH + i) * 32, kp + 32 * i);
+            }
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const int row = base + 2 * t + (r & 1) + 8 * (r >> 1);
+                const T *vp = vbase + (size_t)min(row, last) * D + 8 * g;
+#pragma unroll
+                for (int h = 0; h < VH; h++) cp_async_16(dst + (2 * KCH + r * VH + h) * 32, vp + 64 * h);
+            }
         }
+        cp_async_commit();  // one group per tile slot, empty past the end, so the wait count stays uniform
+    };
+    const int tile_stride = 16 * kAttnWarps;
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const int row = base + 2 * t + (r & 1) + 8 * (r >> 1);
-            const T *vp = vbase + (size_t)min(row, last) * D + 8 * g;
+    for (int s = 0; s < kKvDepth; s++) issue_tile(row_beg + 16 * warp + s * tile_stride, s);
+
+    int stage = 0;
+    for (int base = row_beg + 16 * warp; base < row_end; base += tile_stride) {
+        cp_async_wait<kKvDepth - 1>();
+        uint4 kr[2][KCH], vr[4][VH];
+        {
+            const uint4 *src = my_ring + (size_t)stage * CH * 32;
 #pragma unroll
-            for (int h = 0; h < VH; h++) vr[r][h] = ldg_16(vp + 64 * h);
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int i = 0; i < KCH; i++) kr[nt][i] = src[(nt * KCH + i) * 32];
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int h = 0; h < VH; h++) vr[r][h] = src[(2 * KCH + r * VH + h) * 32];
         }
         // ---- S = Q K^T ----
         float s[2][4];
@@ -187,7 +224,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 3) attention_decode_kernel(co
                 mma_kv<T>(acc, pa0, pa1, pa2, pa3, b0, b1);
             }
         }
+        // the tile's registers have been consumed: refill its ring slot with the tile kKvDepth ahead
+        issue_tile(base + kKvDepth * tile_stride, stage);
+        stage = stage + 1 == kKvDepth ? 0 : stage + 1;
     }
+    cp_async_wait<0>();
 
     // ---- merge the warps of this CTA ----
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -316,10 +357,12 @@ __global__ void attention_generic_kernel(T *out, const T *q, const T *k, const T
 }
 
 static int decode_splits(int B, int Hkv, int rows_bound) {
+    // All CTAs of a launch last equally long, so the grid should fit in ONE wave: two CTAs are resident per SM
+    // (148 SMs), and a partly filled second wave would cost as much time as a full one.
     const int pairs = B * Hkv;
-    int want = (3 * 148 + pairs - 1) / pairs;             // about three CTAs per SM
-    int cap = rows_bound / (16 * kAttnWarps);              // at least one tile per warp and split
-    int s = want < cap ? want : cap;
+    int s = (2 * 148) / pairs;
+    const int cap = rows_bound / (16 * kAttnWarps);  // at least one tile per warp and split
+    if (s > cap) s = cap;
     if (s < 1) s = 1;
     if (s > kMaxSplits) s = kMaxSplits;
     return s;
@@ -364,7 +407,13 @@ static int launch_generic(cudaStream_t st, void *out, const void *q, const void 
 
 template <typename T, int D>
 static int launch_decode(cudaStream_t st, const DecodeParams &p, int B) {
-    attention_decode_kernel<T, D><<<dim3(p.splits, p.Hkv, B), kAttnWarps * 32, 0, st>>>(p);
+    constexpr size_t ring_bytes = (size_t)kAttnWarps * kKvDepth * (2 * (D / 32) + 4 * (D / 64)) * 32 * sizeof(uint4);
+    static bool attr_set = false;
+    if (!attr_set) {
+        MYNN_CUDA_OK(cudaFuncSetAttribute(attention_decode_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring_bytes));
+        attr_set = true;
+    }
+    attention_decode_kernel<T, D><<<dim3(p.splits, p.Hkv, B), kAttnWarps * 32, ring_bytes, st>>>(p);
     MYNN_LAUNCH_OK("attention_decode_kernel");
     return MYNN_OK;
 }
