@@ -85,6 +85,25 @@ int mynn_b200_attention(void *stream, void *out, const void *q, const void *k, c
                         const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
                         size_t workspace_bytes);
 
+/* Decode attention (one query row per sequence) that takes no workspace and allocates nothing.  This entry point
+ * has no counterpart in the engine.  It exists for callers that cannot hand over scratch memory and cannot allocate
+ * any: the engine's Attention operator has no workspace operand and its planner fixes every device buffer when the
+ * model is compiled, so code generated for that operator has nothing to pass and no allocator to call mid-step.
+ * The split-KV partial results go to an array built into the library, mynn_b200_attention_decode_noalloc_max_bytes()
+ * (2 MiB) of device memory that every GPU using the library holds until the process exits.
+ *   - Same tensors and meaning as mynn_b200_attention with Sq = 1; bf16/f16, head_dim 64 or 128, at most 8 query heads
+ *     per kv head, 16-byte aligned pointers; anything else, or a problem whose partial results exceed the array,
+ *     returns MYNN_E_UNSUPPORTED with the sizes in the error text.
+ *   - The first call on a device resolves the array's device address (once per device, that device current); issue
+ *     that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents; its arrival counters are re-zeroed on
+ *     the stream by each call.  Calls whose kernels may overlap on the GPU race on it: keep them ordered.
+ *   - No cudaMalloc, cudaFree or other allocating routine is called. */
+size_t mynn_b200_attention_decode_noalloc_max_bytes(void);
+int mynn_b200_attention_decode_noalloc(void *stream, void *out, const void *q, const void *k, const void *v, float scale,
+                                       int B, int Hq, int Hkv, int D, int cache_seq_len, int active_seq_kv,
+                                       const int32_t *active_seq_kv_dev, int dtype);
+
 /* KVCacheUpdate: cache[bh, offset+t, :] = new[bh, t, :] in place.
  * Replaces: kvcache_update (cpp/kvcache_update.cuh:6-26, dispatch src/codegen/cuda.rs:2176-2228).
  * Unlike the engine (no bounds check) rows that would land past cache_seq_len are rejected with MYNN_E_ARG when

@@ -16,6 +16,7 @@
 //     CTA to arrive (atomic ticket, no spinning) combines the partial results and writes the output.
 // Everything else (f32 tensors, head dims other than 64/128, groups larger than 8, more than one query row,
 // causal masks) goes to a generic one-warp-per-query-row kernel that follows the CPU recurrence literally.
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -473,6 +474,105 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
         p.ws_ml = (float *)w;
         w += align_up(pairs * kMaxSplits * 8 * 2 * sizeof(float), 256);
         p.ws_o = (float *)w;
+    }
+    if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B) : launch_decode<__nv_bfloat16, 128>(st, p, B);
+    return D == 64 ? launch_decode<__half, 64>(st, p, B) : launch_decode<__half, 128>(st, p, B);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Decode attention for callers that have no scratch memory to give and must not allocate.
+//
+// Who that is: the engine's Attention operator has no workspace operand (its 13 input slots are tensors and scalars,
+// src/graph/operator.rs:1024-1042), and its memory planner assigns every device byte to arenas when the model is
+// compiled; an operator called from that generated code therefore has neither a buffer to pass for the split-KV
+// partial results nor an allocator it may call in the middle of a step.  The same holds for any host that fixes its
+// device-memory budget up front.
+//
+// The partial results live in the fixed array below instead.  It is part of the library image: every GPU that loads
+// the library sets aside kStaticScratchBytes for it until the process exits.
+//
+// Rules that follow from sharing one array:
+//   * it keeps whatever the previous call left; the arrival counters, the only part that must start at zero, are
+//     cleared on the stream at the beginning of every call;
+//   * two calls whose kernels overlap on the GPU (different streams, different threads) race on it: order them;
+//   * the first call on each device looks up the array's device address (cudaGetSymbolAddress, once per device, with
+//     that device current); make that first call before beginning any stream capture;
+//   * problems whose partial results exceed the array are refused with MYNN_E_UNSUPPORTED.
+namespace mynn {
+
+constexpr size_t kStaticScratchBytes = 2u << 20;  // 2 MiB: enough for a full wave of CTAs at head_dim 128
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static std::atomic<unsigned char *> g_static_scratch_ptr[kMaxDevices];
+
+// In host code `g_attn_static_scratch` names a host-side shadow, not device memory: the device address has to be
+// asked for, per device.
+static int static_scratch_address(unsigned char **out) {
+    int dev = -1;
+    MYNN_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(MYNN_E_UNSUPPORTED, "attention_decode_noalloc: device index %d not supported", dev);
+    unsigned char *p = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!p) {
+        void *sym = nullptr;
+        MYNN_CUDA_OK(cudaGetSymbolAddress(&sym, g_attn_static_scratch));
+        if (!sym) return fail(MYNN_E_CUDA, "attention_decode_noalloc: the scratch array has no device address");
+        p = static_cast<unsigned char *>(sym);
+        g_static_scratch_ptr[dev].store(p, std::memory_order_release);
+    }
+    *out = p;
+    return MYNN_OK;
+}
+
+}  // namespace mynn
+
+extern "C" size_t mynn_b200_attention_decode_noalloc_max_bytes(void) { return mynn::kStaticScratchBytes; }
+
+extern "C" int mynn_b200_attention_decode_noalloc(void *stream, void *out, const void *q, const void *k, const void *v,
+                                                  float scale, int B, int Hq, int Hkv, int D, int cache_seq_len,
+                                                  int active_seq_kv, const int32_t *active_seq_kv_dev, int dtype) {
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || cache_seq_len < 0 || active_seq_kv < 0)
+        return fail(MYNN_E_ARG, "attention_decode_noalloc: bad shape");
+    if (Hq % Hkv != 0) return fail(MYNN_E_ARG, "attention_decode_noalloc: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
+    if (B == 0) return MYNN_OK;
+    if (!out || !q || !k || !v) return fail(MYNN_E_ARG, "attention_decode_noalloc: null pointer");
+    const int G = Hq / Hkv;
+    const bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % 16) == 0;
+    if (!((D == 64 || D == 128) && G <= 8 && (dtype == MYNN_BF16 || dtype == MYNN_F16) && aligned))
+        return fail(MYNN_E_UNSUPPORTED, "attention_decode_noalloc: needs bf16/f16, head_dim 64 or 128, group size <= 8, 16-byte aligned tensors");
+    cudaStream_t st = (cudaStream_t)stream;
+    DecodeParams p;
+    p.out = out;
+    p.q = q;
+    p.k = k;
+    p.v = v;
+    p.scale = scale;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.G = G;
+    p.cache_seq = cache_seq_len;
+    p.active_host = active_seq_kv;
+    p.active_dev = active_seq_kv_dev;
+    const int rows_bound = active_seq_kv_dev ? cache_seq_len : (active_seq_kv < cache_seq_len ? active_seq_kv : cache_seq_len);
+    p.splits = decode_splits(B, Hkv, rows_bound);
+    p.ws_o = nullptr;
+    p.ws_ml = nullptr;
+    p.ws_ticket = nullptr;
+    if (p.splits > 1) {
+        const size_t pairs = (size_t)B * Hkv;
+        const size_t tickets = align_up(pairs * sizeof(unsigned), 256);
+        const size_t ml = align_up(pairs * p.splits * 8 * 2 * sizeof(float), 256);
+        const size_t o = pairs * p.splits * 8 * (size_t)D * sizeof(float);
+        if (tickets + ml + o > kStaticScratchBytes)
+            return fail(MYNN_E_UNSUPPORTED, "attention_decode_noalloc: %zu bytes of partial results exceed the %zu-byte built-in scratch (B=%d, kv heads=%d, %d splits)",
+                        tickets + ml + o, kStaticScratchBytes, B, Hkv, p.splits);
+        unsigned char *base = nullptr;
+        int rc = static_scratch_address(&base);
+        if (rc) return rc;
+        MYNN_CUDA_OK(cudaMemsetAsync(base, 0, tickets, st));  // arrival counters start from zero on every call
+        p.ws_ticket = (unsigned *)base;
+        p.ws_ml = (float *)(base + tickets);
+        p.ws_o = (float *)(base + tickets + ml);
     }
     if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B) : launch_decode<__nv_bfloat16, 128>(st, p, B);
     return D == 64 ? launch_decode<__half, 64>(st, p, B) : launch_decode<__half, 128>(st, p, B);

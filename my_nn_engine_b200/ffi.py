@@ -42,6 +42,8 @@ SIGNATURES = {
     "mynn_b200_dequant_matmul_check": (c_int, [c_void_p, c_void_p]),
     "mynn_b200_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "mynn_b200_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_size_t]),
+    "mynn_b200_attention_decode_noalloc_max_bytes": (c_size_t, []),
+    "mynn_b200_attention_decode_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int]),
     "mynn_b200_kv_cache_update": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int]),
     "mynn_b200_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int]),
     "mynn_b200_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int]),
