@@ -152,43 +152,37 @@ __global__ void __launch_bounds__(1024) argmax_last_kernel(int32_t *out_idx, con
 
 
 // ---- fused RoPE + KV append ------------------------------------------------------------------------------
-// blockIdx.x = token row (b * S + s); threads sweep (head, j < D/2) over q heads, k heads and v heads.
+// grid (token row b*S+s, head slot): slots [0,Hq) rotate q, [Hq,Hq+Hkv) rotate k into the cache, the rest copy v into
+// the cache.  One thread per (low, high) element pair.
 template <typename T>
 __global__ void rope_kv_append_kernel(T *q_out, T *k_cache, T *v_cache, const T *q, const T *k, const T *v,
                                       long long q_stride, long long k_stride, long long v_stride, const T *cos_t,
                                       const T *sin_t, const int64_t *positions, int S, int Hq, int Hkv, int D,
                                       int cache_seq, const int32_t *past_len_dev) {
     const int row = blockIdx.x, b = row / S, s = row - b * S;
+    const int slot = blockIdx.y;
     const int half = D >> 1;
-    const long long pos = positions[s];
     const int cache_row = *past_len_dev + s;
-    const T *cr = cos_t + (size_t)pos * D, *sr = sin_t + (size_t)pos * D;
-    const int n_rot = (Hq + Hkv) * half;
-    for (int i = threadIdx.x; i < n_rot + Hkv * half; i += blockDim.x) {
-        if (i < n_rot) {
-            const int h = i / half, j = i - h * half;
-            const bool is_q = h < Hq;
-            const T *src = is_q ? q + (size_t)row * q_stride + (size_t)h * D : k + (size_t)row * k_stride + (size_t)(h - Hq) * D;
+    const bool in_cache = cache_row >= 0 && cache_row < cache_seq;
+    if (slot < Hq + Hkv) {
+        const long long pos = positions[s];
+        const T *cr = cos_t + (size_t)pos * D, *sr = sin_t + (size_t)pos * D;
+        const bool is_q = slot < Hq;
+        const int h = is_q ? slot : slot - Hq;
+        if (!is_q && !in_cache) return;
+        const T *src = is_q ? q + (size_t)row * q_stride + (size_t)h * D : k + (size_t)row * k_stride + (size_t)h * D;
+        T *dst = is_q ? q_out + (((size_t)b * Hq + h) * S + s) * D : k_cache + (((size_t)b * Hkv + h) * cache_seq + cache_row) * D;
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
             const float xl = to_f32<T>(src[j]), xh = to_f32<T>(src[j + half]);
-            const T lo = from_f32<T>(xl * to_f32<T>(cr[j]) - xh * to_f32<T>(sr[j]));
-            const T hi = from_f32<T>(xh * to_f32<T>(cr[j + half]) + xl * to_f32<T>(sr[j + half]));
-            T *dst;
-            if (is_q) {
-                dst = q_out + (((size_t)b * Hq + h) * S + s) * D;
-            } else {
-                if (cache_row < 0 || cache_row >= cache_seq) continue;
-                dst = k_cache + (((size_t)b * Hkv + (h - Hq)) * cache_seq + cache_row) * D;
-            }
-            dst[j] = lo;
-            dst[j + half] = hi;
-        } else {
-            if (cache_row < 0 || cache_row >= cache_seq) continue;
-            const int i2 = i - n_rot, h = i2 / half, j = i2 - h * half;
-            const T *src = v + (size_t)row * v_stride + (size_t)h * D;
-            T *dst = v_cache + (((size_t)b * Hkv + h) * cache_seq + cache_row) * D;
-            dst[j] = src[j];
-            dst[j + half] = src[j + half];
+            dst[j] = from_f32<T>(xl * to_f32<T>(cr[j]) - xh * to_f32<T>(sr[j]));
+            dst[j + half] = from_f32<T>(xh * to_f32<T>(cr[j + half]) + xl * to_f32<T>(sr[j + half]));
         }
+    } else {
+        if (!in_cache) return;
+        const int h = slot - Hq - Hkv;
+        const T *src = v + (size_t)row * v_stride + (size_t)h * D;
+        T *dst = v_cache + (((size_t)b * Hkv + h) * cache_seq + cache_row) * D;
+        for (int j = threadIdx.x; j < D; j += blockDim.x) dst[j] = src[j];
     }
 }
 
@@ -197,10 +191,11 @@ int launch_rope_kv_append(cudaStream_t st, int dtype, void *q_out, void *k_cache
                           const void *cos_t, const void *sin_t, const int64_t *positions, int B, int S, int Hq,
                           int Hkv, int D, int cache_seq, const int32_t *past_len_dev) {
     if (B * S == 0) return MYNN_OK;
+    const int threads = D / 2 >= 64 ? 64 : 32;
     MYNN_DISPATCH_DTYPE(dtype, T, {
-        rope_kv_append_kernel<T><<<B * S, 256, 0, st>>>((T *)q_out, (T *)k_cache, (T *)v_cache, (const T *)q, (const T *)k,
-                                                       (const T *)v, q_stride, k_stride, v_stride, (const T *)cos_t,
-                                                       (const T *)sin_t, positions, S, Hq, Hkv, D, cache_seq, past_len_dev);
+        rope_kv_append_kernel<T><<<dim3(B * S, Hq + 2 * Hkv), threads, 0, st>>>(
+            (T *)q_out, (T *)k_cache, (T *)v_cache, (const T *)q, (const T *)k, (const T *)v, q_stride, k_stride, v_stride,
+            (const T *)cos_t, (const T *)sin_t, positions, S, Hq, Hkv, D, cache_seq, past_len_dev);
     });
     MYNN_LAUNCH_OK("rope_kv_append_kernel");
     return MYNN_OK;

@@ -408,6 +408,111 @@ __global__ void __launch_bounds__(256) act_to_limbs_kernel(int8_t *limbs, float 
     }
 }
 
+// ---- fused producers: an operator's output row goes straight to limbs --------------------------------------------
+// The row (already rounded to the storage dtype, i.e. after the operator's store point) sits in shared memory as f32.
+// Block-wide: row maximum -> power-of-two scale -> three int8 limbs per element, written 4 elements at a time.
+__device__ __forceinline__ void smem_row_to_limbs(const float *row_s, int K, int8_t *limb_row0, float *ascale_m,
+                                                  float *red /* >= 33 floats */) {
+    float mx = 0.f;
+    bool bad = false;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        const float a = fabsf(row_s[k]);
+        bad |= !(a <= 3.0e38f);
+        mx = fmaxf(mx, a);
+    }
+    mx = warp_max(mx);
+    const unsigned anybad = __syncthreads_or(bad);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); i++) t = fmaxf(t, red[i]);
+        int e = 0;
+        if (t > 0.f) frexpf(t, &e);
+        red[32] = t > 0.f ? ldexpf(1.0f, 22 - e) : 1.0f;
+    }
+    __syncthreads();
+    const float sc = red[32];
+    if (threadIdx.x == 0) *ascale_m = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc;
+    uint32_t *l0 = reinterpret_cast<uint32_t *>(limb_row0);
+    uint32_t *l1 = reinterpret_cast<uint32_t *>(limb_row0 + K);
+    uint32_t *l2 = reinterpret_cast<uint32_t *>(limb_row0 + 2 * (size_t)K);
+    for (int gi = threadIdx.x; gi < (K >> 2); gi += blockDim.x) {
+        uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int A = anybad ? 0 : __float2int_rn(row_s[4 * gi + i] * sc);
+            const int d0 = (int)(int8_t)(A & 0xFF);
+            A = (A - d0) >> 8;
+            const int d1 = (int)(int8_t)(A & 0xFF);
+            A = (A - d1) >> 8;
+            w0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
+            w1 |= (uint32_t)(d1 & 0xFF) << (8 * i);
+            w2 |= (uint32_t)(A & 0xFF) << (8 * i);
+        }
+        l0[gi] = w0;
+        l1[gi] = w1;
+        l2[gi] = w2;
+    }
+}
+
+// RMSNorm whose output feeds only DequantMatMuls: y = round(x * rsqrt(mean x^2 + eps) * w) -> limbs.
+// With `part`: first s = round(x + round(part)) is stored to sum_out (residual add of an all-reduced f32 partial sum).
+// norm_out (optional) also receives y in the storage dtype.
+template <typename T>
+__global__ void __launch_bounds__(512)
+rms_norm_limbs_kernel(int8_t *limbs, float *ascale, T *norm_out, T *sum_out, const T *x, const float *part, const T *w,
+                      float eps, int D) {
+    extern __shared__ float row_s[];
+    __shared__ float red[40];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int m = blockIdx.x;
+    const size_t base = (size_t)m * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = to_f32<T>(x[base + i]);
+        if (part != nullptr) {
+            v = round_store<T>(v + round_store<T>(part[base + i]));
+            sum_out[base + i] = from_f32<T>(v);
+        }
+        row_s[i] = v;
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); i++) tot += red[i];
+        red[33] = 1.0f / sqrtf(tot / (float)D + eps);
+    }
+    __syncthreads();
+    const float inv = red[33];
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const T y = from_f32<T>(row_s[i] * inv * to_f32<T>(w[i]));
+        if (norm_out != nullptr) norm_out[base + i] = y;
+        row_s[i] = to_f32<T>(y);
+    }
+    __syncthreads();
+    smem_row_to_limbs(row_s, D, limbs + (size_t)(3 * m) * D, ascale + m, red);
+}
+
+// h = round(swish(gate) * up) -> limbs; gate/up rows are in_stride elements apart.
+template <typename T>
+__global__ void __launch_bounds__(512)
+swiglu_limbs_kernel(int8_t *limbs, float *ascale, const T *gate, const T *up, int F, long long in_stride) {
+    extern __shared__ float row_s[];
+    __shared__ float red[40];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int m = blockIdx.x;
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+        const float g = to_f32<T>(gate[(size_t)m * in_stride + i]);
+        row_s[i] = round_store<T>((g / (1.0f + expf(-g))) * to_f32<T>(up[(size_t)m * in_stride + i]));
+    }
+    __syncthreads();
+    smem_row_to_limbs(row_s, F, limbs + (size_t)(3 * m) * F, ascale + m, red);
+}
+
 // ---- host side --------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -508,13 +613,15 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
     float *ascale = (float *)((char *)workspace + 256);
     int8_t *limbs = (int8_t *)workspace + 512;  // rows 3M..NC-1 are padding: whatever they hold only reaches
                                                  // accumulator columns that are never read
-    switch (act_dtype) {
-        case MYNN_BF16: act_to_limbs_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(limbs, ascale, (const __nv_bfloat16 *)act, K); break;
-        case MYNN_F16: act_to_limbs_kernel<__half><<<M, 256, 0, st>>>(limbs, ascale, (const __half *)act, K); break;
-        case MYNN_F32: act_to_limbs_kernel<float><<<M, 256, 0, st>>>(limbs, ascale, (const float *)act, K); break;
-        default: return fail(MYNN_E_ARG, "dequant_matmul: bad activation dtype %d", act_dtype);
+    if (act != nullptr) {  // act == nullptr: a fused producer has already left limbs and row scales in the workspace
+        switch (act_dtype) {
+            case MYNN_BF16: act_to_limbs_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(limbs, ascale, (const __nv_bfloat16 *)act, K); break;
+            case MYNN_F16: act_to_limbs_kernel<__half><<<M, 256, 0, st>>>(limbs, ascale, (const __half *)act, K); break;
+            case MYNN_F32: act_to_limbs_kernel<float><<<M, 256, 0, st>>>(limbs, ascale, (const float *)act, K); break;
+            default: return fail(MYNN_E_ARG, "dequant_matmul: bad activation dtype %d", act_dtype);
+        }
+        MYNN_LAUNCH_OK("act_to_limbs_kernel");
     }
-    MYNN_LAUNCH_OK("act_to_limbs_kernel");
     CUtensorMap mw, ma;
     int rc = make_map(&mw, wq, (uint64_t)N, (uint64_t)K, (uint64_t)K, kTileRows);
     if (rc) return rc;
@@ -545,6 +652,48 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
     BY_NC(float)
 #undef BY_NC
 #undef GO
+}
+
+static int fused_ws(void *workspace, size_t workspace_bytes, int M, int K, int8_t **limbs, float **ascale) {
+    if (M < 1 || M > kI8MaxRows || K % 16) return fail(MYNN_E_UNSUPPORTED, "fused limb producer: M=%d K=%d not supported", M, K);
+    if (!workspace || workspace_bytes < i8_gemm_workspace_bytes(M, K) || (uintptr_t)workspace % 256)
+        return fail(MYNN_E_ARG, "fused limb producer: workspace too small or misaligned");
+    if ((size_t)K * 4 > 200 * 1024) return fail(MYNN_E_UNSUPPORTED, "fused limb producer: row of %d elements exceeds shared memory", K);
+    *ascale = (float *)((char *)workspace + 256);
+    *limbs = (int8_t *)workspace + 512;
+    return MYNN_OK;
+}
+
+int launch_rms_norm_limbs(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, void *norm_out, void *sum_out,
+                          const void *x, const float *part, const void *w, float eps, int rows, int D) {
+    int8_t *limbs;
+    float *ascale;
+    int rc = fused_ws(workspace, workspace_bytes, rows, D, &limbs, &ascale);
+    if (rc) return rc;
+    const size_t smem = (size_t)D * 4;
+    MYNN_DISPATCH_DTYPE(dtype, T, {
+        auto kern = rms_norm_limbs_kernel<T>;
+        if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<rows, 512, smem, st>>>(limbs, ascale, (T *)norm_out, (T *)sum_out, (const T *)x, part, (const T *)w, eps, D);
+    });
+    MYNN_LAUNCH_OK("rms_norm_limbs_kernel");
+    return MYNN_OK;
+}
+
+int launch_swiglu_limbs(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, const void *gate, const void *up,
+                        int rows, int F, long long in_stride) {
+    int8_t *limbs;
+    float *ascale;
+    int rc = fused_ws(workspace, workspace_bytes, rows, F, &limbs, &ascale);
+    if (rc) return rc;
+    const size_t smem = (size_t)F * 4;
+    MYNN_DISPATCH_DTYPE(dtype, T, {
+        auto kern = swiglu_limbs_kernel<T>;
+        if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<rows, 512, smem, st>>>(limbs, ascale, (const T *)gate, (const T *)up, F, in_stride);
+    });
+    MYNN_LAUNCH_OK("swiglu_limbs_kernel");
+    return MYNN_OK;
 }
 
 }  // namespace mynn

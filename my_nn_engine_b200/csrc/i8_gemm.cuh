@@ -11,5 +11,12 @@ size_t i8_gemm_workspace_bytes(int M, int K);
 bool i8_gemm_supported(int M, int N, int K, const void *wq, int act_dtype, int out_dtype);
 int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
                    int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes);
+// Fused producers: leave limbs + row scales in `workspace`; the following i8_gemm_launch is called with act == nullptr.
+// rms_norm: y = round(RMSNorm(x) * w); with part != nullptr first sum_out = round(x + round(part)) is stored and
+// normalised.  norm_out may be null.  swiglu: h = round(swish(gate) * up).
+int launch_rms_norm_limbs(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, void *norm_out, void *sum_out,
+                          const void *x, const float *part, const void *w, float eps, int rows, int D);
+int launch_swiglu_limbs(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, const void *gate, const void *up,
+                        int rows, int F, long long in_stride);
 extern int g_i8_split_override;
 }  // namespace mynn

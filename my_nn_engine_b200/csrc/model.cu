@@ -21,6 +21,7 @@
 
 #include "comm.cuh"
 #include "common.cuh"
+#include "i8_gemm.cuh"
 #include "ops_internal.cuh"
 
 namespace mynn {
@@ -88,8 +89,17 @@ static int gemm(cudaStream_t st, const Model &m, void *out, const void *act, con
     return MYNN_OK;
 }
 
+// DequantMatMul whose activations a fused producer has already left as limbs in the GEMM workspace.
+static int gemm_prequant(cudaStream_t st, const Model &m, void *out, const int8_t *w, const void *scale, const void *resid,
+                         int M, int N, int K, int out_dtype) {
+    return i8_gemm_launch(st, out, nullptr, w, scale, resid, M, N, K, m.c.dtype, out_dtype, m.gemm_ws, m.gemm_ws_bytes);
+}
+
 // Enqueue one forward pass over S tokens per sequence (S == 1: decode).  Inputs are the device buffers
-// ids_dev [B*S], pos_dev [S], past_dev, active_dev.  Leaves logits (and token ids) in device buffers.
+// ids_dev [B*S], pos0_dev / pos_dev [S], past_dev, active_dev.  Leaves logits (and token ids) in device buffers.
+// When the step has at most 32 rows and the int8 tensor-core GEMM is enabled, RMSNorm and Swish*Mul write their
+// (rounded) outputs directly as activation limbs into the GEMM workspace, so no separate pre-pass runs for the
+// q/k/v, gate/up, down and lm_head products.
 static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     const mynn_b200_model_config &c = m.c;
     const int B = c.batch, H = c.hidden, D = c.head_dim, dt = c.dtype;
@@ -98,9 +108,24 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     const size_t esz = dtype_size(dt);
     const int Nq = m.Hq * D, Nkv = m.Hkv * D;
     const float attn_scale = 1.0f / sqrtf((float)D);
+    const bool fused = m.gemm_ws != nullptr && M <= kI8MaxRows && H % 16 == 0 && m.ffn % 16 == 0 &&
+                       (size_t)std::max(H, m.ffn) * 4 <= 200 * 1024;
+
+    // norm(x [+ part]) feeding a DequantMatMul: either limbs in the workspace (fused) or the bf16 tensor m.n
+    auto norm = [&](const void *w, const float *part, int rows, const void *src) -> int {
+        if (fused && rows <= kI8MaxRows)
+            return launch_rms_norm_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, nullptr, part ? m.x : nullptr, src, part, w,
+                                         c.rms_eps, rows, H);
+        if (part) return launch_add_f32_rms_norm(st, dt, m.x, m.n, m.x, part, w, c.rms_eps, rows, H);
+        return mynn_b200_rms_norm(st, m.n, src, w, c.rms_eps, rows, H, dt);
+    };
+    auto gemm_n = [&](void *out, const int8_t *w, const void *scale, int rows, int N, int out_dtype) -> int {
+        if (fused && rows <= kI8MaxRows) return gemm_prequant(st, m, out, w, scale, nullptr, rows, N, H, out_dtype);
+        return gemm(st, m, out, m.n, w, scale, nullptr, rows, N, H, out_dtype);
+    };
 
     RC(mynn_b200_embed_gather_dequant(st, m.x, m.embed, m.embed_scale, m.ids_dev, M, H, c.vocab, dt));
-    RC(mynn_b200_rms_norm(st, m.n, m.x, m.layers[0].ln1, c.rms_eps, M, H, dt));
+    RC(norm(m.layers[0].ln1, nullptr, M, m.x));
     for (int l = 0; l < c.n_layers; l++) {
         const LayerW &L = m.layers[l];
         // --- attention block ---
@@ -109,51 +134,59 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         const char *kb, *vb;
         if (L.qkv_fused) {
             const int Nt = Nq + 2 * Nkv;
-            RC(gemm(st, m, qb, m.n, L.wq, L.sq, nullptr, M, Nt, H, dt));
+            RC(gemm_n(qb, L.wq, L.sq, M, Nt, dt));
             qs = ks = vs = Nt;
             kb = qb + (size_t)Nq * esz;
             vb = qb + (size_t)(Nq + Nkv) * esz;
         } else {
             char *k_ = qb + (size_t)M * Nq * esz, *v_ = k_ + (size_t)M * Nkv * esz;
-            RC(gemm(st, m, qb, m.n, L.wq, L.sq, nullptr, M, Nq, H, dt));
-            RC(gemm(st, m, k_, m.n, L.wk, L.sk, nullptr, M, Nkv, H, dt));
-            RC(gemm(st, m, v_, m.n, L.wv, L.sv, nullptr, M, Nkv, H, dt));
+            RC(gemm_n(qb, L.wq, L.sq, M, Nq, dt));
+            RC(gemm_n(k_, L.wk, L.sk, M, Nkv, dt));
+            RC(gemm_n(v_, L.wv, L.sv, M, Nkv, dt));
             qs = Nq;
             ks = vs = Nkv;
             kb = k_;
             vb = v_;
         }
-        RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t, S == 1 ? m.pos0_dev : m.pos_dev, B, S,
-                                 m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
+        RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
+                                 S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
         RC(launch_attention(st, m.attn, m.q_rot, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
                             c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
         if (tp == 1) {
             RC(gemm(st, m, m.x, m.attn, L.wo, L.so, m.x, M, H, Nq, dt));  // x = round(x + round(o))
-            RC(mynn_b200_rms_norm(st, m.n, m.x, L.ln2, c.rms_eps, M, H, dt));
+            RC(norm(L.ln2, nullptr, M, m.x));
         } else {
             RC(gemm(st, m, m.part, m.attn, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
             RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
-            RC(launch_add_f32_rms_norm(st, dt, m.x, m.n, m.x, m.part, L.ln2, c.rms_eps, M, H));
+            RC(norm(L.ln2, m.part, M, m.x));  // x = round(x + round(sum of partials)), then the norm
         }
         // --- MLP block ---
+        const bool fuse_mlp = fused && L.gu_fused;
         if (L.gu_fused) {
-            RC(gemm(st, m, m.gu, m.n, L.wg, L.sg, nullptr, M, 2 * m.ffn, H, dt));
-            RC(launch_swiglu_strided(st, dt, m.h, m.gu, (char *)m.gu + (size_t)m.ffn * esz, M, m.ffn, 2LL * m.ffn));
+            RC(gemm_n(m.gu, L.wg, L.sg, M, 2 * m.ffn, dt));
+            if (fuse_mlp)
+                RC(launch_swiglu_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, m.gu, (char *)m.gu + (size_t)m.ffn * esz, M, m.ffn,
+                                       2LL * m.ffn));
+            else
+                RC(launch_swiglu_strided(st, dt, m.h, m.gu, (char *)m.gu + (size_t)m.ffn * esz, M, m.ffn, 2LL * m.ffn));
         } else {
             char *u_ = (char *)m.gu + (size_t)M * m.ffn * esz;
-            RC(gemm(st, m, m.gu, m.n, L.wg, L.sg, nullptr, M, m.ffn, H, dt));
-            RC(gemm(st, m, u_, m.n, L.wu, L.su, nullptr, M, m.ffn, H, dt));
+            RC(gemm_n(m.gu, L.wg, L.sg, M, m.ffn, dt));
+            RC(gemm_n(u_, L.wu, L.su, M, m.ffn, dt));
             RC(launch_swiglu_strided(st, dt, m.h, m.gu, u_, M, m.ffn, m.ffn));
         }
         const bool last = l + 1 == c.n_layers;
         const void *next_norm = last ? nullptr : m.layers[l + 1].ln1;
         if (tp == 1) {
-            RC(gemm(st, m, m.x, m.h, L.wd, L.sd, m.x, M, H, m.ffn, dt));
-            if (!last) RC(mynn_b200_rms_norm(st, m.n, m.x, next_norm, c.rms_eps, M, H, dt));
+            if (fuse_mlp) RC(gemm_prequant(st, m, m.x, L.wd, L.sd, m.x, M, H, m.ffn, dt));
+            else RC(gemm(st, m, m.x, m.h, L.wd, L.sd, m.x, M, H, m.ffn, dt));
+            if (!last) RC(norm(next_norm, nullptr, M, m.x));
         } else {
-            RC(gemm(st, m, m.part, m.h, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
+            if (fuse_mlp) RC(gemm_prequant(st, m, m.part, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
+            else RC(gemm(st, m, m.part, m.h, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
             RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
-            RC(launch_add_f32_rms_norm(st, dt, m.x, last ? nullptr : m.n, m.x, m.part, next_norm, c.rms_eps, M, H));
+            if (last) RC(launch_add_f32_rms_norm(st, dt, m.x, nullptr, m.x, m.part, nullptr, c.rms_eps, M, H));
+            else RC(norm(next_norm, m.part, M, m.x));
         }
     }
     // --- head: only the last token of each sequence is needed ---
@@ -163,8 +196,14 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
                                        (size_t)S * H * esz, (size_t)H * esz, B, cudaMemcpyDeviceToDevice, st));
         xl = m.last_x;
     }
-    RC(mynn_b200_rms_norm(st, m.n, xl, m.final_norm, c.rms_eps, B, H, dt));
-    RC(gemm(st, m, m.logits, m.n, m.lm_w, m.lm_scale, nullptr, B, m.vocab_l, H, dt));
+    const bool fused_head = m.gemm_ws != nullptr && B <= kI8MaxRows && H % 16 == 0 && (size_t)H * 4 <= 200 * 1024;
+    if (fused_head) {
+        RC(launch_rms_norm_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, nullptr, nullptr, xl, nullptr, m.final_norm, c.rms_eps, B, H));
+        RC(gemm_prequant(st, m, m.logits, m.lm_w, m.lm_scale, nullptr, B, m.vocab_l, H, dt));
+    } else {
+        RC(mynn_b200_rms_norm(st, m.n, xl, m.final_norm, c.rms_eps, B, H, dt));
+        RC(gemm(st, m, m.logits, m.n, m.lm_w, m.lm_scale, nullptr, B, m.vocab_l, H, dt));
+    }
     if (c.output_mode == 1) {
         if (tp == 1) {
             RC(mynn_b200_argmax_last(st, m.tok_dev, m.logits, B, m.vocab_l, dt));
