@@ -90,7 +90,7 @@ int mynn_b200_attention(void *stream, void *out, const void *q, const void *k, c
  * any: the engine's Attention operator has no workspace operand and its planner fixes every device buffer when the
  * model is compiled, so code generated for that operator has nothing to pass and no allocator to call mid-step.
  * The split-KV partial results go to an array built into the library, mynn_b200_attention_decode_noalloc_max_bytes()
- * (2 MiB) of device memory that every GPU using the library holds until the process exits.
+ * (4 MiB) of device memory that every GPU using the library holds until the process exits.
  *   - Same tensors and meaning as mynn_b200_attention with Sq = 1; bf16/f16, head_dim 64 or 128, at most 8 query heads
  *     per kv head, 16-byte aligned pointers; anything else, or a problem whose partial results exceed the array,
  *     returns MYNN_E_UNSUPPORTED with the sizes in the error text.

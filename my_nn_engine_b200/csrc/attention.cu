@@ -4,14 +4,14 @@
 //   * assigns one CTA to (kv-row split, kv head, batch) so that all query heads of a GQA group share a single
 //     pass over their KV head (the engine's kernel re-reads the KV head once per query head and walks the rows
 //     serially, src/codegen/cuda/cpp/attention.cuh:495-606);
-//   * lets each of its 4 warps take 16-row tiles whose K and V bytes every lane fetches in 16-byte pieces laid out
-//     as mma.m16n8k16 B fragments: the head-dim index (for QK^T) and the kv-row pairing (for PV) are permuted so
-//     that no shared-memory transpose is needed.  The pieces travel through a private per-lane ring in shared
-//     memory filled by cp.async three tiles deep, so each warp keeps 16 KB of HBM reads in flight while it
-//     computes (a lane only ever reads back what it copied itself: no barriers, no bank conflicts);
-//   * computes S = Q K^T and O += P V on the tensor cores with f32 accumulation and an online softmax in f32.
-//     The A tile has 16 rows but a group has at most 8 heads: rows 0-7 carry the high 16-bit part of P and rows
-//     8-15 the rounding remainder, so P enters the product with ~16 significant bits;
+//   * lets each of its 4 warps take 16-row tiles whose K and V bytes every lane pulls straight from global memory
+//     into registers with 128-bit loads, laid out as mma.m16n8k16 operand fragments: the head-dim index (for
+//     QK^T) and the kv-row pairing (for PV) are permuted so that no shared-memory transpose is needed;
+//   * computes S = Q K^T (A = Q, padded to 16 heads) and O^T = V^T P^T (A = V^T, B = P^T, so the 8-column B tile is
+//     the head group and no accumulator register is wasted) on the tensor cores with f32 accumulation and an
+//     online softmax in f32; P enters as a high 16-bit part plus its rounding remainder (~16 significant bits);
+//   * stays within 128 registers and 17 KB of shared memory so that 16 warps per SM hide the latency of the
+//     dependent load -> MMA chain -> softmax -> MMA sequence;
 //   * merges the warps through shared memory, and the splits through a small global workspace where the last
 //     CTA to arrive (atomic ticket, no spinning) combines the partial results and writes the output.
 // Everything else (f32 tensors, head dims other than 64/128, groups larger than 8, more than one query row,
@@ -26,7 +26,7 @@ namespace mynn {
 
 constexpr int kAttnWarps = 4;
 constexpr int kMaxSplits = 64;
-constexpr int kKvDepth = 3;  // tiles in the per-lane cp.async ring
+constexpr int kAttnCtasPerSm = 4;  // resident CTAs per SM the kernel is built for (<= 128 registers, 17 KB smem)
 
 __device__ __forceinline__ uint4 ldg_16(const void *p) {
     uint4 v;
@@ -35,14 +35,6 @@ __device__ __forceinline__ uint4 ldg_16(const void *p) {
                  : "l"(p));
     return v;
 }
-
-__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem) {
-    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <typename T>
 __device__ __forceinline__ void mma_kv(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -82,9 +74,8 @@ struct DecodeParams {
 
 // grid (splits, Hkv, B), block 128.
 template <typename T, int D>
-__global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(const DecodeParams p) {
     constexpr int KS = D / 16;   // k16 steps of QK^T
-    constexpr int NTO = D / 8;   // n8 tiles of the output
     constexpr int KCH = D / 32;  // 16-byte K chunks per lane per row
     constexpr int VH = D / 64;   // 16-byte V chunks per lane per row
     __shared__ float sm_o[kAttnWarps][8][D];
@@ -116,57 +107,33 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_decode_kernel(co
         }
     }
 
-    float o[NTO][4];
+    // O^T accumulators: tile (h, j) holds head-dim rows d = 64h + 8g + 2j (+1 for the g+8 half) against head columns
+    // 2t, 2t+1 -- every register is useful for an 8-head group, so the whole output needs D/4 registers.
+    float o[VH * 4][4];
 #pragma unroll
-    for (int j = 0; j < NTO; j++)
+    for (int j = 0; j < VH * 4; j++)
 #pragma unroll
         for (int i = 0; i < 4; i++) o[j][i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
-
-    // per-lane ring: chunk j of stage s of this warp lives at ring[((warp*kKvDepth + s)*CH + j)*32 + lane]
-    constexpr int CH = 2 * KCH + 4 * VH;
-    extern __shared__ uint4 kv_ring[];
-    uint4 *my_ring = kv_ring + (size_t)warp * kKvDepth * CH * 32 + lane;
     const int last = row_end - 1;
-    auto issue_tile = [&](int base, int stage) {
-        if (base < row_end) {
-            uint4 *dst = my_ring + (size_t)stage * CH * 32;
-#pragma unroll
-            for (int nt = 0; nt < 2; nt++) {
-                const T *kp = kbase + (size_t)min(base + 8 * nt + g, last) * D + 8 * t;
-#pragma unroll
-                for (int i = 0; i < KCH; i++) cp_async_16(dst + (nt * KCH + i) * 32, kp + 32 * i);
-            }
-#pragma unroll
-            for (int r = 0; r < 4; r++) {
-                const int row = base + 2 * t + (r & 1) + 8 * (r >> 1);
-                const T *vp = vbase + (size_t)min(row, last) * D + 8 * g;
-#pragma unroll
-                for (int h = 0; h < VH; h++) cp_async_16(dst + (2 * KCH + r * VH + h) * 32, vp + 64 * h);
-            }
-        }
-        cp_async_commit();  // one group per tile slot, empty past the end, so the wait count stays uniform
-    };
-    const int tile_stride = 16 * kAttnWarps;
-#pragma unroll
-    for (int s = 0; s < kKvDepth; s++) issue_tile(row_beg + 16 * warp + s * tile_stride, s);
 
-    int stage = 0;
-    for (int base = row_beg + 16 * warp; base < row_end; base += tile_stride) {
-        cp_async_wait<kKvDepth - 1>();
+    for (int base = row_beg + 16 * warp; base < row_end; base += 16 * kAttnWarps) {
+        // ---- issue all loads of this tile (rows past the end are clamped to a valid row and masked below) ----
         uint4 kr[2][KCH], vr[4][VH];
-        {
-            const uint4 *src = my_ring + (size_t)stage * CH * 32;
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++)
+        for (int nt = 0; nt < 2; nt++) {
+            const T *kp = kbase + (size_t)min(base + 8 * nt + g, last) * D + 8 * t;
 #pragma unroll
-                for (int i = 0; i < KCH; i++) kr[nt][i] = src[(nt * KCH + i) * 32];
-#pragma unroll
-            for (int r = 0; r < 4; r++)
-#pragma unroll
-                for (int h = 0; h < VH; h++) vr[r][h] = src[(2 * KCH + r * VH + h) * 32];
+            for (int i = 0; i < KCH; i++) kr[nt][i] = ldg_16(kp + 32 * i);
         }
-        // ---- S = Q K^T ----
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int row = base + 2 * t + (r & 1) + 8 * (r >> 1);
+            const T *vp = vbase + (size_t)min(row, last) * D + 8 * g;
+#pragma unroll
+            for (int h = 0; h < VH; h++) vr[r][h] = ldg_16(vp + 64 * h);
+        }
+        // ---- S = Q K^T: s[nt][e] = S[head g][kv row base + 8nt + 2t + e] ----
         float s[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; nt++) {
@@ -177,7 +144,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_decode_kernel(co
                 mma_kv<T>(s[nt], qa0[2 * i + 1], 0u, qa2[2 * i + 1], 0u, kr[nt][i].z, kr[nt][i].w);
             }
         }
-        // ---- online softmax for head g: this lane holds kv rows base + 8nt + 2t + {0,1} ----
+        // ---- online softmax for head g ----
         float pv[2][2];
         float tmax = -INFINITY;
 #pragma unroll
@@ -202,10 +169,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_decode_kernel(co
             }
         l_run = l_run * alpha + psum;  // per-lane partial; lanes of a group are summed at the end
         m_run = m_new;
-        uint32_t pa0, pa1, pa2, pa3;
-        split_pack<T>(pv[0][0], pv[0][1], pa0, pa1);
-        split_pack<T>(pv[1][0], pv[1][1], pa2, pa3);
-        // ---- O = O * alpha + P V ----
+        // P^T is the B operand of O^T = V^T P^T: (kv rows 2t,2t+1 | 2t+8,2t+9) x head g is exactly what this lane
+        // holds.  P enters as a high 16-bit part and its rounding remainder (two MMAs), i.e. with ~16 significant bits.
+        uint32_t pb0h, pb0l, pb1h, pb1l;
+        split_pack<T>(pv[0][0], pv[0][1], pb0h, pb0l);
+        split_pack<T>(pv[1][0], pv[1][1], pb1h, pb1l);
+        // the accumulator columns of this lane are heads 2t and 2t+1: fetch their rescale factors
+        const float al0 = __shfl_sync(0xffffffffu, alpha, 8 * t), al1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
+        // ---- O^T = O^T * alpha + V^T P^T ----
 #pragma unroll
         for (int h = 0; h < VH; h++) {
             const uint32_t r0[4] = {vr[0][h].x, vr[0][h].y, vr[0][h].z, vr[0][h].w};
@@ -213,23 +184,20 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_decode_kernel(co
             const uint32_t r2[4] = {vr[2][h].x, vr[2][h].y, vr[2][h].z, vr[2][h].w};
             const uint32_t r3[4] = {vr[3][h].x, vr[3][h].y, vr[3][h].z, vr[3][h].w};
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const unsigned sel = (j & 1) ? 0x7632u : 0x5410u;
-                const uint32_t b0 = __byte_perm(r0[j >> 1], r1[j >> 1], sel);
-                const uint32_t b1 = __byte_perm(r2[j >> 1], r3[j >> 1], sel);
-                float(&acc)[4] = o[8 * h + j];
-                acc[0] *= alpha;
-                acc[1] *= alpha;
-                acc[2] *= alpha;
-                acc[3] *= alpha;
-                mma_kv<T>(acc, pa0, pa1, pa2, pa3, b0, b1);
+            for (int j = 0; j < 4; j++) {
+                // A = V^T: rows (g | g+8) are head-dim elements 2j | 2j+1 of this lane's 8, columns are kv-row pairs
+                const uint32_t a0 = __byte_perm(r0[j], r1[j], 0x5410u), a1 = __byte_perm(r0[j], r1[j], 0x7632u);
+                const uint32_t a2 = __byte_perm(r2[j], r3[j], 0x5410u), a3 = __byte_perm(r2[j], r3[j], 0x7632u);
+                float(&acc)[4] = o[4 * h + j];
+                acc[0] *= al0;
+                acc[1] *= al1;
+                acc[2] *= al0;
+                acc[3] *= al1;
+                mma_kv<T>(acc, a0, a1, a2, a3, pb0h, pb1h);
+                mma_kv<T>(acc, a0, a1, a2, a3, pb0l, pb1l);
             }
         }
-        // the tile's registers have been consumed: refill its ring slot with the tile kKvDepth ahead
-        issue_tile(base + kKvDepth * tile_stride, stage);
-        stage = stage + 1 == kKvDepth ? 0 : stage + 1;
     }
-    cp_async_wait<0>();
 
     // ---- merge the warps of this CTA ----
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -241,11 +209,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_decode_kernel(co
 #pragma unroll
     for (int h = 0; h < VH; h++)
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const float(&acc)[4] = o[8 * h + j];
-            // accumulator column x of tile (h, j) is head-dim index 64h + 8x + j; rows g and g+8 are the two parts of P
-            sm_o[warp][g][64 * h + 8 * (2 * t) + j] = acc[0] + acc[2];
-            sm_o[warp][g][64 * h + 8 * (2 * t + 1) + j] = acc[1] + acc[3];
+        for (int j = 0; j < 4; j++) {
+            const float(&acc)[4] = o[4 * h + j];
+            const int d = 64 * h + 8 * g + 2 * j;
+            sm_o[warp][2 * t][d] = acc[0];
+            sm_o[warp][2 * t + 1][d] = acc[1];
+            sm_o[warp][2 * t][d + 1] = acc[2];
+            sm_o[warp][2 * t + 1][d + 1] = acc[3];
         }
     __syncthreads();
 
@@ -358,10 +328,10 @@ __global__ void attention_generic_kernel(T *out, const T *q, const T *k, const T
 }
 
 static int decode_splits(int B, int Hkv, int rows_bound) {
-    // All CTAs of a launch last equally long, so the grid should fit in ONE wave: two CTAs are resident per SM
-    // (148 SMs), and a partly filled second wave would cost as much time as a full one.
+    // All CTAs of a launch last equally long, so the grid should fit in ONE wave of resident CTAs (148 SMs): a
+    // partly filled second wave would cost as much time as a full one.
     const int pairs = B * Hkv;
-    int s = (2 * 148) / pairs;
+    int s = (kAttnCtasPerSm * 148) / pairs;
     const int cap = rows_bound / (16 * kAttnWarps);  // at least one tile per warp and split
     if (s > cap) s = cap;
     if (s < 1) s = 1;
@@ -408,13 +378,7 @@ static int launch_generic(cudaStream_t st, void *out, const void *q, const void 
 
 template <typename T, int D>
 static int launch_decode(cudaStream_t st, const DecodeParams &p, int B) {
-    constexpr size_t ring_bytes = (size_t)kAttnWarps * kKvDepth * (2 * (D / 32) + 4 * (D / 64)) * 32 * sizeof(uint4);
-    static bool attr_set = false;
-    if (!attr_set) {
-        MYNN_CUDA_OK(cudaFuncSetAttribute(attention_decode_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring_bytes));
-        attr_set = true;
-    }
-    attention_decode_kernel<T, D><<<dim3(p.splits, p.Hkv, B), kAttnWarps * 32, ring_bytes, st>>>(p);
+    attention_decode_kernel<T, D><<<dim3(p.splits, p.Hkv, B), kAttnWarps * 32, 0, st>>>(p);
     MYNN_LAUNCH_OK("attention_decode_kernel");
     return MYNN_OK;
 }
@@ -500,7 +464,7 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
 //   * problems whose partial results exceed the array are refused with MYNN_E_UNSUPPORTED.
 namespace mynn {
 
-constexpr size_t kStaticScratchBytes = 2u << 20;  // 2 MiB: enough for a full wave of CTAs at head_dim 128
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB: a full wave of CTAs (4 per SM) at head_dim 128 needs 2.4 MiB
 static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;

@@ -463,3 +463,12 @@ extern "C" int mynn_b200_debug_set_ksplit(int s) {
     mynn::g_i8_split_override = s;
     return MYNN_OK;
 }
+
+// Tuning hook: device buffer (8 x uint64) that CTA (0,0) of the tcgen05 GEMM fills with nanosecond timestamps of its
+// phases (start, set-up done, predecessor complete, accumulators complete, cluster ready, outputs stored, end); NULL = off.
+extern "C" int mynn_b200_debug_set_timing_buffer(void *buf) {
+    mynn::g_i8_timing = (unsigned long long *)buf;
+    return MYNN_OK;
+}
+
+extern "C" int mynn_b200_debug_set_mode(int m) { mynn::g_i8_dbg = m; return 0; }

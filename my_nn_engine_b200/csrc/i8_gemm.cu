@@ -64,6 +64,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const 
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
+        __nanosleep(i < 16 ? 20 : 100);  // back off: a spinning try_wait competes for the SM's shared-memory pipe
         if ((i & 63) == 63) {
             if (*(volatile const int *)abort_flag) return false;
             const unsigned long long now = global_ns();
@@ -143,6 +144,8 @@ struct I8GemmParams {
     const float *ascale;  // [M] activation row scales 2^(e-22)
     int M, N, K;
     int *status;          // device int, set non-zero on a timed-out wait
+    unsigned long long *timing;  // optional: 8 timestamps (ns) of CTA (0,0) for tuning, or null
+    int dbg;
 };
 
 // grid (ceil(N/128), S), cluster (1, S, 1).  NC = activation columns (3 limbs x rows, padded to 16).
@@ -159,9 +162,12 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     __shared__ uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ float sh_ascale[32];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = gridDim.y;
+    const bool stamp = p.timing != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+    if (stamp && threadIdx.x == 0) p.timing[0] = global_ns();
     const int rank = S > 1 ? (int)cluster_ctarank() : 0;
     const int row0 = blockIdx.x * kTileRows;
     // this CTA's contiguous share of the k blocks
@@ -184,6 +190,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
+    if (stamp && threadIdx.x == 0) p.timing[1] = global_ns();  // set-up done
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -198,6 +205,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 tma_load_2d(smem + i * kStageBytes, &map_w, (kb_beg + i) * kBlockK, row0, &full_bar[i]);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (stamp) p.timing[2] = global_ns();  // predecessor grid complete
             for (int i = 0; i < pre; i++)
                 tma_load_2d(smem + i * kStageBytes + kWBytes, &map_a, (kb_beg + i) * kBlockK, 0, &full_bar[i]);
             for (int i = pre; i < nkb; i++) {
@@ -242,85 +250,138 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
 
     // ---------------- epilogue: warps 2..5 own TMEM lane quadrants (warp & 3) ----------------
-    int *red = reinterpret_cast<int *>(smem);  // [NC][128] int32, aliases the stage buffers once the MMAs are done
-    uint32_t acc[NC];
+    // S == 1: thread t finishes weight row t of the tile for every activation row m.
+    // S  > 1: every CTA first pushes its int64 partial sums (limbs already combined, still exact) into the shared
+    //         memory of the CTA that owns the row (rows are dealt out in S contiguous groups), with remote stores
+    //         that need no round trip; after a cluster barrier each CTA adds what it received and finishes its rows.
+    //         The receive buffer aliases the stage buffers, so a first cluster barrier makes sure every CTA of the
+    //         cluster is past its main loop before anybody writes into a peer.
     const int quad = warp & 3;
     const int r_local = quad * 32 + lane;
+    const OutT *scale_p = reinterpret_cast<const OutT *>(p.scale);
+    const OutT *resid_p = reinterpret_cast<const OutT *>(p.resid);
+    OutT *out_p = reinterpret_cast<OutT *>(p.out);
+    constexpr int MR = NC / 3;                       // activation rows this instantiation can hold
+    const int rows_per = kTileRows / S, mstep = S;   // S > 1: this thread finishes row r_own for m = m_own + j * S
+    const int et = threadIdx.x - 64;                 // epilogue thread index 0..127 (warps >= 2)
+    const int r_own = S == 1 ? r_local : rank * rows_per + (et % rows_per);
+    const int m_own = S == 1 ? 0 : et / rows_per;
+    const int n_own = row0 + r_own;
+    constexpr int kMaxOut = MR;                      // outputs per thread: MR for S == 1, ceil(MR / S) otherwise
+    float wscale = 0.f, res[kMaxOut];
     bool have_acc = false;
     if (warp >= 2) {
         asm volatile("griddepcontrol.wait;" ::: "memory");  // row scales and the residual come from earlier grids
-        const bool ok = mbar_wait(&accum_bar, 0, &abort_flag);
+        // everything the finish needs from global memory is requested before waiting for the accumulators
+        if (et < 32) sh_ascale[et] = et < p.M ? p.ascale[et] : 0.f;
+        if (n_own < p.N) wscale = to_f32<OutT>(scale_p[n_own]);
+        if (S == 1) {
+#pragma unroll
+            for (int m = 0; m < kMaxOut; m++)
+                res[m] = (resid_p && n_own < p.N && m < p.M) ? to_f32<OutT>(resid_p[(size_t)m * p.N + n_own]) : 0.f;
+        }
+        // one lane per warp polls the barrier (128 spinning threads would flood the shared-memory pipe that the
+        // co-resident CTA needs); the outcome is broadcast to the warp
+        int ok_i = 1;
+        if (lane == 0) ok_i = mbar_wait(&accum_bar, 0, &abort_flag) ? 1 : 0;
+        const bool ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
+        if (stamp && threadIdx.x == 64) p.timing[3] = global_ns();  // accumulators complete
         if (!ok) {
             atomicExch(&abort_flag, 1);
             atomicExch(p.status, 3);
         }
         tc_fence_after();
-        if (ok && nkb > 0 && !*(volatile int *)&abort_flag) {
+        // warp-uniform, because tcgen05.ld below must be executed by whole warps
+        have_acc = __all_sync(0xffffffffu, ok && nkb > 0 && !*(volatile int *)&abort_flag);
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // sh_ascale visible to the four epilogue warps (128 threads)
+    }
+    // The accumulators are read 48 columns (16 activation rows x 3 limbs) at a time to keep registers in check.
+    constexpr int kChunk = NC < 48 ? NC : 48;
+    auto load_chunk = [&](int c0, int ncols, uint32_t (&acc)[kChunk]) {
+        if (have_acc) {
 #pragma unroll
-            for (int c = 0; c < NC / 16; c++) {
-                uint32_t v[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + c * 16, v);
+            for (int c = 0; c < kChunk / 16; c++) {
+                if (c * 16 < ncols) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0 + c * 16, v);
 #pragma unroll
-                for (int j = 0; j < 16; j++) acc[c * 16 + j] = v[j];
+                    for (int j = 0; j < 16; j++) acc[c * 16 + j] = v[j];
+                }
             }
             tmem_ld_wait();
-            have_acc = true;
-        }
-        if (!have_acc) {
+        } else {
 #pragma unroll
-            for (int c = 0; c < NC; c++) acc[c] = 0u;
+            for (int c = 0; c < kChunk; c++) acc[c] = 0u;
         }
-    }
-
-    auto finalize = [&](int r, int m, int s0, int s1, int s2) {
-        const int n = row0 + r;
-        if (n >= p.N) return;
-        const float dot = ((float)s2 * 65536.0f + (float)s1 * 256.0f + (float)s0) * p.ascale[m];
-        float v = dot * to_f32<OutT>(reinterpret_cast<const OutT *>(p.scale)[n]);
-        if (p.resid) v = round_store<OutT>(v) + to_f32<OutT>(reinterpret_cast<const OutT *>(p.resid)[(size_t)m * p.N + n]);
-        reinterpret_cast<OutT *>(p.out)[(size_t)m * p.N + n] = from_f32<OutT>(v);
+    };
+    auto combine = [](const uint32_t *a3) {
+        return (long long)(int)a3[2] * 65536 + (long long)(int)a3[1] * 256 + (long long)(int)a3[0];
+    };
+    auto finish = [&](int m, long long sum, float resv) {
+        float v = (float)sum * sh_ascale[m] * wscale;
+        if (resid_p) v = round_store<OutT>(v) + resv;
+        out_p[(size_t)m * p.N + n_own] = from_f32<OutT>(v);
     };
 
     if (S == 1) {
         if (warp >= 2) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < NC; c0 += kChunk) {  // rolled: keeps the once-per-CTA epilogue code small
+                uint32_t acc[kChunk];
+                load_chunk(c0, NC - c0 < kChunk ? NC - c0 : kChunk, acc);
 #pragma unroll
-            for (int m = 0; m < NC / 3; m++)
-                if (m < p.M) finalize(r_local, m, (int)acc[3 * m], (int)acc[3 * m + 1], (int)acc[3 * m + 2]);
-        }
-    } else {
-        // all MMAs of this CTA have completed (accum_bar), so the stage buffers can hold the partial sums
-        if (warp >= 2) {
-#pragma unroll
-            for (int c = 0; c < NC; c++) red[c * kTileRows + r_local] = (int)acc[c];
-        }
-        cluster_sync_all();
-        if (warp >= 2) {
-            const int rows_per = kTileRows / S;  // S is 2, 4 or 8
-            const int t = threadIdx.x - 64;      // 0..127
-            const int r = rank * rows_per + (t % rows_per);
-            for (int m = t / rows_per; m < p.M; m += kTileRows / rows_per) {
-                // issue all (independent) remote reads first, then add
-                int part[3][8];
-#pragma unroll
-                for (int l = 0; l < 3; l++) {
-                    const uint32_t a = smem_u32(&red[(3 * m + l) * kTileRows + r]);
-#pragma unroll
-                    for (int rr = 0; rr < 8; rr++) part[l][rr] = rr < S ? ld_dsmem_s32(a, (uint32_t)rr) : 0;
+                for (int i = 0; i < kChunk / 3; i++) {
+                    const int m = c0 / 3 + i;
+                    if (m < MR && m < p.M && n_own < p.N) finish(m, combine(&acc[3 * i]), res[m]);
                 }
-                int s[3] = {0, 0, 0};
-#pragma unroll
-                for (int l = 0; l < 3; l++)
-#pragma unroll
-                    for (int rr = 0; rr < 8; rr++) s[l] += part[l][rr];
-                finalize(r, m, s[0], s[1], s[2]);
             }
         }
-        cluster_sync_all();  // peers may still be reading this CTA's shared memory
+    } else {
+        long long *recv = reinterpret_cast<long long *>(smem);  // [S source ranks][MR][rows_per] int64 <= 32 KB
+        cluster_sync_all();  // every CTA of the cluster is past its main loop: stage buffers are free everywhere
+        if (warp >= 2) {
+            const uint32_t owner = (uint32_t)(r_local / rows_per);
+            const int r_in = r_local % rows_per;
+#pragma unroll 1
+            for (int c0 = 0; c0 < NC; c0 += kChunk) {  // rolled: keeps the once-per-CTA epilogue code small
+                uint32_t acc[kChunk];
+                load_chunk(c0, NC - c0 < kChunk ? NC - c0 : kChunk, acc);
+#pragma unroll
+                for (int i = 0; i < kChunk / 3; i++) {
+                    const int m = c0 / 3 + i;
+                    if (m < MR && m < p.M) {
+                        const long long v = combine(&acc[3 * i]);
+                        const uint32_t local = smem_u32(&recv[((size_t)rank * MR + m) * rows_per + r_in]);
+                        uint32_t remote;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
+                        asm volatile("st.shared::cluster.b64 [%0], %1;" ::"r"(remote), "l"(v) : "memory");
+                    }
+                }
+            }
+        }
+        cluster_sync_all();  // release/acquire: the partial sums pushed by every peer are visible
+        if (stamp && threadIdx.x == 64) p.timing[4] = global_ns();
+        if (warp >= 2 && n_own < p.N) {
+            // a compact rolled loop: straight-line code that runs once per CTA pays an instruction-cache miss per line
+            const int r_in = et % rows_per;
+#pragma unroll 1
+            for (int m = m_own; m < p.M; m += mstep) {
+                const float resv = resid_p ? to_f32<OutT>(resid_p[(size_t)m * p.N + n_own]) : 0.f;
+                const long long *src = recv + (size_t)m * rows_per + r_in;
+                long long sum = 0;
+#pragma unroll
+                for (int rr = 0; rr < 8; rr++)
+                    if (rr < S) sum += src[(size_t)rr * MR * rows_per];
+                finish(m, sum, resv);
+            }
+        }
     }
 
+    if (stamp && threadIdx.x == 64) p.timing[5] = global_ns();  // outputs stored
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+    if (stamp && threadIdx.x == 0) p.timing[6] = global_ns();
 }
 
 // ---- activation pre-pass: rows -> three int8 limbs + power-of-two row scale -----------------------------------
@@ -572,6 +633,8 @@ static int pick_split(int row_tiles, int kblocks) {
 }
 
 int g_i8_split_override = 0;
+int g_i8_dbg = 0;
+unsigned long long *g_i8_timing = nullptr;  // tuning hook: device buffer of 8 timestamps, see I8GemmParams::timing
 
 template <typename OutT, int NC>
 static int launch_i8(cudaStream_t st, const CUtensorMap &mw, const CUtensorMap &ma, const I8GemmParams &p, int S) {
@@ -636,6 +699,8 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
     p.N = N;
     p.K = K;
     p.status = status;
+    p.timing = g_i8_timing;
+    p.dbg = g_i8_dbg;
     const int row_tiles = (N + kTileRows - 1) / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
     const int S = g_i8_split_override > 0 ? g_i8_split_override : pick_split(row_tiles, kblocks);
 #define GO(OT, NCV) return launch_i8<OT, NCV>(st, mw, ma, p, S)

@@ -19,4 +19,6 @@ int launch_rms_norm_limbs(cudaStream_t st, int dtype, void *workspace, size_t wo
 int launch_swiglu_limbs(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, const void *gate, const void *up,
                         int rows, int F, long long in_stride);
 extern int g_i8_split_override;
+extern unsigned long long *g_i8_timing;
+extern int g_i8_dbg;
 }  // namespace mynn

@@ -71,7 +71,7 @@ SIGNATURES = {
     "free_pinned": (None, [c_void_p]),
 }
 # tuning hooks that are not part of the engine-facing header
-_EXTRA = {"mynn_b200_debug_set_ksplit": (c_int, [c_int])}
+_EXTRA = {"mynn_b200_debug_set_ksplit": (c_int, [c_int]), "mynn_b200_debug_set_timing_buffer": (c_int, [c_void_p]), "mynn_b200_debug_set_mode": (c_int, [c_int])}
 
 _lib = None
 
