@@ -82,6 +82,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
     __shared__ float sm_m[kAttnWarps][8], sm_l[kAttnWarps][8];
     __shared__ unsigned sm_last;
 
+    pdl_trigger();
+    pdl_wait();  // q, the newest kv row and the active length come from the preceding kernels
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int G = p.G;
@@ -378,7 +380,7 @@ static int launch_generic(cudaStream_t st, void *out, const void *q, const void 
 
 template <typename T, int D>
 static int launch_decode(cudaStream_t st, const DecodeParams &p, int B) {
-    attention_decode_kernel<T, D><<<dim3(p.splits, p.Hkv, B), kAttnWarps * 32, 0, st>>>(p);
+    MYNN_CUDA_OK(launch_pdl(attention_decode_kernel<T, D>, dim3(p.splits, p.Hkv, B), dim3(kAttnWarps * 32), 0, st, p));
     MYNN_LAUNCH_OK("attention_decode_kernel");
     return MYNN_OK;
 }

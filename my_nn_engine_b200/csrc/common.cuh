@@ -84,6 +84,31 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// ---- programmatic dependent launch -----------------------------------------------------------------------------
+// Kernels of the decode chain are launched with the programmatic-stream-serialization attribute: a kernel may be
+// scheduled while its predecessor is still running, and orders itself with pdl_wait() before it touches anything an
+// earlier kernel produces (and before it writes anything an earlier kernel may still read).  pdl_trigger() lets the
+// successor be scheduled early.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern int g_pdl_level;  // 0: only the GEMM overlaps its producer; 1: every decode-chain kernel; 2: GEMM also triggers early
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl_level >= 1 ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // Dispatch a launcher template over the three storage dtypes.
 #define MYNN_DISPATCH_DTYPE(dt, T, ...)                       \
     switch (dt) {                                             \

@@ -159,6 +159,8 @@ __global__ void rope_kv_append_kernel(T *q_out, T *k_cache, T *v_cache, const T 
                                       long long q_stride, long long k_stride, long long v_stride, const T *cos_t,
                                       const T *sin_t, const int64_t *positions, int S, int Hq, int Hkv, int D,
                                       int cache_seq, const int32_t *past_len_dev) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x, b = row / S, s = row - b * S;
     const int slot = blockIdx.y;
     const int half = D >> 1;
@@ -193,9 +195,9 @@ int launch_rope_kv_append(cudaStream_t st, int dtype, void *q_out, void *k_cache
     if (B * S == 0) return MYNN_OK;
     const int threads = D / 2 >= 64 ? 64 : 32;
     MYNN_DISPATCH_DTYPE(dtype, T, {
-        rope_kv_append_kernel<T><<<dim3(B * S, Hq + 2 * Hkv), threads, 0, st>>>(
-            (T *)q_out, (T *)k_cache, (T *)v_cache, (const T *)q, (const T *)k, (const T *)v, q_stride, k_stride, v_stride,
-            (const T *)cos_t, (const T *)sin_t, positions, S, Hq, Hkv, D, cache_seq, past_len_dev);
+        MYNN_CUDA_OK(launch_pdl(rope_kv_append_kernel<T>, dim3(B * S, Hq + 2 * Hkv), dim3(threads), 0, st, (T *)q_out, (T *)k_cache,
+                                (T *)v_cache, (const T *)q, (const T *)k, (const T *)v, q_stride, k_stride, v_stride,
+                                (const T *)cos_t, (const T *)sin_t, positions, S, Hq, Hkv, D, cache_seq, past_len_dev));
     });
     MYNN_LAUNCH_OK("rope_kv_append_kernel");
     return MYNN_OK;
@@ -322,6 +324,61 @@ int launch_argmax_pairs(cudaStream_t st, int dtype, float *pairs, const void *lo
     });
     MYNN_LAUNCH_OK("argmax_pairs_kernel");
     return MYNN_OK;
+}
+
+// Two-stage greedy pick for long rows: `chunks` CTAs per row each find (max, last index) of a slice, then the slices
+// are merged in ascending order (>= keeps the last maximum).  pairs: scratch of chunks * rows * 2 floats.
+template <typename T>
+__global__ void __launch_bounds__(1024) argmax_chunk_kernel(float *pairs, const T *logits, int rows, int V, int chunks) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const int r = blockIdx.x / chunks, c = blockIdx.x - r * chunks;
+    const int per = (V + chunks - 1) / chunks;
+    const int beg = c * per, end = min(V, beg + per);
+    const T *row = logits + (size_t)r * V;
+    float best = -INFINITY;
+    int besti = -1;
+    for (int i = beg + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = to_f32<T>(row[i]);
+        if (v >= best || besti < 0) {
+            best = v;
+            besti = i;
+        }
+    }
+    auto better = [](float v, int i, float bv_, int bi_) { return bi_ < 0 || (i >= 0 && (v > bv_ || (v == bv_ && i > bi_))); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+        if (better(ov, oi, best, besti)) { best = ov; besti = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = besti; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int nw = blockDim.x >> 5;
+        best = threadIdx.x < nw ? bv[threadIdx.x] : -INFINITY;
+        besti = threadIdx.x < nw ? bi[threadIdx.x] : -1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+            if (better(ov, oi, best, besti)) { best = ov; besti = oi; }
+        }
+        if (threadIdx.x == 0) {
+            pairs[((size_t)c * rows + r) * 2] = best;
+            pairs[((size_t)c * rows + r) * 2 + 1] = __int_as_float(besti);
+        }
+    }
+}
+
+int launch_argmax_two_stage(cudaStream_t st, int dtype, int32_t *out_idx, float *pairs, const void *logits, int rows, int V,
+                            int chunks) {
+    if (rows == 0) return MYNN_OK;
+    MYNN_DISPATCH_DTYPE(dtype, T, {
+        argmax_chunk_kernel<T><<<rows * chunks, 512, 0, st>>>(pairs, (const T *)logits, rows, V, chunks);
+    });
+    MYNN_LAUNCH_OK("argmax_chunk_kernel");
+    return launch_argmax_merge(st, out_idx, pairs, rows, chunks);
 }
 
 int launch_argmax_merge(cudaStream_t st, int32_t *out_idx, const float *pairs, int rows, int world) {

@@ -285,6 +285,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         int ok_i = 1;
         if (lane == 0) ok_i = mbar_wait(&accum_bar, 0, &abort_flag) ? 1 : 0;
         const bool ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
+        if (threadIdx.x == 64 && p.dbg == 2) pdl_trigger();  // main loop over: the next kernel may be scheduled during the epilogue
         if (stamp && threadIdx.x == 64) p.timing[3] = global_ns();  // accumulators complete
         if (!ok) {
             atomicExch(&abort_flag, 1);
@@ -392,7 +393,8 @@ __global__ void __launch_bounds__(256) act_to_limbs_kernel(int8_t *limbs, float 
     constexpr int kMaxPer = 16;  // 4-element groups held per thread: rows up to 256 * 4 * 16 = 16384 stay in registers
     __shared__ float wmax[8];
     __shared__ float s_scale;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMM may begin streaming its weights
+    pdl_trigger();  // the GEMM may begin streaming its weights
+    pdl_wait();     // the activations come from the preceding kernel
     const int m = blockIdx.x;
     const ActT *row = act + (size_t)m * K;
     const int groups = K >> 2;  // K % 16 == 0
@@ -470,17 +472,39 @@ __global__ void __launch_bounds__(256) act_to_limbs_kernel(int8_t *limbs, float 
 }
 
 // ---- fused producers: an operator's output row goes straight to limbs --------------------------------------------
-// The row (already rounded to the storage dtype, i.e. after the operator's store point) sits in shared memory as f32.
-// Block-wide: row maximum -> power-of-two scale -> three int8 limbs per element, written 4 elements at a time.
-__device__ __forceinline__ void smem_row_to_limbs(const float *row_s, int K, int8_t *limb_row0, float *ascale_m,
-                                                  float *red /* >= 33 floats */) {
-    float mx = 0.f;
-    bool bad = false;
-    for (int k = threadIdx.x; k < K; k += blockDim.x) {
-        const float a = fabsf(row_s[k]);
-        bad |= !(a <= 3.0e38f);
-        mx = fmaxf(mx, a);
+// One CTA of 1024 threads per row.  The row (already rounded to the storage dtype, i.e. after the operator's store
+// point) is kept in shared memory as f32; each thread tracks the maximum of what it produced, one block reduction
+// gives the power-of-two scale, and the three int8 limbs per element are written 4 elements at a time.
+constexpr int kRowThreads = 1024;
+
+template <typename T>
+__device__ __forceinline__ void load8(const T *p, float (&v)[8]) {
+    if constexpr (sizeof(T) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(p);
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = to_f32<T>(e[i]);
+    } else {
+        const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T *p, const float (&v)[8]) {
+    if constexpr (sizeof(T) == 2) {
+        uint4 raw;
+        T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; i++) e[i] = from_f32<T>(v[i]);
+        *reinterpret_cast<uint4 *>(p) = raw;
+    } else {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
+// Block-wide maximum -> limb scale (broadcast through red[32]); writes the row scale; returns 0 for a bad row.
+__device__ __forceinline__ float block_limb_scale(float mx, bool bad, float *ascale_m, float *red /* >= 34 floats */) {
     mx = warp_max(mx);
     const unsigned anybad = __syncthreads_or(bad);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
@@ -490,19 +514,25 @@ __device__ __forceinline__ void smem_row_to_limbs(const float *row_s, int K, int
         for (int i = 0; i < (int)(blockDim.x >> 5); i++) t = fmaxf(t, red[i]);
         int e = 0;
         if (t > 0.f) frexpf(t, &e);
-        red[32] = t > 0.f ? ldexpf(1.0f, 22 - e) : 1.0f;
+        const float sc = t > 0.f ? ldexpf(1.0f, 22 - e) : 1.0f;
+        red[32] = anybad ? 0.f : sc;
+        *ascale_m = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc;  // non-finite input -> NaN outputs
     }
     __syncthreads();
-    const float sc = red[32];
-    if (threadIdx.x == 0) *ascale_m = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc;
+    return red[32];
+}
+
+__device__ __forceinline__ void smem_row_to_limbs(const float *row_s, int K, int8_t *limb_row0, float sc) {
     uint32_t *l0 = reinterpret_cast<uint32_t *>(limb_row0);
     uint32_t *l1 = reinterpret_cast<uint32_t *>(limb_row0 + K);
     uint32_t *l2 = reinterpret_cast<uint32_t *>(limb_row0 + 2 * (size_t)K);
     for (int gi = threadIdx.x; gi < (K >> 2); gi += blockDim.x) {
+        const float4 x4 = reinterpret_cast<const float4 *>(row_s)[gi];
+        const float x[4] = {x4.x, x4.y, x4.z, x4.w};
         uint32_t w0 = 0, w1 = 0, w2 = 0;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            int A = anybad ? 0 : __float2int_rn(row_s[4 * gi + i] * sc);
+            int A = sc == 0.f ? 0 : __float2int_rn(x[i] * sc);
             const int d0 = (int)(int8_t)(A & 0xFF);
             A = (A - d0) >> 8;
             const int d1 = (int)(int8_t)(A & 0xFF);
@@ -519,59 +549,111 @@ __device__ __forceinline__ void smem_row_to_limbs(const float *row_s, int K, int
 
 // RMSNorm whose output feeds only DequantMatMuls: y = round(x * rsqrt(mean x^2 + eps) * w) -> limbs.
 // With `part`: first s = round(x + round(part)) is stored to sum_out (residual add of an all-reduced f32 partial sum).
-// norm_out (optional) also receives y in the storage dtype.
+// norm_out (optional) also receives y in the storage dtype.  D % 8 == 0, rows 16-byte aligned.
 template <typename T>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(kRowThreads)
 rms_norm_limbs_kernel(int8_t *limbs, float *ascale, T *norm_out, T *sum_out, const T *x, const float *part, const T *w,
                       float eps, int D) {
-    extern __shared__ float row_s[];
+    extern __shared__ __align__(16) float row_s[];
     __shared__ float red[40];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_trigger();
+    pdl_wait();
     const int m = blockIdx.x;
     const size_t base = (size_t)m * D;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        float v = to_f32<T>(x[base + i]);
+    for (int i = 8 * threadIdx.x; i < D; i += 8 * kRowThreads) {
+        float v[8];
+        load8<T>(x + base + i, v);
         if (part != nullptr) {
-            v = round_store<T>(v + round_store<T>(part[base + i]));
-            sum_out[base + i] = from_f32<T>(v);
+            float pp[8];
+            load8<float>(part + base + i, pp);
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = round_store<T>(v[j] + round_store<T>(pp[j]));
+            store8<T>(sum_out + base + i, v);
         }
-        row_s[i] = v;
-        ss += v * v;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            row_s[i + j] = v[j];
+            ss += v[j] * v[j];
+        }
     }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
     if (threadIdx.x == 0) {
         float tot = 0.f;
-        for (int i = 0; i < (int)(blockDim.x >> 5); i++) tot += red[i];
+        for (int i = 0; i < kRowThreads / 32; i++) tot += red[i];
         red[33] = 1.0f / sqrtf(tot / (float)D + eps);
     }
     __syncthreads();
     const float inv = red[33];
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        const T y = from_f32<T>(row_s[i] * inv * to_f32<T>(w[i]));
-        if (norm_out != nullptr) norm_out[base + i] = y;
-        row_s[i] = to_f32<T>(y);
+    float mx = 0.f;
+    bool bad = false;
+    for (int i = 8 * threadIdx.x; i < D; i += 8 * kRowThreads) {
+        float wv[8], y[8];
+        load8<T>(w + i, wv);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            y[j] = round_store<T>(row_s[i + j] * inv * wv[j]);
+            row_s[i + j] = y[j];
+            bad |= !(fabsf(y[j]) <= 3.0e38f);
+            mx = fmaxf(mx, fabsf(y[j]));
+        }
+        if (norm_out != nullptr) store8<T>(norm_out + base + i, y);
     }
-    __syncthreads();
-    smem_row_to_limbs(row_s, D, limbs + (size_t)(3 * m) * D, ascale + m, red);
+    const float sc = block_limb_scale(mx, bad, ascale + m, red);  // its barriers also publish row_s
+    smem_row_to_limbs(row_s, D, limbs + (size_t)(3 * m) * D, sc);
 }
 
-// h = round(swish(gate) * up) -> limbs; gate/up rows are in_stride elements apart.
+// h = round(swish(gate) * up) -> limbs; gate/up rows are in_stride elements apart.  F % 8 == 0, 16-byte aligned rows.
 template <typename T>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(kRowThreads)
 swiglu_limbs_kernel(int8_t *limbs, float *ascale, const T *gate, const T *up, int F, long long in_stride) {
-    extern __shared__ float row_s[];
+    extern __shared__ __align__(16) float row_s[];
     __shared__ float red[40];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_trigger();
+    pdl_wait();
     const int m = blockIdx.x;
-    for (int i = threadIdx.x; i < F; i += blockDim.x) {
-        const float g = to_f32<T>(gate[(size_t)m * in_stride + i]);
-        row_s[i] = round_store<T>((g / (1.0f + expf(-g))) * to_f32<T>(up[(size_t)m * in_stride + i]));
+    float mx = 0.f;
+    bool bad = false;
+    for (int i = 8 * threadIdx.x; i < F; i += 8 * kRowThreads) {
+        float g[8], u[8];
+        load8<T>(gate + (size_t)m * in_stride + i, g);
+        load8<T>(up + (size_t)m * in_stride + i, u);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float h = round_store<T>((g[j] / (1.0f + expf(-g[j]))) * u[j]);
+            row_s[i + j] = h;
+            bad |= !(fabsf(h) <= 3.0e38f);
+            mx = fmaxf(mx, fabsf(h));
+        }
     }
-    __syncthreads();
-    smem_row_to_limbs(row_s, F, limbs + (size_t)(3 * m) * F, ascale + m, red);
+    const float sc = block_limb_scale(mx, bad, ascale + m, red);
+    smem_row_to_limbs(row_s, F, limbs + (size_t)(3 * m) * F, sc);
+}
+
+// Plain pre-pass in the same style (one 1024-thread CTA per row, 16-byte loads): act -> limbs.  K % 8 == 0.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) act_limbs_row_kernel(int8_t *limbs, float *ascale, const T *act, int K) {
+    extern __shared__ __align__(16) float row_s[];
+    __shared__ float red[40];
+    pdl_trigger();
+    pdl_wait();
+    const int m = blockIdx.x;
+    float mx = 0.f;
+    bool bad = false;
+    for (int i = 8 * threadIdx.x; i < K; i += 8 * kRowThreads) {
+        float v[8];
+        load8<T>(act + (size_t)m * K + i, v);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            row_s[i + j] = v[j];
+            bad |= !(fabsf(v[j]) <= 3.0e38f);
+            mx = fmaxf(mx, fabsf(v[j]));
+        }
+    }
+    const float sc = block_limb_scale(mx, bad, ascale + m, red);
+    smem_row_to_limbs(row_s, K, limbs + (size_t)(3 * m) * K, sc);
 }
 
 // ---- host side --------------------------------------------------------------------------------------------------
@@ -677,12 +759,23 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
     int8_t *limbs = (int8_t *)workspace + 512;  // rows 3M..NC-1 are padding: whatever they hold only reaches
                                                  // accumulator columns that are never read
     if (act != nullptr) {  // act == nullptr: a fused producer has already left limbs and row scales in the workspace
+        const bool row_kernel = K % 8 == 0 && (size_t)K * 4 <= 200 * 1024 && ((uintptr_t)act % 16) == 0;
+        const size_t smem = (size_t)K * 4;
+#define PREP(T)                                                                                                          \
+    if (row_kernel) {                                                                                                    \
+        auto kern = act_limbs_row_kernel<T>;                                                                             \
+        if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        MYNN_CUDA_OK(launch_pdl(kern, dim3(M), dim3(kRowThreads), smem, st, limbs, ascale, (const T *)act, K));          \
+    } else {                                                                                                             \
+        MYNN_CUDA_OK(launch_pdl(act_to_limbs_kernel<T>, dim3(M), dim3(256), 0, st, limbs, ascale, (const T *)act, K));   \
+    }
         switch (act_dtype) {
-            case MYNN_BF16: act_to_limbs_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(limbs, ascale, (const __nv_bfloat16 *)act, K); break;
-            case MYNN_F16: act_to_limbs_kernel<__half><<<M, 256, 0, st>>>(limbs, ascale, (const __half *)act, K); break;
-            case MYNN_F32: act_to_limbs_kernel<float><<<M, 256, 0, st>>>(limbs, ascale, (const float *)act, K); break;
+            case MYNN_BF16: PREP(__nv_bfloat16) break;
+            case MYNN_F16: PREP(__half) break;
+            case MYNN_F32: PREP(float) break;
             default: return fail(MYNN_E_ARG, "dequant_matmul: bad activation dtype %d", act_dtype);
         }
+#undef PREP
         MYNN_LAUNCH_OK("act_to_limbs_kernel");
     }
     CUtensorMap mw, ma;
@@ -700,7 +793,7 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
     p.K = K;
     p.status = status;
     p.timing = g_i8_timing;
-    p.dbg = g_i8_dbg;
+    p.dbg = g_pdl_level >= 2 ? 2 : 0;
     const int row_tiles = (N + kTileRows - 1) / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
     const int S = g_i8_split_override > 0 ? g_i8_split_override : pick_split(row_tiles, kblocks);
 #define GO(OT, NCV) return launch_i8<OT, NCV>(st, mw, ma, p, S)
@@ -739,7 +832,7 @@ int launch_rms_norm_limbs(cudaStream_t st, int dtype, void *workspace, size_t wo
     MYNN_DISPATCH_DTYPE(dtype, T, {
         auto kern = rms_norm_limbs_kernel<T>;
         if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<rows, 512, smem, st>>>(limbs, ascale, (T *)norm_out, (T *)sum_out, (const T *)x, part, (const T *)w, eps, D);
+        MYNN_CUDA_OK(launch_pdl(kern, dim3(rows), dim3(kRowThreads), smem, st, limbs, ascale, (T *)norm_out, (T *)sum_out, (const T *)x, part, (const T *)w, eps, D));
     });
     MYNN_LAUNCH_OK("rms_norm_limbs_kernel");
     return MYNN_OK;
@@ -755,7 +848,7 @@ int launch_swiglu_limbs(cudaStream_t st, int dtype, void *workspace, size_t work
     MYNN_DISPATCH_DTYPE(dtype, T, {
         auto kern = swiglu_limbs_kernel<T>;
         if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<rows, 512, smem, st>>>(limbs, ascale, (const T *)gate, (const T *)up, F, in_stride);
+        MYNN_CUDA_OK(launch_pdl(kern, dim3(rows), dim3(kRowThreads), smem, st, limbs, ascale, (const T *)gate, (const T *)up, F, in_stride));
     });
     MYNN_LAUNCH_OK("swiglu_limbs_kernel");
     return MYNN_OK;

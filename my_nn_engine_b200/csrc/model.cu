@@ -206,7 +206,8 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     }
     if (c.output_mode == 1) {
         if (tp == 1) {
-            RC(mynn_b200_argmax_last(st, m.tok_dev, m.logits, B, m.vocab_l, dt));
+            if (m.vocab_l >= 16384) RC(launch_argmax_two_stage(st, dt, m.tok_dev, m.pairs_all, m.logits, B, m.vocab_l, 16));
+            else RC(mynn_b200_argmax_last(st, m.tok_dev, m.logits, B, m.vocab_l, dt));
         } else {
             RC(launch_argmax_pairs(st, dt, m.pairs, m.logits, B, m.vocab_l, c.tp_rank * m.vocab_l));
             RC(comm_all_gather(st, m.pairs_all, m.pairs, (size_t)B * 2 * sizeof(float)));
@@ -284,7 +285,7 @@ static int model_create(Model **out, void **initializer, void **session_state) {
                  o_gu = take(R * 2 * m->ffn * esz), o_h = take(R * m->ffn * esz), o_last = take((size_t)c.batch * H * esz),
                  o_logits = take((size_t)c.batch * m->vocab_l * esz),
                  o_full = take(tp > 1 ? (size_t)c.batch * c.vocab * esz : 0), o_part = take(tp > 1 ? R * H * 4 : 0),
-                 o_pairs = take((size_t)c.batch * 8), o_pairs_all = take((size_t)c.batch * 8 * tp),
+                 o_pairs = take((size_t)c.batch * 8), o_pairs_all = take((size_t)c.batch * 8 * std::max(tp, 16)),
                  o_ws = take(m->attn_ws_bytes), o_gws = take(m->gemm_ws_bytes);
     cudaError_t e = cudaMalloc(&m->arena, off);
     if (e != cudaSuccess) {

@@ -34,6 +34,9 @@ int launch_argmax_pairs(cudaStream_t st, int dtype, float *pairs /*[rows][2]*/, 
                         int index_offset);
 int launch_argmax_merge(cudaStream_t st, int32_t *out_idx, const float *pairs /*[world][rows][2]*/, int rows, int world);
 
+int launch_argmax_two_stage(cudaStream_t st, int dtype, int32_t *out_idx, float *pairs /*[chunks][rows][2]*/, const void *logits,
+                            int rows, int V, int chunks);
+
 // ids[i] = tok[i]: feeds the greedy tokens back as the next step's input ids without leaving the device.
 int launch_tok_feedback(cudaStream_t st, int64_t *ids, const int32_t *tok, int n);
 

@@ -1,5 +1,6 @@
 // Process-wide status plumbing of the library: last-error text, launch counter, version queries and the pinned
 // host allocation helpers the engine's generated library also exports.
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -10,6 +11,7 @@ namespace mynn {
 static std::mutex g_err_mu;
 static char g_err[1024] = "";
 std::atomic<long long> g_launches{0};
+int g_pdl_level = [] { const char *e = getenv("MYNN_PDL_LEVEL"); return e ? atoi(e) : 0; }();
 
 void set_error(const char *fmt, ...) {
     std::lock_guard<std::mutex> lk(g_err_mu);

@@ -112,15 +112,18 @@ def test_llama3_8b_shapes_two_layer_slice_batch32():
     run_parity(cfg, state, "bf16", batch=32, steps=3, max_seq=64, prompt_len=40, prefill_len=20, seed=9)
 
 
-def test_device_argmax_output_and_step_device():
-    """output='ids' returns the last-maximum argmax of the logits the 'logits' model returns; the device-resident
-    step gives the same tokens as the host-buffer step."""
+@pytest.mark.parametrize("vocab", [2048, 32768])
+def test_device_argmax_output_and_step_device(vocab):
+    """output='ids' returns the last-maximum argmax of the logits the 'logits' model returns (one-stage kernel for the
+    small vocabulary, two-stage for the large one); the device-resident step gives the same tokens as the host-buffer
+    step."""
     from my_nn_engine_b200.decoder import DecoderModel
     from my_nn_engine_b200.quantize import random_llama_state
-    state = random_llama_state(MID, seed=4)
-    a = DecoderModel(MID, state, batch=3, max_seq_len=32, output="logits")
-    b = DecoderModel(MID, state, batch=3, max_seq_len=32, output="ids")
-    c = DecoderModel(MID, state, batch=3, max_seq_len=32, output="ids")
+    cfg = dict(MID, vocab_size=vocab)
+    state = random_llama_state(cfg, seed=4)
+    a = DecoderModel(cfg, state, batch=3, max_seq_len=32, output="logits")
+    b = DecoderModel(cfg, state, batch=3, max_seq_len=32, output="ids")
+    c = DecoderModel(cfg, state, batch=3, max_seq_len=32, output="ids")
     tok = np.array([5, 6, 7])
     ids_dev = torch.tensor(tok, device="cuda")
     out_dev = torch.zeros(3, dtype=torch.int32, device="cuda")
