@@ -411,6 +411,10 @@ static int dequant_matmul_dispatch(void *stream, void *out, const void *act, con
     // With scratch memory the tcgen05 int8 kernel takes every [N,K] problem of up to 32 rows.
     if (workspace && w_layout == MYNN_W_NK && i8_gemm_supported(M, N, K, wq, act_dtype, out_dtype))
         return i8_gemm_launch(st, out, act, wq, scale, resid, M, N, K, act_dtype, out_dtype, workspace, workspace_bytes);
+    // More rows: the prefill kernel (two activation limbs, 128 x 128-token tiles) if the scratch is large enough.
+    if (workspace && w_layout == MYNN_W_NK && i8_prefill_supported(M, N, K, wq, act_dtype, out_dtype) &&
+        workspace_bytes >= i8_prefill_workspace_bytes(M, K))
+        return i8_prefill_launch(st, out, act, wq, scale, resid, M, N, K, act_dtype, out_dtype, workspace, workspace_bytes);
 #define CASE(AD, AT, OD, OT)                                                                                        \
     if (act_dtype == AD && out_dtype == OD)                                                                         \
         return dequant_matmul_typed<AT, OT>(st, (OT *)out, (const AT *)act, wq, (const OT *)scale, (const OT *)resid, \
@@ -428,7 +432,8 @@ static int dequant_matmul_dispatch(void *stream, void *out, const void *act, con
 
 extern "C" size_t mynn_b200_dequant_matmul_workspace_bytes(int M, int N, int K) {
     (void)N;
-    return mynn::i8_gemm_workspace_bytes(M < mynn::kI8MaxRows ? M : mynn::kI8MaxRows, K);
+    if (M > mynn::kI8MaxRows) return mynn::i8_prefill_workspace_bytes(M, K);
+    return mynn::i8_gemm_workspace_bytes(M, K);
 }
 
 extern "C" int mynn_b200_dequant_matmul(void *stream, void *out, const void *act, const int8_t *wq, const void *scale,

@@ -1,5 +1,6 @@
 // Internal interface of the tcgen05 (kind::i8) weight-streaming DequantMatMul.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -18,6 +19,16 @@ int launch_rms_norm_limbs(cudaStream_t st, int dtype, void *workspace, size_t wo
                           const void *x, const float *part, const void *w, float eps, int rows, int D);
 int launch_swiglu_limbs(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, const void *gate, const void *up,
                         int rows, int F, long long in_stride);
+// TMA descriptor of a 2D int8 tensor [rows][cols] (row stride ld bytes), box = box_rows x 128 bytes, 128-byte swizzle.
+int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows);
+bool tensor_map_api_available();
+
+// Large-M (prefill) variant: activations as two int8 limbs per element, 128 x 128-token tiles, persistent CTAs.
+// Scratch layout: [0,256) status word, then M row scales (rounded up to 256 bytes), then the [2M][K] limb matrix.
+size_t i8_prefill_workspace_bytes(int M, int K);
+bool i8_prefill_supported(int M, int N, int K, const void *wq, int act_dtype, int out_dtype);
+int i8_prefill_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
+                      int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes);
 extern int g_i8_split_override;
 extern unsigned long long *g_i8_timing;
 extern int g_i8_dbg;

@@ -1,0 +1,337 @@
+// Prefill DequantMatMul (many activation rows) on tcgen05 kind::i8:  out[m,n] = scale[n] * sum_k act[m,k] * wq[n,k].
+//
+// This is a dense contraction, judged by tensor-pipe utilisation.  Like the decode kernel it never converts a weight:
+// the activations are rewritten once as fixed point with a per-row power-of-two scale and split into TWO signed
+// int8 limbs (15 significant bits relative to the row maximum: every bf16 element within 2^-7 of its row maximum is
+// exact, the rest carry an absolute error below 2^-15 of the maximum -- finer than the bf16 rounding of the
+// dequantised weights in the engine's own tensor-core prefill kernel).  The product is then an int8 GEMM with exact
+// int32 accumulation, [N weight rows] x [2 x tokens] x K, and the int8 pipe runs at twice the bf16 rate, so two limbs
+// cost the same tensor time as one bf16 product.
+//
+// Kernel: persistent CTAs (one per SM), tile = 128 weight rows x 128 tokens (256 limb columns), UMMA M=128 N=256 K=32;
+// warp 0 streams weight and limb tiles by TMA through a 4-stage mbarrier ring (48 KB per stage), warp 1 issues the
+// MMAs into one of two 256-column TMEM accumulators, warps 2-5 drain the other accumulator (tcgen05.ld), recombine
+// the limbs, scale, add the optional residual and store -- so the epilogue of one tile overlaps the main loop of the
+// next.  Tiles are walked with the token tile fastest, so concurrently running CTAs share weight tiles in L2.
+// All waits are bounded and report through the workspace status word.
+#include "common.cuh"
+#include "i8_gemm.cuh"
+#include "tcgen05.cuh"
+
+namespace mynn {
+
+constexpr int kPfRows = 128;      // weight rows per tile (UMMA M)
+constexpr int kPfTokens = 128;    // activation rows per tile
+constexpr int kPfCols = 2 * kPfTokens;  // limb columns per tile (UMMA N)
+constexpr int kPfBlockK = 128;
+constexpr int kPfStages = 4;
+constexpr int kPfThreads = 192;
+constexpr uint32_t kPfWBytes = kPfRows * kPfBlockK, kPfABytes = kPfCols * kPfBlockK;
+constexpr uint32_t kPfStageBytes = kPfWBytes + kPfABytes;  // 48 KB
+
+// ---- pre-pass: rows -> two int8 limbs + power-of-two row scale ----------------------------------------------------
+// limbs [(2m + l)][K]; with max |row| < 2^e the row is scaled by 2^(14-e), so |A| <= 2^14 and the high limb is within
+// [-64, 64]; ascale[m] = 2^(e-14).
+template <typename T>
+__global__ void __launch_bounds__(1024) act_to_limbs2_kernel(int8_t *limbs, float *ascale, const T *act, int K) {
+    extern __shared__ __align__(16) float row_s[];
+    __shared__ float red[40];
+    pdl_trigger();
+    pdl_wait();
+    const int m = blockIdx.x;
+    float mx = 0.f;
+    bool bad = false;
+    for (int i = 4 * threadIdx.x; i < K; i += 4 * 1024) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float v = to_f32<T>(act[(size_t)m * K + i + j]);
+            row_s[i + j] = v;
+            bad |= !(fabsf(v) <= 3.0e38f);
+            mx = fmaxf(mx, fabsf(v));
+        }
+    }
+    mx = warp_max(mx);
+    const unsigned anybad = __syncthreads_or(bad);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < 32; i++) t = fmaxf(t, red[i]);
+        int e = 0;
+        if (t > 0.f) frexpf(t, &e);
+        const float sc = t > 0.f ? ldexpf(1.0f, 14 - e) : 1.0f;
+        red[32] = anybad ? 0.f : sc;
+        ascale[m] = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc;
+    }
+    __syncthreads();
+    const float sc = red[32];
+    uint32_t *l0 = reinterpret_cast<uint32_t *>(limbs + (size_t)(2 * m) * K);
+    uint32_t *l1 = reinterpret_cast<uint32_t *>(limbs + (size_t)(2 * m + 1) * K);
+    for (int gi = threadIdx.x; gi < (K >> 2); gi += 1024) {
+        uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int A = sc == 0.f ? 0 : __float2int_rn(row_s[4 * gi + i] * sc);
+            const int d0 = (int)(int8_t)(A & 0xFF);
+            A = (A - d0) >> 8;
+            w0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
+            w1 |= (uint32_t)(A & 0xFF) << (8 * i);
+        }
+        l0[gi] = w0;
+        l1[gi] = w1;
+    }
+}
+
+struct PfParams {
+    void *out;
+    const void *scale, *resid;
+    const float *ascale;
+    int M, N, K;
+    int w_tiles, t_tiles;
+    int *status;
+};
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// grid = min(#SMs, #tiles) persistent CTAs; tile index = w_tile * t_tiles + t_tile, walked with stride gridDim.x.
+template <typename OutT>
+__global__ void __launch_bounds__(kPfThreads, 1)
+i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const PfParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[kPfStages], empty_bar[kPfStages], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ float sh_ascale[2][kPfTokens];
+    __shared__ int sh_go[2];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = p.w_tiles * p.t_tiles;
+    const int kblocks = (p.K + kPfBlockK - 1) / kPfBlockK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPfStages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    pdl_wait();  // limbs and row scales come from the pre-pass
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            int kc = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int wt = tile / p.t_tiles, tt = tile - wt * p.t_tiles;
+                for (int kb = 0; kb < kblocks; kb++, kc++) {
+                    const int s = kc % kPfStages, use = kc / kPfStages;
+                    if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, &abort_flag)) {
+                        atomicExch(&abort_flag, 1);
+                        atomicExch(p.status, 11);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *st = smem + s * kPfStageBytes;
+                    mbar_expect_tx(&full_bar[s], kPfStageBytes);
+                    tma_load_2d(st, &map_w, kb * kPfBlockK, wt * kPfRows, &full_bar[s]);
+                    tma_load_2d(st + kPfWBytes, &map_a, kb * kPfBlockK, tt * kPfCols, &full_bar[s]);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kPfCols >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
+            int kc = 0, it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
+                const int buf = it & 1, use = it >> 1;
+                if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1, &abort_flag)) {  // epilogue has drained it
+                    atomicExch(&abort_flag, 1);
+                    atomicExch(p.status, 12);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kPfCols);
+                for (int kb = 0; kb < kblocks; kb++, kc++) {
+                    const int s = kc % kPfStages;
+                    if (!mbar_wait(&full_bar[s], (kc / kPfStages) & 1, &abort_flag)) {
+                        atomicExch(&abort_flag, 1);
+                        atomicExch(p.status, 13);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * kPfStageBytes);
+                    const uint64_t adesc = make_kmajor_sw128_desc(a_addr), bdesc = make_kmajor_sw128_desc(a_addr + kPfWBytes);
+#pragma unroll
+                    for (int k = 0; k < kPfBlockK / 32; k++)
+                        umma_i8(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue warps 2..5: TMEM lane quadrant = warp & 3, one weight row per thread ----------------
+        const int quad = warp & 3, r_local = quad * 32 + lane, et = threadIdx.x - 64;
+        const OutT *scale_p = reinterpret_cast<const OutT *>(p.scale);
+        const OutT *resid_p = reinterpret_cast<const OutT *>(p.resid);
+        OutT *out_p = reinterpret_cast<OutT *>(p.out);
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, it++) {
+            const int wt = tile / p.t_tiles, tt = tile - wt * p.t_tiles;
+            const int buf = it & 1, use = it >> 1;
+            const int n = wt * kPfRows + r_local, tok0 = tt * kPfTokens;
+            const float wscale = n < p.N ? to_f32<OutT>(scale_p[n]) : 0.f;
+            sh_ascale[buf][et] = tok0 + et < p.M ? p.ascale[tok0 + et] : 0.f;
+            // one thread waits for the accumulator and publishes the verdict, so that all four warps take the same
+            // branch (a warp leaving alone would strand the others at the named barrier)
+            if (et == 0) {
+                const bool ok = mbar_wait(&acc_full[buf], use & 1, &abort_flag);
+                if (!ok) {
+                    atomicExch(&abort_flag, 1);
+                    atomicExch(p.status, 14);
+                }
+                sh_go[buf] = ok ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: sh_ascale[buf], sh_go[buf] are set
+            if (!sh_go[buf]) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c0 = 0; c0 < kPfCols; c0 += 32) {  // 32 accumulator columns = 16 tokens x 2 limbs
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * kPfCols + c0), v);
+                tmem_ld_wait();
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int m = tok0 + c0 / 2 + j;
+                        if (m < p.M) {
+                            const float dot = (float)((long long)(int)v[2 * j + 1] * 256 + (long long)(int)v[2 * j]) * sh_ascale[buf][c0 / 2 + j];
+                            float r = dot * wscale;
+                            if (resid_p) r = round_store<OutT>(r) + to_f32<OutT>(resid_p[(size_t)m * p.N + n]);
+                            out_p[(size_t)m * p.N + n] = from_f32<OutT>(r);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);  // this warp has drained its quadrant of the accumulator
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------
+static size_t pf_scale_bytes(int M) { return ((size_t)M * sizeof(float) + 255) / 256 * 256; }
+
+size_t i8_prefill_workspace_bytes(int M, int K) {
+    if (M <= 0 || K <= 0) return 0;
+    return 256 + pf_scale_bytes(M) + ((size_t)2 * M * K + 255) / 256 * 256;
+}
+
+bool i8_prefill_supported(int M, int N, int K, const void *wq, int act_dtype, int out_dtype) {
+    (void)out_dtype;
+    // two limbs carry 15 bits: right for 16-bit activations, not for f32 graphs (those keep the f32-accurate kernels)
+    return act_dtype != MYNN_F32 && M > kI8MaxRows && N >= 1 && K >= 16 && K % 16 == 0 && (size_t)K * 4 <= 200 * 1024 && ((uintptr_t)wq % 16) == 0 &&
+           tensor_map_api_available();
+}
+
+template <typename OutT>
+static int launch_pf(cudaStream_t st, const CUtensorMap &mw, const CUtensorMap &ma, const PfParams &p) {
+    const size_t smem = (size_t)kPfStages * kPfStageBytes + 1024;
+    auto kern = i8_prefill_gemm_kernel<OutT>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = p.w_tiles * p.t_tiles;
+    MYNN_CUDA_OK(launch_pdl(kern, dim3(tiles < sms ? tiles : sms), dim3(kPfThreads), smem, st, mw, ma, p));
+    MYNN_LAUNCH_OK("i8_prefill_gemm_kernel");
+    return MYNN_OK;
+}
+
+int i8_prefill_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
+                      int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes) {
+    const size_t need = i8_prefill_workspace_bytes(M, K);
+    if (!workspace || workspace_bytes < need)
+        return fail(MYNN_E_ARG, "dequant_matmul: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+    if ((uintptr_t)workspace % 256) return fail(MYNN_E_ARG, "dequant_matmul: workspace must be 256-byte aligned");
+    int *status = (int *)workspace;
+    float *ascale = (float *)((char *)workspace + 256);
+    int8_t *limbs = (int8_t *)workspace + 256 + pf_scale_bytes(M);
+    const size_t smem = (size_t)K * 4;
+#define PREP(T)                                                                                                          \
+    {                                                                                                                    \
+        auto kern = act_to_limbs2_kernel<T>;                                                                             \
+        if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        MYNN_CUDA_OK(launch_pdl(kern, dim3(M), dim3(1024), smem, st, limbs, ascale, (const T *)act, K));                 \
+    }
+    switch (act_dtype) {
+        case MYNN_BF16: PREP(__nv_bfloat16) break;
+        case MYNN_F16: PREP(__half) break;
+        case MYNN_F32: PREP(float) break;
+        default: return fail(MYNN_E_ARG, "dequant_matmul: bad activation dtype %d", act_dtype);
+    }
+#undef PREP
+    MYNN_LAUNCH_OK("act_to_limbs2_kernel");
+    CUtensorMap mw, ma;
+    int rc = make_map(&mw, wq, (uint64_t)N, (uint64_t)K, (uint64_t)K, kPfRows);
+    if (rc) return rc;
+    rc = make_map(&ma, limbs, (uint64_t)2 * M, (uint64_t)K, (uint64_t)K, (uint32_t)kPfCols);
+    if (rc) return rc;
+    PfParams p;
+    p.out = out;
+    p.scale = scale;
+    p.resid = resid;
+    p.ascale = ascale;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.w_tiles = (N + kPfRows - 1) / kPfRows;
+    p.t_tiles = (M + kPfTokens - 1) / kPfTokens;
+    p.status = status;
+    if (out_dtype == MYNN_BF16) return launch_pf<__nv_bfloat16>(st, mw, ma, p);
+    if (out_dtype == MYNN_F16) return launch_pf<__half>(st, mw, ma, p);
+    return launch_pf<float>(st, mw, ma, p);
+}
+
+}  // namespace mynn

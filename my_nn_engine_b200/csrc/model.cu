@@ -75,6 +75,11 @@ static int gemm(cudaStream_t st, const Model &m, void *out, const void *act, con
                 const void *resid, int M, int N, int K, int out_dtype) {
     const int dt = m.c.dtype;
     const size_t esz = dtype_size(dt), osz = dtype_size(out_dtype);
+    if (M > 32 && m.gemm_ws && m.gemm_ws_bytes >= mynn_b200_dequant_matmul_workspace_bytes(M, N, K)) {
+        // prefill: one launch of the large-tile tensor-core kernel over all rows
+        if (resid) return mynn_b200_dequant_matmul_residual(st, out, act, w, scale, resid, M, N, K, dt, m.gemm_ws, m.gemm_ws_bytes);
+        return mynn_b200_dequant_matmul(st, out, act, w, scale, M, N, K, dt, out_dtype, MYNN_W_NK, m.gemm_ws, m.gemm_ws_bytes);
+    }
     for (int m0 = 0; m0 < M; m0 += 32) {
         const int mm = M - m0 < 32 ? M - m0 : 32;
         char *o = (char *)out + (size_t)m0 * N * osz;
@@ -277,6 +282,8 @@ static int model_create(Model **out, void **initializer, void **session_state) {
     {
         const int kmax = std::max(std::max(H, m->ffn), m->Hq * D);
         m->gemm_ws_bytes = c.use_tensor_gemm ? mynn_b200_dequant_matmul_workspace_bytes(32, 0, kmax) : 0;
+        if (c.use_tensor_gemm && m->max_rows > 32)
+            m->gemm_ws_bytes = std::max(m->gemm_ws_bytes, mynn_b200_dequant_matmul_workspace_bytes(m->max_rows, 0, kmax));
     }
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += up256(bytes); return o; };

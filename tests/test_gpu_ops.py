@@ -79,6 +79,29 @@ def test_dequant_matmul_vs_oracle(path, dtype, m, n, k):
         assert np.abs(to_np(out) - w).max() <= np.abs(w).max() * 2.0 ** -7
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(33, 128, 128), (128, 512, 1024), (200, 384, 512), (256, 1024, 4096), (300, 1008, 448),
+                                   (1024, 256, 2048)])
+def test_dequant_matmul_prefill_kernel_vs_oracle(dtype, m, n, k):
+    """More than 32 activation rows with a workspace: the large-tile tcgen05 int8 kernel (two activation limbs).
+    Tile edges in every dimension: rows 33/200/300 (128-token tiles), n 1008 (128-row tiles), k 448 (128-wide blocks)."""
+    rng = np.random.default_rng(m * 7 + n * 3 + k)
+    wq = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    scale = torch.from_numpy(rng.uniform(0.002, 0.02, size=n).astype(np.float32)).to(dtype)
+    act = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(dtype)
+    out = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda())
+    ops.check_workspace(ops.dequant_matmul_workspace(m, n, k, "cuda"))
+    want = R.dequant_matmul(act.float().numpy(), wq, scale.float().numpy())
+    assert rel_err(to_np(out), want) <= 1e-2
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    assert np.abs(to_np(out) - want).max() <= np.abs(want).max() * ulp
+    out2 = ops.dequant_matmul_residual(act.cuda(), dev(wq), scale.cuda(), res.cuda())
+    name = "bf16" if dtype == torch.bfloat16 else "f16"
+    want2 = R.store_round(R.store_round(want, name) + res.float().numpy(), name)
+    assert np.abs(to_np(out2) - want2).max() <= np.abs(want2).max() * 2 * ulp
+
+
 @pytest.mark.parametrize("path", ["tcgen05_i8", "mma_sync"])
 @pytest.mark.parametrize("ksplit", [1, 2, 4, 8])
 def test_dequant_matmul_cluster_splits_agree(ksplit, path):
