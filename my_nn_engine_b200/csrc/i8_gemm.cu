@@ -33,7 +33,8 @@ namespace mynn {
 
 constexpr int kTileRows = 128;   // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;     // int8 k values per pipeline stage = one 128-byte swizzle row
-constexpr int kStages = 3;
+constexpr int kStages = 3;      // pipeline depth when two CTAs share an SM
+constexpr int kMaxStages = 7;   // depth when the grid has at most one CTA per SM (196 KB of tiles in flight)
 constexpr int kGemmThreads = 192;
 
 struct I8GemmParams {
@@ -42,6 +43,7 @@ struct I8GemmParams {
     const float *ascale;  // [M] activation row scales 2^(e-22)
     int M, N, K;
     int *status;          // device int, set non-zero on a timed-out wait
+    int stages;           // pipeline depth: kStages or kMaxStages
     unsigned long long *timing;  // optional: 8 timestamps (ns) of CTA (0,0) for tuning, or null
     int dbg;
 };
@@ -57,7 +59,8 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     static_assert(kStages * kStageBytes >= NC * kTileRows * 4, "reduction buffer aliases the stage buffers");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzled tiles need 1024-byte alignment
-    __shared__ uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
+    __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], accum_bar;
+    const int stages = p.stages;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ float sh_ascale[32];
@@ -75,7 +78,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const int nkb = q + (rank < rem ? 1 : 0);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; s++) {
+        for (int s = 0; s < stages; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
@@ -97,7 +100,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             // The weights do not depend on the preceding kernel: start streaming them at once, and only then wait
             // (programmatic dependent launch) for the grid that writes the activation limbs.
-            const int pre = min(nkb, kStages);
+            const int pre = min(nkb, stages);
             for (int i = 0; i < pre; i++) {
                 mbar_expect_tx(&full_bar[i], kWBytes + kABytes);
                 tma_load_2d(smem + i * kStageBytes, &map_w, (kb_beg + i) * kBlockK, row0, &full_bar[i]);
@@ -107,7 +110,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             for (int i = 0; i < pre; i++)
                 tma_load_2d(smem + i * kStageBytes + kWBytes, &map_a, (kb_beg + i) * kBlockK, 0, &full_bar[i]);
             for (int i = pre; i < nkb; i++) {
-                const int s = i % kStages, it = i / kStages;
+                const int s = i % stages, it = i / stages;
                 if (!mbar_wait(&empty_bar[s], (it - 1) & 1, &abort_flag)) {
                     atomicExch(&abort_flag, 1);
                     atomicExch(p.status, 1);
@@ -127,7 +130,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             constexpr uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NC >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
             bool ok = true;
             for (int i = 0; i < nkb && ok; i++) {
-                const int s = i % kStages, it = i / kStages;
+                const int s = i % stages, it = i / stages;
                 if (!mbar_wait(&full_bar[s], it & 1, &abort_flag)) {
                     atomicExch(&abort_flag, 1);
                     atomicExch(p.status, 2);
@@ -608,8 +611,9 @@ bool i8_gemm_supported(int M, int N, int K, const void *wq, int act_dtype, int o
 }
 
 static int pick_split(int row_tiles, int kblocks) {
-    // Few row tiles cannot pull the full HBM bandwidth (one SM streams ~100 GB/s), so split K over a cluster of
-    // 2, 4 or 8 until there are about 120 CTAs, keeping at least 8 k blocks (128 KB of weights) per CTA.
+    // One SM ingests roughly 60-70 GB/s of tiles, so a GEMM with few row tiles cannot pull the full HBM bandwidth:
+    // split K over a cluster of 2, 4 or 8 until there are about 120 CTAs, keeping at least 8 k blocks (128 KB of
+    // weights) per CTA.  (Measured on the Llama-3-8B shapes at 32 rows: 4 is best for qkv, o and down.)
     int s = 1;
     while (s < 8 && row_tiles * s < 120 && kblocks / (s * 2) >= 8) s *= 2;
     return s;
@@ -622,11 +626,11 @@ unsigned long long *g_i8_timing = nullptr;  // tuning hook: device buffer of 8 t
 template <typename OutT, int NC>
 static int launch_i8(cudaStream_t st, const CUtensorMap &mw, const CUtensorMap &ma, const I8GemmParams &p, int S) {
     constexpr uint32_t kStageBytes = kTileRows * kBlockK + ((NC * kBlockK + 1023) / 1024) * 1024;
-    const size_t smem = (size_t)kStages * kStageBytes + 1024;
+    const size_t smem = (size_t)p.stages * kStageBytes + 1024;
     auto kern = i8_stream_gemm_kernel<OutT, NC>;
     static bool attr_set = false;
     if (!attr_set) {
-        MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kMaxStages * kStageBytes + 1024)));
         attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -697,6 +701,7 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
     p.dbg = g_pdl_level >= 2 ? 2 : 0;
     const int row_tiles = (N + kTileRows - 1) / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
     const int S = g_i8_split_override > 0 ? g_i8_split_override : pick_split(row_tiles, kblocks);
+    p.stages = (long long)row_tiles * S <= 148 ? kMaxStages : kStages;
 #define GO(OT, NCV) return launch_i8<OT, NCV>(st, mw, ma, p, S)
 #define BY_NC(OT)                \
     switch (NC) {                \
