@@ -198,6 +198,13 @@ int mynn_b200_model_step_device(void *state, void *stream, const int64_t *ids_de
  * (crates/llm/src/session.rs:426-480) without its padding rows.  ids_host int64 [batch, T] (host memory); out_host
  * receives what model() would return for the last position.  T <= max_prefill. */
 int mynn_b200_model_prefill(void *state, const int64_t *ids_host, int T, int past_len, void *out_host);
+/* Fused tensor-parallel reduction over NVLink peer memory (tp_world > 1): each rank exports a 64-byte handle of its
+ * partial-sum block; the host gathers the handles in rank order (as it distributes the communicator id) and attaches
+ * them before the first step.  The per-layer all-reduce then happens inside the residual-add + RMSNorm kernel, which
+ * reads every peer's f32 partial sums directly.  Without attach the step calls ncclAllReduce instead.  No counterpart in
+ * the engine, whose AllReduce operator has no CUDA lowering (src/codegen/cuda.rs:2577-2580). */
+int mynn_b200_model_tp_export(void *state, void *handle_out_64_bytes);
+int mynn_b200_model_tp_attach(void *state, const void *handles_world_x_64_bytes);
 /* Kernels launched by this library since load (monotonic). */
 int64_t mynn_b200_launch_count(void);
 

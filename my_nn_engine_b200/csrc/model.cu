@@ -23,6 +23,7 @@
 #include "common.cuh"
 #include "i8_gemm.cuh"
 #include "ops_internal.cuh"
+#include "tp_fused.cuh"
 
 namespace mynn {
 
@@ -51,7 +52,11 @@ struct Model {
     int32_t *tok_dev;
     char *h_in = nullptr;  // pinned mirror of the input block
     void *x, *n, *qkv, *q_rot, *attn, *gu, *h, *last_x, *logits, *logits_full;
-    float *part, *pairs, *pairs_all;
+    float *part, *pairs, *pairs_all;  // part = partial-sum buffer 0 of the peer-shared block (tp_world > 1)
+    char *tp_block = nullptr;         // cudaMalloc'd block shared with the peers: TpLocal header + two partial-sum buffers
+    size_t tp_block_bytes = 0;
+    TpPeers tp = {};
+    bool tp_attached = false;
     void *attn_ws, *gemm_ws;
     size_t attn_ws_bytes, gemm_ws_bytes;
     cudaStream_t stream = nullptr;
@@ -113,6 +118,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     const size_t esz = dtype_size(dt);
     const int Nq = m.Hq * D, Nkv = m.Hkv * D;
     const float attn_scale = 1.0f / sqrtf((float)D);
+    const bool tp_fused = tp > 1 && m.tp_attached && m.gemm_ws != nullptr && M <= kI8MaxRows && H % 16 == 0 && (size_t)H * 4 <= 200 * 1024;
     const bool fused = m.gemm_ws != nullptr && M <= kI8MaxRows && H % 16 == 0 && m.ffn % 16 == 0 &&
                        (size_t)std::max(H, m.ffn) * 4 <= 200 * 1024;
 
@@ -162,8 +168,12 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
             RC(norm(L.ln2, nullptr, M, m.x));
         } else {
             RC(gemm(st, m, m.part, m.attn, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
-            RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
-            RC(norm(L.ln2, m.part, M, m.x));  // x = round(x + round(sum of partials)), then the norm
+            if (tp_fused) {  // peers' partial sums are read over NVLink inside the add + norm + limbs kernel
+                RC(launch_tp_reduce_norm_limbs(st, dt, m.tp, 0, m.gemm_ws, m.gemm_ws_bytes, m.x, L.ln2, c.rms_eps, M, H));
+            } else {
+                RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
+                RC(norm(L.ln2, m.part, M, m.x));  // x = round(x + round(sum of partials)), then the norm
+            }
         }
         // --- MLP block ---
         const bool fuse_mlp = fused && L.gu_fused;
@@ -187,11 +197,16 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
             else RC(gemm(st, m, m.x, m.h, L.wd, L.sd, m.x, M, H, m.ffn, dt));
             if (!last) RC(norm(next_norm, nullptr, M, m.x));
         } else {
-            if (fuse_mlp) RC(gemm_prequant(st, m, m.part, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
-            else RC(gemm(st, m, m.part, m.h, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
-            RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
-            if (last) RC(launch_add_f32_rms_norm(st, dt, m.x, nullptr, m.x, m.part, nullptr, c.rms_eps, M, H));
-            else RC(norm(next_norm, m.part, M, m.x));
+            float *pdst = tp_fused ? tp_part(m.tp.local, m.tp.part_off[1]) : m.part;
+            if (fuse_mlp) RC(gemm_prequant(st, m, pdst, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
+            else RC(gemm(st, m, pdst, m.h, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
+            if (tp_fused) {
+                RC(launch_tp_reduce_norm_limbs(st, dt, m.tp, 1, m.gemm_ws, m.gemm_ws_bytes, m.x, next_norm, c.rms_eps, M, H));
+            } else {
+                RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
+                if (last) RC(launch_add_f32_rms_norm(st, dt, m.x, nullptr, m.x, m.part, nullptr, c.rms_eps, M, H));
+                else RC(norm(next_norm, m.part, M, m.x));
+            }
         }
     }
     // --- head: only the last token of each sequence is needed ---
@@ -291,7 +306,7 @@ static int model_create(Model **out, void **initializer, void **session_state) {
                  o_qkv = take(R * nqkv * esz), o_qrot = take(R * m->Hq * D * esz), o_attn = take(R * m->Hq * D * esz),
                  o_gu = take(R * 2 * m->ffn * esz), o_h = take(R * m->ffn * esz), o_last = take((size_t)c.batch * H * esz),
                  o_logits = take((size_t)c.batch * m->vocab_l * esz),
-                 o_full = take(tp > 1 ? (size_t)c.batch * c.vocab * esz : 0), o_part = take(tp > 1 ? R * H * 4 : 0),
+                 o_full = take(tp > 1 ? (size_t)c.batch * c.vocab * esz : 0), 
                  o_pairs = take((size_t)c.batch * 8), o_pairs_all = take((size_t)c.batch * 8 * std::max(tp, 16)),
                  o_ws = take(m->attn_ws_bytes), o_gws = take(m->gemm_ws_bytes);
     cudaError_t e = cudaMalloc(&m->arena, off);
@@ -309,9 +324,27 @@ static int model_create(Model **out, void **initializer, void **session_state) {
     m->tok_dev = (int32_t *)(a + o_tok);
     m->x = a + o_x; m->n = a + o_n; m->qkv = a + o_qkv; m->q_rot = a + o_qrot; m->attn = a + o_attn;
     m->gu = a + o_gu; m->h = a + o_h; m->last_x = a + o_last; m->logits = a + o_logits;
-    m->logits_full = a + o_full; m->part = (float *)(a + o_part); m->pairs = (float *)(a + o_pairs);
+    m->logits_full = a + o_full; m->pairs = (float *)(a + o_pairs);
     m->pairs_all = (float *)(a + o_pairs_all); m->attn_ws = a + o_ws;
     m->gemm_ws = m->gemm_ws_bytes ? a + o_gws : nullptr;
+    m->part = nullptr;
+    if (tp > 1) {
+        const size_t pbytes = up256(R * H * 4);
+        m->tp_block_bytes = 256 + 2 * pbytes;
+        e = cudaMalloc(&m->tp_block, m->tp_block_bytes);
+        if (e != cudaSuccess) {
+            cudaFree(m->arena);
+            delete m;
+            return fail(MYNN_E_CUDA, "model_init: cudaMalloc of the peer-shared block failed: %s", cudaGetErrorString(e));
+        }
+        cudaMemset(m->tp_block, 0, m->tp_block_bytes);
+        m->tp.local = (TpLocal *)m->tp_block;
+        m->tp.part_off[0] = 256;
+        m->tp.part_off[1] = 256 + pbytes;
+        m->tp.rank = c.tp_rank;
+        m->tp.world = tp;
+        m->part = tp_part(m->tp.local, m->tp.part_off[0]);
+    }
     e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMallocHost((void **)&m->h_in, 16 + R * 8);
     if (e != cudaSuccess) {
@@ -367,6 +400,11 @@ static int copy_result_to_host(Model &m, void *dst) {
     }
     MYNN_CUDA_OK(cudaStreamSynchronize(m.stream));
     if (m.gemm_ws) RC(mynn_b200_dequant_matmul_check(m.stream, m.gemm_ws));
+    if (m.tp_attached) {
+        int st_ = 0;
+        MYNN_CUDA_OK(cudaMemcpy(&st_, &m.tp.local->status, sizeof st_, cudaMemcpyDeviceToHost));
+        if (st_) return fail(MYNN_E_COMM, "tensor-parallel reduction: a wait for a peer timed out (status %d)", st_);
+    }
     return MYNN_OK;
 }
 
@@ -433,6 +471,9 @@ extern "C" void model_destroy(void *state) {
     if (m->stream) cudaStreamDestroy(m->stream);
     if (m->arena) cudaFree(m->arena);
     if (m->h_in) cudaFreeHost(m->h_in);
+    for (int r = 0; r < m->tp.world; r++)
+        if (m->tp_attached && r != m->tp.rank && m->tp.remote[r]) cudaIpcCloseMemHandle(m->tp.remote[r]);
+    if (m->tp_block) cudaFree(m->tp_block);
     delete m;
 }
 
@@ -476,4 +517,38 @@ extern "C" int mynn_b200_model_prefill(void *state, const int64_t *ids_host, int
     MYNN_CUDA_OK(cudaStreamSynchronize(st));  // the sources above are short-lived host memory
     RC(enqueue_forward(m, st, T));
     return copy_result_to_host(m, out_host);
+}
+
+// Peer-memory set-up of the fused tensor-parallel reduction.  Each rank exports a 64-byte handle of its shared block
+// (cudaIpcGetMemHandle); after the host has gathered the handles of all ranks in rank order, attach maps the peers'
+// blocks.  Call both before the first step (the captured graph holds the mapped addresses).  Without attach the
+// step uses ncclAllReduce followed by separate kernels.
+extern "C" int mynn_b200_model_tp_export(void *state, void *handle_out_64_bytes) {
+    if (!state || !handle_out_64_bytes) return fail(MYNN_E_ARG, "model_tp_export: null pointer");
+    Model &m = *(Model *)state;
+    if (!m.tp_block) return fail(MYNN_E_STATE, "model_tp_export: the model is not tensor parallel");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    MYNN_CUDA_OK(cudaIpcGetMemHandle((cudaIpcMemHandle_t *)handle_out_64_bytes, m.tp_block));
+    return MYNN_OK;
+}
+
+extern "C" int mynn_b200_model_tp_attach(void *state, const void *handles_world_x_64_bytes) {
+    if (!state || !handles_world_x_64_bytes) return fail(MYNN_E_ARG, "model_tp_attach: null pointer");
+    Model &m = *(Model *)state;
+    if (!m.tp_block) return fail(MYNN_E_STATE, "model_tp_attach: the model is not tensor parallel");
+    if (m.tp_attached) return fail(MYNN_E_STATE, "model_tp_attach: already attached");
+    if (m.graph_exec) return fail(MYNN_E_STATE, "model_tp_attach: call before the first step");
+    for (int r = 0; r < m.tp.world; r++) {
+        if (r == m.tp.rank) {
+            m.tp.remote[r] = m.tp.local;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles_world_x_64_bytes + (size_t)r * 64, 64);
+        void *p = nullptr;
+        MYNN_CUDA_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        m.tp.remote[r] = (TpLocal *)p;
+    }
+    m.tp_attached = true;
+    return MYNN_OK;
 }

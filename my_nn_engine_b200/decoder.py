@@ -75,7 +75,7 @@ class DecoderModel:
 
     def __init__(self, cfg: dict, state: dict, dtype: str = "bf16", max_seq_len: int = 256, batch: int = 1,
                  tp_rank: int = 0, tp_world: int = 1, output: str = "logits", use_graph: bool = True,
-                 max_prefill: int = 0, device=None, tensor_gemm: bool = True):
+                 max_prefill: int = 0, device=None, tensor_gemm: bool = True, tp_fused: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("DecoderModel needs a CUDA device: the decode path has no CPU implementation")
         self.lib = ffi.lib()
@@ -170,6 +170,17 @@ class DecoderModel:
         ffi.check(self.lib.mynn_b200_model_status())
         if not self.state:
             raise RuntimeError("model_init returned no state")
+        self.tp_fused = False
+        if G > 1 and tp_fused and tensor_gemm:
+            # hand every rank's partial-sum block to every other rank (64-byte IPC handles over torch.distributed)
+            import torch.distributed as dist
+            buf = ctypes.create_string_buffer(64)
+            ffi.check(self.lib.mynn_b200_model_tp_export(self.state, buf))
+            handles = [None] * G
+            dist.all_gather_object(handles, buf.raw)
+            blob = ctypes.create_string_buffer(b"".join(handles), 64 * G)
+            ffi.check(self.lib.mynn_b200_model_tp_attach(self.state, blob))
+            self.tp_fused = True
 
         # host staging in pinned memory, as the engine's alloc_pinned buffers
         self._ids = torch.zeros(batch, dtype=torch.int64).pin_memory()

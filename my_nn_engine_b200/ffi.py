@@ -66,6 +66,8 @@ SIGNATURES = {
     "mynn_b200_model_status": (c_int, []),
     "mynn_b200_model_step_device": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "mynn_b200_model_prefill": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "mynn_b200_model_tp_export": (c_int, [c_void_p, c_void_p]),
+    "mynn_b200_model_tp_attach": (c_int, [c_void_p, c_void_p]),
     "mynn_b200_launch_count": (c_int64, []),
     "alloc_pinned": (c_void_p, [c_size_t]),
     "free_pinned": (None, [c_void_p]),

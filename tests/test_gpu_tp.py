@@ -1,5 +1,6 @@
 """Tensor-parallel decode on 2 GPUs (skipped with fewer): every rank's logits / greedy ids equal the single-GPU model's
-to the end-to-end tolerance, through NCCL all-reduce inside the captured step.  Ranks are child processes; failures
+to the end-to-end tolerance, with the per-layer reduction done either by reading the peers' partial sums over NVLink
+inside the residual-add + RMSNorm kernel or by ncclAllReduce inside the captured step.  Ranks are child processes; failures
 are host-side (a rank exits with a non-zero code), no GPU fault is provoked."""
 import os
 import socket
@@ -37,8 +38,10 @@ def _rank_main(rank, world, port, q):
     assert t.cpu().tolist() == [3.0] * 1000
     state = random_llama_state(MID, seed=3)
     outs = {}
-    for output in ("logits", "ids"):
-        m = DecoderModel(MID, state, batch=4, max_seq_len=48, tp_rank=rank, tp_world=world, output=output, max_prefill=8)
+    for output, fused in (("logits", True), ("ids", True), ("logits_nccl", False)):
+        m = DecoderModel(MID, state, batch=4, max_seq_len=48, tp_rank=rank, tp_world=world, output=output.split("_")[0],
+                         max_prefill=8, tp_fused=fused)
+        assert m.tp_fused == fused
         rng = np.random.default_rng(0)
         prompt = rng.integers(0, 2048, size=(4, 8))
         res = [m.prefill(prompt, 0).clone()]
@@ -80,8 +83,10 @@ def test_tp2_matches_single_gpu():
     ref = torch.stack(ref).numpy()
     m.close()
     for rank in (0, 1):
-        lg = got[rank]["logits"]
-        assert np.abs(lg - ref).max() <= 3e-2 * np.abs(ref).max()
+        for key in ("logits", "logits_nccl"):  # peer-memory reduction fused into the norm kernel, and ncclAllReduce
+            lg = got[rank][key]
+            assert np.abs(lg - ref).max() <= 3e-2 * np.abs(ref).max(), key
+        assert np.array_equal(got[rank]["logits"], got[0]["logits"])  # every rank computes the identical sum
         assert np.array_equal(got[rank]["ids"], got[0]["ids"])
     ids_ref = np.array([[len(r) - 1 - np.argmax(r[::-1]) for r in step] for step in got[0]["logits"]])
     assert np.array_equal(got[0]["ids"].astype(np.int64), ids_ref)  # sharded argmax == argmax of gathered logits
