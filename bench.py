@@ -11,7 +11,7 @@ needed between iterations.
 
 Printed JSON (rank 0): value = device-resident throughput (token ids fed back on the device, CUDA events around
 exactly K steps, max over ranks); e2e = the same through model(state, outputs, inputs) with HOST buffers (pinned
-ids in, token ids out every step); roofline = the dominant kernel (gate/up DequantMatMul at M=32) timed live over
+ids in, token ids out every step); roofline = the dominant kernel (the tcgen05 int8 DequantMatMul, gate/up shape at M=32) timed live over
 the model's own per-layer weights; cpu_baseline = the CPU oracle on a bounded slice of the same workload.
 `--impl reference` times the CPU restatement of the engine's CPU backend instead (the engine itself, Rust + LLVM 18,
 cannot be built here) with all host threads.
@@ -276,7 +276,8 @@ def run_gpu_arm(args, cfg):
         line = {"metric": METRIC, "value": BATCH * 1e3 / ms_dev, "unit": UNIT, "n_gpus": world, "steps": steps,
                 "warmup": warm, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": workload_name(cfg), "parallelism": f"tp{world}", "l2": "inputs larger than L2"},
+                "config": {"workload": workload_name(cfg), "parallelism": f"tp{world}", "l2": "inputs larger than L2",
+                           "tp_reduce": ("nvlink peer loads fused into add+rmsnorm" if model.tp_fused else ("nccl" if world > 1 else "none"))},
                 "clocks": clocks.summary(),
                 "e2e": {"value": BATCH * 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": model.h2d_bytes_per_step, "d2h_bytes_per_step": model.d2h_bytes_per_step},
@@ -336,8 +337,13 @@ def kernel_roofline(model, cfg, world, dev):
     us = e0.elapsed_time(e1) * 1e3 / len(blocks)
     n, k, m = 2 * f, h, BATCH
     alg = n * k + n * 2 + m * k * 2 + m * n * 2
-    return {"kernel": "dequant_gemm_stream_kernel (gate/up, M=32, N=%d, K=%d)" % (n, k), "bound": "hbm",
-            "achieved": alg / us / 1e3, "unit": "GB/s", "us_per_launch": us, "algorithmic_bytes": alg, "traffic": None}
+    # DRAM traffic of one launch from the ncu capture summarised in profiles/i8_stream_gemm_gateup_m32.md
+    # (dram__bytes_read.sum + dram__bytes_write.sum at TP1: 117,935,616 + 4,291,328 bytes); the weight stream is
+    # proportional to the shard, so it is scaled by 1/world for a tensor-parallel rank.
+    traffic = (117935616 + 4291328) // world
+    return {"kernel": "i8_stream_gemm_kernel (gate/up DequantMatMul incl. limb pre-pass, M=32, N=%d, K=%d)" % (n, k),
+            "bound": "hbm", "achieved": alg / us / 1e3, "unit": "GB/s", "us_per_launch": us, "algorithmic_bytes": alg,
+            "traffic": traffic}
 
 
 def main():
