@@ -209,12 +209,15 @@ def run_gpu_arm(args, cfg):
     max_seq = CONTEXT + 2 * (steps + warm) + 64
     state = random_llama_state(cfg, seed=0, device=str(dev))  # identical on every rank (same seed)
     model = DecoderModel(cfg, state, dtype="bf16", max_seq_len=max_seq, batch=BATCH, tp_rank=rank, tp_world=world,
-                         output="ids", use_graph=True)
+                         output="ids", use_graph=True, kv_int8=args.kv == "int8")
     del state
     torch.cuda.empty_cache()
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     for t in model.k_cache + model.v_cache:  # synthetic 2048-token context
-        t[:, :, :CONTEXT].copy_(torch.randn(t[:, :, :CONTEXT].shape, generator=g, device=dev, dtype=torch.float32) * 0.5)
+        r = torch.randn(t[:, :, :CONTEXT].shape, generator=g, device=dev, dtype=torch.float32) * 0.5
+        t[:, :, :CONTEXT].copy_((r * 40).clamp(-127, 127).round() if model.kv_int8 else r)
+    for t in model.k_scale + model.v_scale:
+        t[:, :, :CONTEXT].fill_(1.0 / 80)
     ids0 = torch.randint(0, cfg["vocab_size"], (BATCH,), device=dev, dtype=torch.int64,
                          generator=torch.Generator(device=dev).manual_seed(7))
     stream = torch.cuda.Stream(device=dev)  # a real stream handle: the library treats NULL as the model's own stream
@@ -277,6 +280,7 @@ def run_gpu_arm(args, cfg):
                 "warmup": warm, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": workload_name(cfg), "parallelism": f"tp{world}", "l2": "inputs larger than L2",
+                           "kv_cache": "int8 + per-token scale (quant_kv_cache option; not the headline configuration)" if model.kv_int8 else "bf16",
                            "tp_reduce": ("nvlink peer loads fused into add+rmsnorm" if model.tp_fused else ("nccl" if world > 1 else "none"))},
                 "clocks": clocks.summary(),
                 "e2e": {"value": BATCH * 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e,
@@ -288,7 +292,8 @@ def run_gpu_arm(args, cfg):
             roof["frac"] = roof["achieved"] / peak
             line["roofline"] = roof
         # algorithmic bytes of a whole step on this rank: weights once + KV once (per KV head) over HBM
-        kv_bytes = 2 * cfg["num_hidden_layers"] * BATCH * (cfg["num_key_value_heads"] // world) * (CONTEXT + warm + steps // 2) * cfg["head_dim"] * 2
+        kv_row_bytes = cfg["head_dim"] + 2 if model.kv_int8 else cfg["head_dim"] * 2
+        kv_bytes = 2 * cfg["num_hidden_layers"] * BATCH * (cfg["num_key_value_heads"] // world) * (CONTEXT + warm + steps // 2) * kv_row_bytes
         step_bytes = model.weight_bytes() - cfg["vocab_size"] * cfg["hidden_size"] + kv_bytes
         line["step_hbm"] = {"algorithmic_bytes_per_gpu": int(step_bytes), "achieved_gbs": step_bytes / ms_dev / 1e6,
                             "frac_of_peak": step_bytes / ms_dev / 1e6 / peak}
@@ -354,6 +359,8 @@ def main():
     ap.add_argument("--impl", default="mynn_b200", choices=["mynn_b200", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="override the depth (testing only; the default is the full model)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "int8"],
+                    help="KV cache storage; the headline configuration is bf16, int8 is the engine's quant_kv_cache option")
     args = ap.parse_args()
     cfg = dict(LLAMA3_8B)
     if args.layers:

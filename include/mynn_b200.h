@@ -111,6 +111,26 @@ int mynn_b200_attention_decode_noalloc(void *stream, void *out, const void *q, c
 int mynn_b200_kv_cache_update(void *stream, void *cache, const void *new_kv, int BH, int cache_seq_len,
                               int new_seq_len, int D, int offset, const int32_t *offset_dev, int dtype);
 
+/* QuantizingKVCacheUpdate (the engine's `quant_kv_cache` option): the new rows are quantized to int8 with one scale
+ * per token, cache[bh, offset+t, :] = q, scale[bh, offset+t] = s, in place.
+ *   s = max_d|x| * (1/127); inv = 127 / max (0 for an all-zero row); q = trunc(x * inv +- 0.5) clamped to [-128, 127]
+ * which is the CPU backend's arithmetic (src/codegen/cpu/translator.rs:4090-4372), so the bytes are identical to it.
+ * Replaces: quantizing_kvcache_update (cpp/quantizing_kvcache_update.cuh, dispatch src/codegen/cuda.rs:2116-2174).
+ * cache int8 [BH, cache_seq_len, D]; scale [BH, cache_seq_len] and new_kv [BH, new_seq_len, D] in `dtype`.
+ * Bounds are handled as in mynn_b200_kv_cache_update. */
+int mynn_b200_quantizing_kv_cache_update(void *stream, int8_t *cache, void *scale, const void *new_kv, int BH,
+                                         int cache_seq_len, int new_seq_len, int D, int offset,
+                                         const int32_t *offset_dev, int dtype);
+
+/* Attention over an int8 KV cache: as mynn_b200_attention, with k/v int8 [B, Hkv, cache_seq_len, D] and per-token
+ * scales k_scale/v_scale [B, Hkv, cache_seq_len] in `dtype`; qk = (q . k_int) * k_scale * scale and the softmax weight
+ * of a row is multiplied by its v_scale before it meets v_int (src/codegen/cpu/translator.rs:4440-5008; CUDA:
+ * the QUANT template paths of cpp/attention.cuh:318-606).  The workspace rules are those of mynn_b200_attention. */
+int mynn_b200_attention_q8(void *stream, void *out, const void *q, const int8_t *k, const int8_t *v, const void *k_scale,
+                           const void *v_scale, float scale, int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len,
+                           int active_seq_kv, const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
+                           size_t workspace_bytes);
+
 /* RMSNorm over the last axis: y = x * rsqrt(mean(x^2) + eps) * w.  Replaces rms_norm (cpp/rms_norm.cuh:9-59). */
 int mynn_b200_rms_norm(void *stream, void *out, const void *x, const void *weight, float eps, int rows, int D,
                        int dtype);
@@ -182,6 +202,8 @@ typedef struct mynn_b200_model_config {
     int32_t use_graph;   /* capture the step in a CUDA graph and replay it */
     int32_t max_prefill; /* largest T accepted by mynn_b200_model_prefill (0 = decode only) */
     int32_t use_tensor_gemm; /* 1: DequantMatMul on the tcgen05 int8 kernel (needs scratch); 0: mma.sync streaming kernel */
+    int32_t kv_int8;         /* 1: the engine's `quant_kv_cache` option: int8 K/V caches with one scale per cached token;
+                                session_state then holds FOUR buffers per layer: K int8, V int8, K scale, V scale */
     float rms_eps;
 } mynn_b200_model_config;
 

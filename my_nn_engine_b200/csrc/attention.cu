@@ -19,57 +19,14 @@
 #include <atomic>
 #include <type_traits>
 
+#include "attention_internal.cuh"
 #include "common.cuh"
 #include "ops_internal.cuh"
 
 namespace mynn {
 
-constexpr int kAttnWarps = 4;
-constexpr int kMaxSplits = 64;
-constexpr int kAttnCtasPerSm = 4;  // resident CTAs per SM the kernel is built for (<= 128 registers, 17 KB smem)
-
-__device__ __forceinline__ uint4 ldg_16(const void *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-
-template <typename T>
-__device__ __forceinline__ void mma_kv(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                       uint32_t b1) {
-    if constexpr (std::is_same<T, __half>::value) {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    } else {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    }
-}
-
-// pack hi parts of (x, y) into one 32-bit register and the rounding remainders into another
-template <typename T>
-__device__ __forceinline__ void split_pack(float x, float y, uint32_t &hi, uint32_t &lo) {
-    const T xh = from_f32<T>(x), yh = from_f32<T>(y);
-    const T xl = from_f32<T>(x - to_f32<T>(xh)), yl = from_f32<T>(y - to_f32<T>(yh));
-    hi = (uint32_t)reinterpret_cast<const uint16_t &>(xh) | ((uint32_t)reinterpret_cast<const uint16_t &>(yh) << 16);
-    lo = (uint32_t)reinterpret_cast<const uint16_t &>(xl) | ((uint32_t)reinterpret_cast<const uint16_t &>(yl) << 16);
-}
-
-struct DecodeParams {
-    void *out;
-    const void *q, *k, *v;
-    float scale;
-    int Hq, Hkv, G, cache_seq;
-    int active_host;
-    const int32_t *active_dev;
-    int splits;
-    float *ws_o;    // [B*Hkv][splits][8][D]
-    float *ws_ml;   // [B*Hkv][splits][8][2]
-    unsigned *ws_ticket;  // [B*Hkv], zero before first use; the combining CTA re-zeroes it
+struct Map16 {  // accumulator tile i = 4h + j of the 16-bit kernel holds head-dim rows 64h + 8g + 2j (+1)
+    static __device__ __forceinline__ int d(int i, int g) { return 64 * (i >> 2) + 8 * g + 2 * (i & 3); }
 };
 
 // grid (splits, Hkv, B), block 128.
@@ -78,10 +35,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
     constexpr int KS = D / 16;   // k16 steps of QK^T
     constexpr int KCH = D / 32;  // 16-byte K chunks per lane per row
     constexpr int VH = D / 64;   // 16-byte V chunks per lane per row
-    __shared__ float sm_o[kAttnWarps][8][D];
-    __shared__ float sm_m[kAttnWarps][8], sm_l[kAttnWarps][8];
-    __shared__ unsigned sm_last;
-
     pdl_trigger();
     pdl_wait();  // q, the newest kv row and the active length come from the preceding kernels
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -201,78 +154,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
         }
     }
 
-    // ---- merge the warps of this CTA ----
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    if (t == 0) {
-        sm_m[warp][g] = m_run;
-        sm_l[warp][g] = l_run;
-    }
-#pragma unroll
-    for (int h = 0; h < VH; h++)
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float(&acc)[4] = o[4 * h + j];
-            const int d = 64 * h + 8 * g + 2 * j;
-            sm_o[warp][2 * t][d] = acc[0];
-            sm_o[warp][2 * t + 1][d] = acc[1];
-            sm_o[warp][2 * t][d + 1] = acc[2];
-            sm_o[warp][2 * t + 1][d + 1] = acc[3];
-        }
-    __syncthreads();
-
-    const size_t pair = (size_t)b * p.Hkv + kvh;
-    T *outp = reinterpret_cast<T *>(p.out) + (size_t)(b * p.Hq + kvh * G) * D;
-    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-        const int hd = idx / D, d = idx - hd * D;
-        float mx = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kAttnWarps; w++) mx = fmaxf(mx, sm_m[w][hd]);
-        float L = 0.f, O = 0.f;
-        if (mx > -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < kAttnWarps; w++) {
-                const float f = __expf(sm_m[w][hd] - mx);
-                L += sm_l[w][hd] * f;
-                O += sm_o[w][hd][d] * f;
-            }
-        }
-        if (p.splits == 1) {
-            outp[(size_t)hd * D + d] = from_f32<T>(O / L);
-        } else {
-            const size_t slot = (pair * p.splits + split) * 8 + hd;
-            p.ws_o[slot * D + d] = O;
-            if (d == 0) {
-                p.ws_ml[slot * 2] = mx;
-                p.ws_ml[slot * 2 + 1] = L;
-            }
-        }
-    }
-    if (p.splits == 1) return;
-
-    // ---- last CTA of this (batch, kv head) combines the splits ----
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) sm_last = (atomicAdd(&p.ws_ticket[pair], 1u) == (unsigned)(p.splits - 1)) ? 1u : 0u;
-    __syncthreads();
-    if (!sm_last) return;
-    __threadfence();
-    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-        const int hd = idx / D, d = idx - hd * D;
-        float mx = -INFINITY;
-        for (int sp = 0; sp < p.splits; sp++) mx = fmaxf(mx, __ldcg(&p.ws_ml[((pair * p.splits + sp) * 8 + hd) * 2]));
-        float L = 0.f, O = 0.f;
-        for (int sp = 0; sp < p.splits; sp++) {
-            const size_t slot = (pair * p.splits + sp) * 8 + hd;
-            const float ms = __ldcg(&p.ws_ml[slot * 2]);
-            if (ms == -INFINITY) continue;
-            const float f = __expf(ms - mx);
-            L += __ldcg(&p.ws_ml[slot * 2 + 1]) * f;
-            O += __ldcg(&p.ws_o[slot * D + d]) * f;
-        }
-        outp[(size_t)hd * D + d] = from_f32<T>(O / L);
-    }
-    if (threadIdx.x == 0) p.ws_ticket[pair] = 0u;
+    decode_tail<T, D, VH * 4, Map16>(p, o, m_run, l_run);
 }
 
 // Generic attention: one warp per (b, h, sq) query row, the CPU kernel's recurrence row by row
@@ -329,19 +211,23 @@ __global__ void attention_generic_kernel(T *out, const T *q, const T *k, const T
     }
 }
 
-static int decode_splits(int B, int Hkv, int rows_bound) {
-    // All CTAs of a launch last equally long, so the grid should fit in ONE wave of resident CTAs (148 SMs): a
-    // partly filled second wave would cost as much time as a full one.
-    const int pairs = B * Hkv;
-    int s = (kAttnCtasPerSm * 148) / pairs;
-    const int cap = rows_bound / (16 * kAttnWarps);  // at least one tile per warp and split
-    if (s > cap) s = cap;
-    if (s < 1) s = 1;
-    if (s > kMaxSplits) s = kMaxSplits;
-    return s;
+int decode_bind_workspace(DecodeParams &p, int B, int D, void *workspace, size_t workspace_bytes) {
+    p.ws_o = nullptr;
+    p.ws_ml = nullptr;
+    p.ws_ticket = nullptr;
+    if (p.splits <= 1) return MYNN_OK;
+    const size_t need = mynn_b200_attention_workspace_bytes(B, p.Hq, p.Hkv, D, p.cache_seq);
+    if (!workspace || workspace_bytes < need)
+        return fail(MYNN_E_ARG, "attention: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+    const size_t pairs = (size_t)B * p.Hkv;
+    char *w = (char *)workspace;
+    p.ws_ticket = (unsigned *)w;
+    w += align_up(pairs * sizeof(unsigned), 256);
+    p.ws_ml = (float *)w;
+    w += align_up(pairs * kMaxSplits * 8 * 2 * sizeof(float), 256);
+    p.ws_o = (float *)w;
+    return MYNN_OK;
 }
-
-static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace mynn
 
@@ -426,21 +312,9 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
     p.active_dev = active_seq_kv_dev;
     const int rows_bound = active_seq_kv_dev ? cache_seq_len : (active_seq_kv < cache_seq_len ? active_seq_kv : cache_seq_len);
     p.splits = decode_splits(B, Hkv, rows_bound);
-    p.ws_o = nullptr;
-    p.ws_ml = nullptr;
-    p.ws_ticket = nullptr;
-    if (p.splits > 1) {
-        const size_t need = mynn_b200_attention_workspace_bytes(B, Hq, Hkv, D, cache_seq_len);
-        if (!workspace || workspace_bytes < need)
-            return fail(MYNN_E_ARG, "attention: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
-        const size_t pairs = (size_t)B * Hkv;
-        char *w = (char *)workspace;
-        p.ws_ticket = (unsigned *)w;
-        w += align_up(pairs * sizeof(unsigned), 256);
-        p.ws_ml = (float *)w;
-        w += align_up(pairs * kMaxSplits * 8 * 2 * sizeof(float), 256);
-        p.ws_o = (float *)w;
-    }
+    p.k_scale = nullptr;
+    p.v_scale = nullptr;
+    if (int rc = decode_bind_workspace(p, B, D, workspace, workspace_bytes)) return rc;
     if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B) : launch_decode<__nv_bfloat16, 128>(st, p, B);
     return D == 64 ? launch_decode<__half, 64>(st, p, B) : launch_decode<__half, 128>(st, p, B);
 }
@@ -519,6 +393,8 @@ extern "C" int mynn_b200_attention_decode_noalloc(void *stream, void *out, const
     p.cache_seq = cache_seq_len;
     p.active_host = active_seq_kv;
     p.active_dev = active_seq_kv_dev;
+    p.k_scale = nullptr;
+    p.v_scale = nullptr;
     const int rows_bound = active_seq_kv_dev ? cache_seq_len : (active_seq_kv < cache_seq_len ? active_seq_kv : cache_seq_len);
     p.splits = decode_splits(B, Hkv, rows_bound);
     p.ws_o = nullptr;

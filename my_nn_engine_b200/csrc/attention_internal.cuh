@@ -1,0 +1,163 @@
+// Pieces shared by the decode-attention kernels (16-bit KV cache and int8 KV cache): launch parameters, the
+// mma.m16n8k16 wrappers, the split of the kv rows over CTAs and the tail that merges warps and splits.
+#pragma once
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace mynn {
+
+constexpr int kAttnWarps = 4;
+constexpr int kMaxSplits = 64;
+constexpr int kAttnCtasPerSm = 4;  // resident CTAs per SM the kernels are built for (<= 128 registers, 17 KB smem)
+
+__device__ __forceinline__ uint4 ldg_16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_8(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void mma_kv(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    if constexpr (std::is_same<T, __half>::value) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// pack hi parts of (x, y) into one 32-bit register and the rounding remainders into another
+template <typename T>
+__device__ __forceinline__ void split_pack(float x, float y, uint32_t &hi, uint32_t &lo) {
+    const T xh = from_f32<T>(x), yh = from_f32<T>(y);
+    const T xl = from_f32<T>(x - to_f32<T>(xh)), yl = from_f32<T>(y - to_f32<T>(yh));
+    hi = (uint32_t)reinterpret_cast<const uint16_t &>(xh) | ((uint32_t)reinterpret_cast<const uint16_t &>(yh) << 16);
+    lo = (uint32_t)reinterpret_cast<const uint16_t &>(xl) | ((uint32_t)reinterpret_cast<const uint16_t &>(yl) << 16);
+}
+
+struct DecodeParams {
+    void *out;
+    const void *q, *k, *v;
+    const void *k_scale, *v_scale;  // int8 cache only: one scale per (batch, kv head, row), storage dtype
+    float scale;
+    int Hq, Hkv, G, cache_seq;
+    int active_host;
+    const int32_t *active_dev;
+    int splits;
+    float *ws_o;          // [B*Hkv][splits][8][D]
+    float *ws_ml;         // [B*Hkv][splits][8][2]
+    unsigned *ws_ticket;  // [B*Hkv], zero before first use; the combining CTA re-zeroes it
+};
+
+// Tail of a decode CTA.  Every lane holds NACC accumulator tiles of O^T: tile i, registers {0,1,2,3} are
+// (head 2t, d), (head 2t+1, d), (head 2t, d+1), (head 2t+1, d+1) with d = DMap::d(i, g).  The warps are merged through
+// shared memory; with more than one split the partial result goes to the workspace and the last CTA of the
+// (batch, kv head) pair to arrive (atomic ticket, no spinning) combines the splits and writes the output.
+template <typename T, int D, int NACC, typename DMap>
+__device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (&o)[NACC][4], float m_run, float l_run) {
+    __shared__ float sm_o[kAttnWarps][8][D];
+    __shared__ float sm_m[kAttnWarps][8], sm_l[kAttnWarps][8];
+    __shared__ unsigned sm_last;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int G = p.G;
+
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (t == 0) {
+        sm_m[warp][g] = m_run;
+        sm_l[warp][g] = l_run;
+    }
+#pragma unroll
+    for (int i = 0; i < NACC; i++) {
+        const int d = DMap::d(i, g);
+        sm_o[warp][2 * t][d] = o[i][0];
+        sm_o[warp][2 * t + 1][d] = o[i][1];
+        sm_o[warp][2 * t][d + 1] = o[i][2];
+        sm_o[warp][2 * t + 1][d + 1] = o[i][3];
+    }
+    __syncthreads();
+
+    const size_t pair = (size_t)b * p.Hkv + kvh;
+    T *outp = reinterpret_cast<T *>(p.out) + (size_t)(b * p.Hq + kvh * G) * D;
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+        const int hd = idx / D, d = idx - hd * D;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; w++) mx = fmaxf(mx, sm_m[w][hd]);
+        float L = 0.f, O = 0.f;
+        if (mx > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < kAttnWarps; w++) {
+                const float f = __expf(sm_m[w][hd] - mx);
+                L += sm_l[w][hd] * f;
+                O += sm_o[w][hd][d] * f;
+            }
+        }
+        if (p.splits == 1) {
+            outp[(size_t)hd * D + d] = from_f32<T>(O / L);
+        } else {
+            const size_t slot = (pair * p.splits + split) * 8 + hd;
+            p.ws_o[slot * D + d] = O;
+            if (d == 0) {
+                p.ws_ml[slot * 2] = mx;
+                p.ws_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+    if (p.splits == 1) return;
+
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) sm_last = (atomicAdd(&p.ws_ticket[pair], 1u) == (unsigned)(p.splits - 1)) ? 1u : 0u;
+    __syncthreads();
+    if (!sm_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+        const int hd = idx / D, d = idx - hd * D;
+        float mx = -INFINITY;
+        for (int sp = 0; sp < p.splits; sp++) mx = fmaxf(mx, __ldcg(&p.ws_ml[((pair * p.splits + sp) * 8 + hd) * 2]));
+        float L = 0.f, O = 0.f;
+        for (int sp = 0; sp < p.splits; sp++) {
+            const size_t slot = (pair * p.splits + sp) * 8 + hd;
+            const float ms = __ldcg(&p.ws_ml[slot * 2]);
+            if (ms == -INFINITY) continue;
+            const float f = __expf(ms - mx);
+            L += __ldcg(&p.ws_ml[slot * 2 + 1]) * f;
+            O += __ldcg(&p.ws_o[slot * D + d]) * f;
+        }
+        outp[(size_t)hd * D + d] = from_f32<T>(O / L);
+    }
+    if (threadIdx.x == 0) p.ws_ticket[pair] = 0u;
+}
+
+// All CTAs of a launch last equally long, so the grid should fit in ONE wave of resident CTAs (148 SMs): a partly
+// filled second wave would cost as much time as a full one.
+inline int decode_splits(int B, int Hkv, int rows_bound, int tile_rows = 16) {
+    const int pairs = B * Hkv;
+    int s = (kAttnCtasPerSm * 148) / pairs;
+    const int cap = rows_bound / (tile_rows * kAttnWarps);  // at least one tile per warp and split
+    if (s > cap) s = cap;
+    if (s < 1) s = 1;
+    if (s > kMaxSplits) s = kMaxSplits;
+    return s;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Splits `workspace` into the ticket / (max, sum) / partial-output areas of a decode launch; fails if it is too small.
+int decode_bind_workspace(DecodeParams &p, int B, int D, void *workspace, size_t workspace_bytes);
+
+}  // namespace mynn

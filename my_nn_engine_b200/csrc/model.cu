@@ -32,6 +32,7 @@ struct LayerW {
     const int8_t *wq, *wk, *wv, *wo, *wg, *wu, *wd;
     const void *sq, *sk, *sv, *so, *sg, *su, *sd;
     void *kc, *vc;
+    void *ksc, *vsc;  // per-token scales of an int8 cache
     bool qkv_fused, gu_fused;
 };
 
@@ -159,10 +160,17 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
             kb = k_;
             vb = v_;
         }
-        RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
-                                 S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
-        RC(launch_attention(st, m.attn, m.q_rot, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
-                            c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
+        if (c.kv_int8) {
+            RC(launch_rope_kv_append_q8(st, dt, m.q_rot, L.kc, L.vc, L.ksc, L.vsc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
+                                        S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
+            RC(launch_attention_q8(st, m.attn, m.q_rot, L.kc, L.vc, L.ksc, L.vsc, attn_scale, B, m.Hq, m.Hkv, S, D,
+                                   c.max_seq_len, c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
+        } else {
+            RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
+                                     S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
+            RC(launch_attention(st, m.attn, m.q_rot, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
+                                c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
+        }
         if (tp == 1) {
             RC(gemm(st, m, m.x, m.attn, L.wo, L.so, m.x, M, H, Nq, dt));  // x = round(x + round(o))
             RC(norm(L.ln2, nullptr, M, m.x));
@@ -271,8 +279,15 @@ static int model_create(Model **out, void **initializer, void **session_state) {
         L.wg = (const int8_t *)initializer[i++]; L.sg = initializer[i++];
         L.wu = (const int8_t *)initializer[i++]; L.su = initializer[i++];
         L.wd = (const int8_t *)initializer[i++]; L.sd = initializer[i++];
-        L.kc = session_state[2 * l];
-        L.vc = session_state[2 * l + 1];
+        const int per_layer = c.kv_int8 ? 4 : 2;
+        L.kc = session_state[per_layer * l];
+        L.vc = session_state[per_layer * l + 1];
+        L.ksc = c.kv_int8 ? session_state[4 * l + 2] : nullptr;
+        L.vsc = c.kv_int8 ? session_state[4 * l + 3] : nullptr;
+        if (!L.kc || !L.vc || (c.kv_int8 && (!L.ksc || !L.vsc))) {
+            delete m;
+            return fail(MYNN_E_ARG, "model_init: a KV buffer of layer %d is null", l);
+        }
         const size_t nq = (size_t)m->Hq * D, nkv = (size_t)m->Hkv * D;
         L.qkv_fused = L.wk == L.wq + nq * H && L.wv == L.wk + nkv * H &&
                       (const char *)L.sk == (const char *)L.sq + nq * esz &&

@@ -15,6 +15,20 @@ int launch_rope_kv_append(cudaStream_t st, int dtype, void *q_out, void *k_cache
                           const void *cos_t, const void *sin_t, const int64_t *positions, int B, int S, int Hq,
                           int Hkv, int D, int cache_seq, const int32_t *past_len_dev);
 
+// The same step for an int8 KV cache: K (after RoPE and its store rounding) and V are quantized per token into
+// k_cache/v_cache int8 [B, Hkv, cache_seq, D] with their scales [B, Hkv, cache_seq] in the storage dtype.
+int launch_rope_kv_append_q8(cudaStream_t st, int dtype, void *q_out, void *k_cache, void *v_cache, void *k_scale,
+                             void *v_scale, const void *q, const void *k, const void *v, long long q_stride,
+                             long long k_stride, long long v_stride, const void *cos_t, const void *sin_t,
+                             const int64_t *positions, int B, int S, int Hq, int Hkv, int D, int cache_seq,
+                             const int32_t *past_len_dev);
+
+// Attention over an int8 KV cache (per-token scales), with the output-layout choice of launch_attention.
+int launch_attention_q8(cudaStream_t st, void *out, const void *q, const void *k, const void *v, const void *k_scale,
+                        const void *v_scale, float scale, int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len,
+                        int active_seq_kv, const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
+                        size_t workspace_bytes, int out_bshd);
+
 // out[m, f] = swish(gate[m, f]) * up[m, f] with gate/up rows `in_stride` elements apart.
 int launch_swiglu_strided(cudaStream_t st, int dtype, void *out, const void *gate, const void *up, int M, int F,
                           long long in_stride);

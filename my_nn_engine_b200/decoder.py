@@ -75,7 +75,8 @@ class DecoderModel:
 
     def __init__(self, cfg: dict, state: dict, dtype: str = "bf16", max_seq_len: int = 256, batch: int = 1,
                  tp_rank: int = 0, tp_world: int = 1, output: str = "logits", use_graph: bool = True,
-                 max_prefill: int = 0, device=None, tensor_gemm: bool = True, tp_fused: bool = True):
+                 max_prefill: int = 0, device=None, tensor_gemm: bool = True, tp_fused: bool = True,
+                 kv_int8: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("DecoderModel needs a CUDA device: the decode path has no CPU implementation")
         self.lib = ffi.lib()
@@ -151,16 +152,24 @@ class DecoderModel:
 
         # KV SessionState buffers: zero-initialised, owned here, persistent across steps
         kv_shape = (batch, self.n_kv // G, max_seq_len, self.head_dim)
-        self.k_cache = [torch.zeros(kv_shape, dtype=td, device=dev) for _ in range(self.n_layers)]
-        self.v_cache = [torch.zeros(kv_shape, dtype=td, device=dev) for _ in range(self.n_layers)]
+        # kv_int8 (the engine's quant_kv_cache build option): int8 caches plus one scale per cached token
+        self.kv_int8 = bool(kv_int8)
+        cache_dt = torch.int8 if kv_int8 else td
+        self.k_cache = [torch.zeros(kv_shape, dtype=cache_dt, device=dev) for _ in range(self.n_layers)]
+        self.v_cache = [torch.zeros(kv_shape, dtype=cache_dt, device=dev) for _ in range(self.n_layers)]
+        self.k_scale = [torch.zeros(kv_shape[:3], dtype=td, device=dev) for _ in range(self.n_layers if kv_int8 else 0)]
+        self.v_scale = [torch.zeros(kv_shape[:3], dtype=td, device=dev) for _ in range(self.n_layers if kv_int8 else 0)]
         states = []
-        for kc, vc in zip(self.k_cache, self.v_cache):
+        for l, (kc, vc) in enumerate(zip(self.k_cache, self.v_cache)):
             states += [kc.data_ptr(), vc.data_ptr()]
+            if kv_int8:
+                states += [self.k_scale[l].data_ptr(), self.v_scale[l].data_ptr()]
 
         c = ffi.ModelConfig(n_layers=self.n_layers, hidden=h, n_heads=self.n_heads, n_kv_heads=self.n_kv,
                             head_dim=self.head_dim, ffn=self.ffn, vocab=self.vocab, max_seq_len=max_seq_len, batch=batch,
                             dtype=_FFI_DT[dtype], output_mode=1 if output == "ids" else 0, tp_rank=r, tp_world=G,
                             use_graph=int(use_graph), max_prefill=max_prefill, use_tensor_gemm=int(tensor_gemm),
+                            kv_int8=int(kv_int8),
                             rms_eps=cfg["rms_norm_eps"])
         ffi.check(self.lib.mynn_b200_model_configure(ctypes.byref(c)))
         self._init_arr = (ctypes.c_void_p * len(init))(*init)
@@ -220,7 +229,7 @@ class DecoderModel:
                                                        past_len, None if out_dev is None else out_dev.data_ptr()))
 
     def reset_cache(self):
-        for t in self.k_cache + self.v_cache:
+        for t in self.k_cache + self.v_cache + self.k_scale + self.v_scale:
             t.zero_()
 
     def weight_bytes(self) -> int:

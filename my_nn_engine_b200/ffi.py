@@ -28,7 +28,7 @@ class ModelConfig(ctypes.Structure):
 
     _fields_ = [(n, c_int32) for n in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab",
                                        "max_seq_len", "batch", "dtype", "output_mode", "tp_rank", "tp_world",
-                                       "use_graph", "max_prefill", "use_tensor_gemm")] + [("rms_eps", c_float)]
+                                       "use_graph", "max_prefill", "use_tensor_gemm", "kv_int8")] + [("rms_eps", c_float)]
 
 
 # name -> (restype, argtypes); every symbol declared in include/mynn_b200.h
@@ -45,6 +45,8 @@ SIGNATURES = {
     "mynn_b200_attention_decode_noalloc_max_bytes": (c_size_t, []),
     "mynn_b200_attention_decode_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int]),
     "mynn_b200_kv_cache_update": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int]),
+    "mynn_b200_quantizing_kv_cache_update": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int]),
+    "mynn_b200_attention_q8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_size_t]),
     "mynn_b200_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int]),
     "mynn_b200_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int]),
     "mynn_b200_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int]),

@@ -89,19 +89,28 @@ def gemm(m, n, k, dtype="bf16", ksplit=0, copies=None, quiet=False, kernel="tcge
     return res
 
 
-def attn(b, hq, hkv, d, length, dtype="bf16", copies=None, quiet=False):
+def attn(b, hq, hkv, d, length, dtype="bf16", copies=None, quiet=False, kv="16bit"):
+    """Decode attention; kv="int8" times the kernel for the int8 cache (bytes: int8 rows + one scale per row)."""
     td = _DT[dtype]
-    kv_bytes = 2 * b * hkv * length * d * 2
+    q8 = kv == "int8"
+    kv_bytes = 2 * b * hkv * length * (d + 2) if q8 else 2 * b * hkv * length * d * 2
     copies = copies or max(3, int(600e6 // kv_bytes) + 1)
-    ks = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(copies)]
-    vs = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(copies)]
     q = torch.randn(b, hq, 1, d, device="cuda").to(td)
     out = torch.empty_like(q)
     ws = ops.attention_workspace(b, hq, hkv, d, length, q.device)
-    us = _time_graph([(lambda k=k, v=v: ops.attention(q, k, v, 1 / np.sqrt(d), length, out=out, workspace=ws))
-                      for k, v in zip(ks, vs)])
+    if q8:
+        ks = [torch.randint(-127, 128, (b, hkv, length, d), device="cuda", dtype=torch.int8) for _ in range(copies)]
+        vs = [torch.randint(-127, 128, (b, hkv, length, d), device="cuda", dtype=torch.int8) for _ in range(copies)]
+        sc = [(torch.rand(b, hkv, length, device="cuda") * 0.02 + 0.005).to(td) for _ in range(copies)]
+        us = _time_graph([(lambda k=k, v=v, s=s: ops.attention_q8(q, k, v, s, s, 1 / np.sqrt(d), length, out=out, workspace=ws))
+                          for k, v, s in zip(ks, vs, sc)])
+    else:
+        ks = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(copies)]
+        vs = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(copies)]
+        us = _time_graph([(lambda k=k, v=v: ops.attention(q, k, v, 1 / np.sqrt(d), length, out=out, workspace=ws))
+                          for k, v in zip(ks, vs)])
     alg = kv_bytes + 2 * q.numel() * 2
-    res = {"kernel": "attention_decode", "b": b, "hq": hq, "hkv": hkv, "d": d, "len": length, "dtype": dtype, "us": us,
+    res = {"kernel": "attention_decode_q8" if q8 else "attention_decode", "b": b, "hq": hq, "hkv": hkv, "d": d, "len": length, "dtype": dtype, "us": us,
            "GBps": alg / us / 1e3, "frac_of_measured_peak": alg / us / 1e3 / _peak(), "algorithmic_bytes": alg}
     if not quiet:
         print(json.dumps(res), flush=True)
@@ -140,12 +149,13 @@ def main():
     a.add_argument("--len", type=int, default=4096)
     a.add_argument("--dtype", default="bf16")
     a.add_argument("--copies", type=int, default=None)
+    a.add_argument("--kv", default="16bit", choices=["16bit", "int8"])
     sub.add_parser("suite")
     args = ap.parse_args()
     if args.cmd == "gemm":
         gemm(args.m, args.n, args.k, args.dtype, args.ksplit, args.copies, kernel=args.kernel)
     elif args.cmd == "attn":
-        attn(args.b, args.hq, args.hkv, args.d, args.len, args.dtype, args.copies)
+        attn(args.b, args.hq, args.hkv, args.d, args.len, args.dtype, args.copies, kv=args.kv)
     else:
         suite()
 

@@ -139,6 +139,51 @@ def kv_cache_update(cache, new, offset):
     return cache
 
 
+def quantizing_kv_cache_update(cache, scale, new, offset):
+    """``QuantizingKVCacheUpdate``: quantize new[b,h,t,:] to int8 with one scale per token and write both into the
+    int8 cache [B,H,S,D] / scale [B,H,S] (dtype of ``new``) in place; offset int or int32 CUDA tensor."""
+    if cache.dtype != torch.int8:
+        raise TypeError("cache must be int8")
+    if scale.dtype != new.dtype:
+        raise TypeError("scale and new rows must share a dtype")
+    bh = cache.shape[0] * cache.shape[1]
+    dev_ptr, host_val = None, 0
+    if isinstance(offset, torch.Tensor):
+        dev_ptr = _ptr(offset)
+    else:
+        host_val = int(offset)
+    ffi.check(ffi.lib().mynn_b200_quantizing_kv_cache_update(_stream(), _ptr(cache), _ptr(scale), _ptr(new), bh,
+                                                             cache.shape[2], new.shape[2], cache.shape[3], host_val,
+                                                             dev_ptr, _dt(new)))
+    return cache, scale
+
+
+def attention_q8(q, k, v, k_scale, v_scale, scale: float, active_seq_kv=None, is_causal: bool = False, out=None,
+                 workspace=None):
+    """``Attention`` over an int8 KV cache: k, v int8 [B,Hkv,S,D], k_scale/v_scale [B,Hkv,S] in q's dtype."""
+    b, hq, sq, d = q.shape
+    hkv, sk = k.shape[1], k.shape[2]
+    if k.dtype != torch.int8 or v.dtype != torch.int8:
+        raise TypeError("k and v must be int8")
+    if k_scale.dtype != q.dtype or v_scale.dtype != q.dtype:
+        raise TypeError("scales must have the dtype of q")
+    if out is None:
+        out = torch.empty_like(q)
+    dev_ptr, host_val = None, sk
+    if isinstance(active_seq_kv, torch.Tensor):
+        if active_seq_kv.dtype != torch.int32:
+            raise TypeError("device active_seq_kv must be int32")
+        dev_ptr = _ptr(active_seq_kv)
+    elif active_seq_kv is not None:
+        host_val = int(active_seq_kv)
+    if workspace is None:
+        workspace = attention_workspace(b, hq, hkv, d, sk, q.device)
+    ffi.check(ffi.lib().mynn_b200_attention_q8(_stream(), _ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(k_scale),
+                                               _ptr(v_scale), float(scale), b, hq, hkv, sq, d, sk, host_val, dev_ptr,
+                                               int(is_causal), _dt(q), _ptr(workspace), workspace.numel()))
+    return out
+
+
 def rms_norm(x, weight, eps: float, out=None):
     d = x.shape[-1]
     if out is None:

@@ -42,8 +42,12 @@ class OracleLlama:
     """weights: dict of HF tensor names -> float array, or name -> int8 with name+'.scale' -> f32 array
     whose values are already representable in the storage dtype."""
 
-    def __init__(self, cfg: LlamaConfig, weights: dict, dtype: str, max_seq_len: int, batch: int = 1):
+    def __init__(self, cfg: LlamaConfig, weights: dict, dtype: str, max_seq_len: int, batch: int = 1,
+                 kv_int8: bool = False):
+        """kv_int8: the engine's ``quant_kv_cache`` build option (crates/llm/src/decoder.rs:405-470): int8 caches with
+        one scale per cached token, written by QuantizingKVCacheUpdate and read by the attention's scale operands."""
         self.cfg, self.dtype, self.max_seq, self.batch = cfg, dtype, max_seq_len, batch
+        self.kv_int8 = kv_int8
         self.w = {}
         for name, arr in weights.items():
             if name.endswith(".scale"):
@@ -54,8 +58,11 @@ class OracleLlama:
                 self.w[name] = ("f", R.store_round(np.asarray(arr, dtype=np.float32), dtype), None)
         self.cos, self.sin = R.rope_table(max_seq_len, cfg.head_dim, cfg.rope_theta, dtype)
         shape = (batch, cfg.n_kv_heads, max_seq_len, cfg.head_dim)
-        self.k_cache = [np.zeros(shape, dtype=np.float32) for _ in range(cfg.n_layers)]
-        self.v_cache = [np.zeros(shape, dtype=np.float32) for _ in range(cfg.n_layers)]
+        cdt = np.int8 if kv_int8 else np.float32
+        self.k_cache = [np.zeros(shape, dtype=cdt) for _ in range(cfg.n_layers)]
+        self.v_cache = [np.zeros(shape, dtype=cdt) for _ in range(cfg.n_layers)]
+        self.k_scale = [np.zeros(shape[:3], dtype=np.float32) for _ in range(cfg.n_layers)]
+        self.v_scale = [np.zeros(shape[:3], dtype=np.float32) for _ in range(cfg.n_layers)]
         self.past_len = 0
 
     def _st(self, x):
@@ -95,9 +102,15 @@ class OracleLlama:
             v = self._linear(n1, p + "self_attn.v_proj.weight").reshape(b, s, c.n_kv_heads, c.head_dim).transpose(0, 2, 1, 3)
             q = self._st(R.rope(q, cos_r, sin_r))
             k = self._st(R.rope(k, cos_r, sin_r))
-            R.kv_cache_update(self.k_cache[l], k, past_len)
-            R.kv_cache_update(self.v_cache[l], v, past_len)
-            a = self._st(R.attention(q, self.k_cache[l], self.v_cache[l], scale, active, is_causal=is_prefill))
+            if self.kv_int8:
+                R.quantizing_kv_cache_update(self.k_cache[l], self.k_scale[l], k, past_len, self.dtype)
+                R.quantizing_kv_cache_update(self.v_cache[l], self.v_scale[l], v, past_len, self.dtype)
+                a = self._st(R.attention(q, self.k_cache[l], self.v_cache[l], scale, active, is_causal=is_prefill,
+                                         k_scale=self.k_scale[l], v_scale=self.v_scale[l]))
+            else:
+                R.kv_cache_update(self.k_cache[l], k, past_len)
+                R.kv_cache_update(self.v_cache[l], v, past_len)
+                a = self._st(R.attention(q, self.k_cache[l], self.v_cache[l], scale, active, is_causal=is_prefill))
             a = a.transpose(0, 2, 1, 3).reshape(b, s, c.n_heads * c.head_dim)
             o = self._linear(a, p + "self_attn.o_proj.weight")
             x = self._st(x + o)

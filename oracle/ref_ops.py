@@ -197,6 +197,25 @@ def kv_cache_update(cache: np.ndarray, new: np.ndarray, offset: int) -> np.ndarr
     return cache
 
 
+def quantizing_kv_cache_update(cache: np.ndarray, scale: np.ndarray, new: np.ndarray, offset: int, scale_dtype: str = "bf16"):
+    """INT8 KV cache append with one scale per token (src/codegen/cpu/translator.rs:4090-4372):
+    s = max_d |new| * (1/127) in f32; inv = 127 / max (0 for an all-zero row); q = trunc(v * inv +- 0.5) clamped to
+    [-128, 127]; cache[b,h,offset+t,:] = q, scale[b,h,offset+t] = s stored in the scale dtype.  In place.
+    cache int8 [B,H,S,D]; scale f32 values [B,H,S]; new f32 values [B,H,T,D]."""
+    new = np.asarray(new, dtype=np.float32)
+    t = new.shape[2]
+    max_abs = np.abs(new).max(axis=-1)
+    s = (max_abs * np.float32(1.0 / 127.0)).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        inv = np.where(max_abs == 0, np.float32(0), np.float32(127.0) / max_abs).astype(np.float32)
+    scaled = (new * inv[..., None]).astype(np.float32)
+    biased = scaled + np.where(scaled >= 0, np.float32(0.5), np.float32(-0.5))
+    q = np.clip(np.trunc(biased).astype(np.int64), -128, 127).astype(np.int8)
+    cache[:, :, offset:offset + t, :] = q
+    scale[:, :, offset:offset + t] = store_round(s, scale_dtype)
+    return cache, scale
+
+
 # --------------------------------------------------------------------------------------
 # glue ops
 # --------------------------------------------------------------------------------------

@@ -27,12 +27,12 @@ def to_oracle_weights(state, dtype):
     return out
 
 
-def run_parity(cfg, state, dtype, batch, steps, max_seq, prompt_len, prefill_len, seed, use_graph=True):
+def run_parity(cfg, state, dtype, batch, steps, max_seq, prompt_len, prefill_len, seed, use_graph=True, kv_int8=False):
     from my_nn_engine_b200.decoder import DecoderModel
     rng = np.random.default_rng(seed)
-    oracle = OracleLlama(LlamaConfig.from_hf(cfg), to_oracle_weights(state, dtype), dtype, max_seq, batch)
+    oracle = OracleLlama(LlamaConfig.from_hf(cfg), to_oracle_weights(state, dtype), dtype, max_seq, batch, kv_int8=kv_int8)
     model = DecoderModel(cfg, state, dtype=dtype, max_seq_len=max_seq, batch=batch, output="logits",
-                         use_graph=use_graph, max_prefill=prefill_len or 0)
+                         use_graph=use_graph, max_prefill=prefill_len or 0, kv_int8=kv_int8)
     prompt = rng.integers(0, cfg["vocab_size"], size=(batch, prompt_len))
     ulp = {"bf16": 2.0 ** -7, "f16": 2.0 ** -10, "f32": 2.0 ** -20}[dtype]
     worst, flips = 0.0, 0
@@ -70,7 +70,15 @@ def run_parity(cfg, state, dtype, batch, steps, max_seq, prompt_len, prefill_len
         tok = nxt
     # KV caches: the device rows equal the oracle's (rounded) rows, rows past the sequence are still zero
     kc = model.k_cache[0].float().cpu().numpy()
-    assert np.abs(kc[:, :, :past] - oracle.k_cache[0][:, :, :past]).max() <= 8 * ulp * np.abs(oracle.k_cache[0]).max()
+    if kv_int8:
+        # int8 rows with their scales: equal to the oracle's up to one quantisation step where the inputs differed by an ulp
+        ks = model.k_scale[0].float().cpu().numpy()
+        assert np.abs(ks[:, :, :past] - oracle.k_scale[0][:, :, :past]).max() <= 8 * ulp * oracle.k_scale[0].max()
+        deq, want = kc * ks[..., None], oracle.k_cache[0].astype(np.float32) * oracle.k_scale[0][..., None]
+        assert np.abs(deq[:, :, :past] - want[:, :, :past]).max() <= 1.5 * oracle.k_scale[0].max() + 8 * ulp * np.abs(want).max()
+        assert not ks[:, :, past:].any()
+    else:
+        assert np.abs(kc[:, :, :past] - oracle.k_cache[0][:, :, :past]).max() <= 8 * ulp * np.abs(oracle.k_cache[0]).max()
     assert not kc[:, :, past:].any()
     model.close()
     assert worst <= {"bf16": 3e-2, "f16": 1e-2, "f32": 1e-4}[dtype], worst
@@ -100,6 +108,33 @@ def test_mid_size_model_32_greedy_steps(dtype, batch, prefill_len, use_graph):
     worst, flips = run_parity(MID, state, dtype, batch, steps=32, max_seq=96, prompt_len=24, prefill_len=prefill_len,
                               seed=batch, use_graph=use_graph)
     assert flips <= batch  # near-ties explained above are rare
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_int8_kv_cache_tiny_model(tiny_llama, dtype):
+    """quant_kv_cache on the 2-layer fixture model (head_dim 4: generic attention over the int8 cache)."""
+    from my_nn_engine_b200.quantize import quantize_state_dict
+    cfg, weights, _, _, _ = tiny_llama
+    state = quantize_state_dict({k: torch.from_numpy(v) for k, v in weights.items()})
+    run_parity(cfg, state, dtype, batch=1, steps=8, max_seq=32, prompt_len=1, prefill_len=None, seed=0, kv_int8=True)
+    run_parity(cfg, state, dtype, batch=2, steps=4, max_seq=32, prompt_len=6, prefill_len=4, seed=1, kv_int8=True)
+
+
+@pytest.mark.parametrize("dtype,batch,prefill_len,use_graph", [("bf16", 1, None, True), ("bf16", 4, 8, True), ("f16", 2, None, False)])
+def test_int8_kv_cache_mid_size_model(dtype, batch, prefill_len, use_graph):
+    from my_nn_engine_b200.quantize import random_llama_state
+    state = random_llama_state(MID, seed=3)
+    worst, flips = run_parity(MID, state, dtype, batch, steps=32, max_seq=96, prompt_len=24, prefill_len=prefill_len,
+                              seed=batch, use_graph=use_graph, kv_int8=True)
+    assert flips <= batch
+
+
+def test_int8_kv_cache_llama3_8b_shapes_batch32():
+    from my_nn_engine_b200.quantize import random_llama_state
+    cfg = dict(hidden_size=4096, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=14336, vocab_size=4096, rms_norm_eps=1e-5, rope_theta=500000.0)
+    state = random_llama_state(cfg, seed=5)
+    run_parity(cfg, state, "bf16", batch=32, steps=3, max_seq=96, prompt_len=70, prefill_len=35, seed=9, kv_int8=True)
 
 
 def test_llama3_8b_shapes_two_layer_slice_batch32():

@@ -65,6 +65,31 @@ def test_kv_cache_update_golden(single_op):
     assert np.array_equal(upd, upd_c)
 
 
+def test_quantizing_kvcache_update_golden(single_op):
+    """Exact int8 match required by the reference (tests/single_op.rs:1233-1244)."""
+    fx = single_op("quantizing_kvcache_update")
+    cache, scale, new, offset = fx.inputs
+    c, s = R.quantizing_kv_cache_update(cache.copy(), R.bf16_bits_to_f32(scale).copy(), R.bf16_bits_to_f32(new), int(offset))
+    assert np.array_equal(c, fx.outputs[0])
+    assert s[:, :, int(offset):int(offset) + new.shape[2]].all() and not s[:, :, :int(offset)].any()
+
+
+def test_attention_with_int8_kv_matches_dequantised_attention():
+    """Attention over an int8 cache with per-token scales == attention over the dequantised cache (the scales enter
+    as qk * k_scale and e * v_scale, src/codegen/cpu/translator.rs:4440-5008)."""
+    rng = np.random.default_rng(2)
+    k = rng.standard_normal((2, 2, 12, 16)).astype(np.float32)
+    v = rng.standard_normal((2, 2, 12, 16)).astype(np.float32)
+    q = rng.standard_normal((2, 4, 1, 16)).astype(np.float32)
+    kc, ks = np.zeros((2, 2, 12, 16), np.int8), np.zeros((2, 2, 12), np.float32)
+    vc, vs = np.zeros((2, 2, 12, 16), np.int8), np.zeros((2, 2, 12), np.float32)
+    R.quantizing_kv_cache_update(kc, ks, k, 0)
+    R.quantizing_kv_cache_update(vc, vs, v, 0)
+    got = R.attention(q, kc, vc, 0.25, 9, k_scale=ks, v_scale=vs)
+    want = R.attention(q, kc.astype(np.float32) * ks[..., None], vc.astype(np.float32) * vs[..., None], 0.25, 9)
+    assert np.abs(got - want).max() < 1e-5
+
+
 def test_dequantize_linear_golden(single_op):
     fx = single_op("dequantize_linear")
     x, scale = fx.inputs
