@@ -220,8 +220,9 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         return (long long)(int)a3[2] * 65536 + (long long)(int)a3[1] * 256 + (long long)(int)a3[0];
     };
     auto finish = [&](int m, long long sum, float resv) {
-        float v = (float)sum * sh_ascale[m] * wscale;
-        if (resid_p) v = round_store<OutT>(v) + resv;
+        // separate roundings (no fused multiply-add), so that every kernel of this operator gives the same bits
+        float v = __fmul_rn(__fmul_rn((float)sum, sh_ascale[m]), wscale);
+        if (resid_p) v = __fadd_rn(round_store<OutT>(v), resv);
         out_p[(size_t)m * p.N + n_own] = from_f32<OutT>(v);
     };
 
