@@ -131,6 +131,26 @@ int mynn_b200_attention_q8(void *stream, void *out, const void *q, const int8_t 
                            int active_seq_kv, const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
                            size_t workspace_bytes);
 
+/* DynamicQuantizeLinear (the engine's W8A8 path, src/graph/operator.rs:265-285): x [slices, inner] in `dtype` ->
+ * y (int8 when symmetric, uint8 otherwise), y_scale (`dtype`) and y_zero_point (type of y); per_row = 1 gives one scale
+ * per slice, per_row = 0 one scale for the whole tensor (outputs of 1 element).
+ * Replaces: dynamic_quantize_linear_kernel (cpp/dynamic_quantize_linear.cuh:41-151) and, for the symmetric per-row form,
+ * the CPU kernel mynn_dynquant_i8 (src/codegen/cpu/kernels/dynquant_i8.rs:13-37) whose rounding it reproduces. */
+int mynn_b200_dynamic_quantize_linear(void *stream, void *y, void *y_scale, void *y_zero_point, const void *x,
+                                      long long slices, long long inner, int symmetric, int per_row, int dtype);
+
+/* QuantizedMatMul: out[m,n] = (sum_k lhs[m,k] * rhs[n,k] in int32) * lhs_scale[m or 0] * rhs_scale[n]; lhs int8 [M,K],
+ * rhs int8 [N,K], scales and out in `dtype` (src/graph/operator.rs:243-263).
+ * Replaces: quantized_gemv_int8 / quantized_matmul_int8 (cpp/quantized_gemv_int8.cuh, cpp/quantized_matmul_int8.cuh) and
+ * mynn_qgemv_i8i8 (src/codegen/cpu/kernels/qgemv_i8i8.rs:38-80).
+ * With a workspace (mynn_b200_quantized_matmul_workspace_bytes, 256-byte aligned, zeroed once; holds a status word that
+ * mynn_b200_dequant_matmul_check reads), K % 16 == 0 and 16-byte aligned operands the product runs on the tcgen05 int8
+ * tensor-core kernel; otherwise (workspace NULL included) on a plain kernel. */
+size_t mynn_b200_quantized_matmul_workspace_bytes(int M, int N, int K);
+int mynn_b200_quantized_matmul(void *stream, void *out, const int8_t *lhs, const void *lhs_scale, int lhs_scale_per_row,
+                               const int8_t *rhs, const void *rhs_scale, int M, int N, int K, int dtype, void *workspace,
+                               size_t workspace_bytes);
+
 /* RMSNorm over the last axis: y = x * rsqrt(mean(x^2) + eps) * w.  Replaces rms_norm (cpp/rms_norm.cuh:9-59). */
 int mynn_b200_rms_norm(void *stream, void *out, const void *x, const void *weight, float eps, int rows, int D,
                        int dtype);

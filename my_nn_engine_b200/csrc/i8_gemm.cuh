@@ -29,6 +29,11 @@ size_t i8_prefill_workspace_bytes(int M, int K);
 bool i8_prefill_supported(int M, int N, int K, const void *wq, int act_dtype, int out_dtype);
 int i8_prefill_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
                       int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes);
+// QuantizedMatMul (int8 x int8, per-row or per-tensor lhs scale, per-channel rhs scale) on the same persistent kernel
+// with one accumulator column per lhs row.  workspace: 256 bytes holding the status word.
+bool i8_w8a8_supported(int M, int N, int K, const void *lhs, const void *rhs);
+int i8_w8a8_launch(cudaStream_t st, void *out, const int8_t *lhs, const void *lhs_scale, int lhs_scale_per_row, const int8_t *rhs,
+                   const void *rhs_scale, int M, int N, int K, int dtype, void *workspace, size_t workspace_bytes);
 extern int g_i8_split_override;
 extern unsigned long long *g_i8_timing;
 extern int g_i8_dbg;

@@ -21,8 +21,8 @@
 namespace mynn {
 
 constexpr int kPfRows = 128;      // weight rows per tile (UMMA M)
-constexpr int kPfTokens = 128;    // activation rows per tile
-constexpr int kPfCols = 2 * kPfTokens;  // limb columns per tile (UMMA N)
+constexpr int kPfCols = 256;      // accumulator columns per tile (UMMA N): LIMBS columns per activation row
+constexpr int kPfTokens = kPfCols / 2;  // activation rows per tile with two limbs (DequantMatMul)
 constexpr int kPfBlockK = 128;
 constexpr int kPfStages = 4;
 constexpr int kPfThreads = 192;
@@ -85,7 +85,9 @@ __global__ void __launch_bounds__(1024) act_to_limbs2_kernel(int8_t *limbs, floa
 struct PfParams {
     void *out;
     const void *scale, *resid;
-    const float *ascale;
+    const float *ascale;    // f32 row scales (DequantMatMul pre-pass), or null when ascale_t is used
+    const void *ascale_t;   // QuantizedMatMul: lhs scales in the output dtype, element m * ascale_stride
+    int ascale_stride;      // 1 = one scale per row, 0 = one scale for the whole tensor
     int M, N, K;
     int w_tiles, t_tiles;
     int *status;
@@ -107,7 +109,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 }
 
 // grid = min(#SMs, #tiles) persistent CTAs; tile index = w_tile * t_tiles + t_tile, walked with stride gridDim.x.
-template <typename OutT>
+// LIMBS = 2: DequantMatMul, limb rows (2m + l), 128 activation rows per tile.
+// LIMBS = 1: QuantizedMatMul (W8A8), the int8 lhs matrix itself is the operand, 256 activation rows per tile.
+template <typename OutT, int LIMBS>
 __global__ void __launch_bounds__(kPfThreads, 1)
 i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const PfParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -115,7 +119,8 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     __shared__ uint64_t full_bar[kPfStages], empty_bar[kPfStages], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ float sh_ascale[2][kPfTokens];
+    constexpr int kTok = kPfCols / LIMBS;  // activation rows per tile
+    __shared__ float sh_ascale[2][kTok];
     __shared__ int sh_go[2];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -169,11 +174,15 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kPfCols >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
             int kc = 0, it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
                 const int buf = it & 1, use = it >> 1;
+                // N of the MMA = the accumulator columns this tile really has (rows past M are zero-filled by TMA and
+                // need no tensor time), rounded up to the instruction's granularity of 16
+                const int tt_ = tile % p.t_tiles;
+                const int cols = min(kPfCols, (((p.M - tt_ * kTok) * LIMBS + 15) >> 4) << 4);
+                const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(cols >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
                 if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1, &abort_flag)) {  // epilogue has drained it
                     atomicExch(&abort_flag, 1);
                     atomicExch(p.status, 12);
@@ -211,9 +220,15 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, it++) {
             const int wt = tile / p.t_tiles, tt = tile - wt * p.t_tiles;
             const int buf = it & 1, use = it >> 1;
-            const int n = wt * kPfRows + r_local, tok0 = tt * kPfTokens;
+            const int n = wt * kPfRows + r_local, tok0 = tt * kTok;
             const float wscale = n < p.N ? to_f32<OutT>(scale_p[n]) : 0.f;
-            sh_ascale[buf][et] = tok0 + et < p.M ? p.ascale[tok0 + et] : 0.f;
+            for (int i = et; i < kTok; i += 128) {
+                float a = 0.f;
+                if (tok0 + i < p.M)
+                    a = p.ascale ? p.ascale[tok0 + i]
+                                 : to_f32<OutT>(reinterpret_cast<const OutT *>(p.ascale_t)[(size_t)(tok0 + i) * p.ascale_stride]);
+                sh_ascale[buf][i] = a;
+            }
             // one thread waits for the accumulator and publishes the verdict, so that all four warps take the same
             // branch (a warp leaving alone would strand the others at the named barrier)
             if (et == 0) {
@@ -228,18 +243,22 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             if (!sh_go[buf]) break;
             tc_fence_after();
 #pragma unroll 1
-            for (int c0 = 0; c0 < kPfCols; c0 += 32) {  // 32 accumulator columns = 16 tokens x 2 limbs
+            for (int c0 = 0; c0 < kPfCols; c0 += 32) {  // 32 accumulator columns = 32 / LIMBS activation rows
+                if (tok0 + c0 / LIMBS >= p.M) break;  // uniform: the remaining columns belong to rows past M
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * kPfCols + c0), v);
                 tmem_ld_wait();
                 if (n < p.N) {
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int m = tok0 + c0 / 2 + j;
+                    for (int j = 0; j < 32 / LIMBS; j++) {
+                        const int m = tok0 + c0 / LIMBS + j;
                         if (m < p.M) {
-                            const float dot = (float)((long long)(int)v[2 * j + 1] * 256 + (long long)(int)v[2 * j]) * sh_ascale[buf][c0 / 2 + j];
-                            float r = dot * wscale;
-                            if (resid_p) r = round_store<OutT>(r) + to_f32<OutT>(resid_p[(size_t)m * p.N + n]);
+                            float acc;
+                            if constexpr (LIMBS == 2) acc = (float)((long long)(int)v[2 * j + 1] * 256 + (long long)(int)v[2 * j]);
+                            else acc = (float)(int)v[j];
+                            // (acc * lhs scale) * weight scale with separate roundings, as the CPU kernels compute it
+                            float r = __fmul_rn(__fmul_rn(acc, sh_ascale[buf][c0 / LIMBS + j]), wscale);
+                            if (resid_p) r = __fadd_rn(round_store<OutT>(r), to_f32<OutT>(resid_p[(size_t)m * p.N + n]));
                             out_p[(size_t)m * p.N + n] = from_f32<OutT>(r);
                         }
                     }
@@ -271,10 +290,10 @@ bool i8_prefill_supported(int M, int N, int K, const void *wq, int act_dtype, in
            tensor_map_api_available();
 }
 
-template <typename OutT>
+template <typename OutT, int LIMBS>
 static int launch_pf(cudaStream_t st, const CUtensorMap &mw, const CUtensorMap &ma, const PfParams &p) {
     const size_t smem = (size_t)kPfStages * kPfStageBytes + 1024;
-    auto kern = i8_prefill_gemm_kernel<OutT>;
+    auto kern = i8_prefill_gemm_kernel<OutT, LIMBS>;
     static bool attr_set = false;
     if (!attr_set) {
         MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -323,15 +342,51 @@ int i8_prefill_launch(cudaStream_t st, void *out, const void *act, const int8_t 
     p.scale = scale;
     p.resid = resid;
     p.ascale = ascale;
+    p.ascale_t = nullptr;
+    p.ascale_stride = 1;
     p.M = M;
     p.N = N;
     p.K = K;
     p.w_tiles = (N + kPfRows - 1) / kPfRows;
     p.t_tiles = (M + kPfTokens - 1) / kPfTokens;
     p.status = status;
-    if (out_dtype == MYNN_BF16) return launch_pf<__nv_bfloat16>(st, mw, ma, p);
-    if (out_dtype == MYNN_F16) return launch_pf<__half>(st, mw, ma, p);
-    return launch_pf<float>(st, mw, ma, p);
+    if (out_dtype == MYNN_BF16) return launch_pf<__nv_bfloat16, 2>(st, mw, ma, p);
+    if (out_dtype == MYNN_F16) return launch_pf<__half, 2>(st, mw, ma, p);
+    return launch_pf<float, 2>(st, mw, ma, p);
+}
+
+// QuantizedMatMul (W8A8): out[m,n] = (sum_k lhs[m,k] * rhs[n,k]) * lhs_scale[m] * rhs_scale[n].  The int8 lhs matrix is
+// the TMA source as it is (no pre-pass, one accumulator column per row), so the int8 pipe does a quarter of the work
+// per output that a bf16 product would need.  workspace: 256 bytes (status word), zeroed once.
+bool i8_w8a8_supported(int M, int N, int K, const void *lhs, const void *rhs) {
+    return M >= 1 && N >= 1 && K >= 16 && K % 16 == 0 && (((uintptr_t)lhs | (uintptr_t)rhs) % 16) == 0 && tensor_map_api_available();
+}
+
+int i8_w8a8_launch(cudaStream_t st, void *out, const int8_t *lhs, const void *lhs_scale, int lhs_scale_per_row, const int8_t *rhs,
+                   const void *rhs_scale, int M, int N, int K, int dtype, void *workspace, size_t workspace_bytes) {
+    if (!workspace || workspace_bytes < 256 || (uintptr_t)workspace % 256)
+        return fail(MYNN_E_ARG, "quantized_matmul: a 256-byte aligned workspace of at least 256 bytes is needed");
+    CUtensorMap mw, ma;
+    int rc = make_map(&mw, rhs, (uint64_t)N, (uint64_t)K, (uint64_t)K, kPfRows);
+    if (rc) return rc;
+    rc = make_map(&ma, lhs, (uint64_t)M, (uint64_t)K, (uint64_t)K, (uint32_t)kPfCols);
+    if (rc) return rc;
+    PfParams p;
+    p.out = out;
+    p.scale = rhs_scale;
+    p.resid = nullptr;
+    p.ascale = nullptr;
+    p.ascale_t = lhs_scale;
+    p.ascale_stride = lhs_scale_per_row ? 1 : 0;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.w_tiles = (N + kPfRows - 1) / kPfRows;
+    p.t_tiles = (M + kPfCols - 1) / kPfCols;
+    p.status = (int *)workspace;
+    if (dtype == MYNN_BF16) return launch_pf<__nv_bfloat16, 1>(st, mw, ma, p);
+    if (dtype == MYNN_F16) return launch_pf<__half, 1>(st, mw, ma, p);
+    return launch_pf<float, 1>(st, mw, ma, p);
 }
 
 }  // namespace mynn

@@ -117,6 +117,27 @@ def attn(b, hq, hkv, d, length, dtype="bf16", copies=None, quiet=False, kv="16bi
     return res
 
 
+def w8a8(m, n, k, dtype="bf16", copies=None, quiet=False):
+    """QuantizedMatMul (int8 x int8) on the tcgen05 kernel; TFLOP/s counts 2 M N K integer operations."""
+    td = _DT[dtype]
+    copies = copies or max(3, int(300e6 // (n * k)) + 1)
+    ws = [torch.randint(-127, 128, (n, k), device="cuda", dtype=torch.int8) for _ in range(copies)]
+    lhs = torch.randint(-127, 128, (m, k), device="cuda", dtype=torch.int8)
+    ls = (torch.rand(m, device="cuda") * 0.05 + 0.005).to(td)
+    rs = (torch.rand(n, device="cuda") * 0.018 + 0.002).to(td)
+    out = torch.empty(m, n, device="cuda", dtype=td)
+    wsp = ops.dequant_matmul_workspace(1, n, k, "cuda")
+    us = _time_graph([(lambda w=w: ops.quantized_matmul(lhs, ls, w, rs, out=out, workspace=wsp)) for w in ws])
+    ops.check_workspace(wsp)
+    alg = n * k + m * k + 2 * (m + n) + 2 * m * n
+    res = {"kernel": "quantized_matmul/tcgen05_i8", "m": m, "n": n, "k": k, "dtype": dtype, "us": us, "TOPs": 2.0 * m * n * k / us / 1e6,
+           "frac_of_measured_bf16_peak": 2.0 * m * n * k / us / 1e6 / _peak_tflops(), "GBps": alg / us / 1e3,
+           "frac_of_measured_hbm_peak": alg / us / 1e3 / _peak(), "algorithmic_bytes": alg}
+    if not quiet:
+        print(json.dumps(res), flush=True)
+    return res
+
+
 def suite():
     """The shapes of the benchmark configurations: Llama-3-8B and TinyLlama projections at batch 1 and 32, the
     config-1 GEMV, and the decode-attention microbenchmark."""
@@ -150,10 +171,18 @@ def main():
     a.add_argument("--dtype", default="bf16")
     a.add_argument("--copies", type=int, default=None)
     a.add_argument("--kv", default="16bit", choices=["16bit", "int8"])
+    q = sub.add_parser("w8a8")
+    q.add_argument("--m", type=int, default=2048)
+    q.add_argument("--n", type=int, default=14336)
+    q.add_argument("--k", type=int, default=4096)
+    q.add_argument("--dtype", default="bf16")
+    q.add_argument("--copies", type=int, default=None)
     sub.add_parser("suite")
     args = ap.parse_args()
     if args.cmd == "gemm":
         gemm(args.m, args.n, args.k, args.dtype, args.ksplit, args.copies, kernel=args.kernel)
+    elif args.cmd == "w8a8":
+        w8a8(args.m, args.n, args.k, args.dtype, args.copies)
     elif args.cmd == "attn":
         attn(args.b, args.hq, args.hkv, args.d, args.len, args.dtype, args.copies, kv=args.kv)
     else:

@@ -184,6 +184,41 @@ def attention_q8(q, k, v, k_scale, v_scale, scale: float, active_seq_kv=None, is
     return out
 
 
+def dynamic_quantize_linear(x, symmetric: bool = True, per_row: bool = True):
+    """``DynamicQuantizeLinear{axis, symmetric}`` on a 2-D tensor: returns (y, scale, zero_point); y is int8 when
+    symmetric, uint8 otherwise; per_row=True gives one scale per row, False one for the whole tensor."""
+    rows, inner = x.shape
+    qdt = torch.int8 if symmetric else torch.uint8
+    y = torch.empty(x.shape, dtype=qdt, device=x.device)
+    n = rows if per_row else 1
+    scale = torch.empty(n, dtype=x.dtype, device=x.device)
+    zp = torch.empty(n, dtype=qdt, device=x.device)
+    ffi.check(ffi.lib().mynn_b200_dynamic_quantize_linear(_stream(), _ptr(y), _ptr(scale), _ptr(zp), _ptr(x), rows, inner,
+                                                          int(symmetric), int(per_row), _dt(x)))
+    if not per_row:
+        return y, scale.reshape(()), zp.reshape(())
+    return y, scale, zp
+
+
+def quantized_matmul(lhs, lhs_scale, rhs, rhs_scale, out=None, workspace="auto"):
+    """``QuantizedMatMul``: lhs int8 [M,K] with scale [M] (or a scalar), rhs int8 [N,K] with per-channel scale [N];
+    the output has the dtype of the scales.  workspace None selects the plain kernel."""
+    m, k = lhs.shape
+    n = rhs.shape[0]
+    if lhs.dtype != torch.int8 or rhs.dtype != torch.int8:
+        raise TypeError("lhs and rhs must be int8")
+    if out is None:
+        out = torch.empty(m, n, dtype=rhs_scale.dtype, device=lhs.device)
+    if isinstance(workspace, str):
+        workspace = dequant_matmul_workspace(1, n, k, lhs.device)
+    per_row = lhs_scale.dim() > 0 and lhs_scale.numel() == m and not (m == 1 and lhs_scale.dim() == 0)
+    ffi.check(ffi.lib().mynn_b200_quantized_matmul(_stream(), _ptr(out), _ptr(lhs), _ptr(lhs_scale), int(per_row), _ptr(rhs),
+                                                   _ptr(rhs_scale), m, n, k, _dt(rhs_scale),
+                                                   None if workspace is None else _ptr(workspace),
+                                                   0 if workspace is None else workspace.numel()))
+    return out
+
+
 def rms_norm(x, weight, eps: float, out=None):
     d = x.shape[-1]
     if out is None:

@@ -113,6 +113,59 @@ def dequant_matmul(act: np.ndarray, wq: np.ndarray, scale: np.ndarray) -> np.nda
     return out.reshape(act.shape[:-1] + (wq.shape[0],))
 
 
+def _round_half_away(x):
+    return np.sign(x) * np.floor(np.abs(x) + np.float32(0.5))
+
+
+def dynamic_quantize_linear(x: np.ndarray, symmetric: bool, per_row: bool, dtype: str = "bf16"):
+    """DynamicQuantizeLinear, the engine's extension of the ONNX operator (src/graph/operator.rs:265-285).
+    Returns (y, scale stored in ``dtype``, zero_point).  x [rows, inner] f32 values.
+
+    symmetric per-row follows the CPU kernel mynn_dynquant_i8 (src/codegen/cpu/kernels/dynquant_i8.rs:13-37):
+    sc = amax / 127 (1 for an all-zero row), inv = 1 / sc, y = round-half-away(x * inv) clamped to [-127, 127].
+    The other three variants exist only in the CUDA backend (src/codegen/cuda/cpp/dynamic_quantize_linear.cuh:41-151):
+    y = nearbyint(x / scale) + zp with scale = max|x| / 127, zp = 0 (symmetric, int8) or, asymmetric (uint8), the
+    range widened to contain 0, scale = (max - min) / 255 (1 if 0), zp = clamp(nearbyint(-min / scale), 0, 255)."""
+    x = np.asarray(x, dtype=np.float32)
+    rows = x if per_row else x.reshape(1, -1)
+    f32 = np.float32
+    if symmetric and per_row:
+        amax = np.abs(rows).max(axis=1)
+        sc = np.where(amax > 0, amax / f32(127.0), f32(1.0)).astype(f32)
+        inv = (f32(1.0) / sc).astype(f32)
+        y = np.clip(_round_half_away((rows * inv[:, None]).astype(f32)), -127, 127).astype(np.int8)
+        zp = np.zeros(len(sc), np.int8)
+    elif symmetric:
+        amax = np.abs(rows).max(axis=1)
+        sc = (amax / f32(127.0)).astype(f32)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            q = np.where(sc[:, None] > 0, np.rint((rows / sc[:, None]).astype(f32)), 0)
+        y = np.clip(q, -127, 127).astype(np.int8)
+        zp = np.zeros(len(sc), np.int8)
+    else:
+        mn = np.minimum(rows.min(axis=1), f32(0.0))
+        mx = np.maximum(rows.max(axis=1), f32(0.0))
+        sc = ((mx - mn) / f32(255.0)).astype(f32)
+        sc = np.where(sc == 0, f32(1.0), sc).astype(f32)
+        zp = np.clip(np.rint((-mn / sc).astype(f32)), 0, 255).astype(np.int64)
+        q = np.rint((rows / sc[:, None]).astype(f32)).astype(np.int64) + zp[:, None]
+        y = np.clip(q, 0, 255).astype(np.uint8)
+        zp = zp.astype(np.uint8)
+    scale = store_round(sc, dtype)
+    if not per_row:
+        return y.reshape(x.shape), scale.reshape(()), zp.reshape(())
+    return y, scale, zp
+
+
+def quantized_matmul(lhs: np.ndarray, lhs_scale: np.ndarray, rhs: np.ndarray, rhs_scale: np.ndarray) -> np.ndarray:
+    """QuantizedMatMul: out[m,n] = (int32 sum_k lhs[m,k] * rhs[n,k]) * lhs_scale[m] * rhs_scale[n], products taken left
+    to right in f32 (src/codegen/cpu/kernels/qgemv_i8i8.rs:59-78).  lhs_scale [M] or a scalar; the caller rounds the
+    result to the storage dtype."""
+    acc = lhs.astype(np.int64) @ rhs.astype(np.int64).T
+    ls = np.asarray(lhs_scale, dtype=np.float32).reshape(-1, 1) if np.ndim(lhs_scale) else np.float32(lhs_scale)
+    return (acc.astype(np.float32) * ls).astype(np.float32) * np.asarray(rhs_scale, dtype=np.float32)[None, :]
+
+
 # --------------------------------------------------------------------------------------
 # Attention / KV cache
 # --------------------------------------------------------------------------------------

@@ -31,6 +31,9 @@ HOT_PATH_DIRS = [
     "attention_decode", "attention_decode_gqa", "attention_decode_runtime_kv", "attention_causal",
     "attention_no_causal", "attention_causal_large", "kv_cache_update", "quantizing_kvcache_update",
     "dequantize_linear", "swish", "gather_default_axis",
+    "dyn_quantize_linear_sym_per_row", "dyn_quantize_linear_sym_per_tensor", "dyn_quantize_linear_asym_per_row",
+    "dyn_quantize_linear_asym_per_tensor", "quantized_matmul_64x64x64", "quantized_matmul_128x128x128",
+    "quantized_matmul_256x128x128", "quantized_matmul_128x256x64", "quantized_matmul_1x128x128",
 ]
 
 

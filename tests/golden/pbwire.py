@@ -50,7 +50,7 @@ def fields(buf):
         yield fno, wt, v
 
 
-_DTYPES = {1: np.float32, 3: np.int8, 6: np.int32, 7: np.int64, 11: np.float64, 16: np.uint16}
+_DTYPES = {1: np.float32, 2: np.uint8, 3: np.int8, 6: np.int32, 7: np.int64, 11: np.float64, 16: np.uint16}
 
 
 def parse_tensor(buf):

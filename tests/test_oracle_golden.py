@@ -90,6 +90,34 @@ def test_attention_with_int8_kv_matches_dequantised_attention():
     assert np.abs(got - want).max() < 1e-5
 
 
+@pytest.mark.parametrize("name,symmetric,per_row", [("dyn_quantize_linear_sym_per_row", True, True),
+                                                    ("dyn_quantize_linear_sym_per_tensor", True, False),
+                                                    ("dyn_quantize_linear_asym_per_row", False, True),
+                                                    ("dyn_quantize_linear_asym_per_tensor", False, False)])
+def test_dynamic_quantize_linear_goldens(single_op, name, symmetric, per_row):
+    """The reference's rule (tests/single_op.rs:1140-1180): y and zero_point exact, scale within 1e-3."""
+    fx = single_op(name)
+    assert bool(fx.attr("symmetric", 0)) == symmetric and (fx.attr("axis", None) is not None) == per_row
+    y, scale, zp = R.dynamic_quantize_linear(R.bf16_bits_to_f32(fx.inputs[0]), symmetric, per_row, "bf16")
+    assert y.dtype == fx.outputs[0].dtype and np.array_equal(y, fx.outputs[0])
+    ok, md = eq_with_epsilon(scale, R.bf16_bits_to_f32(fx.outputs[1]), 1e-3)
+    assert ok, md
+    assert np.array_equal(zp, fx.outputs[2])
+
+
+@pytest.mark.parametrize("name", ["quantized_matmul_64x64x64", "quantized_matmul_128x128x128", "quantized_matmul_256x128x128",
+                                  "quantized_matmul_128x256x64", "quantized_matmul_1x128x128"])
+def test_quantized_matmul_goldens(single_op, name):
+    """tests/single_op.rs:1182-1199: tolerance 1e-1 (either rule); the restatement is far inside it."""
+    fx = single_op(name)
+    lhs, ls, rhs, rs = fx.inputs
+    out = R.round_bf16(R.quantized_matmul(lhs, R.bf16_bits_to_f32(ls), rhs, R.bf16_bits_to_f32(rs)))
+    want = R.bf16_bits_to_f32(fx.outputs[0])
+    ok, md = eq_with_epsilon(out, want, 1e-1)
+    assert ok, md
+    assert np.abs(out - want).max() <= np.abs(want).max() * 2.0 ** -7  # in fact within one bf16 ulp of the output scale
+
+
 def test_dequantize_linear_golden(single_op):
     fx = single_op("dequantize_linear")
     x, scale = fx.inputs
