@@ -203,6 +203,14 @@ class DecoderModel:
         self.d2h_bytes_per_step = self._out.numel() * self._out.element_size()
 
     # ---- the engine's Session::run for the decode graph ----
+    @classmethod
+    def from_pretrained(cls, model_dir: str, **kwargs):
+        """Build the model from a Hugging Face style directory: ``config.json`` plus ``model.int8.safetensors`` (the
+        engine's quantized layout), or float safetensors that are quantized while loading."""
+        from .checkpoint import load_model_dir
+        cfg, state = load_model_dir(model_dir)
+        return cls(cfg, state, **kwargs)
+
     def step(self, tokens, past_len: int, active_seq_kv: int | None = None):
         """One decode step through ``model(state, outputs, inputs)`` with HOST buffers: inputs are
         input_ids [batch,1], position_id [1] = past_len, past_len, active_seq_kv = past_len + 1

@@ -174,6 +174,26 @@ def test_device_argmax_output_and_step_device(vocab):
         m.close()
 
 
+def test_from_pretrained_directory_matches_in_memory_model(tmp_path, tiny_llama):
+    """config.json + model.safetensors -> quantize_int8 command -> model.int8.safetensors -> DecoderModel: the same logits
+    as the model built from the in-memory quantized state."""
+    import json
+    from my_nn_engine_b200 import checkpoint as C
+    from my_nn_engine_b200.decoder import DecoderModel
+    from my_nn_engine_b200.quantize import quantize_state_dict
+    cfg, weights, prompt, _, _ = tiny_llama
+    state = {k: torch.from_numpy(v) for k, v in weights.items()}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    C.write_safetensors(str(tmp_path / "model.safetensors"), state)
+    assert C.main([str(tmp_path / "model.safetensors"), str(tmp_path / C.QUANTIZED_SAFETENSORS)]) == 0
+    a = DecoderModel.from_pretrained(str(tmp_path), dtype="bf16", max_seq_len=32)
+    b = DecoderModel(cfg, quantize_state_dict(state), dtype="bf16", max_seq_len=32)
+    ids = np.asarray([[int(prompt[0])]])
+    assert torch.equal(a.step(ids[:, 0], 0), b.step(ids[:, 0], 0))
+    a.close()
+    b.close()
+
+
 def test_llm_session_on_device_model():
     from my_nn_engine_b200 import LlmSession
     from my_nn_engine_b200.decoder import DecoderModel
