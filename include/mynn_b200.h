@@ -151,6 +151,26 @@ int mynn_b200_quantized_matmul(void *stream, void *out, const int8_t *lhs, const
                                const int8_t *rhs, const void *rhs_scale, int M, int N, int K, int dtype, void *workspace,
                                size_t workspace_bytes);
 
+/* KVCacheUpdate with the ring operands of the streaming cache: cache[bh, phys(offset + t), :] = new[bh, t, :] with
+ * phys(r) = r for r < ring_sink (or ring_window == 0), else ring_sink + (ring_start + r - ring_sink) % ring_window.
+ * Replaces: kvcache_update with ring arguments (cpp/kvcache_update.cuh:6-26, ring_phys_index cpp/common.cuh:55-60). */
+int mynn_b200_kv_cache_update_ring(void *stream, void *cache, const void *new_kv, int BH, int cache_seq_len, int new_seq_len,
+                                   int D, int offset, int ring_sink, int ring_window, int ring_start, int dtype);
+
+/* The engine's `rope_fused` over a cache: out[bh, s, :] = RoPE(cache[bh, s, :]) at table row kv_position[s] for the
+ * slots s < active_seq_kv (the rest of `out` is left alone).  kv_position: device int64 [cache_seq_len].
+ * Replaces: rope_fused applied to the K cache in streaming mode (crates/llm/src/decoder.rs:327-336, cpp/rope.cuh). */
+int mynn_b200_rope_cache_rows(void *stream, void *out, const void *cache, const void *cos_table, const void *sin_table,
+                              const int64_t *kv_position, int BH, int cache_seq_len, int D, int active_seq_kv, int dtype);
+
+/* Attention whose K/V rows are addressed through the ring: logical row r of the 0..active_seq_kv-1 visited rows is read
+ * from slot phys(r) (cpp/attention.cuh:546-600, the ring_sink/ring_window/ring_start operands of the Attention node).
+ * Workspace as for mynn_b200_attention. */
+int mynn_b200_attention_ring(void *stream, void *out, const void *q, const void *k, const void *v, float scale, int B,
+                             int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv, int is_causal,
+                             int ring_sink, int ring_window, int ring_start, int dtype, void *workspace,
+                             size_t workspace_bytes);
+
 /* RMSNorm over the last axis: y = x * rsqrt(mean(x^2) + eps) * w.  Replaces rms_norm (cpp/rms_norm.cuh:9-59). */
 int mynn_b200_rms_norm(void *stream, void *out, const void *x, const void *weight, float eps, int rows, int D,
                        int dtype);
@@ -222,6 +242,9 @@ typedef struct mynn_b200_model_config {
     int32_t use_graph;   /* capture the step in a CUDA graph and replay it */
     int32_t max_prefill; /* largest T accepted by mynn_b200_model_prefill (0 = decode only) */
     int32_t use_tensor_gemm; /* 1: DequantMatMul on the tcgen05 int8 kernel (needs scratch); 0: mma.sync streaming kernel */
+    int32_t stream_sink;     /* streaming (sink + ring) KV cache, the engine's `streaming_kv` option: the first stream_sink */
+    int32_t stream_window;   /* tokens stay, the last stream_window tokens live in a ring; 0 = off.  Steps then go through
+                                mynn_b200_model_stream; sink + window <= max_seq_len; not combined with kv_int8 */
     int32_t kv_int8;         /* 1: the engine's `quant_kv_cache` option: int8 K/V caches with one scale per cached token;
                                 session_state then holds FOUR buffers per layer: K int8, V int8, K scale, V scale */
     float rms_eps;
@@ -233,6 +256,13 @@ void model(void *state, void **output, void **input);
 void model_destroy(void *state);
 /* Status of the last model_init / model call (they return void to keep the engine's signatures). */
 int mynn_b200_model_status(void);
+
+/* One step of a model configured with stream_window > 0: appends the T tokens ids_host [batch, T] that sit at absolute
+ * positions stream_pos .. stream_pos + T - 1 of the stream (T == 1: a decode step; T > 1: a prefill chunk, which must not
+ * evict, i.e. stream_pos + T <= sink + window, and T <= max_prefill) and returns the last position's logits / token ids
+ * in out_host as model() does.  The index math of the engine's streaming session (crates/llm/src/session.rs:539-635:
+ * write slot, query position, active rows, ring start, per-slot key positions) is done inside. */
+int mynn_b200_model_stream(void *state, const int64_t *ids_host, int T, long long stream_pos, void *out_host);
 /* Device-resident variant of model(): ids and outputs stay on the device, no host synchronisation.
  * ids_dev int64 [batch]; past_len is advanced by the caller.  out_dev as output[0] of model(). */
 int mynn_b200_model_step_device(void *state, void *stream, const int64_t *ids_dev, int past_len, void *out_dev);

@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
 template <typename T, int MAXE>
 __global__ void attention_generic_kernel(T *out, const T *q, const T *k, const T *v, float scale, int B, int Hq,
                                          int Hkv, int Sq, int Sk, int D, int active_host, const int32_t *active_dev,
-                                         int is_causal, int out_bshd) {
+                                         int is_causal, int out_bshd, int ring_sink, int ring_window, int ring_start) {
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wid >= (long long)B * Hq * Sq) return;
@@ -185,7 +185,9 @@ __global__ void attention_generic_kernel(T *out, const T *q, const T *k, const T
         o[e] = 0.f;
     }
     float m = -INFINITY, s = 0.f;
-    for (int r = 0; r < bound; r++) {
+    for (int lr = 0; lr < bound; lr++) {
+        // logical row -> physical slot of a sink + ring cache (identity when ring_window == 0)
+        const int r = (ring_window == 0 || lr < ring_sink) ? lr : ring_sink + (ring_start + (lr - ring_sink)) % ring_window;
         float dot = 0.f;
 #pragma unroll
         for (int e = 0; e < MAXE; e++) {
@@ -247,12 +249,13 @@ extern "C" size_t mynn_b200_attention_workspace_bytes(int B, int Hq, int Hkv, in
 template <typename T>
 static int launch_generic(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
                           int Hq, int Hkv, int Sq, int Sk, int D, int active, const int32_t *active_dev, int causal,
-                          int out_bshd) {
+                          int out_bshd, int ring_sink = 0, int ring_window = 0, int ring_start = 0) {
     const long long rows = (long long)B * Hq * Sq;
     const unsigned blocks = (unsigned)((rows * 32 + 127) / 128);
 #define GEN(MAXE)                                                                                                     \
     attention_generic_kernel<T, MAXE><<<blocks, 128, 0, st>>>((T *)out, (const T *)q, (const T *)k, (const T *)v, scale, B, \
-                                                             Hq, Hkv, Sq, Sk, D, active, active_dev, causal, out_bshd)
+                                                             Hq, Hkv, Sq, Sk, D, active, active_dev, causal, out_bshd,   \
+                                                             ring_sink, ring_window, ring_start)
     if (D <= 32) GEN(1);
     else if (D <= 64) GEN(2);
     else if (D <= 128) GEN(4);
@@ -277,6 +280,37 @@ extern "C" int mynn_b200_attention(void *stream, void *out, const void *q, const
                                    size_t workspace_bytes) {
     return mynn::launch_attention((cudaStream_t)stream, out, q, k, v, scale, B, Hq, Hkv, Sq, D, cache_seq_len,
                                   active_seq_kv, active_seq_kv_dev, is_causal, dtype, workspace, workspace_bytes, 0);
+}
+
+// Attention over a sink + ring cache.  One query row: the softmax does not depend on the order of the rows, and the
+// logical rows 0..active-1 occupy the physical slots 0..active-1 whenever the ring is either not yet wrapped
+// (ring_start == 0) or full (active == sink + window), so the tuned decode kernel runs unchanged; every other case
+// (several query rows with a causal bound per logical rank, a partly filled wrapped ring) walks the ring in the plain
+// kernel.
+extern "C" int mynn_b200_attention_ring(void *stream, void *out, const void *q, const void *k, const void *v, float scale,
+                                        int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
+                                        int is_causal, int ring_sink, int ring_window, int ring_start, int dtype,
+                                        void *workspace, size_t workspace_bytes) {
+    if (ring_sink < 0 || ring_window < 0 || ring_start < 0 || (ring_window > 0 && ring_start >= ring_window) ||
+        ring_sink + ring_window > cache_seq_len)
+        return fail(MYNN_E_ARG, "attention_ring: bad ring (sink %d, window %d, start %d, cache %d)", ring_sink, ring_window, ring_start, cache_seq_len);
+    if (ring_window > 0 && active_seq_kv > ring_sink + ring_window)
+        return fail(MYNN_E_ARG, "attention_ring: %d active rows exceed sink + window = %d", active_seq_kv, ring_sink + ring_window);
+    const bool identity = ring_window == 0 || ring_start == 0 || active_seq_kv <= ring_sink;
+    const bool full = ring_window > 0 && active_seq_kv == ring_sink + ring_window;
+    if (Sq == 1 && (identity || full))
+        return mynn::launch_attention((cudaStream_t)stream, out, q, k, v, scale, B, Hq, Hkv, Sq, D, cache_seq_len, active_seq_kv,
+                                      nullptr, is_causal, dtype, workspace, workspace_bytes, 0);
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || Sq < 0 || D <= 0 || cache_seq_len < 0 || active_seq_kv < 0 || Hq % Hkv)
+        return fail(MYNN_E_ARG, "attention_ring: bad shape");
+    if (!dtype_ok(dtype)) return fail(MYNN_E_ARG, "attention_ring: bad dtype %d", dtype);
+    if (B == 0 || Sq == 0) return MYNN_OK;
+    if (!out || !q || !k || !v) return fail(MYNN_E_ARG, "attention_ring: null pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int rs = identity ? 0 : ring_sink, rw = identity ? 0 : ring_window, r0 = identity ? 0 : ring_start;
+    if (dtype == MYNN_F32) return launch_generic<float>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, nullptr, is_causal, 0, rs, rw, r0);
+    if (dtype == MYNN_BF16) return launch_generic<__nv_bfloat16>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, nullptr, is_causal, 0, rs, rw, r0);
+    return launch_generic<__half>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, nullptr, is_causal, 0, rs, rw, r0);
 }
 
 int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,

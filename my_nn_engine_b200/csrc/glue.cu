@@ -158,7 +158,7 @@ template <typename T>
 __global__ void rope_kv_append_kernel(T *q_out, T *k_cache, T *v_cache, const T *q, const T *k, const T *v,
                                       long long q_stride, long long k_stride, long long v_stride, const T *cos_t,
                                       const T *sin_t, const int64_t *positions, int S, int Hq, int Hkv, int D,
-                                      int cache_seq, const int32_t *past_len_dev) {
+                                      int cache_seq, const int32_t *past_len_dev, int rotate_k) {
     pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x, b = row / S, s = row - b * S;
@@ -166,7 +166,13 @@ __global__ void rope_kv_append_kernel(T *q_out, T *k_cache, T *v_cache, const T 
     const int half = D >> 1;
     const int cache_row = *past_len_dev + s;
     const bool in_cache = cache_row >= 0 && cache_row < cache_seq;
-    if (slot < Hq + Hkv) {
+    if (slot >= Hq && slot < Hq + Hkv && !rotate_k) {  // streaming cache: keys are stored as the projection left them
+        if (!in_cache) return;
+        const int h = slot - Hq;
+        const T *src = k + (size_t)row * k_stride + (size_t)h * D;
+        T *dst = k_cache + (((size_t)b * Hkv + h) * cache_seq + cache_row) * D;
+        for (int j = threadIdx.x; j < D; j += blockDim.x) dst[j] = src[j];
+    } else if (slot < Hq + Hkv) {
         const long long pos = positions[s];
         const T *cr = cos_t + (size_t)pos * D, *sr = sin_t + (size_t)pos * D;
         const bool is_q = slot < Hq;
@@ -191,13 +197,13 @@ __global__ void rope_kv_append_kernel(T *q_out, T *k_cache, T *v_cache, const T 
 int launch_rope_kv_append(cudaStream_t st, int dtype, void *q_out, void *k_cache, void *v_cache, const void *q,
                           const void *k, const void *v, long long q_stride, long long k_stride, long long v_stride,
                           const void *cos_t, const void *sin_t, const int64_t *positions, int B, int S, int Hq,
-                          int Hkv, int D, int cache_seq, const int32_t *past_len_dev) {
+                          int Hkv, int D, int cache_seq, const int32_t *past_len_dev, int rotate_k) {
     if (B * S == 0) return MYNN_OK;
     const int threads = D / 2 >= 64 ? 64 : 32;
     MYNN_DISPATCH_DTYPE(dtype, T, {
         MYNN_CUDA_OK(launch_pdl(rope_kv_append_kernel<T>, dim3(B * S, Hq + 2 * Hkv), dim3(threads), 0, st, (T *)q_out, (T *)k_cache,
                                 (T *)v_cache, (const T *)q, (const T *)k, (const T *)v, q_stride, k_stride, v_stride,
-                                (const T *)cos_t, (const T *)sin_t, positions, S, Hq, Hkv, D, cache_seq, past_len_dev));
+                                (const T *)cos_t, (const T *)sin_t, positions, S, Hq, Hkv, D, cache_seq, past_len_dev, rotate_k));
     });
     MYNN_LAUNCH_OK("rope_kv_append_kernel");
     return MYNN_OK;

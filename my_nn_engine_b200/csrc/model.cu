@@ -60,6 +60,10 @@ struct Model {
     bool tp_attached = false;
     void *attn_ws, *gemm_ws;
     size_t attn_ws_bytes, gemm_ws_bytes;
+    // streaming (sink + ring) cache: per-slot key positions and the scratch that holds one layer's rotated keys
+    int64_t *kvpos_dev = nullptr;
+    void *k_rot = nullptr;
+    cudaGraphExec_t stream_graph_exec = nullptr;
     cudaStream_t stream = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
 };
@@ -165,6 +169,14 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
                                         S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
             RC(launch_attention_q8(st, m.attn, m.q_rot, L.kc, L.vc, L.ksc, L.vsc, attn_scale, B, m.Hq, m.Hkv, S, D,
                                    c.max_seq_len, c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
+        } else if (c.stream_window > 0) {
+            // streaming cache: K is appended unrotated at the slot in past_dev; the live rows are rotated at their
+            // recency rank into the scratch copy that attention reads.  The live rows are the slots [0, active).
+            RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
+                                     S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev, 0));
+            RC(launch_rope_cache_rows(st, dt, m.k_rot, L.kc, m.cos_t, m.sin_t, m.kvpos_dev, B * m.Hkv, c.max_seq_len, D, 0, m.active_dev));
+            RC(launch_attention(st, m.attn, m.q_rot, m.k_rot, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
+                                c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
         } else {
             RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
                                      S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
@@ -323,7 +335,9 @@ static int model_create(Model **out, void **initializer, void **session_state) {
                  o_logits = take((size_t)c.batch * m->vocab_l * esz),
                  o_full = take(tp > 1 ? (size_t)c.batch * c.vocab * esz : 0), 
                  o_pairs = take((size_t)c.batch * 8), o_pairs_all = take((size_t)c.batch * 8 * std::max(tp, 16)),
-                 o_ws = take(m->attn_ws_bytes), o_gws = take(m->gemm_ws_bytes);
+                 o_ws = take(m->attn_ws_bytes), o_gws = take(m->gemm_ws_bytes),
+                 o_kvpos = take(c.stream_window > 0 ? (size_t)c.max_seq_len * 8 : 0),
+                 o_krot = take(c.stream_window > 0 ? (size_t)c.batch * m->Hkv * c.max_seq_len * D * esz : 0);
     cudaError_t e = cudaMalloc(&m->arena, off);
     if (e != cudaSuccess) {
         delete m;
@@ -342,6 +356,8 @@ static int model_create(Model **out, void **initializer, void **session_state) {
     m->logits_full = a + o_full; m->pairs = (float *)(a + o_pairs);
     m->pairs_all = (float *)(a + o_pairs_all); m->attn_ws = a + o_ws;
     m->gemm_ws = m->gemm_ws_bytes ? a + o_gws : nullptr;
+    m->kvpos_dev = (int64_t *)(a + o_kvpos);
+    m->k_rot = a + o_krot;
     m->part = nullptr;
     if (tp > 1) {
         const size_t pbytes = up256(R * H * 4);
@@ -426,6 +442,7 @@ static int copy_result_to_host(Model &m, void *dst) {
 static int model_run(Model &m, void **output, void **input) {
     if (!output || !input || !output[0] || !input[0] || !input[1] || !input[2] || !input[3])
         return fail(MYNN_E_ARG, "model: null input/output pointer");
+    if (m.c.stream_window > 0) return fail(MYNN_E_STATE, "model: this model has a streaming cache; step it with mynn_b200_model_stream");
     const int64_t past = *(const int64_t *)input[2], active = *(const int64_t *)input[3];
     if (past < 0 || past >= m.c.max_seq_len || active < 0 || active > m.c.max_seq_len)
         return fail(MYNN_E_ARG, "model: past_len %lld / active_seq_kv %lld outside the %d-row cache", (long long)past,
@@ -459,6 +476,11 @@ extern "C" int mynn_b200_model_configure(const mynn_b200_model_config *cfg) {
     if (c.tp_world > 1 && (comm_world() != c.tp_world || comm_rank() != c.tp_rank))
         return fail(MYNN_E_STATE, "model_configure: communicator is rank %d of %d, config says %d of %d", comm_rank(), comm_world(), c.tp_rank, c.tp_world);
     if (c.head_dim & 1) return fail(MYNN_E_ARG, "model_configure: odd head_dim");
+    if (c.stream_window < 0 || c.stream_sink < 0 || (c.stream_window == 0 && c.stream_sink != 0))
+        return fail(MYNN_E_ARG, "model_configure: bad streaming cache (sink %d, window %d)", c.stream_sink, c.stream_window);
+    if (c.stream_window > 0 && c.stream_sink + c.stream_window > c.max_seq_len)
+        return fail(MYNN_E_ARG, "model_configure: sink %d + window %d exceed max_seq_len %d", c.stream_sink, c.stream_window, c.max_seq_len);
+    if (c.stream_window > 0 && c.kv_int8) return fail(MYNN_E_UNSUPPORTED, "model_configure: a streaming cache with int8 KV is not supported");
     g_cfg = c;
     g_cfg_set = true;
     return MYNN_OK;
@@ -483,6 +505,7 @@ extern "C" void model_destroy(void *state) {
     Model *m = (Model *)state;
     if (m->stream) cudaStreamSynchronize(m->stream);
     if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+    if (m->stream_graph_exec) cudaGraphExecDestroy(m->stream_graph_exec);
     if (m->stream) cudaStreamDestroy(m->stream);
     if (m->arena) cudaFree(m->arena);
     if (m->h_in) cudaFreeHost(m->h_in);
@@ -497,6 +520,7 @@ extern "C" int mynn_b200_model_status(void) { return g_status; }
 extern "C" int mynn_b200_model_step_device(void *state, void *stream, const int64_t *ids_dev, int past_len, void *out_dev) {
     if (!state) return fail(MYNN_E_STATE, "model_step_device: null state");
     Model &m = *(Model *)state;
+    if (m.c.stream_window > 0) return fail(MYNN_E_STATE, "model_step_device: this model has a streaming cache; step it with mynn_b200_model_stream");
     if (past_len < 0 || past_len >= m.c.max_seq_len) return fail(MYNN_E_ARG, "model_step_device: past_len %d outside the cache", past_len);
     cudaStream_t st = stream ? (cudaStream_t)stream : m.stream;
     // The 16-byte header is passed by value through a pageable copy (staged by the runtime before it returns).
@@ -518,6 +542,7 @@ extern "C" int mynn_b200_model_step_device(void *state, void *stream, const int6
 extern "C" int mynn_b200_model_prefill(void *state, const int64_t *ids_host, int T, int past_len, void *out_host) {
     if (!state) return fail(MYNN_E_STATE, "model_prefill: null state");
     Model &m = *(Model *)state;
+    if (m.c.stream_window > 0) return fail(MYNN_E_STATE, "model_prefill: this model has a streaming cache; step it with mynn_b200_model_stream");
     const int cap = m.c.max_prefill > 0 ? m.c.max_prefill : 1;
     if (T <= 0 || T > cap) return fail(MYNN_E_ARG, "model_prefill: %d tokens, capacity %d", T, cap);
     if (past_len < 0 || past_len + T > m.c.max_seq_len) return fail(MYNN_E_ARG, "model_prefill: rows [%d, %d) outside the %d-row cache", past_len, past_len + T, m.c.max_seq_len);
@@ -531,6 +556,65 @@ extern "C" int mynn_b200_model_prefill(void *state, const int64_t *ids_host, int
     MYNN_CUDA_OK(cudaMemcpyAsync(m.past_dev, &hdr, 16, cudaMemcpyHostToDevice, st));
     MYNN_CUDA_OK(cudaStreamSynchronize(st));  // the sources above are short-lived host memory
     RC(enqueue_forward(m, st, T));
+    return copy_result_to_host(m, out_host);
+}
+
+// Streaming step.  Token P of the stream lives in slot P (P < sink) or sink + (P - sink) % window.  After the append
+// `active` = min(stream_pos + T, sink + window) slots are live, the oldest ring entry sits at ring offset ring_start, a
+// cached key rotates at its recency rank and the query of token P at min(P, sink + window - 1).  While nothing has been
+// evicted this is the engine's own host math (crates/llm/src/session.rs:539-635); afterwards it keeps the layout that
+// code documents (the engine derives the write slot and the rank table from the position before the append, which do
+// not agree with each other once the ring has wrapped).
+extern "C" int mynn_b200_model_stream(void *state, const int64_t *ids_host, int T, long long stream_pos, void *out_host) {
+    if (!state) return fail(MYNN_E_STATE, "model_stream: null state");
+    Model &m = *(Model *)state;
+    const mynn_b200_model_config &c = m.c;
+    if (c.stream_window <= 0) return fail(MYNN_E_STATE, "model_stream: the model was not configured with a streaming cache");
+    const int sink = c.stream_sink, window = c.stream_window, max_active = sink + window;
+    const int cap = c.max_prefill > 0 ? c.max_prefill : 1;
+    if (T <= 0 || T > cap) return fail(MYNN_E_ARG, "model_stream: %d tokens, capacity %d", T, cap);
+    if (stream_pos < 0 || !ids_host || !out_host) return fail(MYNN_E_ARG, "model_stream: bad argument");
+    if (T > 1 && stream_pos + T > max_active)
+        return fail(MYNN_E_ARG, "model_stream: a chunk of %d tokens at position %lld would evict (sink + window = %d); feed those tokens one at a time", T, stream_pos, max_active);
+    const long long after = stream_pos + T;
+    const int slot0 = stream_pos < sink ? (int)stream_pos : sink + (int)((stream_pos - sink) % window);
+    const int active = (int)std::min<long long>(after, max_active);
+    const int ring_start = after <= max_active ? 0 : (int)((after - sink) % window);
+    std::vector<int64_t> kvpos(c.max_seq_len), qpos(T);
+    for (int s = 0; s < c.max_seq_len; s++) {
+        kvpos[s] = s;
+        if (s >= sink && s < max_active) {
+            const int rank = sink + ((s - sink) - ring_start + window) % window;
+            if (rank < active) kvpos[s] = rank;
+        }
+    }
+    for (int i = 0; i < T; i++) qpos[i] = std::min<long long>(stream_pos + i, max_active - 1);
+    cudaStream_t st = m.stream;
+    struct { int32_t past, active; int64_t pos; } hdr = {slot0, active, qpos[0]};
+    MYNN_CUDA_OK(cudaMemcpyAsync(m.ids_dev, ids_host, (size_t)c.batch * T * 8, cudaMemcpyHostToDevice, st));
+    MYNN_CUDA_OK(cudaMemcpyAsync(m.pos_dev, qpos.data(), (size_t)T * 8, cudaMemcpyHostToDevice, st));
+    MYNN_CUDA_OK(cudaMemcpyAsync(m.kvpos_dev, kvpos.data(), (size_t)c.max_seq_len * 8, cudaMemcpyHostToDevice, st));
+    MYNN_CUDA_OK(cudaMemcpyAsync(m.past_dev, &hdr, 16, cudaMemcpyHostToDevice, st));
+    MYNN_CUDA_OK(cudaStreamSynchronize(st));  // the sources above are short-lived host memory
+    if (T == 1 && c.use_graph) {
+        if (!m.stream_graph_exec) {
+            cudaGraph_t graph = nullptr;
+            MYNN_CUDA_OK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+            int rc = enqueue_forward(m, st, 1);
+            cudaError_t e = cudaStreamEndCapture(st, &graph);
+            if (rc) {
+                if (graph) cudaGraphDestroy(graph);
+                return rc;
+            }
+            if (e != cudaSuccess) return fail(MYNN_E_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+            e = cudaGraphInstantiate(&m.stream_graph_exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) return fail(MYNN_E_CUDA, "graph instantiation failed: %s", cudaGetErrorString(e));
+        }
+        MYNN_CUDA_OK(cudaGraphLaunch(m.stream_graph_exec, st));
+    } else {
+        RC(enqueue_forward(m, st, T));
+    }
     return copy_result_to_host(m, out_host);
 }
 

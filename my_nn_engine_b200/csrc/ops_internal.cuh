@@ -9,11 +9,15 @@ namespace mynn {
 // RoPE(q), RoPE(k) and the KV append of one step in a single launch.
 // q/k/v: [B*S rows] with row strides (elements) q_stride/k_stride/v_stride, heads contiguous inside a row.
 // positions int64 [S] (device) select the cos/sin rows; K and V rows go to cache row (*past_len_dev + s).
-// q_out [B, Hq, S, D].
+// q_out [B, Hq, S, D].  rotate_k = 0 appends K unrotated (streaming cache: keys are rotated when they are read).
 int launch_rope_kv_append(cudaStream_t st, int dtype, void *q_out, void *k_cache, void *v_cache, const void *q,
                           const void *k, const void *v, long long q_stride, long long k_stride, long long v_stride,
                           const void *cos_t, const void *sin_t, const int64_t *positions, int B, int S, int Hq,
-                          int Hkv, int D, int cache_seq, const int32_t *past_len_dev);
+                          int Hkv, int D, int cache_seq, const int32_t *past_len_dev, int rotate_k = 1);
+
+// out[bh, s, :] = RoPE(x[bh, s, :]) at position kv_position[s] for the slots s < active of a [BH, cache_seq, D] cache.
+int launch_rope_cache_rows(cudaStream_t st, int dtype, void *out, const void *x, const void *cos_t, const void *sin_t,
+                           const int64_t *kv_position, int BH, int cache_seq, int D, int active_host, const int32_t *active_dev);
 
 // The same step for an int8 KV cache: K (after RoPE and its store rounding) and V are quantized per token into
 // k_cache/v_cache int8 [B, Hkv, cache_seq, D] with their scales [B, Hkv, cache_seq] in the storage dtype.

@@ -76,7 +76,7 @@ class DecoderModel:
     def __init__(self, cfg: dict, state: dict, dtype: str = "bf16", max_seq_len: int = 256, batch: int = 1,
                  tp_rank: int = 0, tp_world: int = 1, output: str = "logits", use_graph: bool = True,
                  max_prefill: int = 0, device=None, tensor_gemm: bool = True, tp_fused: bool = True,
-                 kv_int8: bool = False):
+                 kv_int8: bool = False, streaming=None):
         if not torch.cuda.is_available():
             raise RuntimeError("DecoderModel needs a CUDA device: the decode path has no CPU implementation")
         self.lib = ffi.lib()
@@ -154,6 +154,8 @@ class DecoderModel:
         kv_shape = (batch, self.n_kv // G, max_seq_len, self.head_dim)
         # kv_int8 (the engine's quant_kv_cache build option): int8 caches plus one scale per cached token
         self.kv_int8 = bool(kv_int8)
+        # streaming = (sink, window): the engine's streaming_kv option; steps then go through stream()
+        self.streaming = tuple(streaming) if streaming else None
         cache_dt = torch.int8 if kv_int8 else td
         self.k_cache = [torch.zeros(kv_shape, dtype=cache_dt, device=dev) for _ in range(self.n_layers)]
         self.v_cache = [torch.zeros(kv_shape, dtype=cache_dt, device=dev) for _ in range(self.n_layers)]
@@ -169,7 +171,8 @@ class DecoderModel:
                             head_dim=self.head_dim, ffn=self.ffn, vocab=self.vocab, max_seq_len=max_seq_len, batch=batch,
                             dtype=_FFI_DT[dtype], output_mode=1 if output == "ids" else 0, tp_rank=r, tp_world=G,
                             use_graph=int(use_graph), max_prefill=max_prefill, use_tensor_gemm=int(tensor_gemm),
-                            kv_int8=int(kv_int8),
+                            kv_int8=int(kv_int8), stream_sink=streaming[0] if streaming else 0,
+                            stream_window=streaming[1] if streaming else 0,
                             rms_eps=cfg["rms_norm_eps"])
         ffi.check(self.lib.mynn_b200_model_configure(ctypes.byref(c)))
         self._init_arr = (ctypes.c_void_p * len(init))(*init)
@@ -228,6 +231,13 @@ class DecoderModel:
         last position."""
         ids = torch.as_tensor(tokens, dtype=torch.int64).reshape(self.batch, -1).contiguous()
         ffi.check(self.lib.mynn_b200_model_prefill(self.state, ids.data_ptr(), ids.shape[1], past_len, self._out.data_ptr()))
+        return self._out if self.output == "ids" else self._out.view(self.batch, self.vocab)
+
+    def stream(self, tokens, stream_pos: int):
+        """Streaming-cache step: tokens [batch] (a decode step) or [batch, T] (a prefill chunk that must not evict) at
+        absolute stream positions stream_pos..; returns what step() returns for the last position."""
+        ids = torch.as_tensor(tokens, dtype=torch.int64).reshape(self.batch, -1).contiguous()
+        ffi.check(self.lib.mynn_b200_model_stream(self.state, ids.data_ptr(), ids.shape[1], int(stream_pos), self._out.data_ptr()))
         return self._out if self.output == "ids" else self._out.view(self.batch, self.vocab)
 
     def step_device(self, ids_dev, past_len: int, out_dev=None, stream=None):

@@ -28,7 +28,7 @@ class ModelConfig(ctypes.Structure):
 
     _fields_ = [(n, c_int32) for n in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab",
                                        "max_seq_len", "batch", "dtype", "output_mode", "tp_rank", "tp_world",
-                                       "use_graph", "max_prefill", "use_tensor_gemm", "kv_int8")] + [("rms_eps", c_float)]
+                                       "use_graph", "max_prefill", "use_tensor_gemm", "stream_sink", "stream_window", "kv_int8")] + [("rms_eps", c_float)]
 
 
 # name -> (restype, argtypes); every symbol declared in include/mynn_b200.h
@@ -50,6 +50,9 @@ SIGNATURES = {
     "mynn_b200_dynamic_quantize_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int]),
     "mynn_b200_quantized_matmul_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "mynn_b200_quantized_matmul": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t]),
+    "mynn_b200_kv_cache_update_ring": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "mynn_b200_rope_cache_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
+    "mynn_b200_attention_ring": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t]),
     "mynn_b200_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int]),
     "mynn_b200_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int]),
     "mynn_b200_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int]),
@@ -71,6 +74,7 @@ SIGNATURES = {
     "mynn_b200_model_status": (c_int, []),
     "mynn_b200_model_step_device": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "mynn_b200_model_prefill": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "mynn_b200_model_stream": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
     "mynn_b200_model_tp_export": (c_int, [c_void_p, c_void_p]),
     "mynn_b200_model_tp_attach": (c_int, [c_void_p, c_void_p]),
     "mynn_b200_launch_count": (c_int64, []),

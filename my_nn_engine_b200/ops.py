@@ -219,6 +219,39 @@ def quantized_matmul(lhs, lhs_scale, rhs, rhs_scale, out=None, workspace="auto")
     return out
 
 
+def kv_cache_update_ring(cache, new, offset: int, ring_sink: int, ring_window: int, ring_start: int):
+    """``KVCacheUpdate`` with ring operands: row offset+t goes to slot ring_phys_index(offset+t)."""
+    bh = cache.shape[0] * cache.shape[1]
+    ffi.check(ffi.lib().mynn_b200_kv_cache_update_ring(_stream(), _ptr(cache), _ptr(new), bh, cache.shape[2], new.shape[2],
+                                                       cache.shape[3], int(offset), ring_sink, ring_window, ring_start, _dt(cache)))
+    return cache
+
+
+def rope_cache_rows(cache, cos_table, sin_table, kv_position, active_seq_kv: int, out=None):
+    """``rope_fused`` over a cache [B,H,S,D]: slot s < active rotates at table row kv_position[s] (int64 CUDA [S])."""
+    b, h, s, d = cache.shape
+    if out is None:
+        out = torch.zeros_like(cache)
+    ffi.check(ffi.lib().mynn_b200_rope_cache_rows(_stream(), _ptr(out), _ptr(cache), _ptr(cos_table), _ptr(sin_table),
+                                                  _ptr(kv_position), b * h, s, d, int(active_seq_kv), _dt(cache)))
+    return out
+
+
+def attention_ring(q, k, v, scale: float, active_seq_kv: int, ring_sink: int, ring_window: int, ring_start: int,
+                   is_causal: bool = False, out=None, workspace=None):
+    """``Attention`` with the ring operands of the streaming cache."""
+    b, hq, sq, d = q.shape
+    hkv, sk = k.shape[1], k.shape[2]
+    if out is None:
+        out = torch.empty_like(q)
+    if workspace is None:
+        workspace = attention_workspace(b, hq, hkv, d, sk, q.device)
+    ffi.check(ffi.lib().mynn_b200_attention_ring(_stream(), _ptr(out), _ptr(q), _ptr(k), _ptr(v), float(scale), b, hq, hkv, sq,
+                                                 d, sk, int(active_seq_kv), int(is_causal), ring_sink, ring_window, ring_start,
+                                                 _dt(q), _ptr(workspace), workspace.numel()))
+    return out
+
+
 def rms_norm(x, weight, eps: float, out=None):
     d = x.shape[-1]
     if out is None:

@@ -48,6 +48,28 @@ class LlmSession:
         self.prefill_len = prefill_len if prefill is not None else None
         self.tokenizer = tokenizer
         self._past_len = 0
+        self.streaming = None  # (sink, window) when bound to a streaming-cache model: the stream has no length limit
+
+    @classmethod
+    def for_llama_streaming(cls, model, eos_token_id: int, prefill_len: Optional[int] = None, tokenizer=None):
+        """Bind to a ``DecoderModel`` built with ``streaming=(sink, window)`` (``LlmSession::for_llama_streaming``,
+        crates/llm/src/session.rs:539-635): ``past_len`` is the absolute stream position and never hits a limit; prompt
+        chunks are prefilled while they fit without evicting, later prompt tokens are fed one at a time."""
+        if model.batch != 1 or not model.streaming:
+            raise ValueError("for_llama_streaming needs a batch-1 model built with streaming=(sink, window)")
+
+        def pick(out):
+            return int(out[0]) if model.output == "ids" else argmax_last(out[0].float().tolist())
+
+        def step(token, stream_pos):
+            return pick(model.stream([token], stream_pos))
+
+        def prefill(ids, stream_pos):
+            return pick(model.stream([list(ids)], stream_pos))
+
+        self = cls(step, model.max_seq_len, eos_token_id, prefill if prefill_len else None, prefill_len, tokenizer)
+        self.streaming = model.streaming
+        return self
 
     @classmethod
     def for_llama(cls, model, eos_token_id: int, prefill_len: Optional[int] = None, tokenizer=None):
@@ -96,8 +118,15 @@ class LlmSession:
         token (crates/llm/src/session.rs:426-480)."""
         pos, tok = 0, None
         while pos < len(prompt_ids):
-            chunk = prompt_ids[pos:pos + self.prefill_len]
-            tok = self._prefill(chunk, self._past_len)
+            size = self.prefill_len
+            if self.streaming:  # a chunk must not evict: shrink it to the room left, then go token by token
+                size = min(size, sum(self.streaming) - self._past_len)
+            if size >= 2:
+                chunk = prompt_ids[pos:pos + size]
+                tok = self._prefill(chunk, self._past_len)
+            else:
+                chunk = prompt_ids[pos:pos + 1]
+                tok = self._decode_step(chunk[0], self._past_len)
             self._past_len += len(chunk)
             pos += len(chunk)
         return tok
@@ -119,10 +148,10 @@ class LlmSession:
             needed = self._past_len + -(-len(prompt_ids) // self.prefill_len) * self.prefill_len
         else:
             needed = self._past_len + len(prompt_ids)
-        if self.max_seq_len < needed:
+        if not self.streaming and self.max_seq_len < needed:
             raise PromptTooLong(needed, self.max_seq_len, self._past_len)
         for i in range(opts.max_new_tokens):
-            if self.max_seq_len < self._past_len + 1:
+            if not self.streaming and self.max_seq_len < self._past_len + 1:
                 break
             if i == 0:
                 if self.prefill_len:

@@ -43,11 +43,17 @@ class OracleLlama:
     whose values are already representable in the storage dtype."""
 
     def __init__(self, cfg: LlamaConfig, weights: dict, dtype: str, max_seq_len: int, batch: int = 1,
-                 kv_int8: bool = False):
-        """kv_int8: the engine's ``quant_kv_cache`` build option (crates/llm/src/decoder.rs:405-470): int8 caches with
+                 kv_int8: bool = False, streaming=None):
+        """streaming = (sink, window): the engine's ``streaming_kv`` build option (crates/llm/src/decoder.rs:280-360): K is
+        cached UNROTATED in a sink + ring layout, every step re-rotates the cached keys at their recency rank
+        (``rope_fused`` with ``kv_position``) and attention walks the ring in age order.  Index math: ref_ops.streaming_state.
+        kv_int8: the engine's ``quant_kv_cache`` build option (crates/llm/src/decoder.rs:405-470): int8 caches with
         one scale per cached token, written by QuantizingKVCacheUpdate and read by the attention's scale operands."""
         self.cfg, self.dtype, self.max_seq, self.batch = cfg, dtype, max_seq_len, batch
         self.kv_int8 = kv_int8
+        self.streaming = streaming
+        if streaming and kv_int8:
+            raise ValueError("streaming with an int8 cache is not modelled")
         self.w = {}
         for name, arr in weights.items():
             if name.endswith(".scale"):
@@ -87,8 +93,9 @@ class OracleLlama:
             rows = self._st(rows * scale[ids][..., None])
         return rows
 
-    def forward(self, ids: np.ndarray, positions: np.ndarray, past_len: int, active: int, is_prefill: bool):
-        """ids [B,S] -> logits [B,S,V] (f32 values representable in the storage dtype)."""
+    def forward(self, ids: np.ndarray, positions: np.ndarray, past_len: int, active: int, is_prefill: bool, stream=None):
+        """ids [B,S] -> logits [B,S,V] (f32 values representable in the storage dtype).  ``stream``: the dict of
+        ref_ops.streaming_state for a streaming step (positions are then the query positions)."""
         c = self.cfg
         b, s = ids.shape
         x = self._embed(ids)
@@ -101,6 +108,25 @@ class OracleLlama:
             k = self._linear(n1, p + "self_attn.k_proj.weight").reshape(b, s, c.n_kv_heads, c.head_dim).transpose(0, 2, 1, 3)
             v = self._linear(n1, p + "self_attn.v_proj.weight").reshape(b, s, c.n_kv_heads, c.head_dim).transpose(0, 2, 1, 3)
             q = self._st(R.rope(q, cos_r, sin_r))
+            if stream is not None:
+                for t, slot in enumerate(stream["slots"]):  # keys are cached as the projection left them
+                    self.k_cache[l][:, :, slot, :] = k[:, :, t, :]
+                    self.v_cache[l][:, :, slot, :] = v[:, :, t, :]
+                kp = stream["kv_position"]
+                k_rot = self._st(R.rope(self.k_cache[l], self.cos[kp], self.sin[kp]))
+                sink, window = self.streaming
+                a = self._st(R.attention_ring(q, k_rot, self.v_cache[l], scale, stream["active"], sink, window,
+                                              stream["ring_start"], is_causal=is_prefill))
+                a = a.transpose(0, 2, 1, 3).reshape(b, s, c.n_heads * c.head_dim)
+                o = self._linear(a, p + "self_attn.o_proj.weight")
+                x = self._st(x + o)
+                n2 = self._st(R.rms_norm(x, self.w[p + "post_attention_layernorm.weight"][1], c.eps))
+                g = self._linear(n2, p + "mlp.gate_proj.weight")
+                u = self._linear(n2, p + "mlp.up_proj.weight")
+                h = self._st(R.swish_mul(g, u))
+                d = self._linear(h, p + "mlp.down_proj.weight")
+                x = self._st(x + d)
+                continue
             k = self._st(R.rope(k, cos_r, sin_r))
             if self.kv_int8:
                 R.quantizing_kv_cache_update(self.k_cache[l], self.k_scale[l], k, past_len, self.dtype)
@@ -127,7 +153,11 @@ class OracleLlama:
     def decode_step(self, tokens: np.ndarray) -> np.ndarray:
         """tokens [B] -> next tokens [B]; inputs are [token], [past_len], past_len, past_len+1."""
         ids = np.asarray(tokens, dtype=np.int64).reshape(self.batch, 1)
-        logits = self.forward(ids, np.array([self.past_len]), self.past_len, self.past_len + 1, False)
+        if self.streaming:
+            st = R.streaming_state(self.past_len, 1, self.streaming[0], self.streaming[1], self.max_seq)
+            logits = self.forward(ids, st["q_positions"], self.past_len, st["active"], False, stream=st)
+        else:
+            logits = self.forward(ids, np.array([self.past_len]), self.past_len, self.past_len + 1, False)
         self.last_logits = logits[:, 0, :]
         self.past_len += 1
         return np.array([R.argmax_last(row.astype(np.float64)) for row in logits[:, 0, :]], dtype=np.int64)
@@ -143,8 +173,14 @@ class OracleLlama:
             chunk = min(t - pos0, prefill_len)
             padded = np.zeros((self.batch, prefill_len), dtype=np.int64)
             padded[:, :chunk] = prompt[:, pos0:pos0 + chunk]
-            positions = self.past_len + np.arange(prefill_len)
-            logits = self.forward(padded, positions, self.past_len, self.past_len + prefill_len, True)
+            if self.streaming:
+                # the engine pads streaming chunks too; padding rows would occupy ring slots, so the chunk is run at
+                # its real length here (rows past it influence nothing that is kept)
+                st = R.streaming_state(self.past_len, chunk, self.streaming[0], self.streaming[1], self.max_seq)
+                logits = self.forward(padded[:, :chunk], st["q_positions"], self.past_len, st["active"], True, stream=st)
+            else:
+                positions = self.past_len + np.arange(prefill_len)
+                logits = self.forward(padded, positions, self.past_len, self.past_len + prefill_len, True)
             self.past_len += chunk
             pos0 += chunk
             if pos0 == t:
@@ -158,7 +194,7 @@ class OracleLlama:
         prompt = np.asarray(prompt, dtype=np.int64).reshape(self.batch, -1)
         out = []
         for i in range(max_new_tokens):
-            if self.max_seq < self.past_len + 1:
+            if not self.streaming and self.max_seq < self.past_len + 1:
                 break
             if i == 0:
                 if prefill_len:

@@ -250,6 +250,64 @@ def kv_cache_update(cache: np.ndarray, new: np.ndarray, offset: int) -> np.ndarr
     return cache
 
 
+def ring_phys_index(rank: int, ring_sink: int, ring_window: int, ring_start: int) -> int:
+    """Logical row -> physical cache slot of the sink + ring layout (src/codegen/cuda/cpp/common.cuh:55-60).  The first
+    ``ring_sink`` rows stay in place; later rows live in a ring of ``ring_window`` slots whose oldest entry is at ring
+    offset ``ring_start``.  ring_window == 0 switches the mapping off.  Only the CUDA backend of the reference has it (the
+    CPU backend ignores the ring operands), so everything built on it here restates the CUDA kernels."""
+    if ring_window == 0 or rank < ring_sink:
+        return rank
+    return ring_sink + (ring_start + (rank - ring_sink)) % ring_window
+
+
+def kv_cache_update_ring(cache: np.ndarray, new: np.ndarray, offset: int, ring_sink: int, ring_window: int, ring_start: int):
+    """KVCacheUpdate with ring operands: cache[b,h,phys(offset+t),:] = new[b,h,t,:]
+    (src/codegen/cuda/cpp/kvcache_update.cuh:6-26)."""
+    for t in range(new.shape[2]):
+        cache[:, :, ring_phys_index(offset + t, ring_sink, ring_window, ring_start), :] = new[:, :, t, :]
+    return cache
+
+
+def attention_ring(q, k, v, scale, active_seq_kv, ring_sink, ring_window, ring_start, is_causal=False):
+    """Attention over a sink + ring cache: logical rows 0..active-1 are visited in order, each read from its physical
+    slot (src/codegen/cuda/cpp/attention.cuh:546-600).  Implemented as a gather into logical order followed by the plain
+    recurrence, which is the same arithmetic in the same order."""
+    active = int(active_seq_kv)
+    idx = [ring_phys_index(r, ring_sink, ring_window, ring_start) for r in range(active)]
+    kg, vg = np.asarray(k)[:, :, idx, :], np.asarray(v)[:, :, idx, :]
+    return attention(q, kg, vg, scale, active, is_causal=is_causal)
+
+
+def streaming_state(stream_pos: int, n_new: int, sink: int, window: int, max_seq_len: int):
+    """Host-side index math of a streaming (sink + ring) step that appends tokens stream_pos .. stream_pos+n_new-1.
+
+    Token P lives in slot P while P < sink + window... precisely: slot(P) = P for P < sink, else sink + (P - sink) % window.
+    After the append ``active`` rows are live; the oldest ring entry sits at ring offset ``ring_start``; the RoPE
+    position of a cached row is its logical (recency) rank and the query of token P rotates at min(P, sink+window-1).
+    Returns dict(slots, q_positions, active, ring_start, kv_position[max_seq_len]).
+
+    While nothing has been evicted (stream_pos + n_new <= sink + window) this is exactly what the engine computes
+    (crates/llm/src/session.rs:539-635: identity slots, ring_start 0, kv_position = slot).  After that point the
+    engine's host code derives ring_start and kv_position from the position BEFORE the append and reuses ring_start for
+    the write slot, which sends the new row to slot sink + 2*((P-sink) % window) % window and rotates the newest key as if
+    it were the oldest; that regime is not covered by any test of the engine.  This function follows the layout the
+    engine documents (sink rows fixed, ring holds the last ``window`` tokens in age order) consistently instead."""
+    max_active = sink + window
+    after = stream_pos + n_new
+    slots = [p if p < sink else sink + (p - sink) % window for p in range(stream_pos, after)]
+    active = min(after, max_active)
+    ring_start = 0 if after <= max_active else (after - sink) % window
+    kv_position = np.arange(max_seq_len, dtype=np.int64)
+    for slot in range(sink, min(max_active, max_seq_len)):
+        rank = sink + ((slot - sink) - ring_start + window) % window
+        if rank < active:
+            kv_position[slot] = rank
+    q_positions = np.minimum(np.arange(stream_pos, after), max_active - 1).astype(np.int64)
+    if after > max_active:  # a chunk that evicts: every query row sits at the end of what it can see
+        q_positions = np.minimum(q_positions, max_active - 1)
+    return dict(slots=slots, q_positions=q_positions, active=active, ring_start=ring_start, kv_position=kv_position)
+
+
 def quantizing_kv_cache_update(cache: np.ndarray, scale: np.ndarray, new: np.ndarray, offset: int, scale_dtype: str = "bf16"):
     """INT8 KV cache append with one scale per token (src/codegen/cpu/translator.rs:4090-4372):
     s = max_d |new| * (1/127) in f32; inv = 127 / max (0 for an all-zero row); q = trunc(v * inv +- 0.5) clamped to

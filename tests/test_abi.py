@@ -50,7 +50,7 @@ def test_model_configure_validation():
     lib = ffi.lib()
     cfg = ffi.ModelConfig(n_layers=2, hidden=64, n_heads=4, n_kv_heads=3, head_dim=16, ffn=128, vocab=100,
                           max_seq_len=32, batch=1, dtype=ffi.BF16, output_mode=0, tp_rank=0, tp_world=1, use_graph=0,
-                          max_prefill=0, use_tensor_gemm=1, kv_int8=0, rms_eps=1e-5)
+                          max_prefill=0, use_tensor_gemm=1, stream_sink=0, stream_window=0, kv_int8=0, rms_eps=1e-5)
     assert lib.mynn_b200_model_configure(cfg) == ffi.E_ARG  # 4 heads not a multiple of 3 kv heads
     cfg.n_kv_heads = 2
     assert lib.mynn_b200_model_configure(cfg) == ffi.OK

@@ -118,6 +118,63 @@ def test_quantized_matmul_goldens(single_op, name):
     assert np.abs(out - want).max() <= np.abs(want).max() * 2.0 ** -7  # in fact within one bf16 ulp of the output scale
 
 
+def test_ring_index_and_streaming_state_properties():
+    """ring_phys_index is the engine's formula; streaming_state keeps sink rows in place, the last `window` tokens in the
+    ring, ranks equal to recency order, and reduces to the engine's host math while nothing has been evicted."""
+    assert [R.ring_phys_index(r, 2, 3, 1) for r in range(5)] == [0, 1, 3, 4, 2]
+    assert [R.ring_phys_index(r, 2, 0, 1) for r in range(5)] == [0, 1, 2, 3, 4]
+    sink, window, ms = 3, 5, 12
+    owner = {}
+    for p in range(40):
+        st = R.streaming_state(p, 1, sink, window, ms)
+        owner[st["slots"][0]] = p
+        live = sorted(owner.values())
+        assert live == list(range(min(sink, p + 1))) + list(range(max(sink, p + 1 - window), p + 1))
+        assert st["active"] == len(live) and st["q_positions"][0] == st["active"] - 1
+        for rank, tok in enumerate(live):  # logical rank -> slot -> token, and the slot's RoPE position is its rank
+            slot = R.ring_phys_index(rank, sink, window, st["ring_start"])
+            assert owner[slot] == tok and st["kv_position"][slot] == rank
+        if p + 1 <= sink + window:
+            assert st["ring_start"] == 0 and st["slots"] == [p] and list(st["kv_position"]) == list(range(ms))
+
+
+def test_attention_ring_equals_plain_attention_over_the_gathered_rows():
+    rng = np.random.default_rng(4)
+    k = rng.standard_normal((2, 2, 10, 8)).astype(np.float32)
+    v = rng.standard_normal((2, 2, 10, 8)).astype(np.float32)
+    q = rng.standard_normal((2, 4, 1, 8)).astype(np.float32)
+    order = [0, 1, 5, 6, 7, 2, 3, 4]  # sink 2, window 6, ring_start 3
+    got = R.attention_ring(q, k, v, 0.3, 8, 2, 6, 3)
+    want = R.attention(q, k[:, :, order], v[:, :, order], 0.3, 8)
+    assert np.array_equal(got, want)
+    cache = np.zeros((1, 1, 10, 2), np.float32)
+    R.kv_cache_update_ring(cache, np.arange(1, 7, dtype=np.float32).reshape(1, 1, 3, 2), 6, 2, 6, 3)
+    assert [int(cache[0, 0, s, 0]) for s in range(10)] == [0, 0, 0, 1, 3, 5, 0, 0, 0, 0]  # ranks 6, 7, 8 -> slots 3, 4, 5
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_tiny_llama_streaming_reproduces_expected_ids(tiny_llama, dtype):
+    """crates/llm/tests/tinyllama_random.rs:23-49: the golden ids are produced in streaming mode, sink 4 + window 28."""
+    cfg, weights, prompt, _, expected = tiny_llama
+    m = OracleLlama(LlamaConfig.from_hf(cfg), weights, dtype, 32, streaming=(4, 28))
+    assert m.generate(prompt[None, :], len(expected))[0].tolist() == expected.tolist()
+
+
+def test_streaming_oracle_matches_plain_oracle_until_eviction_and_differs_after(tiny_llama):
+    cfg, weights, prompt, _, _ = tiny_llama
+    c = LlamaConfig.from_hf(cfg)
+    plain = OracleLlama(c, weights, "f32", 64)
+    stream = OracleLlama(c, weights, "f32", 64, streaming=(2, 6))
+    toks = np.array([[int(prompt[0])]])
+    same = []
+    for step in range(14):
+        a = plain.decode_step(toks[:, 0])
+        b = stream.decode_step(toks[:, 0])
+        same.append(np.abs(plain.last_logits - stream.last_logits).max() < 1e-5)
+        toks = a[:, None]
+    assert all(same[:8]) and not all(same[8:])  # 8 = sink + window tokens fit; the 9th evicts one
+
+
 def test_dequantize_linear_golden(single_op):
     fx = single_op("dequantize_linear")
     x, scale = fx.inputs
