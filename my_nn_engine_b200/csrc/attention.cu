@@ -327,6 +327,10 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
     const bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % 16) == 0;
     const bool fast = Sq == 1 && (D == 64 || D == 128) && G <= 8 && dtype != MYNN_F32 && aligned;
     if (!fast) {
+        static const bool use_tiled = [] { const char *e = getenv("MYNN_PREFILL_ATTENTION"); return !e || atoi(e) != 0; }();
+        if (use_tiled && attention_prefill_supported(Sq, D, dtype, q, k, v, out))
+            return launch_attention_prefill(st, out, q, k, v, scale, B, Hq, Hkv, Sq, D, cache_seq_len, active_seq_kv, active_seq_kv_dev,
+                                            is_causal, dtype, out_bshd);
         if (dtype == MYNN_F32) return launch_generic<float>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, active_seq_kv_dev, is_causal, out_bshd);
         if (dtype == MYNN_BF16) return launch_generic<__nv_bfloat16>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, active_seq_kv_dev, is_causal, out_bshd);
         return launch_generic<__half>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, active_seq_kv_dev, is_causal, out_bshd);

@@ -117,6 +117,22 @@ def attn(b, hq, hkv, d, length, dtype="bf16", copies=None, quiet=False, kv="16bi
     return res
 
 
+def prefill_attn(b, hq, hkv, d, length, dtype="bf16", quiet=False):
+    """Causal self-attention of a whole prompt (Sq = kv length): 4 * Sq^2 / 2 * D * Hq * B flops."""
+    td = _DT[dtype]
+    q = torch.randn(b, hq, length, d, device="cuda").to(td)
+    ks = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(2)]
+    vs = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(2)]
+    out = torch.empty_like(q)
+    us = _time_graph([(lambda k=k, v=v: ops.attention(q, k, v, 1 / np.sqrt(d), length, True, out=out)) for k, v in zip(ks, vs)])
+    flops = 4.0 * length * (length + 1) / 2 * d * hq * b
+    res = {"kernel": "attention_prefill", "b": b, "hq": hq, "hkv": hkv, "d": d, "len": length, "dtype": dtype, "us": us,
+           "TFLOPs": flops / us / 1e6, "frac_of_measured_bf16_peak": flops / us / 1e6 / _peak_tflops()}
+    if not quiet:
+        print(json.dumps(res), flush=True)
+    return res
+
+
 def w8a8(m, n, k, dtype="bf16", copies=None, quiet=False):
     """QuantizedMatMul (int8 x int8) on the tcgen05 kernel; TFLOP/s counts 2 M N K integer operations."""
     td = _DT[dtype]
@@ -171,6 +187,13 @@ def main():
     a.add_argument("--dtype", default="bf16")
     a.add_argument("--copies", type=int, default=None)
     a.add_argument("--kv", default="16bit", choices=["16bit", "int8"])
+    pa = sub.add_parser("prefill_attn")
+    pa.add_argument("--b", type=int, default=1)
+    pa.add_argument("--hq", type=int, default=32)
+    pa.add_argument("--hkv", type=int, default=8)
+    pa.add_argument("--d", type=int, default=128)
+    pa.add_argument("--len", type=int, default=2048)
+    pa.add_argument("--dtype", default="bf16")
     q = sub.add_parser("w8a8")
     q.add_argument("--m", type=int, default=2048)
     q.add_argument("--n", type=int, default=14336)
@@ -181,6 +204,8 @@ def main():
     args = ap.parse_args()
     if args.cmd == "gemm":
         gemm(args.m, args.n, args.k, args.dtype, args.ksplit, args.copies, kernel=args.kernel)
+    elif args.cmd == "prefill_attn":
+        prefill_attn(args.b, args.hq, args.hkv, args.d, args.len, args.dtype)
     elif args.cmd == "w8a8":
         w8a8(args.m, args.n, args.k, args.dtype, args.copies)
     elif args.cmd == "attn":

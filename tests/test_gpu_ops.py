@@ -220,6 +220,29 @@ def test_attention_decode_vs_oracle(dtype, b, hq, hkv, d, sk, active):
     assert rel_err(to_np(out2), want) <= 1e-2
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,hq,hkv,sq,d,cache,active,causal", [(2, 8, 2, 100, 128, 300, 250, True), (1, 4, 4, 64, 64, 64, 64, True),
+                                                               (1, 2, 1, 130, 128, 512, 130, True), (2, 4, 2, 33, 64, 200, 77, False),
+                                                               (1, 32, 8, 2, 128, 40, 9, True), (3, 6, 3, 65, 64, 129, 129, True),
+                                                               (1, 8, 8, 257, 128, 257, 257, False)])
+def test_attention_prefill_tiled_kernel_vs_oracle(dtype, b, hq, hkv, sq, d, cache, active, causal):
+    """Several query rows on the tiled tensor-core kernel: tile edges in the query rows (100, 130, 33, 2, 65, 257 over
+    64-row tiles) and in the kv rows, a past longer than the chunk, GQA groups 1..4, causal and full attention, and rows
+    past active_seq_kv filled with NaN (they must not matter).  Also the device-scalar form of active_seq_kv."""
+    rng = np.random.default_rng(sq * 7 + active + d)
+    q = torch.from_numpy(rng.standard_normal((b, hq, sq, d)).astype(np.float32)).to(dtype)
+    k = torch.from_numpy(rng.standard_normal((b, hkv, cache, d)).astype(np.float32)).to(dtype)
+    v = torch.from_numpy(rng.standard_normal((b, hkv, cache, d)).astype(np.float32)).to(dtype)
+    scale = 1.0 / np.sqrt(d)
+    want = R.attention(q.float().numpy(), k.float().numpy(), v.float().numpy(), scale, active, is_causal=causal)
+    k[:, :, active:] = float("nan")
+    v[:, :, active:] = float("nan")
+    out = ops.attention(q.cuda(), k.cuda(), v.cuda(), scale, active, causal)
+    assert rel_err(to_np(out), want) <= 1e-2
+    out2 = ops.attention(q.cuda(), k.cuda(), v.cuda(), scale, torch.tensor([active], dtype=torch.int32, device="cuda"), causal)
+    assert torch.equal(out, out2)
+
+
 def test_attention_ignores_rows_past_active_even_if_nan():
     b, hq, hkv, d, sk, active = 1, 8, 2, 128, 128, 70
     rng = np.random.default_rng(5)
