@@ -66,6 +66,12 @@ int mynn_b200_dequant_matmul_residual(void *stream, void *out, const void *act, 
                                       const void *residual, int M, int N, int K, int dtype, void *workspace,
                                       size_t workspace_bytes);
 
+/* DequantMatMul with the activations of the PREVIOUS mynn_b200_dequant_matmul call on the same workspace (same M, K
+ * and activation tensor): the limb conversion is skipped.  For several weight matrices applied to one activation tensor
+ * (q/k/v, gate/up when they are not stored adjacently).  Needs the tensor-core path: workspace, M <= 32, K % 16 == 0. */
+int mynn_b200_dequant_matmul_same_act(void *stream, void *out, const int8_t *wq, const void *scale, int M, int N, int K,
+                                      int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes);
+
 /* Synchronises the stream and reads the workspace status word: MYNN_E_CUDA if a bounded pipeline wait inside the
  * tcgen05 kernel expired (the outputs of that call are then invalid), MYNN_OK otherwise. */
 int mynn_b200_dequant_matmul_check(void *stream, const void *workspace);

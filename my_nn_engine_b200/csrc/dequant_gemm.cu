@@ -429,6 +429,19 @@ extern "C" int mynn_b200_dequant_matmul_residual(void *stream, void *out, const 
                                          workspace, workspace_bytes);
 }
 
+// DequantMatMul for activations that the PREVIOUS call on this workspace already converted: several weight matrices
+// applied to one activation tensor (q, k and v of a layer; gate and up) need the conversion to limbs only once.
+extern "C" int mynn_b200_dequant_matmul_same_act(void *stream, void *out, const int8_t *wq, const void *scale, int M, int N,
+                                                 int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes) {
+    using namespace mynn;
+    if (M <= 0 || N <= 0 || K <= 0) return fail(MYNN_E_ARG, "dequant_matmul_same_act: bad shape");
+    if (!out || !wq || !scale) return fail(MYNN_E_ARG, "dequant_matmul_same_act: null pointer");
+    if (!dtype_ok(act_dtype) || !dtype_ok(out_dtype)) return fail(MYNN_E_ARG, "dequant_matmul_same_act: bad dtype");
+    if (!workspace || !i8_gemm_supported(M, N, K, wq, act_dtype, out_dtype))
+        return fail(MYNN_E_UNSUPPORTED, "dequant_matmul_same_act: needs the tensor-core path (a workspace, at most %d rows, K %% 16 == 0, 16-byte aligned weights)", kI8MaxRows);
+    return i8_gemm_launch((cudaStream_t)stream, out, nullptr, wq, scale, nullptr, M, N, K, act_dtype, out_dtype, workspace, workspace_bytes);
+}
+
 // Reads the status word of a DequantMatMul workspace after synchronising the stream: non-zero means a pipeline
 // wait inside the tcgen05 kernel ran out of time and the outputs of that call are invalid.
 extern "C" int mynn_b200_dequant_matmul_check(void *stream, const void *workspace) {

@@ -39,6 +39,7 @@ SIGNATURES = {
     "mynn_b200_dequant_matmul_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "mynn_b200_dequant_matmul": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t]),
     "mynn_b200_dequant_matmul_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t]),
+    "mynn_b200_dequant_matmul_same_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t]),
     "mynn_b200_dequant_matmul_check": (c_int, [c_void_p, c_void_p]),
     "mynn_b200_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "mynn_b200_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_size_t]),

@@ -76,6 +76,22 @@ def dequant_matmul(act, wq, scale, axis: int = 0, out=None, workspace="auto"):
     return out
 
 
+def dequant_matmul_same_act(act_like, wq, scale, out=None, workspace="auto"):
+    """DequantMatMul of another weight matrix with the activations of the previous ``dequant_matmul`` call on the same
+    workspace; ``act_like`` only supplies shape and dtype (its data is not read)."""
+    k = wq.shape[1]
+    m = act_like.numel() // k
+    n = wq.shape[0]
+    if out is None:
+        out = torch.empty(act_like.shape[:-1] + (n,), dtype=scale.dtype, device=wq.device)
+    if isinstance(workspace, str):
+        workspace = dequant_matmul_workspace(m, n, k, wq.device)
+    ffi.check(ffi.lib().mynn_b200_dequant_matmul_same_act(_stream(), _ptr(out), _ptr(wq), _ptr(scale), m, n, k, _dt(act_like),
+                                                          _dt(scale), None if workspace is None else _ptr(workspace),
+                                                          0 if workspace is None else workspace.numel()))
+    return out
+
+
 def dequant_matmul_residual(act, wq, scale, residual, out=None, workspace="auto"):
     """round(residual + round(DequantMatMul(act, wq, scale))); ``out`` may alias ``residual``."""
     n, k = wq.shape

@@ -127,6 +127,22 @@ def test_dequant_matmul_cluster_splits_agree(ksplit, path):
     assert torch.equal(a, b)
 
 
+def test_dequant_matmul_same_activations_skip_the_conversion():
+    """Two weight matrices on one activation tensor: the second call reuses the limbs left in the workspace and gives
+    exactly what a full call gives."""
+    rng = np.random.default_rng(17)
+    act = torch.from_numpy(rng.standard_normal((32, 4096)).astype(np.float32)).bfloat16().cuda()
+    w1, w2 = (dev(rng.integers(-127, 128, size=(n, 4096), dtype=np.int8)) for n in (1024, 6144))
+    s1, s2 = (torch.from_numpy(rng.uniform(0.002, 0.02, n).astype(np.float32)).bfloat16().cuda() for n in (1024, 6144))
+    full2 = ops.dequant_matmul(act, w2, s2)
+    ops.dequant_matmul(act, w1, s1)
+    again2 = ops.dequant_matmul_same_act(act, w2, s2)
+    assert torch.equal(again2, full2)
+    from my_nn_engine_b200 import ffi
+    with pytest.raises(ffi.MynnError):
+        ops.dequant_matmul_same_act(act, w2, s2, workspace=None)
+
+
 def test_dequant_matmul_config1_both_layouts():
     """BASELINE config 1: int8 W [2048,5632] uniform in [-127,127], f32 per-output-channel scale U(0.002,0.02),
     f32 activation [1,2048] ~ N(0,1), seed 0 — as the literal [K,N]/axis-1 graph and as the fused [N,K]/axis-0 op."""
