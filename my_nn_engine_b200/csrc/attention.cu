@@ -217,14 +217,18 @@ int decode_bind_workspace(DecodeParams &p, int B, int D, void *workspace, size_t
     p.ws_o = nullptr;
     p.ws_ml = nullptr;
     p.ws_ticket = nullptr;
-    if (p.splits <= 1) return MYNN_OK;
+    p.row_ticket = nullptr;
     const size_t need = mynn_b200_attention_workspace_bytes(B, p.Hq, p.Hkv, D, p.cache_seq);
-    if (!workspace || workspace_bytes < need)
-        return fail(MYNN_E_ARG, "attention: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+    const bool have_ws = workspace && workspace_bytes >= need;
     const size_t pairs = (size_t)B * p.Hkv;
+    if (have_ws) p.row_ticket = (unsigned *)workspace + pairs;
+    if (p.limbs && !have_ws) return fail(MYNN_E_ARG, "attention: the limb output needs the attention workspace (%zu bytes)", need);
+    if (p.splits <= 1) return MYNN_OK;
+    if (!have_ws)
+        return fail(MYNN_E_ARG, "attention: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
     char *w = (char *)workspace;
     p.ws_ticket = (unsigned *)w;
-    w += align_up(pairs * sizeof(unsigned), 256);
+    w += align_up((pairs + (size_t)B) * sizeof(unsigned), 256);
     p.ws_ml = (float *)w;
     w += align_up(pairs * kMaxSplits * 8 * 2 * sizeof(float), 256);
     p.ws_o = (float *)w;
@@ -238,7 +242,7 @@ using namespace mynn;
 extern "C" size_t mynn_b200_attention_workspace_bytes(int B, int Hq, int Hkv, int D, int cache_seq_len) {
     if (B <= 0 || Hkv <= 0 || D <= 0) return 0;
     const size_t pairs = (size_t)B * Hkv;
-    const size_t tickets = align_up(pairs * sizeof(unsigned), 256);
+    const size_t tickets = align_up((pairs + (size_t)B) * sizeof(unsigned), 256);  // per (batch, kv head) and per batch row
     const size_t ml = align_up(pairs * kMaxSplits * 8 * 2 * sizeof(float), 256);
     const size_t o = pairs * kMaxSplits * 8 * (size_t)D * sizeof(float);
     (void)Hq;
@@ -313,10 +317,15 @@ extern "C" int mynn_b200_attention_ring(void *stream, void *out, const void *q, 
     return launch_generic<__half>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, nullptr, is_causal, 0, rs, rw, r0);
 }
 
+bool mynn::attention_decode_fast_path(int Sq, int D, int Hq, int Hkv, int dtype, const void *q, const void *k, const void *v) {
+    const bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % 16) == 0;
+    return Sq == 1 && (D == 64 || D == 128) && Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 8 && dtype != MYNN_F32 && aligned;
+}
+
 int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
                            int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
                            const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
-                           size_t workspace_bytes, int out_bshd) {
+                           size_t workspace_bytes, int out_bshd, int8_t *limbs_out, float *ascale_out) {
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Sq < 0 || D <= 0 || cache_seq_len < 0 || active_seq_kv < 0)
         return fail(MYNN_E_ARG, "attention: bad shape");
     if (Hq % Hkv != 0) return fail(MYNN_E_ARG, "attention: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
@@ -326,6 +335,7 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
     const int G = Hq / Hkv;
     const bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % 16) == 0;
     const bool fast = Sq == 1 && (D == 64 || D == 128) && G <= 8 && dtype != MYNN_F32 && aligned;
+    if (!fast && limbs_out) return fail(MYNN_E_UNSUPPORTED, "attention: the limb output exists only on the decode fast path");
     if (!fast) {
         static const bool use_tiled = [] { const char *e = getenv("MYNN_PREFILL_ATTENTION"); return !e || atoi(e) != 0; }();
         if (use_tiled && attention_prefill_supported(Sq, D, dtype, q, k, v, out))
@@ -352,6 +362,8 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
     p.splits = decode_splits(B, Hkv, rows_bound);
     p.k_scale = nullptr;
     p.v_scale = nullptr;
+    p.limbs = limbs_out;
+    p.ascale = ascale_out;
     if (int rc = decode_bind_workspace(p, B, D, workspace, workspace_bytes)) return rc;
     if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B) : launch_decode<__nv_bfloat16, 128>(st, p, B);
     return D == 64 ? launch_decode<__half, 64>(st, p, B) : launch_decode<__half, 128>(st, p, B);
@@ -438,6 +450,9 @@ extern "C" int mynn_b200_attention_decode_noalloc(void *stream, void *out, const
     p.ws_o = nullptr;
     p.ws_ml = nullptr;
     p.ws_ticket = nullptr;
+    p.limbs = nullptr;
+    p.ascale = nullptr;
+    p.row_ticket = nullptr;
     if (p.splits > 1) {
         const size_t pairs = (size_t)B * Hkv;
         const size_t tickets = align_up(pairs * sizeof(unsigned), 256);

@@ -59,7 +59,92 @@ struct DecodeParams {
     float *ws_o;          // [B*Hkv][splits][8][D]
     float *ws_ml;         // [B*Hkv][splits][8][2]
     unsigned *ws_ticket;  // [B*Hkv], zero before first use; the combining CTA re-zeroes it
+    // Optional: the finished output row of a sequence ([Hq * D], one query row) is also left as activation limbs for the
+    // DequantMatMul that follows (o_proj), by the CTA that completes the row.
+    int8_t *limbs;        // [3 B][Hq * D] limb rows (3 b + l), or null
+    float *ascale;        // [B] row scales
+    unsigned *row_ticket; // [B], zero before first use; re-zeroed by the CTA that converts the row
 };
+
+// Called by every CTA that has stored final outputs of (batch b, one kv head): the last of the Hkv to arrive converts the
+// whole row to limbs with the arithmetic of the limb pre-pass (23-bit fixed point, power-of-two row scale).
+template <typename T, int D>
+__device__ __forceinline__ void decode_row_limbs(const DecodeParams &p, int b, unsigned *sm_flag, float *sm_red) {
+    if (p.limbs == nullptr) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) *sm_flag = (atomicAdd(&p.row_ticket[b], 1u) == (unsigned)(p.Hkv - 1)) ? 1u : 0u;
+    __syncthreads();
+    if (!*sm_flag) return;
+    __threadfence();
+    const int K = p.Hq * D;
+    const T *row = reinterpret_cast<const T *>(p.out) + (size_t)b * K;
+    // up to 8 x 4 elements per thread are fetched in one go (one L2 round trip) and kept for the second pass; longer rows
+    // are read again
+    constexpr int kKeep = 8, kStride = 4 * kAttnWarps * 32;
+    uint2 raw[kKeep];
+    float mx = 0.f;
+    bool bad = false;
+#pragma unroll
+    for (int u = 0; u < kKeep; u++) {
+        const int i = 4 * threadIdx.x + u * kStride;
+        raw[u] = i < K ? __ldcg(reinterpret_cast<const uint2 *>(row + i)) : make_uint2(0u, 0u);
+    }
+    auto scan = [&](const uint2 &r) {
+        const T *e = reinterpret_cast<const T *>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float v = to_f32<T>(e[j]);
+            bad |= !(fabsf(v) <= 3.0e38f);
+            mx = fmaxf(mx, fabsf(v));
+        }
+    };
+#pragma unroll
+    for (int u = 0; u < kKeep; u++) scan(raw[u]);
+#pragma unroll 1
+    for (int i = 4 * threadIdx.x + kKeep * kStride; i < K; i += kStride) scan(__ldcg(reinterpret_cast<const uint2 *>(row + i)));
+    mx = warp_max(mx);
+    const unsigned anybad = __syncthreads_or(bad);
+    if ((threadIdx.x & 31) == 0) sm_red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    float t = sm_red[0];
+#pragma unroll
+    for (int w = 1; w < kAttnWarps; w++) t = fmaxf(t, sm_red[w]);
+    int e2 = 0;
+    if (t > 0.f) frexpf(t, &e2);
+    const float sc1 = t > 0.f ? ldexpf(1.0f, 22 - e2) : 1.0f;
+    const float sc = anybad ? 0.f : sc1;
+    if (threadIdx.x == 0) p.ascale[b] = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc1;
+    uint32_t *l0 = reinterpret_cast<uint32_t *>(p.limbs + (size_t)(3 * b) * K);
+    uint32_t *l1 = reinterpret_cast<uint32_t *>(p.limbs + (size_t)(3 * b + 1) * K);
+    uint32_t *l2 = reinterpret_cast<uint32_t *>(p.limbs + (size_t)(3 * b + 2) * K);
+    auto emit = [&](const uint2 &r, int i) {
+        const T *e = reinterpret_cast<const T *>(&r);
+        uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int A = sc == 0.f ? 0 : __float2int_rn(to_f32<T>(e[j]) * sc);
+            const int d0 = (int)(int8_t)(A & 0xFF);
+            A = (A - d0) >> 8;
+            const int d1 = (int)(int8_t)(A & 0xFF);
+            A = (A - d1) >> 8;
+            w0 |= (uint32_t)(d0 & 0xFF) << (8 * j);
+            w1 |= (uint32_t)(d1 & 0xFF) << (8 * j);
+            w2 |= (uint32_t)(A & 0xFF) << (8 * j);
+        }
+        l0[i >> 2] = w0;
+        l1[i >> 2] = w1;
+        l2[i >> 2] = w2;
+    };
+#pragma unroll
+    for (int u = 0; u < kKeep; u++) {
+        const int i = 4 * threadIdx.x + u * kStride;
+        if (i < K) emit(raw[u], i);
+    }
+#pragma unroll 1
+    for (int i = 4 * threadIdx.x + kKeep * kStride; i < K; i += kStride) emit(__ldcg(reinterpret_cast<const uint2 *>(row + i)), i);
+    if (threadIdx.x == 0) p.row_ticket[b] = 0u;
+}
 
 // Tail of a decode CTA.  Every lane holds NACC accumulator tiles of O^T: tile i, registers {0,1,2,3} are
 // (head 2t, d), (head 2t+1, d), (head 2t, d+1), (head 2t+1, d+1) with d = DMap::d(i, g).  The warps are merged through
@@ -69,7 +154,8 @@ template <typename T, int D, int NACC, typename DMap>
 __device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (&o)[NACC][4], float m_run, float l_run) {
     __shared__ float sm_o[kAttnWarps][8][D];
     __shared__ float sm_m[kAttnWarps][8], sm_l[kAttnWarps][8];
-    __shared__ unsigned sm_last;
+    __shared__ unsigned sm_last, sm_row_last;
+    __shared__ float sm_red[kAttnWarps];
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int G = p.G;
@@ -117,7 +203,10 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (
             }
         }
     }
-    if (p.splits == 1) return;
+    if (p.splits == 1) {
+        decode_row_limbs<T, D>(p, b, &sm_row_last, sm_red);
+        return;
+    }
 
     __threadfence();
     __syncthreads();
@@ -141,6 +230,7 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (
         outp[(size_t)hd * D + d] = from_f32<T>(O / L);
     }
     if (threadIdx.x == 0) p.ws_ticket[pair] = 0u;
+    decode_row_limbs<T, D>(p, b, &sm_row_last, sm_red);
 }
 
 // All CTAs of a launch last equally long, so the grid should fit in ONE wave of resident CTAs (148 SMs): a partly

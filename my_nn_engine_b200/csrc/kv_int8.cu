@@ -483,6 +483,8 @@ int launch_attention_q8(cudaStream_t st, void *out, const void *q, const void *k
     p.v = v;
     p.k_scale = k_scale;
     p.v_scale = v_scale;
+    p.limbs = nullptr;
+    p.ascale = nullptr;
     p.scale = scale;
     p.Hq = Hq;
     p.Hkv = Hkv;

@@ -146,6 +146,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         const LayerW &L = m.layers[l];
         // --- attention block ---
         char *qb = (char *)m.qkv;
+        bool attn_limbs = false;
         long long qs, ks, vs;
         const char *kb, *vb;
         if (L.qkv_fused) {
@@ -180,14 +181,21 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         } else {
             RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
                                      S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
+            // decode: the attention kernel also leaves its output rows as the activation limbs of o_proj
+            attn_limbs = fused && S == 1 && Nq % 16 == 0 && (size_t)Nq * 4 <= 200 * 1024 &&
+                         attention_decode_fast_path(S, D, m.Hq, m.Hkv, dt, m.q_rot, L.kc, L.vc);
             RC(launch_attention(st, m.attn, m.q_rot, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
-                                c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
+                                c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1,
+                                attn_limbs ? (int8_t *)m.gemm_ws + 512 : nullptr, attn_limbs ? (float *)((char *)m.gemm_ws + 256) : nullptr));
         }
         if (tp == 1) {
-            RC(gemm(st, m, m.x, m.attn, L.wo, L.so, m.x, M, H, Nq, dt));  // x = round(x + round(o))
+            // x = round(x + round(o))
+            if (attn_limbs) RC(gemm_prequant(st, m, m.x, L.wo, L.so, m.x, M, H, Nq, dt));
+            else RC(gemm(st, m, m.x, m.attn, L.wo, L.so, m.x, M, H, Nq, dt));
             RC(norm(L.ln2, nullptr, M, m.x));
         } else {
-            RC(gemm(st, m, m.part, m.attn, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
+            if (attn_limbs) RC(gemm_prequant(st, m, m.part, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
+            else RC(gemm(st, m, m.part, m.attn, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
             if (tp_fused) {  // peers' partial sums are read over NVLink inside the add + norm + limbs kernel
                 RC(launch_tp_reduce_norm_limbs(st, dt, m.tp, 0, m.gemm_ws, m.gemm_ws_bytes, m.x, L.ln2, c.rms_eps, M, H));
             } else {

@@ -42,10 +42,13 @@ int launch_add_f32_rms_norm(cudaStream_t st, int dtype, void *sum_out, void *nor
                             const void *weight, float eps, int rows, int D);
 
 // Attention with a choice of output layout: out_bshd != 0 writes [B, Sq, Hq, D] instead of [B, Hq, Sq, D].
+// limbs_out / ascale_out (decode fast path only, see attention_decode_fast_path): the output rows are also left as
+// activation limbs [3 B][Hq * D] + row scales [B] for the DequantMatMul that follows; needs the workspace.
 int launch_attention(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
                      int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
                      const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
-                     size_t workspace_bytes, int out_bshd);
+                     size_t workspace_bytes, int out_bshd, int8_t *limbs_out = nullptr, float *ascale_out = nullptr);
+bool attention_decode_fast_path(int Sq, int D, int Hq, int Hkv, int dtype, const void *q, const void *k, const void *v);
 
 // Tiled tensor-core attention for several query rows (prefill chunks); see attention_prefill.cu.
 bool attention_prefill_supported(int Sq, int D, int dtype, const void *q, const void *k, const void *v, const void *out);
