@@ -94,3 +94,43 @@ def test_argmax_last_tie_rule():
     assert argmax_last([1.0, 5.0, 5.0, 2.0]) == 2
     with pytest.raises(ValueError):
         argmax_last([1.0, float("nan")])
+
+
+class FakeStreamingModel:
+    """Stands in for DecoderModel(streaming=(sink, window)): records the calls, answers from the logit table."""
+
+    def __init__(self, sink, window):
+        self.batch, self.streaming, self.output, self.max_seq_len = 1, (sink, window), "ids", sink + window
+        self.calls = []
+
+    def stream(self, tokens, stream_pos):
+        toks = tokens[0] if isinstance(tokens[0], (list, tuple)) else tokens
+        self.calls.append((tuple(toks), stream_pos))
+        return [SEQUENCE[(stream_pos + len(toks) - 1) % len(SEQUENCE)]]
+
+
+def test_streaming_session_has_no_length_limit_and_never_evicts_inside_a_chunk():
+    """LlmSession::for_llama_streaming: the stream position keeps growing past sink + window; prompt chunks are
+    prefilled only while they fit into the live rows, afterwards prompt tokens go in one at a time."""
+    model = FakeStreamingModel(sink=2, window=6)
+    s = LlmSession.for_llama_streaming(model, eos_token_id=999, prefill_len=4)
+    out = s.generate_ids(list(range(1, 12)), 9)  # 11 prompt tokens, 8 live rows
+    assert len(out) == 9 and s.past_len() == 11 + 8
+    sizes = [(len(t), pos) for t, pos in model.calls]
+    assert sizes[:2] == [(4, 0), (4, 4)]           # two chunks fill the 8 live rows exactly
+    assert sizes[2:5] == [(1, 8), (1, 9), (1, 10)]  # the rest of the prompt would evict: token by token
+    assert all(n == 1 for n, _ in sizes[2:]) and [pos for _, pos in sizes[2:]] == list(range(8, 19))
+    # without prefill every prompt token is a streaming step
+    model2 = FakeStreamingModel(sink=1, window=3)
+    s2 = LlmSession.for_llama_streaming(model2, eos_token_id=999)
+    s2.generate_ids([1, 2, 3, 4, 5, 1], 3)
+    assert [pos for _, pos in model2.calls] == list(range(8))
+    with pytest.raises(ValueError):
+        LlmSession.for_llama_streaming(type("M", (), {"batch": 2, "streaming": (1, 3)})(), eos_token_id=0)
+
+
+def test_streaming_chunk_shrinks_to_the_room_left():
+    model = FakeStreamingModel(sink=2, window=4)  # 6 live rows
+    s = LlmSession.for_llama_streaming(model, eos_token_id=999, prefill_len=4)
+    s.generate_ids([1, 2, 3, 4, 5, 1, 2], 1)
+    assert [(len(t), pos) for t, pos in model.calls] == [(4, 0), (2, 4), (1, 6)]
