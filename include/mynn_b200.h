@@ -90,6 +90,10 @@ int mynn_b200_attention(void *stream, void *out, const void *q, const void *k, c
                         int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
                         const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
                         size_t workspace_bytes);
+/* Prefill chunks (Sq >= 64, D 64/128, 16-bit, 16-byte aligned tensors) run on a TMA-fed tcgen05 kernel whose pipeline
+ * waits are bounded.  This call synchronises the stream and returns MYNN_E_CUDA if one of them expired in an earlier
+ * attention call (the engine checks cudaGetLastError after its launches: src/codegen/cuda/cpp/common.cuh). */
+int mynn_b200_attention_check(void *stream);
 
 /* Decode attention (one query row per sequence) that takes no workspace and allocates nothing.  This entry point
  * has no counterpart in the engine.  It exists for callers that cannot hand over scratch memory and cannot allocate

@@ -338,6 +338,9 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
     if (!fast && limbs_out) return fail(MYNN_E_UNSUPPORTED, "attention: the limb output exists only on the decode fast path");
     if (!fast) {
         static const bool use_tiled = [] { const char *e = getenv("MYNN_PREFILL_ATTENTION"); return !e || atoi(e) != 0; }();
+        if (use_tiled && attention_prefill_tc_supported(B, Hq, Hkv, Sq, D, cache_seq_len, dtype, q, k, v, out))
+            return launch_attention_prefill_tc(st, out, q, k, v, scale, B, Hq, Hkv, Sq, D, cache_seq_len, active_seq_kv, active_seq_kv_dev,
+                                               is_causal, dtype, out_bshd);
         if (use_tiled && attention_prefill_supported(Sq, D, dtype, q, k, v, out))
             return launch_attention_prefill(st, out, q, k, v, scale, B, Hq, Hkv, Sq, D, cache_seq_len, active_seq_kv, active_seq_kv_dev,
                                             is_causal, dtype, out_bshd);

@@ -55,6 +55,12 @@ bool attention_prefill_supported(int Sq, int D, int dtype, const void *q, const 
 int launch_attention_prefill(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B, int Hq,
                              int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv, const int32_t *active_seq_kv_dev,
                              int is_causal, int dtype, int out_bshd);
+// The same on tcgen05 / tensor memory (128 query rows per CTA, TMA-fed); see attention_prefill_tc.cu.
+bool attention_prefill_tc_supported(int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len, int dtype, const void *q, const void *k,
+                                    const void *v, const void *out);
+int launch_attention_prefill_tc(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B, int Hq,
+                                int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv, const int32_t *active_seq_kv_dev,
+                                int is_causal, int dtype, int out_bshd);
 
 // Per-row (max value, last index of the maximum) of a logits shard, and the merge over tensor-parallel shards.
 int launch_argmax_pairs(cudaStream_t st, int dtype, float *pairs /*[rows][2]*/, const void *logits, int rows, int V,

@@ -42,6 +42,7 @@ SIGNATURES = {
     "mynn_b200_dequant_matmul_same_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t]),
     "mynn_b200_dequant_matmul_check": (c_int, [c_void_p, c_void_p]),
     "mynn_b200_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "mynn_b200_attention_check": (c_int, [c_void_p]),
     "mynn_b200_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_size_t]),
     "mynn_b200_attention_decode_noalloc_max_bytes": (c_size_t, []),
     "mynn_b200_attention_decode_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int]),
@@ -83,7 +84,8 @@ SIGNATURES = {
     "free_pinned": (None, [c_void_p]),
 }
 # tuning hooks that are not part of the engine-facing header
-_EXTRA = {"mynn_b200_debug_set_ksplit": (c_int, [c_int]), "mynn_b200_debug_set_timing_buffer": (c_int, [c_void_p]), "mynn_b200_debug_set_mode": (c_int, [c_int])}
+_EXTRA = {"mynn_b200_debug_set_ksplit": (c_int, [c_int]), "mynn_b200_debug_set_timing_buffer": (c_int, [c_void_p]), "mynn_b200_debug_set_mode": (c_int, [c_int]),
+          "mynn_b200_debug_prefill_attention": (c_int, [c_int, ctypes.c_uint, ctypes.c_uint])}
 
 _lib = None
 

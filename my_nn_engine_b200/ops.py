@@ -54,6 +54,11 @@ def check_workspace(ws):
     ffi.check(ffi.lib().mynn_b200_dequant_matmul_check(_stream(), _ptr(ws)))
 
 
+def attention_check():
+    """Raise if a bounded wait inside the tcgen05 prefill-attention kernel expired during an earlier call."""
+    ffi.check(ffi.lib().mynn_b200_attention_check(_stream()))
+
+
 def dequant_matmul(act, wq, scale, axis: int = 0, out=None, workspace="auto"):
     """``DequantMatMul{axis}(act, wq, scale[, workspace])``: act [..., K]; wq int8 [N, K] (axis 0) or [K, N] (axis 1);
     scale [N].  Output dtype = scale dtype (src/transform/shape.rs:326-345).  workspace: 'auto' (a cached scratch

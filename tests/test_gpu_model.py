@@ -110,6 +110,17 @@ def test_mid_size_model_32_greedy_steps(dtype, batch, prefill_len, use_graph):
     assert flips <= batch  # near-ties explained above are rare
 
 
+def test_mid_size_model_long_prefill_chunks_use_the_tensor_core_attention():
+    """Prefill chunks of 70 tokens (two chunks, the second over a past of 70 rows): attention of 64 or more query rows runs
+    on the tcgen05 kernel and writes [B, S, Hq, D] rows for o_proj."""
+    from my_nn_engine_b200 import ops
+    from my_nn_engine_b200.quantize import random_llama_state
+    state = random_llama_state(MID, seed=3)
+    worst, flips = run_parity(MID, state, "bf16", batch=2, steps=4, max_seq=160, prompt_len=140, prefill_len=70, seed=11)
+    ops.attention_check()
+    assert flips <= 2
+
+
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 def test_int8_kv_cache_tiny_model(tiny_llama, dtype):
     """quant_kv_cache on the 2-layer fixture model (head_dim 4: generic attention over the int8 cache)."""
