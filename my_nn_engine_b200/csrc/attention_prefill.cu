@@ -13,7 +13,8 @@
 //     kv tile any of its rows can see.
 // P is rounded to the 16-bit storage type before the second product (relative error 2^-9 per term, below the rounding of
 // the output itself).  Shapes outside this kernel (f32, head dims other than 64/128, unaligned tensors) keep the plain
-// kernel.  The legacy mma.sync path is used here; a tcgen05/TMEM version is future work.
+// kernel.  This is the legacy mma.sync path; chunks of 64 and more query rows run on the tcgen05 / tensor-memory kernels of
+// attention_prefill_tc.cu, and this kernel serves the shorter chunks and the shapes those do not take.
 #include "attention_internal.cuh"
 #include "ops_internal.cuh"
 

@@ -54,7 +54,6 @@ struct TcAttnParams {
     int is_causal, out_bshd;
     uint32_t v_lbo, v_sbo;  // byte offsets of the MN-major V descriptor
     int p_tmem;  // probabilities handed to the second product through tensor memory (over the S columns) instead of shared memory
-    unsigned long long *timing;  // tuning hook: timestamps of the first tiles of CTA (0, 0, 0), or null
 };
 
 // (x, y) -> two 16-bit values in one register, x in the low half: one cvt instruction
@@ -83,6 +82,14 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, const 
     if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     __syncwarp();  // what lane 0 acquired is ordered before the other lanes' reads
+    return ok != 0;
+}
+
+__device__ __forceinline__ bool warp_wait_spin(uint64_t *bar, uint32_t parity, const int *abort_flag) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait_spin(bar, parity, abort_flag) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
     return ok != 0;
 }
 
@@ -144,8 +151,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
-    const bool stamp = p.timing != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-#define TC_STAMP(cond, idx) do { if (stamp && (cond)) p.timing[idx] = global_ns(); } while (0)
     auto give_up = [&](int code) {
         atomicExch(&abort_flag, 1);
         atomicExch(&g_pfa_status, code);
@@ -214,13 +219,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             ok = ok && issue_s(0);
             for (int j = 0; j < n_tiles && ok; j++) {
                 if (j + 1 < n_tiles && !issue_s(j + 1)) break;
-                TC_STAMP(j < 8, 64 + j * 4);
                 const int s = j & 1, u = j >> 1;
                 if (!mbar_wait(&p_full, j & 1, &abort_flag) || !mbar_wait(&v_full[s], u & 1, &abort_flag)) {
                     give_up(4);
                     break;
                 }
-                TC_STAMP(j < 8, 64 + j * 4 + 1);
                 tc_fence_after();
                 const uint32_t pa = smem_u32(s_p), va = smem_u32(s_kv + s * kStage + kTile);
 #pragma unroll
@@ -232,7 +235,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 umma_commit(&v_empty[s]);  // the V buffer may be refilled once these MMAs have read it
                 umma_commit(&pv_done);
-                TC_STAMP(j < 8, 64 + j * 4 + 2);
             }
         }
         __syncwarp();
@@ -256,7 +258,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ok = false;
                 break;
             }
-            TC_STAMP(threadIdx.x == 64 && j < 8, j * 8);
             tc_fence_after();
             float s[HC];
 #pragma unroll
@@ -264,8 +265,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tmem_ld_wait();
             tc_fence_before();
             if (!p.p_tmem) warp_arrive(&s_empty[sb]);  // the rows are in registers: the S buffer may take tile j + 2
-            TC_STAMP(threadIdx.x == 64 && j < 8, j * 8 + 1);
-            TC_STAMP(lane == 0 && j < 6, 128 + (j * 8 + warp - 2) * 5 + 0);
 
             if (col0 + HC > bound) {  // only the diagonal and the last tile carry masked columns
 #pragma unroll
@@ -286,8 +285,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ok = false;
                 break;
             }
-            TC_STAMP(threadIdx.x == 64 && j < 8, j * 8 + 2);
-            TC_STAMP(lane == 0 && j < 6, 128 + (j * 8 + warp - 2) * 5 + 1);
             const float tmax = fmaxf(sh_max[sb][0][row], sh_max[sb][1][row]) * sl2;  // scale > 0: the maximum commutes with it
             float alpha = 1.f;
             bool moved = false;
@@ -308,8 +305,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 pk[i] = pack_pair<T>(p0, p1);
             }
             l += sum0 + sum1;
-            TC_STAMP(threadIdx.x == 64 && j < 8 && l >= 0.f, j * 8 + 3);
-            TC_STAMP(lane == 0 && j < 6 && l >= 0.f, 128 + (j * 8 + warp - 2) * 5 + 2);
 
             if (j > 0) {
                 // the previous second product has read P and written O
@@ -332,8 +327,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tmem_st_wait();
                 }
             }
-            TC_STAMP(threadIdx.x == 64 && j < 8, j * 8 + 4);
-            TC_STAMP(lane == 0 && j < 6, 128 + (j * 8 + warp - 2) * 5 + 3);
             if (kv0 + kTcCols > active) {
                 // rows past the active length: zero them in the V tile (the rows are whole, the swizzle does not matter)
                 if (!warp_wait(&v_full[sb], u & 1, &abort_flag)) {
@@ -368,8 +361,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             fence_proxy_async_smem();
             tc_fence_before();
             warp_arrive(&p_full);
-            TC_STAMP(threadIdx.x == 64 && j < 8, j * 8 + 5);
-            TC_STAMP(lane == 0 && j < 6, 128 + (j * 8 + warp - 2) * 5 + 4);
         }
         // ---- finish: O / sum -> global memory ----
         if (ok && n_tiles > 0) {
@@ -482,6 +473,8 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
+    // the MMA thread and the softmax warps' wait for S sit on the critical path: hardware-suspended waits, no back-off
+    auto wait_fast = [&](uint64_t *bar, uint32_t parity) { return mbar_wait_spin(bar, parity, &abort_flag); };
     auto give_up = [&](int code) {
         atomicExch(&abort_flag, 1);
         atomicExch(&g_pfa_status, code);
@@ -529,7 +522,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 }
                 umma_commit(&s_full[t]);
             };
-            bool ok = mbar_wait(&q_full, 0, &abort_flag) && mbar_wait(&k_full[0], 0, &abort_flag);
+            bool ok = wait_fast(&q_full, 0) && wait_fast(&k_full[0], 0);
             if (!ok) give_up(12);
             if (ok) {
                 tc_fence_after();
@@ -541,7 +534,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 const int st = j & 1, u = j >> 1;
 #pragma unroll
                 for (int t = 0; t < 2; t++) {
-                    if (!mbar_wait(&p_full[t], j & 1, &abort_flag) || (t == 0 && !mbar_wait(&v_full[st], u & 1, &abort_flag))) {
+                    if (!wait_fast(&p_full[t], j & 1) || (t == 0 && !wait_fast(&v_full[st], u & 1))) {
                         give_up(13);
                         ok = false;
                         break;
@@ -555,7 +548,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     umma_commit(&o_done[t]);
                     if (t == 1) umma_commit(&v_empty[st]);
                     if (j + 1 < n_tiles) {
-                        if (t == 0 && !mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, &abort_flag)) {
+                        if (t == 0 && !wait_fast(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) {
                             give_up(14);
                             ok = false;
                             break;
@@ -580,7 +573,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; j++) {
             const int kv0 = j * kTcCols;
-            if (!warp_wait(&s_full[t], j & 1, &abort_flag)) {
+            if (!warp_wait_spin(&s_full[t], j & 1, &abort_flag)) {
                 if (lane == 0) give_up(15);
                 ok = false;
                 break;
@@ -636,7 +629,8 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 uint32_t pk[32];
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
-                    const float p0 = fast_exp2(fmaf(s[64 * c + 2 * i], sl2, neg_m)), p1 = fast_exp2(fmaf(s[64 * c + 2 * i + 1], sl2, neg_m));
+                    const float x0 = fmaf(s[64 * c + 2 * i], sl2, neg_m), x1 = fmaf(s[64 * c + 2 * i + 1], sl2, neg_m);
+                    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                     sum0 += p0;
                     sum1 += p1;
                     pk[i] = pack_pair<T>(p0, p1);
@@ -702,8 +696,8 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-// 0: never; 1: one head per CTA, P through shared memory (default); 2: the same with P through tensor memory; 4: two heads per
-// CTA where the group size is even.  MYNN_PREFILL_ATTENTION_TC overrides, and so does the debug entry below
+// 0: never; 1 (default): two heads per CTA where the group size is even, else one head per CTA; 2: always one head per CTA, P
+// through shared memory; 3: the same with P through tensor memory.  MYNN_PREFILL_ATTENTION_TC overrides, and so does the debug entry below
 int g_pfa_tc_mode = [] {
     const char *e = getenv("MYNN_PREFILL_ATTENTION_TC");
     return e ? atoi(e) : 1;
@@ -767,8 +761,7 @@ int launch_attention_prefill_tc(cudaStream_t st, void *out, const void *q, const
     // slab further (leading offset), the next 8 kv rows 8 x 128 bytes further (stride offset)
     p.v_lbo = g_pfa_v_lbo ? g_pfa_v_lbo : kTcSlab;
     p.v_sbo = g_pfa_v_sbo ? g_pfa_v_sbo : 1024;
-    p.timing = g_i8_timing;
-    p.p_tmem = g_pfa_tc_mode == 2;
+    p.p_tmem = g_pfa_tc_mode == 3;
     // the maps describe the tensors as bytes: rows of D * 2 bytes, boxes of 128 bytes x 128 rows
     CUtensorMap mq, mk, mv;
     const uint64_t row_bytes = (uint64_t)D * 2;
@@ -776,7 +769,7 @@ int launch_attention_prefill_tc(cudaStream_t st, void *out, const void *q, const
     if (int rc = make_map(&mk, k, (uint64_t)B * Hkv * cache_seq_len, row_bytes, row_bytes, kTcCols)) return rc;
     if (int rc = make_map(&mv, v, (uint64_t)B * Hkv * cache_seq_len, row_bytes, row_bytes, kTcCols)) return rc;
     // an even group size can put two query heads of one kv head into every CTA (mode 4)
-    if ((Hq / Hkv) % 2 == 0 && g_pfa_tc_mode == 4) {
+    if ((Hq / Hkv) % 2 == 0 && g_pfa_tc_mode == 1) {
         if (dtype == MYNN_BF16) return D == 64 ? launch_tc2<__nv_bfloat16, 64>(st, mq, mk, mv, p, B) : launch_tc2<__nv_bfloat16, 128>(st, mq, mk, mv, p, B);
         return D == 64 ? launch_tc2<__half, 64>(st, mq, mk, mv, p, B) : launch_tc2<__half, 128>(st, mq, mk, mv, p, B);
     }

@@ -1,6 +1,7 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) asynchronous machinery used by the tensor-core kernels:
-// mbarriers with bounded waits, TMA tile loads, tensor-memory allocation, tcgen05.mma (kind::i8), tcgen05.ld,
-// cluster barriers / distributed shared memory, and the shared-memory matrix descriptor.
+// mbarriers with bounded waits, TMA tile loads, tensor-memory allocation, tcgen05.mma (kind::i8 and kind::f16, the A operand
+// from shared or from tensor memory), tcgen05.ld / st, cluster barriers / distributed shared memory, and the shared-memory
+// matrix descriptors (K-major and MN-major, 128-byte swizzle).
 #pragma once
 #include <cuda.h>
 #include <stdint.h>
@@ -38,6 +39,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const 
         if (done) return true;
         __nanosleep(i < 16 ? 20 : 100);  // back off: a spinning try_wait competes for the SM's shared-memory pipe
         if ((i & 63) == 63) {
+            if (*(volatile const int *)abort_flag) return false;
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitBudgetNs) return false;
+        }
+    }
+}
+// The same without back-off between polls, for the few threads whose wake-up latency is on a kernel's critical path:
+// try_wait is given a suspend-time hint, so the thread sleeps in hardware until the phase completes (or the hint expires)
+// instead of polling.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t *bar, uint32_t parity, const int *abort_flag) {
+    const uint32_t addr = smem_u32(bar);
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity), "r"(100000u)
+            : "memory");
+        if (done) return true;
+        if ((i & 15) == 15) {
             if (*(volatile const int *)abort_flag) return false;
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
