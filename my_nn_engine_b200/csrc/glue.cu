@@ -11,22 +11,42 @@ namespace mynn {
 
 // ---- RMSNorm -------------------------------------------------------------------------------------------
 // One CTA per row.  With ADD: s = round(a + b) is written to sum_out and normalised.
-template <typename T, bool ADD>
+// VEC: 16-bit tensors read and written 8 elements at a time (D a multiple of 8, 16-byte aligned rows).
+template <typename T, bool ADD, bool VEC>
 __global__ void __launch_bounds__(256)
 rms_norm_kernel(T *sum_out, T *norm_out, const T *a, const T *b, const T *w, float eps, int D) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float warp_part[8];
     __shared__ float inv_s;
     const size_t base = (size_t)blockIdx.x * D;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        float v = to_f32<T>(a[base + i]);
-        if constexpr (ADD) {
-            v = round_store<T>(v + to_f32<T>(b[base + i]));
-            sum_out[base + i] = from_f32<T>(v);
+    if constexpr (VEC) {
+        for (int i = 8 * threadIdx.x; i < D; i += 8 * blockDim.x) {
+            T av[8], bv[8], sv[8];
+            *reinterpret_cast<uint4 *>(av) = *reinterpret_cast<const uint4 *>(a + base + i);
+            if constexpr (ADD) *reinterpret_cast<uint4 *>(bv) = *reinterpret_cast<const uint4 *>(b + base + i);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float v = to_f32<T>(av[j]);
+                if constexpr (ADD) {
+                    sv[j] = from_f32<T>(v + to_f32<T>(bv[j]));
+                    v = to_f32<T>(sv[j]);
+                }
+                row[i + j] = v;
+                ss += v * v;
+            }
+            if constexpr (ADD) *reinterpret_cast<uint4 *>(sum_out + base + i) = *reinterpret_cast<const uint4 *>(sv);
         }
-        row[i] = v;
-        ss += v * v;
+    } else {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) {
+            float v = to_f32<T>(a[base + i]);
+            if constexpr (ADD) {
+                v = round_store<T>(v + to_f32<T>(b[base + i]));
+                sum_out[base + i] = from_f32<T>(v);
+            }
+            row[i] = v;
+            ss += v * v;
+        }
     }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
@@ -38,8 +58,28 @@ rms_norm_kernel(T *sum_out, T *norm_out, const T *a, const T *b, const T *w, flo
     }
     __syncthreads();
     const float inv = inv_s;
-    for (int i = threadIdx.x; i < D; i += blockDim.x)
-        norm_out[base + i] = from_f32<T>(row[i] * inv * to_f32<T>(w[i]));
+    if constexpr (VEC) {
+        for (int i = 8 * threadIdx.x; i < D; i += 8 * blockDim.x) {
+            T wv[8], ov[8];
+            *reinterpret_cast<uint4 *>(wv) = *reinterpret_cast<const uint4 *>(w + i);
+#pragma unroll
+            for (int j = 0; j < 8; j++) ov[j] = from_f32<T>(row[i + j] * inv * to_f32<T>(wv[j]));
+            *reinterpret_cast<uint4 *>(norm_out + base + i) = *reinterpret_cast<const uint4 *>(ov);
+        }
+    } else {
+        for (int i = threadIdx.x; i < D; i += blockDim.x)
+            norm_out[base + i] = from_f32<T>(row[i] * inv * to_f32<T>(w[i]));
+    }
+}
+
+template <typename T, bool ADD>
+static int launch_rms_norm(cudaStream_t st, T *sum_out, T *norm_out, const T *a, const T *b, const T *w, float eps, int rows, int D) {
+    const bool vec = sizeof(T) == 2 && D % 8 == 0 &&
+                     (((uintptr_t)sum_out | (uintptr_t)norm_out | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w) % 16) == 0;
+    auto kern = vec ? rms_norm_kernel<T, ADD, sizeof(T) == 2> : rms_norm_kernel<T, ADD, false>;
+    if ((size_t)D * 4 > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, D * 4));
+    kern<<<rows, 256, (size_t)D * 4, st>>>(sum_out, norm_out, a, b, w, eps, D);
+    return MYNN_OK;
 }
 
 // ---- RoPE ------------------------------------------------------------------------------------------------
@@ -194,11 +234,79 @@ __global__ void rope_kv_append_kernel(T *q_out, T *k_cache, T *v_cache, const T 
     }
 }
 
+// The same with 128-bit accesses for 16-bit tensors (D a multiple of 16, everything 16-byte aligned): one thread per
+// (token row, head slot, group of 8 (low, high) pairs); a v slot copies 16 elements per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_append_vec_kernel(T *q_out, T *k_cache, T *v_cache, const T *q, const T *k, const T *v, long long q_stride,
+                          long long k_stride, long long v_stride, const T *cos_t, const T *sin_t, const int64_t *positions,
+                          long long units, int S, int Hq, int Hkv, int D, int cache_seq, const int32_t *past_len_dev, int rotate_k) {
+    pdl_trigger();
+    pdl_wait();
+    const long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (u >= units) return;
+    const int half = D >> 1, groups = half >> 3, slots = Hq + 2 * Hkv;
+    const int g = (int)(u % groups), slot = (int)((u / groups) % slots);
+    const int row = (int)(u / ((long long)groups * slots)), b = row / S, s = row - b * S;
+    const int j0 = 8 * g;
+    const int cache_row = *past_len_dev + s;
+    const bool in_cache = cache_row >= 0 && cache_row < cache_seq;
+    const bool is_q = slot < Hq, is_k = !is_q && slot < Hq + Hkv;
+    if (!is_q && !in_cache) return;
+    const int h = is_q ? slot : (is_k ? slot - Hq : slot - Hq - Hkv);
+    const T *src = is_q ? q + (size_t)row * q_stride + (size_t)h * D
+                        : (is_k ? k + (size_t)row * k_stride + (size_t)h * D : v + (size_t)row * v_stride + (size_t)h * D);
+    T *dst = is_q ? q_out + (((size_t)b * Hq + h) * S + s) * D
+                  : (is_k ? k_cache : v_cache) + (((size_t)b * Hkv + h) * cache_seq + cache_row) * D;
+    const uint4 lo = *reinterpret_cast<const uint4 *>(src + j0), hi = *reinterpret_cast<const uint4 *>(src + j0 + half);
+    if (!is_q && !(is_k && rotate_k)) {  // v, or a key of the streaming cache (stored as the projection left it)
+        *reinterpret_cast<uint4 *>(dst + j0) = lo;
+        *reinterpret_cast<uint4 *>(dst + j0 + half) = hi;
+        return;
+    }
+    const size_t to = (size_t)positions[s] * D;
+    T xl[8], xh[8], cl[8], ch[8], sl[8], sh[8], ol[8], oh[8];
+    *reinterpret_cast<uint4 *>(xl) = lo;
+    *reinterpret_cast<uint4 *>(xh) = hi;
+    *reinterpret_cast<uint4 *>(cl) = *reinterpret_cast<const uint4 *>(cos_t + to + j0);
+    *reinterpret_cast<uint4 *>(ch) = *reinterpret_cast<const uint4 *>(cos_t + to + j0 + half);
+    *reinterpret_cast<uint4 *>(sl) = *reinterpret_cast<const uint4 *>(sin_t + to + j0);
+    *reinterpret_cast<uint4 *>(sh) = *reinterpret_cast<const uint4 *>(sin_t + to + j0 + half);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float a = to_f32<T>(xl[i]), c = to_f32<T>(xh[i]);
+        ol[i] = from_f32<T>(a * to_f32<T>(cl[i]) - c * to_f32<T>(sl[i]));
+        oh[i] = from_f32<T>(c * to_f32<T>(ch[i]) + a * to_f32<T>(sh[i]));
+    }
+    *reinterpret_cast<uint4 *>(dst + j0) = *reinterpret_cast<const uint4 *>(ol);
+    *reinterpret_cast<uint4 *>(dst + j0 + half) = *reinterpret_cast<const uint4 *>(oh);
+}
+
 int launch_rope_kv_append(cudaStream_t st, int dtype, void *q_out, void *k_cache, void *v_cache, const void *q,
                           const void *k, const void *v, long long q_stride, long long k_stride, long long v_stride,
                           const void *cos_t, const void *sin_t, const int64_t *positions, int B, int S, int Hq,
                           int Hkv, int D, int cache_seq, const int32_t *past_len_dev, int rotate_k) {
     if (B * S == 0) return MYNN_OK;
+    const bool vec = dtype != MYNN_F32 && D % 16 == 0 && q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0 &&
+                     (((uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v |
+                       (uintptr_t)cos_t | (uintptr_t)sin_t) % 16) == 0;
+    if (vec) {
+        const long long units = (long long)B * S * (Hq + 2 * Hkv) * (D / 16);
+        const unsigned blocks = (unsigned)((units + 255) / 256);
+        if (dtype == MYNN_BF16) {
+            using T = __nv_bfloat16;
+            MYNN_CUDA_OK(launch_pdl(rope_kv_append_vec_kernel<T>, dim3(blocks), dim3(256), 0, st, (T *)q_out, (T *)k_cache, (T *)v_cache,
+                                    (const T *)q, (const T *)k, (const T *)v, q_stride, k_stride, v_stride, (const T *)cos_t,
+                                    (const T *)sin_t, positions, units, S, Hq, Hkv, D, cache_seq, past_len_dev, rotate_k));
+        } else {
+            using T = __half;
+            MYNN_CUDA_OK(launch_pdl(rope_kv_append_vec_kernel<T>, dim3(blocks), dim3(256), 0, st, (T *)q_out, (T *)k_cache, (T *)v_cache,
+                                    (const T *)q, (const T *)k, (const T *)v, q_stride, k_stride, v_stride, (const T *)cos_t,
+                                    (const T *)sin_t, positions, units, S, Hq, Hkv, D, cache_seq, past_len_dev, rotate_k));
+        }
+        MYNN_LAUNCH_OK("rope_kv_append_vec_kernel");
+        return MYNN_OK;
+    }
     const int threads = D / 2 >= 64 ? 64 : 32;
     MYNN_DISPATCH_DTYPE(dtype, T, {
         MYNN_CUDA_OK(launch_pdl(rope_kv_append_kernel<T>, dim3(B * S, Hq + 2 * Hkv), dim3(threads), 0, st, (T *)q_out, (T *)k_cache,
@@ -218,9 +326,35 @@ __global__ void swiglu_strided_kernel(T *out, const T *gate, const T *up, int F,
     out[(size_t)m * F + f] = from_f32<T>((g / (1.0f + expf(-g))) * to_f32<T>(up[(size_t)m * in_stride + f]));
 }
 
+// 8 elements per thread with 128-bit accesses (16-bit tensors, F and the row stride multiples of 8, 16-byte aligned)
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_strided_vec_kernel(T *out, const T *gate, const T *up, int F, long long in_stride) {
+    const int m = blockIdx.y;
+    const int f = 8 * (blockIdx.x * blockDim.x + threadIdx.x);
+    if (f >= F) return;
+    T g[8], u[8], o[8];
+    *reinterpret_cast<uint4 *>(g) = *reinterpret_cast<const uint4 *>(gate + (size_t)m * in_stride + f);
+    *reinterpret_cast<uint4 *>(u) = *reinterpret_cast<const uint4 *>(up + (size_t)m * in_stride + f);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float x = to_f32<T>(g[i]);
+        o[i] = from_f32<T>((x / (1.0f + expf(-x))) * to_f32<T>(u[i]));
+    }
+    *reinterpret_cast<uint4 *>(out + (size_t)m * F + f) = *reinterpret_cast<const uint4 *>(o);
+}
+
 int launch_swiglu_strided(cudaStream_t st, int dtype, void *out, const void *gate, const void *up, int M, int F,
                           long long in_stride) {
     if (M * F == 0) return MYNN_OK;
+    if (dtype != MYNN_F32 && F % 8 == 0 && in_stride % 8 == 0 && (((uintptr_t)out | (uintptr_t)gate | (uintptr_t)up) % 16) == 0 && M <= 65535) {
+        const dim3 grid((F / 8 + 255) / 256, M);
+        if (dtype == MYNN_BF16)
+            swiglu_strided_vec_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16 *)out, (const __nv_bfloat16 *)gate, (const __nv_bfloat16 *)up, F, in_stride);
+        else
+            swiglu_strided_vec_kernel<__half><<<grid, 256, 0, st>>>((__half *)out, (const __half *)gate, (const __half *)up, F, in_stride);
+        MYNN_LAUNCH_OK("swiglu_strided_vec_kernel");
+        return MYNN_OK;
+    }
     MYNN_DISPATCH_DTYPE(dtype, T, {
         swiglu_strided_kernel<T><<<dim3((F + 255) / 256, M), 256, 0, st>>>((T *)out, (const T *)gate, (const T *)up, F, in_stride);
     });
@@ -417,9 +551,7 @@ extern "C" int mynn_b200_rms_norm(void *stream, void *out, const void *x, const 
     if (!out || !x || !weight) return fail(MYNN_E_ARG, "rms_norm: null pointer");
     if ((size_t)D * 4 > 200 * 1024) return fail(MYNN_E_UNSUPPORTED, "rms_norm: D=%d exceeds the shared-memory row buffer", D);
     MYNN_DISPATCH_DTYPE(dtype, T, {
-        auto kern = rms_norm_kernel<T, false>;
-        if ((size_t)D * 4 > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, D * 4));
-        kern<<<rows, 256, (size_t)D * 4, (cudaStream_t)stream>>>(nullptr, (T *)out, (const T *)x, nullptr, (const T *)weight, eps, D);
+        if (int rc = launch_rms_norm<T, false>((cudaStream_t)stream, nullptr, (T *)out, (const T *)x, nullptr, (const T *)weight, eps, rows, D)) return rc;
     });
     MYNN_LAUNCH_OK("rms_norm_kernel");
     return MYNN_OK;
@@ -432,9 +564,7 @@ extern "C" int mynn_b200_add_rms_norm(void *stream, void *sum_out, void *norm_ou
     if (!sum_out || !norm_out || !a || !b || !weight) return fail(MYNN_E_ARG, "add_rms_norm: null pointer");
     if ((size_t)D * 4 > 200 * 1024) return fail(MYNN_E_UNSUPPORTED, "add_rms_norm: D=%d too large", D);
     MYNN_DISPATCH_DTYPE(dtype, T, {
-        auto kern = rms_norm_kernel<T, true>;
-        if ((size_t)D * 4 > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, D * 4));
-        kern<<<rows, 256, (size_t)D * 4, (cudaStream_t)stream>>>((T *)sum_out, (T *)norm_out, (const T *)a, (const T *)b, (const T *)weight, eps, D);
+        if (int rc = launch_rms_norm<T, true>((cudaStream_t)stream, (T *)sum_out, (T *)norm_out, (const T *)a, (const T *)b, (const T *)weight, eps, rows, D)) return rc;
     });
     MYNN_LAUNCH_OK("add_rms_norm_kernel");
     return MYNN_OK;

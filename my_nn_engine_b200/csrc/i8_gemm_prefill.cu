@@ -32,20 +32,35 @@ constexpr uint32_t kPfStageBytes = kPfWBytes + kPfABytes;  // 48 KB
 // ---- pre-pass: rows -> two int8 limbs + power-of-two row scale ----------------------------------------------------
 // limbs [(2m + l)][K]; with max |row| < 2^e the row is scaled by 2^(14-e), so |A| <= 2^14 and the high limb is within
 // [-64, 64]; ascale[m] = 2^(e-14).
-template <typename T>
-__global__ void __launch_bounds__(1024) act_to_limbs2_kernel(int8_t *limbs, float *ascale, const T *act, int K) {
+// One CTA of 256 threads per row (several rows are resident per SM, which hides the two block-wide reductions); VEC: 16-bit
+// activations read 8 at a time (rows 16-byte aligned); the limbs are always written 8 bytes at a time (K is a multiple of 16).
+constexpr int kLimbThreads = 256;
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kLimbThreads) act_to_limbs2_kernel(int8_t *limbs, float *ascale, const T *act, int K) {
     extern __shared__ __align__(16) float row_s[];
-    __shared__ float red[40];
+    __shared__ float red[kLimbThreads / 32 + 1];
     pdl_trigger();
     pdl_wait();
     const int m = blockIdx.x;
+    const T *src = act + (size_t)m * K;
     float mx = 0.f;
     bool bad = false;
-    for (int i = 4 * threadIdx.x; i < K; i += 4 * 1024) {
+    if constexpr (VEC) {
+        for (int i = 8 * threadIdx.x; i < K; i += 8 * kLimbThreads) {
+            T av[8];
+            *reinterpret_cast<uint4 *>(av) = *reinterpret_cast<const uint4 *>(src + i);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float v = to_f32<T>(act[(size_t)m * K + i + j]);
-            row_s[i + j] = v;
+            for (int j = 0; j < 8; j++) {
+                const float v = to_f32<T>(av[j]);
+                row_s[i + j] = v;
+                bad |= !(fabsf(v) <= 3.0e38f);
+                mx = fmaxf(mx, fabsf(v));
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < K; i += kLimbThreads) {
+            const float v = to_f32<T>(src[i]);
+            row_s[i] = v;
             bad |= !(fabsf(v) <= 3.0e38f);
             mx = fmaxf(mx, fabsf(v));
         }
@@ -56,29 +71,29 @@ __global__ void __launch_bounds__(1024) act_to_limbs2_kernel(int8_t *limbs, floa
     __syncthreads();
     if (threadIdx.x == 0) {
         float t = 0.f;
-        for (int i = 0; i < 32; i++) t = fmaxf(t, red[i]);
+        for (int i = 0; i < kLimbThreads / 32; i++) t = fmaxf(t, red[i]);
         int e = 0;
         if (t > 0.f) frexpf(t, &e);
         const float sc = t > 0.f ? ldexpf(1.0f, 14 - e) : 1.0f;
-        red[32] = anybad ? 0.f : sc;
+        red[kLimbThreads / 32] = anybad ? 0.f : sc;
         ascale[m] = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc;
     }
     __syncthreads();
-    const float sc = red[32];
-    uint32_t *l0 = reinterpret_cast<uint32_t *>(limbs + (size_t)(2 * m) * K);
-    uint32_t *l1 = reinterpret_cast<uint32_t *>(limbs + (size_t)(2 * m + 1) * K);
-    for (int gi = threadIdx.x; gi < (K >> 2); gi += 1024) {
-        uint32_t w0 = 0, w1 = 0;
+    const float sc = red[kLimbThreads / 32];
+    uint2 *l0 = reinterpret_cast<uint2 *>(limbs + (size_t)(2 * m) * K);
+    uint2 *l1 = reinterpret_cast<uint2 *>(limbs + (size_t)(2 * m + 1) * K);
+    for (int gi = threadIdx.x; gi < (K >> 3); gi += kLimbThreads) {
+        uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            int A = sc == 0.f ? 0 : __float2int_rn(row_s[4 * gi + i] * sc);
+        for (int i = 0; i < 8; i++) {
+            int A = sc == 0.f ? 0 : __float2int_rn(row_s[8 * gi + i] * sc);
             const int d0 = (int)(int8_t)(A & 0xFF);
             A = (A - d0) >> 8;
-            w0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
-            w1 |= (uint32_t)(A & 0xFF) << (8 * i);
+            w0[i >> 2] |= (uint32_t)(d0 & 0xFF) << (8 * (i & 3));
+            w1[i >> 2] |= (uint32_t)(A & 0xFF) << (8 * (i & 3));
         }
-        l0[gi] = w0;
-        l1[gi] = w1;
+        l0[gi] = make_uint2(w0[0], w0[1]);
+        l1[gi] = make_uint2(w1[0], w1[1]);
     }
 }
 
@@ -303,11 +318,12 @@ int i8_prefill_launch(cudaStream_t st, void *out, const void *act, const int8_t 
     float *ascale = (float *)((char *)workspace + 256);
     int8_t *limbs = (int8_t *)workspace + 256 + pf_scale_bytes(M);
     const size_t smem = (size_t)K * 4;
+    const bool vec = act_dtype != MYNN_F32 && K % 8 == 0 && ((uintptr_t)act % 16) == 0;
 #define PREP(T)                                                                                                          \
     {                                                                                                                    \
-        auto kern = act_to_limbs2_kernel<T>;                                                                             \
+        auto kern = vec ? act_to_limbs2_kernel<T, sizeof(T) == 2> : act_to_limbs2_kernel<T, false>;                      \
         if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        MYNN_CUDA_OK(launch_pdl(kern, dim3(M), dim3(1024), smem, st, limbs, ascale, (const T *)act, K));                 \
+        MYNN_CUDA_OK(launch_pdl(kern, dim3(M), dim3(kLimbThreads), smem, st, limbs, ascale, (const T *)act, K));         \
     }
     switch (act_dtype) {
         case MYNN_BF16: PREP(__nv_bfloat16) break;

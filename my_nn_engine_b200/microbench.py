@@ -2,6 +2,8 @@
 
     python -m my_nn_engine_b200.microbench gemm --m 32 --n 28672 --k 4096 [--dtype bf16] [--ksplit 0] [--copies 8]
     python -m my_nn_engine_b200.microbench attn --b 16 --hq 32 --hkv 8 --d 128 --len 4096
+    python -m my_nn_engine_b200.microbench prefill_attn --len 8192
+    python -m my_nn_engine_b200.microbench prefill_model --arch llama3-8b --len 2048
     python -m my_nn_engine_b200.microbench suite
 
 Every launch reads a different copy of its weights / KV (copies x size > L2) and the launches are replayed from one
@@ -133,6 +135,46 @@ def prefill_attn(b, hq, hkv, d, length, dtype="bf16", quiet=False):
     return res
 
 
+LLAMA3_8B = dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                 intermediate_size=14336, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0)
+TINYLLAMA = dict(hidden_size=2048, num_hidden_layers=22, num_attention_heads=32, num_key_value_heads=4, head_dim=64,
+                 intermediate_size=5632, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0)
+
+
+def prefill_model(arch="llama3-8b", batch=1, length=2048, chunk=None, layers=None, dtype="bf16", reps=3, quiet=False):
+    """Whole-model prefill of ``length`` prompt tokens per sequence (random int8 weights of the named architecture) in
+    chunks of ``chunk`` tokens: the prefill DequantMatMul and the prefill attention kernels in context.  Wall-clock per
+    prompt, host call to host result (the last token's id)."""
+    import time
+
+    from .decoder import DecoderModel
+    from .quantize import random_llama_state
+    cfg = dict(LLAMA3_8B if arch == "llama3-8b" else TINYLLAMA)
+    if layers:
+        cfg["num_hidden_layers"] = layers
+    chunk = chunk or length
+    state = random_llama_state(cfg, seed=0, device="cuda")
+    model = DecoderModel(cfg, state, dtype=dtype, max_seq_len=length + 8, batch=batch, output="ids", max_prefill=chunk)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg["vocab_size"], size=(batch, length))
+    times = []
+    for _ in range(reps + 1):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for p0 in range(0, length, chunk):
+            model.prefill(prompt[:, p0:p0 + chunk], p0)
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+    ops.attention_check()
+    best = min(times[1:])
+    res = {"kernel": "model_prefill", "arch": arch, "layers": cfg["num_hidden_layers"], "batch": batch, "len": length, "chunk": chunk,
+           "dtype": dtype, "ms": best * 1e3, "first_call_ms": times[0] * 1e3, "prompt_tok_per_s": batch * length / best}
+    model.close()
+    if not quiet:
+        print(json.dumps(res), flush=True)
+    return res
+
+
 def w8a8(m, n, k, dtype="bf16", copies=None, quiet=False):
     """QuantizedMatMul (int8 x int8) on the tcgen05 kernel; TFLOP/s counts 2 M N K integer operations."""
     td = _DT[dtype]
@@ -194,6 +236,13 @@ def main():
     pa.add_argument("--d", type=int, default=128)
     pa.add_argument("--len", type=int, default=2048)
     pa.add_argument("--dtype", default="bf16")
+    pm = sub.add_parser("prefill_model")
+    pm.add_argument("--arch", default="llama3-8b", choices=["llama3-8b", "tinyllama"])
+    pm.add_argument("--b", type=int, default=1)
+    pm.add_argument("--len", type=int, default=2048)
+    pm.add_argument("--chunk", type=int, default=None)
+    pm.add_argument("--layers", type=int, default=None)
+    pm.add_argument("--dtype", default="bf16")
     q = sub.add_parser("w8a8")
     q.add_argument("--m", type=int, default=2048)
     q.add_argument("--n", type=int, default=14336)
@@ -206,6 +255,8 @@ def main():
         gemm(args.m, args.n, args.k, args.dtype, args.ksplit, args.copies, kernel=args.kernel)
     elif args.cmd == "prefill_attn":
         prefill_attn(args.b, args.hq, args.hkv, args.d, args.len, args.dtype)
+    elif args.cmd == "prefill_model":
+        prefill_model(args.arch, args.b, args.len, args.chunk, args.layers, args.dtype)
     elif args.cmd == "w8a8":
         w8a8(args.m, args.n, args.k, args.dtype, args.copies)
     elif args.cmd == "attn":
