@@ -245,6 +245,16 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 #pragma unroll 1
             for (int c0 = 0; c0 < kPfCols; c0 += 32) {  // 32 accumulator columns = 32 / LIMBS activation rows
                 if (tok0 + c0 / LIMBS >= p.M) break;  // uniform: the remaining columns belong to rows past M
+                // the chunk's residuals first, all at once: `out` may alias `resid` (x += ...), so loads written next to their
+                // stores could not be moved ahead of the previous store and every row would pay a global-memory round trip
+                float resv[32 / LIMBS];
+                if (resid_p && n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32 / LIMBS; j++) {
+                        const int m = tok0 + c0 / LIMBS + j;
+                        resv[j] = m < p.M ? to_f32<OutT>(resid_p[(size_t)m * p.N + n]) : 0.f;
+                    }
+                }
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * kPfCols + c0), v);
                 tmem_ld_wait();
@@ -258,7 +268,7 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                             else acc = (float)(int)v[j];
                             // (acc * lhs scale) * weight scale with separate roundings, as the CPU kernels compute it
                             float r = __fmul_rn(__fmul_rn(acc, sh_ascale[buf][c0 / LIMBS + j]), wscale);
-                            if (resid_p) r = __fadd_rn(round_store<OutT>(r), to_f32<OutT>(resid_p[(size_t)m * p.N + n]));
+                            if (resid_p) r = __fadd_rn(round_store<OutT>(r), resv[j]);
                             out_p[(size_t)m * p.N + n] = from_f32<OutT>(r);
                         }
                     }
