@@ -29,6 +29,13 @@ size_t i8_prefill_workspace_bytes(int M, int K);
 bool i8_prefill_supported(int M, int N, int K, const void *wq, int act_dtype, int out_dtype);
 int i8_prefill_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
                       int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes);
+// Fused producers for the prefill kernel (rows > 32): leave two limbs per element + row scales in `workspace`; the following
+// i8_prefill_launch is called with act == nullptr.  prefill_fused_supported: 16-bit dtype, K % 16 == 0, 16-byte aligned inputs.
+bool prefill_fused_supported(int dtype, int K, const void *a, const void *b);
+int launch_rms_norm_limbs2(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, const void *x, const void *w, float eps,
+                           int rows, int D);
+int launch_swiglu_limbs2(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, const void *gate, const void *up, int rows,
+                         int F, long long in_stride);
 // QuantizedMatMul (int8 x int8, per-row or per-tensor lhs scale, per-channel rhs scale) on the same persistent kernel
 // with one accumulator column per lhs row.  workspace: 256 bytes holding the status word.
 bool i8_w8a8_supported(int M, int N, int K, const void *lhs, const void *rhs);

@@ -97,6 +97,141 @@ __global__ void __launch_bounds__(kLimbThreads) act_to_limbs2_kernel(int8_t *lim
     }
 }
 
+// ---- fused producers: the operator that makes a DequantMatMul's activations writes the two limbs itself -------------------
+// (the prefill counterpart of rms_norm_limbs_kernel / swiglu_limbs_kernel of the decode step: no activation tensor is written
+// and read back, and no separate pre-pass runs).  One CTA of 256 threads per row; D, F multiples of 8, rows 16-byte aligned.
+__device__ __forceinline__ float limb2_scale(float mx, bool bad, float *ascale_m, float *red /* kLimbThreads / 32 + 1 floats */) {
+    mx = warp_max(mx);
+    const unsigned anybad = __syncthreads_or(bad);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < kLimbThreads / 32; i++) t = fmaxf(t, red[i]);
+        int e = 0;
+        if (t > 0.f) frexpf(t, &e);
+        const float sc = t > 0.f ? ldexpf(1.0f, 14 - e) : 1.0f;
+        red[kLimbThreads / 32] = anybad ? 0.f : sc;
+        *ascale_m = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc;
+    }
+    __syncthreads();
+    return red[kLimbThreads / 32];
+}
+// row_s holds the row in the storage type T (the values are already rounded to T, so nothing is lost and twice as many
+// rows fit per SM as with f32)
+template <typename T>
+__device__ __forceinline__ void smem_row_to_limbs2(const T *row_s, int K, int8_t *limb_row0, float sc) {
+    uint2 *l0 = reinterpret_cast<uint2 *>(limb_row0);
+    uint2 *l1 = reinterpret_cast<uint2 *>(limb_row0 + K);
+    for (int gi = threadIdx.x; gi < (K >> 3); gi += kLimbThreads) {
+        T x[8];
+        *reinterpret_cast<uint4 *>(x) = reinterpret_cast<const uint4 *>(row_s)[gi];
+        uint32_t w0[2] = {0u, 0u}, w1[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            int A = sc == 0.f ? 0 : __float2int_rn(to_f32<T>(x[i]) * sc);
+            const int d0 = (int)(int8_t)(A & 0xFF);
+            A = (A - d0) >> 8;
+            w0[i >> 2] |= (uint32_t)(d0 & 0xFF) << (8 * (i & 3));
+            w1[i >> 2] |= (uint32_t)(A & 0xFF) << (8 * (i & 3));
+        }
+        l0[gi] = make_uint2(w0[0], w0[1]);
+        l1[gi] = make_uint2(w1[0], w1[1]);
+    }
+}
+template <typename T>
+__device__ __forceinline__ void ld8(const T *p, float (&v)[8]) {
+    T raw[8];
+    *reinterpret_cast<uint4 *>(raw) = *reinterpret_cast<const uint4 *>(p);
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = to_f32<T>(raw[i]);
+}
+template <typename T>
+__device__ __forceinline__ void st8(T *p, const float (&v)[8]) {
+    T raw[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) raw[i] = from_f32<T>(v[i]);
+    *reinterpret_cast<uint4 *>(p) = *reinterpret_cast<const uint4 *>(raw);
+}
+
+// y = round(x * rsqrt(mean x^2 + eps) * w) -> two limbs per element
+template <typename T>
+__global__ void __launch_bounds__(kLimbThreads)
+rms_norm_limbs2_kernel(int8_t *limbs, float *ascale, const T *x, const T *w, float eps, int D) {
+    extern __shared__ __align__(16) uint8_t row_raw[];
+    T *row_s = reinterpret_cast<T *>(row_raw);
+    __shared__ float red[kLimbThreads / 32 + 2];
+    pdl_trigger();
+    pdl_wait();
+    const int m = blockIdx.x;
+    const size_t base = (size_t)m * D;
+    float ss = 0.f;
+    for (int i = 8 * threadIdx.x; i < D; i += 8 * kLimbThreads) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(x + base + i);
+        *reinterpret_cast<uint4 *>(row_s + i) = raw;
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float v = to_f32<T>(e[j]);
+            ss += v * v;
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int i = 0; i < kLimbThreads / 32; i++) tot += red[i];
+        red[kLimbThreads / 32 + 1] = 1.0f / sqrtf(tot / (float)D + eps);
+    }
+    __syncthreads();
+    const float inv = red[kLimbThreads / 32 + 1];
+    float mx = 0.f;
+    bool bad = false;
+    for (int i = 8 * threadIdx.x; i < D; i += 8 * kLimbThreads) {  // each thread revisits the elements it wrote
+        float xv[8], wv[8], y[8];
+        ld8<T>(row_s + i, xv);
+        ld8<T>(w + i, wv);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            y[j] = round_store<T>(xv[j] * inv * wv[j]);
+            bad |= !(fabsf(y[j]) <= 3.0e38f);
+            mx = fmaxf(mx, fabsf(y[j]));
+        }
+        st8<T>(row_s + i, y);
+    }
+    const float sc = limb2_scale(mx, bad, ascale + m, red);  // its barriers also publish row_s
+    smem_row_to_limbs2<T>(row_s, D, limbs + (size_t)(2 * m) * D, sc);
+}
+
+// h = round(swish(gate) * up) -> two limbs per element; gate / up rows are in_stride elements apart
+template <typename T>
+__global__ void __launch_bounds__(kLimbThreads)
+swiglu_limbs2_kernel(int8_t *limbs, float *ascale, const T *gate, const T *up, int F, long long in_stride) {
+    extern __shared__ __align__(16) uint8_t row_raw[];
+    T *row_s = reinterpret_cast<T *>(row_raw);
+    __shared__ float red[kLimbThreads / 32 + 2];
+    pdl_trigger();
+    pdl_wait();
+    const int m = blockIdx.x;
+    float mx = 0.f;
+    bool bad = false;
+    for (int i = 8 * threadIdx.x; i < F; i += 8 * kLimbThreads) {
+        float g[8], u[8], h[8];
+        ld8<T>(gate + (size_t)m * in_stride + i, g);
+        ld8<T>(up + (size_t)m * in_stride + i, u);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            h[j] = round_store<T>((g[j] / (1.0f + expf(-g[j]))) * u[j]);
+            bad |= !(fabsf(h[j]) <= 3.0e38f);
+            mx = fmaxf(mx, fabsf(h[j]));
+        }
+        st8<T>(row_s + i, h);
+    }
+    const float sc = limb2_scale(mx, bad, ascale + m, red);
+    smem_row_to_limbs2<T>(row_s, F, limbs + (size_t)(2 * m) * F, sc);
+}
+
 struct PfParams {
     void *out;
     const void *scale, *resid;
@@ -242,25 +377,26 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: sh_ascale[buf], sh_go[buf] are set
             if (!sh_go[buf]) break;
             tc_fence_after();
-#pragma unroll 1
-            for (int c0 = 0; c0 < kPfCols; c0 += 32) {  // 32 accumulator columns = 32 / LIMBS activation rows
-                if (tok0 + c0 / LIMBS >= p.M) break;  // uniform: the remaining columns belong to rows past M
-                // the chunk's residuals first, all at once: `out` may alias `resid` (x += ...), so loads written next to their
-                // stores could not be moved ahead of the previous store and every row would pay a global-memory round trip
-                float resv[32 / LIMBS];
-                if (resid_p && n < p.N) {
+            // 32 accumulator columns = R activation rows per chunk.  `out` may alias `resid` (x += ...), so a residual load written
+            // next to its store could not be moved ahead of the previous store and every row would pay a global-memory round
+            // trip: the residuals of a chunk are loaded together, two chunks ahead of their use (buffers ra / rb).
+            constexpr int R = 32 / LIMBS;
+            auto load_res = [&](int c0, float (&dst)[R]) {
+                if (resid_p && n < p.N && c0 < kPfCols) {
 #pragma unroll
-                    for (int j = 0; j < 32 / LIMBS; j++) {
+                    for (int j = 0; j < R; j++) {
                         const int m = tok0 + c0 / LIMBS + j;
-                        resv[j] = m < p.M ? to_f32<OutT>(resid_p[(size_t)m * p.N + n]) : 0.f;
+                        dst[j] = m < p.M ? to_f32<OutT>(resid_p[(size_t)m * p.N + n]) : 0.f;
                     }
                 }
+            };
+            auto process = [&](int c0, const float (&res)[R]) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * kPfCols + c0), v);
                 tmem_ld_wait();
                 if (n < p.N) {
 #pragma unroll
-                    for (int j = 0; j < 32 / LIMBS; j++) {
+                    for (int j = 0; j < R; j++) {
                         const int m = tok0 + c0 / LIMBS + j;
                         if (m < p.M) {
                             float acc;
@@ -268,11 +404,23 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                             else acc = (float)(int)v[j];
                             // (acc * lhs scale) * weight scale with separate roundings, as the CPU kernels compute it
                             float r = __fmul_rn(__fmul_rn(acc, sh_ascale[buf][c0 / LIMBS + j]), wscale);
-                            if (resid_p) r = __fadd_rn(round_store<OutT>(r), resv[j]);
+                            if (resid_p) r = __fadd_rn(round_store<OutT>(r), res[j]);
                             out_p[(size_t)m * p.N + n] = from_f32<OutT>(r);
                         }
                     }
                 }
+            };
+            float ra[R], rb[R];
+            load_res(0, ra);
+            load_res(32, rb);
+#pragma unroll 1
+            for (int c0 = 0; c0 < kPfCols; c0 += 64) {
+                if (tok0 + c0 / LIMBS >= p.M) break;  // uniform: the remaining columns belong to rows past M
+                process(c0, ra);
+                load_res(c0 + 64, ra);
+                if (tok0 + (c0 + 32) / LIMBS >= p.M) break;
+                process(c0 + 32, rb);
+                load_res(c0 + 96, rb);
             }
             tc_fence_before();
             __syncwarp();
@@ -328,6 +476,7 @@ int i8_prefill_launch(cudaStream_t st, void *out, const void *act, const int8_t 
     float *ascale = (float *)((char *)workspace + 256);
     int8_t *limbs = (int8_t *)workspace + 256 + pf_scale_bytes(M);
     const size_t smem = (size_t)K * 4;
+    if (act != nullptr) {  // act == nullptr: a fused producer has left limbs and row scales in the workspace
     const bool vec = act_dtype != MYNN_F32 && K % 8 == 0 && ((uintptr_t)act % 16) == 0;
 #define PREP(T)                                                                                                          \
     {                                                                                                                    \
@@ -343,6 +492,7 @@ int i8_prefill_launch(cudaStream_t st, void *out, const void *act, const int8_t 
     }
 #undef PREP
     MYNN_LAUNCH_OK("act_to_limbs2_kernel");
+    }
     CUtensorMap mw, ma;
     int rc = make_map(&mw, wq, (uint64_t)N, (uint64_t)K, (uint64_t)K, kPfRows);
     if (rc) return rc;
@@ -369,6 +519,57 @@ int i8_prefill_launch(cudaStream_t st, void *out, const void *act, const int8_t 
 // QuantizedMatMul (W8A8): out[m,n] = (sum_k lhs[m,k] * rhs[n,k]) * lhs_scale[m] * rhs_scale[n].  The int8 lhs matrix is
 // the TMA source as it is (no pre-pass, one accumulator column per row), so the int8 pipe does a quarter of the work
 // per output that a bf16 product would need.  workspace: 256 bytes (status word), zeroed once.
+// Fused producers of the prefill DequantMatMul (rows > 32): limbs and row scales go to the layout i8_prefill_launch reads.
+static int pf_fused_ws(void *workspace, size_t workspace_bytes, int rows, int K, int8_t **limbs, float **ascale) {
+    const size_t need = i8_prefill_workspace_bytes(rows, K);
+    if (!workspace || workspace_bytes < need)
+        return fail(MYNN_E_ARG, "fused limb producer: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+    if ((uintptr_t)workspace % 256) return fail(MYNN_E_ARG, "fused limb producer: workspace must be 256-byte aligned");
+    *ascale = (float *)((char *)workspace + 256);
+    *limbs = (int8_t *)workspace + 256 + pf_scale_bytes(rows);
+    return MYNN_OK;
+}
+
+bool prefill_fused_supported(int dtype, int K, const void *a, const void *b) {
+    return dtype != MYNN_F32 && K % 16 == 0 && (size_t)K * 4 <= 200 * 1024 && (((uintptr_t)a | (uintptr_t)b) % 16) == 0;
+}
+
+int launch_rms_norm_limbs2(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, const void *x, const void *w, float eps,
+                           int rows, int D) {
+    int8_t *limbs;
+    float *ascale;
+    if (int rc = pf_fused_ws(workspace, workspace_bytes, rows, D, &limbs, &ascale)) return rc;
+    const size_t smem = (size_t)D * 2;
+#define RUN(T)                                                                                                                \
+    {                                                                                                                         \
+        auto kern = rms_norm_limbs2_kernel<T>;                                                                                \
+        if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        MYNN_CUDA_OK(launch_pdl(kern, dim3(rows), dim3(kLimbThreads), smem, st, limbs, ascale, (const T *)x, (const T *)w, eps, D)); \
+    }
+    if (dtype == MYNN_BF16) RUN(__nv_bfloat16) else if (dtype == MYNN_F16) RUN(__half) else return fail(MYNN_E_ARG, "rms_norm_limbs2: bad dtype %d", dtype);
+#undef RUN
+    MYNN_LAUNCH_OK("rms_norm_limbs2_kernel");
+    return MYNN_OK;
+}
+
+int launch_swiglu_limbs2(cudaStream_t st, int dtype, void *workspace, size_t workspace_bytes, const void *gate, const void *up, int rows,
+                         int F, long long in_stride) {
+    int8_t *limbs;
+    float *ascale;
+    if (int rc = pf_fused_ws(workspace, workspace_bytes, rows, F, &limbs, &ascale)) return rc;
+    const size_t smem = (size_t)F * 2;
+#define RUN(T)                                                                                                                \
+    {                                                                                                                         \
+        auto kern = swiglu_limbs2_kernel<T>;                                                                                  \
+        if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        MYNN_CUDA_OK(launch_pdl(kern, dim3(rows), dim3(kLimbThreads), smem, st, limbs, ascale, (const T *)gate, (const T *)up, F, in_stride)); \
+    }
+    if (dtype == MYNN_BF16) RUN(__nv_bfloat16) else if (dtype == MYNN_F16) RUN(__half) else return fail(MYNN_E_ARG, "swiglu_limbs2: bad dtype %d", dtype);
+#undef RUN
+    MYNN_LAUNCH_OK("swiglu_limbs2_kernel");
+    return MYNN_OK;
+}
+
 bool i8_w8a8_supported(int M, int N, int K, const void *lhs, const void *rhs) {
     return M >= 1 && N >= 1 && K >= 16 && K % 16 == 0 && (((uintptr_t)lhs | (uintptr_t)rhs) % 16) == 0 && tensor_map_api_available();
 }

@@ -58,6 +58,7 @@ struct Model {
     size_t tp_block_bytes = 0;
     TpPeers tp = {};
     bool tp_attached = false;
+    bool weights_aligned = false;  // every projection weight is 16-byte aligned (the TMA-fed kernels can take all of them)
     void *attn_ws, *gemm_ws;
     size_t attn_ws_bytes, gemm_ws_bytes;
     // streaming (sink + ring) cache: per-slot key positions and the scratch that holds one layer's rotated keys
@@ -110,6 +111,12 @@ static int gemm_prequant(cudaStream_t st, const Model &m, void *out, const int8_
     return i8_gemm_launch(st, out, nullptr, w, scale, resid, M, N, K, m.c.dtype, out_dtype, m.gemm_ws, m.gemm_ws_bytes);
 }
 
+// The same for more than 32 rows: two limbs per element in the layout of the prefill kernel.
+static int gemm_prequant2(cudaStream_t st, const Model &m, void *out, const int8_t *w, const void *scale, const void *resid,
+                          int M, int N, int K, int out_dtype) {
+    return i8_prefill_launch(st, out, nullptr, w, scale, resid, M, N, K, m.c.dtype, out_dtype, m.gemm_ws, m.gemm_ws_bytes);
+}
+
 // Enqueue one forward pass over S tokens per sequence (S == 1: decode).  Inputs are the device buffers
 // ids_dev [B*S], pos0_dev / pos_dev [S], past_dev, active_dev.  Leaves logits (and token ids) in device buffers.
 // When the step has at most 32 rows and the int8 tensor-core GEMM is enabled, RMSNorm and Swish*Mul write their
@@ -127,16 +134,28 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     const bool fused = m.gemm_ws != nullptr && M <= kI8MaxRows && H % 16 == 0 && m.ffn % 16 == 0 &&
                        (size_t)std::max(H, m.ffn) * 4 <= 200 * 1024;
 
+    // prefill chunks (more than 32 rows): RMSNorm and Swish*Mul write the two limbs of the prefill kernel themselves
+    const bool fused2 = m.gemm_ws != nullptr && M > kI8MaxRows && dt != MYNN_F32 && m.weights_aligned && tensor_map_api_available() &&
+                        H % 16 == 0 && m.ffn % 16 == 0 && (size_t)std::max(H, m.ffn) * 4 <= 200 * 1024 &&
+                        m.gemm_ws_bytes >= i8_prefill_workspace_bytes(M, std::max(H, m.ffn));
+    bool n_limbs2 = false;  // the last norm left two-limb rows in the workspace instead of m.n
+
     // norm(x [+ part]) feeding a DequantMatMul: either limbs in the workspace (fused) or the bf16 tensor m.n
     auto norm = [&](const void *w, const float *part, int rows, const void *src) -> int {
+        n_limbs2 = false;
         if (fused && rows <= kI8MaxRows)
             return launch_rms_norm_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, nullptr, part ? m.x : nullptr, src, part, w,
                                          c.rms_eps, rows, H);
         if (part) return launch_add_f32_rms_norm(st, dt, m.x, m.n, m.x, part, w, c.rms_eps, rows, H);
+        if (fused2 && rows == M && prefill_fused_supported(dt, H, src, w)) {
+            n_limbs2 = true;
+            return launch_rms_norm_limbs2(st, dt, m.gemm_ws, m.gemm_ws_bytes, src, w, c.rms_eps, rows, H);
+        }
         return mynn_b200_rms_norm(st, m.n, src, w, c.rms_eps, rows, H, dt);
     };
     auto gemm_n = [&](void *out, const int8_t *w, const void *scale, int rows, int N, int out_dtype) -> int {
         if (fused && rows <= kI8MaxRows) return gemm_prequant(st, m, out, w, scale, nullptr, rows, N, H, out_dtype);
+        if (n_limbs2) return gemm_prequant2(st, m, out, w, scale, nullptr, rows, N, H, out_dtype);
         return gemm(st, m, out, m.n, w, scale, nullptr, rows, N, H, out_dtype);
     };
 
@@ -190,8 +209,17 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         }
         if (tp == 1) {
             // x = round(x + round(o))
-            if (attn_limbs) RC(gemm_prequant(st, m, m.x, L.wo, L.so, m.x, M, H, Nq, dt));
-            else RC(gemm(st, m, m.x, m.attn, L.wo, L.so, m.x, M, H, Nq, dt));
+            if (attn_limbs) {
+                RC(gemm_prequant(st, m, m.x, L.wo, L.so, m.x, M, H, Nq, dt));
+            } else if (fused2 && Nq <= 8192) {
+                // a prefill chunk with a short reduction: the residual add inside the tensor-core kernel's epilogue (2-byte
+                // accesses, one weight row per thread) takes longer than the main loop of such a tile; the product alone
+                // into m.n (free here) and a 128-bit add cost less.  Same roundings: round(x + round(o)).
+                RC(gemm(st, m, m.n, m.attn, L.wo, L.so, nullptr, M, H, Nq, dt));
+                RC(mynn_b200_add(st, m.x, m.x, m.n, (int64_t)M * H, dt));
+            } else {
+                RC(gemm(st, m, m.x, m.attn, L.wo, L.so, m.x, M, H, Nq, dt));
+            }
             RC(norm(L.ln2, nullptr, M, m.x));
         } else {
             if (attn_limbs) RC(gemm_prequant(st, m, m.part, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
@@ -205,28 +233,40 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         }
         // --- MLP block ---
         const bool fuse_mlp = fused && L.gu_fused;
+        bool h_limbs2 = false;  // Swish*Mul left two-limb rows in the workspace instead of m.h
         if (L.gu_fused) {
             RC(gemm_n(m.gu, L.wg, L.sg, M, 2 * m.ffn, dt));
-            if (fuse_mlp)
-                RC(launch_swiglu_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, m.gu, (char *)m.gu + (size_t)m.ffn * esz, M, m.ffn,
-                                       2LL * m.ffn));
-            else
-                RC(launch_swiglu_strided(st, dt, m.h, m.gu, (char *)m.gu + (size_t)m.ffn * esz, M, m.ffn, 2LL * m.ffn));
+            const char *up_ = (char *)m.gu + (size_t)m.ffn * esz;
+            if (fuse_mlp) {
+                RC(launch_swiglu_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, m.gu, up_, M, m.ffn, 2LL * m.ffn));
+            } else if (fused2 && prefill_fused_supported(dt, m.ffn, m.gu, up_)) {
+                RC(launch_swiglu_limbs2(st, dt, m.gemm_ws, m.gemm_ws_bytes, m.gu, up_, M, m.ffn, 2LL * m.ffn));
+                h_limbs2 = true;
+            } else {
+                RC(launch_swiglu_strided(st, dt, m.h, m.gu, up_, M, m.ffn, 2LL * m.ffn));
+            }
         } else {
             char *u_ = (char *)m.gu + (size_t)M * m.ffn * esz;
             RC(gemm_n(m.gu, L.wg, L.sg, M, m.ffn, dt));
             RC(gemm_n(u_, L.wu, L.su, M, m.ffn, dt));
-            RC(launch_swiglu_strided(st, dt, m.h, m.gu, u_, M, m.ffn, m.ffn));
+            if (fused2 && prefill_fused_supported(dt, m.ffn, m.gu, u_)) {
+                RC(launch_swiglu_limbs2(st, dt, m.gemm_ws, m.gemm_ws_bytes, m.gu, u_, M, m.ffn, m.ffn));
+                h_limbs2 = true;
+            } else {
+                RC(launch_swiglu_strided(st, dt, m.h, m.gu, u_, M, m.ffn, m.ffn));
+            }
         }
         const bool last = l + 1 == c.n_layers;
         const void *next_norm = last ? nullptr : m.layers[l + 1].ln1;
         if (tp == 1) {
             if (fuse_mlp) RC(gemm_prequant(st, m, m.x, L.wd, L.sd, m.x, M, H, m.ffn, dt));
+            else if (h_limbs2) RC(gemm_prequant2(st, m, m.x, L.wd, L.sd, m.x, M, H, m.ffn, dt));
             else RC(gemm(st, m, m.x, m.h, L.wd, L.sd, m.x, M, H, m.ffn, dt));
             if (!last) RC(norm(next_norm, nullptr, M, m.x));
         } else {
             float *pdst = tp_fused ? tp_part(m.tp.local, m.tp.part_off[1]) : m.part;
             if (fuse_mlp) RC(gemm_prequant(st, m, pdst, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
+            else if (h_limbs2) RC(gemm_prequant2(st, m, pdst, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
             else RC(gemm(st, m, pdst, m.h, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
             if (tp_fused) {
                 RC(launch_tp_reduce_norm_limbs(st, dt, m.tp, 1, m.gemm_ws, m.gemm_ws_bytes, m.x, next_norm, c.rms_eps, M, H));
@@ -314,6 +354,10 @@ static int model_create(Model **out, void **initializer, void **session_state) {
                       (const char *)L.sv == (const char *)L.sk + nkv * esz;
         L.gu_fused = L.wu == L.wg + (size_t)m->ffn * H && (const char *)L.su == (const char *)L.sg + (size_t)m->ffn * esz;
     }
+    m->weights_aligned = true;
+    for (const LayerW &L : m->layers)
+        for (const int8_t *wp : {L.wq, L.wk, L.wv, L.wo, L.wg, L.wu, L.wd})
+            if ((uintptr_t)wp % 16) m->weights_aligned = false;
     m->final_norm = initializer[i++];
     m->lm_w = (const int8_t *)initializer[i++];
     m->lm_scale = initializer[i++];
