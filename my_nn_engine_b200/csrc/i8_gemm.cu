@@ -111,7 +111,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 tma_load_2d(smem + i * kStageBytes + kWBytes, &map_a, (kb_beg + i) * kBlockK, 0, &full_bar[i]);
             for (int i = pre; i < nkb; i++) {
                 const int s = i % stages, it = i / stages;
-                if (!mbar_wait(&empty_bar[s], (it - 1) & 1, &abort_flag)) {
+                if (!mbar_wait_spin(&empty_bar[s], (it - 1) & 1, &abort_flag)) {
                     atomicExch(&abort_flag, 1);
                     atomicExch(p.status, 1);
                     break;
@@ -131,7 +131,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             bool ok = true;
             for (int i = 0; i < nkb && ok; i++) {
                 const int s = i % stages, it = i / stages;
-                if (!mbar_wait(&full_bar[s], it & 1, &abort_flag)) {
+                if (!mbar_wait_spin(&full_bar[s], it & 1, &abort_flag)) {
                     atomicExch(&abort_flag, 1);
                     atomicExch(p.status, 2);
                     ok = false;
@@ -184,7 +184,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         // one lane per warp polls the barrier (128 spinning threads would flood the shared-memory pipe that the
         // co-resident CTA needs); the outcome is broadcast to the warp
         int ok_i = 1;
-        if (lane == 0) ok_i = mbar_wait(&accum_bar, 0, &abort_flag) ? 1 : 0;
+        if (lane == 0) ok_i = mbar_wait_spin(&accum_bar, 0, &abort_flag) ? 1 : 0;
         const bool ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
         if (threadIdx.x == 64 && p.dbg == 2) pdl_trigger();  // main loop over: the next kernel may be scheduled during the epilogue
         if (stamp && threadIdx.x == 64) p.timing[3] = global_ns();  // accumulators complete

@@ -292,7 +292,7 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 const int wt = tile / p.t_tiles, tt = tile - wt * p.t_tiles;
                 for (int kb = 0; kb < kblocks; kb++, kc++) {
                     const int s = kc % kPfStages, use = kc / kPfStages;
-                    if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, &abort_flag)) {
+                    if (use > 0 && !mbar_wait_spin(&empty_bar[s], (use - 1) & 1, &abort_flag)) {
                         atomicExch(&abort_flag, 1);
                         atomicExch(p.status, 11);
                         ok = false;
@@ -318,7 +318,7 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 const int tt_ = tile % p.t_tiles;
                 const int cols = min(kPfCols, (((p.M - tt_ * kTok) * LIMBS + 15) >> 4) << 4);
                 const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(cols >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
-                if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1, &abort_flag)) {  // epilogue has drained it
+                if (use > 0 && !mbar_wait_spin(&acc_empty[buf], (use - 1) & 1, &abort_flag)) {  // epilogue has drained it
                     atomicExch(&abort_flag, 1);
                     atomicExch(p.status, 12);
                     break;
@@ -327,7 +327,7 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kPfCols);
                 for (int kb = 0; kb < kblocks; kb++, kc++) {
                     const int s = kc % kPfStages;
-                    if (!mbar_wait(&full_bar[s], (kc / kPfStages) & 1, &abort_flag)) {
+                    if (!mbar_wait_spin(&full_bar[s], (kc / kPfStages) & 1, &abort_flag)) {
                         atomicExch(&abort_flag, 1);
                         atomicExch(p.status, 13);
                         ok = false;
@@ -367,7 +367,7 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             // one thread waits for the accumulator and publishes the verdict, so that all four warps take the same
             // branch (a warp leaving alone would strand the others at the named barrier)
             if (et == 0) {
-                const bool ok = mbar_wait(&acc_full[buf], use & 1, &abort_flag);
+                const bool ok = mbar_wait_spin(&acc_full[buf], use & 1, &abort_flag);
                 if (!ok) {
                     atomicExch(&abort_flag, 1);
                     atomicExch(p.status, 14);
