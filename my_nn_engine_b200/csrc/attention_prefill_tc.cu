@@ -53,6 +53,7 @@ struct TcAttnParams {
     const int32_t *active_dev;
     int is_causal, out_bshd;
     uint32_t v_lbo, v_sbo;  // byte offsets of the MN-major V descriptor
+    int n_qt, heads_per_grid, B;  // 1-D grid: query tiles x (heads or head pairs) x batch, query tile slowest
     int p_tmem;  // probabilities handed to the second product through tensor memory (over the S columns) instead of shared memory
 };
 
@@ -99,7 +100,7 @@ __device__ __forceinline__ void warp_arrive(uint64_t *bar) {
     if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
 }
 
-// grid (ceil(Sq / 128), Hq, B), block 320
+// grid ceil(Sq / 128) x Hq x B (one dimension), block 320
 template <typename T, int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -118,7 +119,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __shared__ float sh_max[2][2][kTcRows];  // [tile parity][column half][row]: the halves of a row exchange their maxima
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;  // causal: the longest tiles are scheduled first
+    // 1-D grid with the query tile as the slowest index, last tile first: with a causal mask the work of a CTA grows with its
+    // query tile, and CTAs are dispatched in index order, so the longest ones of ALL heads start first
+    const int per_qt = p.heads_per_grid * p.B;
+    const int qt = p.n_qt - 1 - (int)blockIdx.x / per_qt, h = ((int)blockIdx.x % per_qt) % p.heads_per_grid, b = ((int)blockIdx.x % per_qt) / p.heads_per_grid;
     const int kvh = h / (p.Hq / p.Hkv);
     int active = p.active_dev ? *p.active_dev : p.active_host;
     active = max(0, min(active, p.cache_seq));
@@ -428,7 +432,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 // The tensor core executes one thread's MMAs in issue order, so S_t(j+1), issued behind O_t(j), cannot overwrite P_t(j) early,
 // and the completion of S_t(j+1) tells the softmax warps that O_t(j) is complete as well (they may rescale O_t).
 //
-// grid (ceil(Sq / 128), Hq / 2, B), block 320: warp 0 TMA, warp 1 MMA, warps 2-5 softmax of head 0, warps 6-9 of head 1.
+// grid ceil(Sq / 128) x Hq / 2 x B (one dimension), block 320: warp 0 TMA, warp 1 MMA, warps 2-5 softmax of head 0, warps 6-9 of head 1.
 template <typename T, int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -443,7 +447,8 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qt = gridDim.x - 1 - blockIdx.x, h0 = 2 * blockIdx.y, b = blockIdx.z;  // causal: the longest tiles are scheduled first
+    const int per_qt = p.heads_per_grid * p.B;  // 1-D grid, query tile slowest and last tile first (see the one-head kernel)
+    const int qt = p.n_qt - 1 - (int)blockIdx.x / per_qt, h0 = 2 * (((int)blockIdx.x % per_qt) % p.heads_per_grid), b = ((int)blockIdx.x % per_qt) / p.heads_per_grid;
     const int kvh = h0 / (p.Hq / p.Hkv);  // the group size is even: both heads read the same kv head
     int active = p.active_dev ? *p.active_dev : p.active_host;
     active = max(0, min(active, p.cache_seq));
@@ -724,7 +729,11 @@ static int launch_tc(cudaStream_t st, const CUtensorMap &mq, const CUtensorMap &
         MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set = true;
     }
-    kern<<<dim3((p.Sq + kTcRows - 1) / kTcRows, p.Hq, B), kTcThreads, smem, st>>>(mq, mk, mv, p);
+    TcAttnParams q = p;
+    q.n_qt = (p.Sq + kTcRows - 1) / kTcRows;
+    q.heads_per_grid = p.Hq;
+    q.B = B;
+    kern<<<dim3((unsigned)((long long)q.n_qt * q.heads_per_grid * B)), kTcThreads, smem, st>>>(mq, mk, mv, q);
     MYNN_LAUNCH_OK("attention_prefill_tc_kernel");
     return MYNN_OK;
 }
@@ -738,7 +747,11 @@ static int launch_tc2(cudaStream_t st, const CUtensorMap &mq, const CUtensorMap 
         MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set = true;
     }
-    kern<<<dim3((p.Sq + kTcRows - 1) / kTcRows, p.Hq / 2, B), kTcThreads, smem, st>>>(mq, mk, mv, p);
+    TcAttnParams q = p;
+    q.n_qt = (p.Sq + kTcRows - 1) / kTcRows;
+    q.heads_per_grid = p.Hq / 2;
+    q.B = B;
+    kern<<<dim3((unsigned)((long long)q.n_qt * q.heads_per_grid * B)), kTcThreads, smem, st>>>(mq, mk, mv, q);
     MYNN_LAUNCH_OK("attention_prefill_tc2_kernel");
     return MYNN_OK;
 }
