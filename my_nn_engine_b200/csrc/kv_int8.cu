@@ -458,6 +458,45 @@ static int launch_decode_q8(cudaStream_t st, const DecodeParams &p, int B) {
     return MYNN_OK;
 }
 
+// out[bh, s, :] = T(cache[bh, s, :] * scale[bh, s]) for the live rows s < active: the 16-bit copy of an int8 cache that the
+// tensor-core prefill attention reads (rounded once to T, like the rows of a 16-bit cache).  16 elements per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dequant_kv_rows_kernel(T *out, const int8_t *cache, const T *scale, int cache_seq, int D, int active_host, const int32_t *active_dev) {
+    const int active = min(active_dev ? *active_dev : active_host, cache_seq);
+    const int groups = D >> 4;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)active * groups) return;
+    const int s = (int)(idx / groups), g = (int)(idx - (long long)s * groups);
+    const size_t row = (size_t)blockIdx.y * cache_seq + s;
+    const float sc = to_f32<T>(scale[row]);
+    int8_t q[16];
+    *reinterpret_cast<uint4 *>(q) = *reinterpret_cast<const uint4 *>(cache + row * D + 16 * g);
+    T o[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) o[i] = from_f32<T>((float)q[i] * sc);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + row * D + 16 * g);
+    dst[0] = reinterpret_cast<const uint4 *>(o)[0];
+    dst[1] = reinterpret_cast<const uint4 *>(o)[1];
+}
+
+int launch_dequant_kv_rows(cudaStream_t st, int dtype, void *out, const void *cache, const void *scale, int BH, int cache_seq, int D,
+                           int active_host, const int32_t *active_dev) {
+    if (BH == 0 || cache_seq == 0) return MYNN_OK;
+    if (dtype == MYNN_F32 || D % 16 || (((uintptr_t)out | (uintptr_t)cache) % 16))
+        return fail(MYNN_E_UNSUPPORTED, "dequant_kv_rows: 16-bit tensors with D a multiple of 16 and 16-byte aligned rows only");
+    const int bound = active_dev ? cache_seq : (active_host < cache_seq ? active_host : cache_seq);
+    if (bound <= 0) return MYNN_OK;
+    const long long n = (long long)bound * (D / 16);
+    const dim3 grid((unsigned)((n + 255) / 256), BH);
+    if (dtype == MYNN_BF16)
+        dequant_kv_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16 *)out, (const int8_t *)cache, (const __nv_bfloat16 *)scale, cache_seq, D, active_host, active_dev);
+    else
+        dequant_kv_rows_kernel<__half><<<grid, 256, 0, st>>>((__half *)out, (const int8_t *)cache, (const __half *)scale, cache_seq, D, active_host, active_dev);
+    MYNN_LAUNCH_OK("dequant_kv_rows_kernel");
+    return MYNN_OK;
+}
+
 int launch_attention_q8(cudaStream_t st, void *out, const void *q, const void *k, const void *v, const void *k_scale,
                         const void *v_scale, float scale, int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len,
                         int active_seq_kv, const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,

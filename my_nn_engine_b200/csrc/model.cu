@@ -64,6 +64,7 @@ struct Model {
     // streaming (sink + ring) cache: per-slot key positions and the scratch that holds one layer's rotated keys
     int64_t *kvpos_dev = nullptr;
     void *k_rot = nullptr;
+    void *k_deq = nullptr, *v_deq = nullptr;  // int8 cache: 16-bit copy of one layer's live rows for the tensor-core prefill attention
     cudaGraphExec_t stream_graph_exec = nullptr;
     cudaStream_t stream = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
@@ -187,8 +188,18 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         if (c.kv_int8) {
             RC(launch_rope_kv_append_q8(st, dt, m.q_rot, L.kc, L.vc, L.ksc, L.vsc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
                                         S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
-            RC(launch_attention_q8(st, m.attn, m.q_rot, L.kc, L.vc, L.ksc, L.vsc, attn_scale, B, m.Hq, m.Hkv, S, D,
-                                   c.max_seq_len, c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
+            if (S >= 64 && m.k_deq &&
+                attention_prefill_tc_supported(B, m.Hq, m.Hkv, S, D, c.max_seq_len, dt, m.q_rot, m.k_deq, m.v_deq, m.attn)) {
+                // a long prefill chunk: the tensor-core kernel over a 16-bit copy of the live rows (value * row scale, rounded
+                // once, i.e. what a 16-bit cache would hold for these quantised rows)
+                RC(launch_dequant_kv_rows(st, dt, m.k_deq, L.kc, L.ksc, B * m.Hkv, c.max_seq_len, D, 0, m.active_dev));
+                RC(launch_dequant_kv_rows(st, dt, m.v_deq, L.vc, L.vsc, B * m.Hkv, c.max_seq_len, D, 0, m.active_dev));
+                RC(launch_attention(st, m.attn, m.q_rot, m.k_deq, m.v_deq, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
+                                    c.max_seq_len, m.active_dev, 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
+            } else {
+                RC(launch_attention_q8(st, m.attn, m.q_rot, L.kc, L.vc, L.ksc, L.vsc, attn_scale, B, m.Hq, m.Hkv, S, D,
+                                       c.max_seq_len, c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
+            }
         } else if (c.stream_window > 0) {
             // streaming cache: K is appended unrotated at the slot in past_dev; the live rows are rotated at their
             // recency rank into the scratch copy that attention reads.  The live rows are the slots [0, active).
@@ -390,6 +401,9 @@ static int model_create(Model **out, void **initializer, void **session_state) {
                  o_ws = take(m->attn_ws_bytes), o_gws = take(m->gemm_ws_bytes),
                  o_kvpos = take(c.stream_window > 0 ? (size_t)c.max_seq_len * 8 : 0),
                  o_krot = take(c.stream_window > 0 ? (size_t)c.batch * m->Hkv * c.max_seq_len * D * esz : 0);
+    const bool want_deq = c.kv_int8 && prefill >= 64 && c.dtype != MYNN_F32 && (D == 64 || D == 128);
+    const size_t deq_bytes = want_deq ? (size_t)c.batch * m->Hkv * c.max_seq_len * D * esz : 0;
+    const size_t o_kdeq = take(deq_bytes), o_vdeq = take(deq_bytes);
     cudaError_t e = cudaMalloc(&m->arena, off);
     if (e != cudaSuccess) {
         delete m;
@@ -410,6 +424,8 @@ static int model_create(Model **out, void **initializer, void **session_state) {
     m->gemm_ws = m->gemm_ws_bytes ? a + o_gws : nullptr;
     m->kvpos_dev = (int64_t *)(a + o_kvpos);
     m->k_rot = a + o_krot;
+    m->k_deq = want_deq ? a + o_kdeq : nullptr;
+    m->v_deq = want_deq ? a + o_vdeq : nullptr;
     m->part = nullptr;
     if (tp > 1) {
         const size_t pbytes = up256(R * H * 4);

@@ -55,6 +55,9 @@ bool attention_prefill_supported(int Sq, int D, int dtype, const void *q, const 
 int launch_attention_prefill(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B, int Hq,
                              int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv, const int32_t *active_seq_kv_dev,
                              int is_causal, int dtype, int out_bshd);
+// 16-bit copy of the live rows of an int8 KV cache (value * per-row scale, rounded once); see kv_int8.cu.
+int launch_dequant_kv_rows(cudaStream_t st, int dtype, void *out, const void *cache, const void *scale, int BH, int cache_seq, int D,
+                           int active_host, const int32_t *active_dev);
 // The same on tcgen05 / tensor memory (128 query rows per CTA, TMA-fed); see attention_prefill_tc.cu.
 bool attention_prefill_tc_supported(int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len, int dtype, const void *q, const void *k,
                                     const void *v, const void *out);

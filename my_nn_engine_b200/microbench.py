@@ -141,7 +141,7 @@ TINYLLAMA = dict(hidden_size=2048, num_hidden_layers=22, num_attention_heads=32,
                  intermediate_size=5632, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0)
 
 
-def prefill_model(arch="llama3-8b", batch=1, length=2048, chunk=None, layers=None, dtype="bf16", reps=3, quiet=False):
+def prefill_model(arch="llama3-8b", batch=1, length=2048, chunk=None, layers=None, dtype="bf16", reps=3, quiet=False, kv_int8=False):
     """Whole-model prefill of ``length`` prompt tokens per sequence (random int8 weights of the named architecture) in
     chunks of ``chunk`` tokens: the prefill DequantMatMul and the prefill attention kernels in context.  Wall-clock per
     prompt, host call to host result (the last token's id)."""
@@ -154,7 +154,7 @@ def prefill_model(arch="llama3-8b", batch=1, length=2048, chunk=None, layers=Non
         cfg["num_hidden_layers"] = layers
     chunk = chunk or length
     state = random_llama_state(cfg, seed=0, device="cuda")
-    model = DecoderModel(cfg, state, dtype=dtype, max_seq_len=length + 8, batch=batch, output="ids", max_prefill=chunk)
+    model = DecoderModel(cfg, state, dtype=dtype, max_seq_len=length + 8, batch=batch, output="ids", max_prefill=chunk, kv_int8=kv_int8)
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, cfg["vocab_size"], size=(batch, length))
     times = []
@@ -168,7 +168,7 @@ def prefill_model(arch="llama3-8b", batch=1, length=2048, chunk=None, layers=Non
     ops.attention_check()
     best = min(times[1:])
     res = {"kernel": "model_prefill", "arch": arch, "layers": cfg["num_hidden_layers"], "batch": batch, "len": length, "chunk": chunk,
-           "dtype": dtype, "ms": best * 1e3, "first_call_ms": times[0] * 1e3, "prompt_tok_per_s": batch * length / best}
+           "dtype": dtype, "kv_cache": "int8" if kv_int8 else dtype, "ms": best * 1e3, "first_call_ms": times[0] * 1e3, "prompt_tok_per_s": batch * length / best}
     model.close()
     if not quiet:
         print(json.dumps(res), flush=True)
@@ -243,6 +243,7 @@ def main():
     pm.add_argument("--chunk", type=int, default=None)
     pm.add_argument("--layers", type=int, default=None)
     pm.add_argument("--dtype", default="bf16")
+    pm.add_argument("--kv", default="16bit", choices=["16bit", "int8"])
     q = sub.add_parser("w8a8")
     q.add_argument("--m", type=int, default=2048)
     q.add_argument("--n", type=int, default=14336)
@@ -256,7 +257,7 @@ def main():
     elif args.cmd == "prefill_attn":
         prefill_attn(args.b, args.hq, args.hkv, args.d, args.len, args.dtype)
     elif args.cmd == "prefill_model":
-        prefill_model(args.arch, args.b, args.len, args.chunk, args.layers, args.dtype)
+        prefill_model(args.arch, args.b, args.len, args.chunk, args.layers, args.dtype, kv_int8=args.kv == "int8")
     elif args.cmd == "w8a8":
         w8a8(args.m, args.n, args.k, args.dtype, args.copies)
     elif args.cmd == "attn":

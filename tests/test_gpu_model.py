@@ -121,6 +121,17 @@ def test_mid_size_model_long_prefill_chunks_use_the_tensor_core_attention():
     assert flips <= 2
 
 
+def test_int8_kv_cache_long_prefill_chunks_use_the_tensor_core_attention():
+    """quant_kv_cache with prefill chunks of 70 tokens: attention runs on the tcgen05 kernel over a 16-bit copy of the
+    quantised rows (value * row scale, rounded once)."""
+    from my_nn_engine_b200 import ops
+    from my_nn_engine_b200.quantize import random_llama_state
+    state = random_llama_state(MID, seed=3)
+    worst, flips = run_parity(MID, state, "bf16", batch=2, steps=4, max_seq=160, prompt_len=140, prefill_len=70, seed=11, kv_int8=True)
+    ops.attention_check()
+    assert flips <= 2
+
+
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 def test_int8_kv_cache_tiny_model(tiny_llama, dtype):
     """quant_kv_cache on the 2-layer fixture model (head_dim 4: generic attention over the int8 cache)."""
