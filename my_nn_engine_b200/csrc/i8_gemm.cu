@@ -702,7 +702,12 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
     p.dbg = g_pdl_level >= 2 ? 2 : 0;
     const int row_tiles = (N + kTileRows - 1) / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
     const int S = g_i8_split_override > 0 ? g_i8_split_override : pick_split(row_tiles, kblocks);
-    p.stages = (long long)row_tiles * S <= 148 ? kMaxStages : kStages;
+    // two CTAs per SM share 227 KB: three stages with 96 limb columns (28 KB per stage), up to five with fewer columns
+    // (measured at 8 and 16 rows: a fourth stage gives 2 %, a fifth nothing)
+    const int stage_bytes = kTileRows * kBlockK + ((NC * kBlockK + 1023) / 1024) * 1024;
+    const int shared_stages = std::max(kStages, std::min(5, (111 * 1024) / stage_bytes));
+    p.stages = (long long)row_tiles * S <= 148 ? kMaxStages : shared_stages;
+    if (g_i8_dbg >= 2 && g_i8_dbg <= kMaxStages) p.stages = g_i8_dbg;  // tuning hook: pipeline depth
 #define GO(OT, NCV) return launch_i8<OT, NCV>(st, mw, ma, p, S)
 #define BY_NC(OT)                \
     switch (NC) {                \
