@@ -364,7 +364,7 @@ i8_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                                  : to_f32<OutT>(reinterpret_cast<const OutT *>(p.ascale_t)[(size_t)(tok0 + i) * p.ascale_stride]);
                 sh_ascale[buf][i] = a;
             }
-            // one thread waits for the accumulator and publishes the verdict, so that all four warps take the same
+            // one thread waits for the accumulator and publishes the outcome, so that all four warps take the same
             // branch (a warp leaving alone would strand the others at the named barrier)
             if (et == 0) {
                 const bool ok = mbar_wait_spin(&acc_full[buf], use & 1, &abort_flag);

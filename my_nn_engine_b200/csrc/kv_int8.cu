@@ -58,13 +58,13 @@ __global__ void __launch_bounds__(64)
 rope_kv_append_q8_kernel(T *q_out, int8_t *k_cache, int8_t *v_cache, T *k_scale, T *v_scale, const T *q, const T *k,
                          const T *v, long long q_stride, long long k_stride, long long v_stride, const T *cos_t,
                          const T *sin_t, const int64_t *positions, int S, int Hq, int Hkv, int D, int cache_seq,
-                         const int32_t *past_len_dev) {
+                         const int32_t *past_len_dev, int slot0) {
     extern __shared__ float rowv[];  // D rotated / copied values
     __shared__ float wmax[2];
     pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x, b = row / S, s = row - b * S;
-    const int slot = blockIdx.y;
+    const int slot = blockIdx.y + slot0;  // slot0 = Hq: the q heads are rotated by another launch
     const int half = D >> 1;
     const int cache_row = *past_len_dev + s;
     const bool in_cache = cache_row >= 0 && cache_row < cache_seq;
@@ -122,11 +122,19 @@ int launch_rope_kv_append_q8(cudaStream_t st, int dtype, void *q_out, void *k_ca
                              const int32_t *past_len_dev) {
     if (B * S == 0) return MYNN_OK;
     if (D > 4096) return fail(MYNN_E_UNSUPPORTED, "rope_kv_append_q8: head dim %d too large", D);
+    // prefill chunks: the q heads (most of the slots) go through the 128-bit RoPE kernel, this one keeps the k / v slots
+    int slot0 = 0;
+    if (S > 1 && dtype != MYNN_F32 && D % 16 == 0) {
+        if (int rc = launch_rope_kv_append(st, dtype, q_out, q_out, q_out, q, q, q, q_stride, q_stride, q_stride, cos_t, sin_t, positions,
+                                           B, S, Hq, 0, D, cache_seq, past_len_dev, 1))
+            return rc;
+        slot0 = Hq;
+    }
     MYNN_DISPATCH_DTYPE(dtype, T, {
-        MYNN_CUDA_OK(launch_pdl(rope_kv_append_q8_kernel<T>, dim3(B * S, Hq + 2 * Hkv), dim3(64), (size_t)D * 4, st, (T *)q_out,
+        MYNN_CUDA_OK(launch_pdl(rope_kv_append_q8_kernel<T>, dim3(B * S, Hq + 2 * Hkv - slot0), dim3(64), (size_t)D * 4, st, (T *)q_out,
                                 (int8_t *)k_cache, (int8_t *)v_cache, (T *)k_scale, (T *)v_scale, (const T *)q, (const T *)k,
                                 (const T *)v, q_stride, k_stride, v_stride, (const T *)cos_t, (const T *)sin_t, positions, S,
-                                Hq, Hkv, D, cache_seq, past_len_dev));
+                                Hq, Hkv, D, cache_seq, past_len_dev, slot0));
     });
     MYNN_LAUNCH_OK("rope_kv_append_q8_kernel");
     return MYNN_OK;
