@@ -1,7 +1,9 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05.mma kind::f16, accumulators in tensor memory).
 //
-// Both products of a prefill chunk, S = Q K^T and O = P V, are dense 16-bit contractions.  One CTA owns 128 query rows of
-// one (batch, query head) pair, i.e. one TMEM lane per query row, and walks the kv rows in tiles of 128:
+// Both products of a prefill chunk, S = Q K^T and O = P V, are dense 16-bit contractions.  Two kernels: the one used whenever
+// the GQA group size is even puts two query heads of one kv head into a CTA (second half of this file); the one described
+// first serves the other group sizes.  There one CTA owns 128 query rows of one (batch, query head) pair, i.e. one TMEM lane
+// per query row, and walks the kv rows in tiles of 128:
 //
 //   warp 0     TMA producer: the Q tile once, then K and V tiles through two buffers each (a K buffer is released by the
 //              first product, a V buffer by the second), every tile as 64-element (128-byte) slabs with the 128-byte
@@ -13,7 +15,11 @@
 //   warps 2-9  softmax, two threads per query row (64 kv columns each; the row maximum is exchanged through shared
 //              memory): tcgen05.ld of the row of S, causal / length mask, running maximum and sum in f32 in units of
 //              log2(e), probabilities rounded to the 16-bit storage type and written to shared memory in the swizzled
-//              K-major layout the second product reads; finally O / sum -> global memory.
+//              K-major layout the second product reads (or, as an option, into tensor memory over the S columns, as the
+//              two-head kernel always does); finally O / sum -> global memory.
+//
+// The grid is one-dimensional, query tile slowest and last tile first, so that with a causal mask the longest CTAs of all
+// heads are dispatched first.
 //
 // Rescaling O when the running maximum moves costs a TMEM round trip (tcgen05.ld, multiply, tcgen05.st), so the maximum
 // in use is only advanced when the true maximum has moved by more than 8 (a factor 256): probabilities then are at most
