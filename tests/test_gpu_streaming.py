@@ -125,6 +125,31 @@ def test_streaming_decoder_matches_oracle_across_eviction(dtype, batch, prefill,
     model.close()
 
 
+def test_streaming_decoder_long_prefill_chunks_then_eviction():
+    """sink 4 + window 156 = 160 live rows; two prefill chunks of 70 tokens (long enough for the tcgen05 attention over the
+    rotated copy of the keys), then 40 decode steps, of which the last 20 evict."""
+    from my_nn_engine_b200 import ops
+    from my_nn_engine_b200.decoder import DecoderModel
+    from my_nn_engine_b200.quantize import random_llama_state
+    state = random_llama_state(MID, seed=11)
+    sink, window, batch, chunk = 4, 156, 2, 70
+    oracle = OracleLlama(LlamaConfig.from_hf(MID), to_oracle_weights(state, "bf16"), "bf16", 160, batch, streaming=(sink, window))
+    model = DecoderModel(MID, state, dtype="bf16", max_seq_len=160, batch=batch, output="logits", max_prefill=chunk,
+                         streaming=(sink, window))
+    rng = np.random.default_rng(5)
+    toks = rng.integers(0, MID["vocab_size"], size=(batch, 180))
+    oracle.prefill(toks[:, :2 * chunk], chunk)
+    model.stream(toks[:, :chunk], 0)
+    out = model.stream(toks[:, chunk:2 * chunk], chunk)
+    ops.attention_check()
+    assert rel_err(out.float().numpy(), oracle.last_logits) <= 3e-2
+    for p in range(2 * chunk, 180):
+        oracle.decode_step(toks[:, p])
+        out = model.stream(toks[:, p], p)
+        assert rel_err(out.float().numpy(), oracle.last_logits) <= 3e-2, p
+    model.close()
+
+
 def test_tiny_llama_streaming_session_reproduces_expected_ids(tiny_llama):
     """crates/llm/tests/tinyllama_random.rs:23-49 with the float weights quantised: the int8 model is not pinned by the
     float ids, so the device model is compared with the oracle on the same int8 weights; the f32 oracle on the float
