@@ -2,19 +2,27 @@
 batch 32, 2048-token context, greedy decode — tokens per second of the whole job.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --case {gemv|gemm|attention|prefill_gemm|prefill_attention|prefill_model|w8a8|suite} [...]
 
-A step is one decode step of the whole batch (32 new tokens).  Weights are random-init (N(0, 0.02), quantised with
-the engine's quantizer), the 2048-token context is synthetic KV (N(0,1) * 0.5): there is no dataset or checkpoint
-on this path.  Tensor parallel over N GPUs of one node (one process per GPU, NCCL): total work is fixed, so scaling
-is "strong".  The working set (7.5 GB of weights + 8.6 GB of KV per step) is far larger than L2, so no flush is
-needed between iterations.
+Default case ("step").  A step is one decode step of the whole batch (32 new tokens).  Weights are random-init (N(0, 0.02),
+quantised with the engine's quantizer), the 2048-token context is synthetic KV (N(0,1) * 0.5, one seed for the whole cache,
+each tensor-parallel rank keeps its heads): there is no dataset or checkpoint on this path.  Tensor parallel over N GPUs of
+one node (one process per GPU, NCCL): total work is fixed, so scaling is "strong".  The working set (7.5 GB of weights +
+8.6 GB of KV per step) is far larger than L2, so no flush is needed between iterations.
 
-Printed JSON (rank 0): value = device-resident throughput (token ids fed back on the device, CUDA events around
-exactly K steps, max over ranks); e2e = the same through model(state, outputs, inputs) with HOST buffers (pinned
-ids in, token ids out every step); roofline = the dominant kernel (the tcgen05 int8 DequantMatMul, gate/up shape at M=32) timed live over
-the model's own per-layer weights; cpu_baseline = the CPU oracle on a bounded slice of the same workload.
+Printed JSON (rank 0): value = device-resident throughput (token ids fed back on the device, CUDA events around exactly K
+steps, max over ranks; the block of K steps is repeated and the median block is reported, with min and max beside it);
+e2e = the same through model(state, outputs, inputs) with HOST buffers (pinned ids in, token ids out every step);
+e2e_logits = the same with the engine's real graph output, full logits to the host every step; roofline = the largest
+launch of the dominant kernel (the tcgen05 int8 DequantMatMul, gate/up shape) timed live over the model's own weights;
+gemm_kernel / attention_kernel = every DequantMatMul launch of one step, and the decode-attention launches of one step,
+each timed in one graph; cpu_baseline = the CPU oracle on a bounded slice of the same workload.
 `--impl reference` times the CPU restatement of the engine's CPU backend instead (the engine itself, Rust + LLVM 18,
 cannot be built here) with all host threads.
+
+The other cases time single kernels of the path the way the step's kernels are fed: every launch reads a different copy of
+its weights / KV (copies x size > L2), the launches are replayed from one CUDA graph, CUDA events on the launching stream.
+Algorithmic bytes: GEMM  N*K + N*sizeof(scale) + M*K*sizeof(act) + M*N*sizeof(out);  attention  2*B*Hkv*L*D*2 + Q + out.
 """
 from __future__ import annotations
 
@@ -25,22 +33,27 @@ import subprocess
 import sys
 import threading
 import time
+import zlib
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 LLAMA3_8B = dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                  intermediate_size=14336, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0)
+TINYLLAMA = dict(hidden_size=2048, num_hidden_layers=22, num_attention_heads=32, num_key_value_heads=4, head_dim=64,
+                 intermediate_size=5632, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0)
 BATCH, CONTEXT = 32, 2048
 METRIC, UNIT = "decode_tokens_per_second", "tok/s"
 
 
-def measured_peak_hbm():
+def measured_peaks():
+    """(HBM GB/s, dense bf16 TFLOP/s, 'measured' | 'fallback'): the driver-written measurement of this pool's B200s."""
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+            j = json.load(f)
+        return float(j["hbm_gbs"]), float(j["bf16_tflops"]), "measured"
     except Exception:
-        return 6650.0, "fallback"
+        return 6650.0, 1590.0, "fallback"
 
 
 def workload_name(cfg):
@@ -164,7 +177,7 @@ class ClockSampler:
                     self.samples.append(parts)
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(0.1)
 
     def __enter__(self):
         self._t = threading.Thread(target=self._run, daemon=True)
@@ -183,6 +196,22 @@ class ClockSampler:
         reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(float(self.samples[0][1])), "reasons": reasons,
                 "samples": len(mhz)}
+
+
+def fill_synthetic_context(model, cfg, rank, world, dev):
+    """The 2048-row context of every layer from ONE seed for the whole (unsharded) cache; a tensor-parallel rank keeps its
+    own kv heads, so the model sees the same context at every N."""
+    import torch
+    hkv, d = cfg["num_key_value_heads"], cfg["head_dim"]
+    per = hkv // world
+    g = torch.Generator(device=dev).manual_seed(1)
+    for t in model.k_cache + model.v_cache:
+        full = torch.randn((BATCH, hkv, CONTEXT, d), generator=g, device=dev, dtype=torch.float32) * 0.5
+        mine = full[:, rank * per:(rank + 1) * per]
+        t[:, :, :CONTEXT].copy_((mine * 40).clamp(-127, 127).round() if model.kv_int8 else mine)
+        del full
+    for t in model.k_scale + model.v_scale:
+        t[:, :, :CONTEXT].fill_(1.0 / 80)
 
 
 def run_gpu_arm(args, cfg):
@@ -205,19 +234,12 @@ def run_gpu_arm(args, cfg):
     collective.set_communicator(rank, world)
     lib = ffi.lib()
 
-    steps, warm = args.steps, max(args.warmup, 3)
-    max_seq = CONTEXT + 2 * (steps + warm) + 64
+    steps, warm, blocks = args.steps, max(args.warmup, 8), max(args.blocks, 1)  # the first 8 steps are always run (their ids are reported)
+    max_seq = CONTEXT + warm + steps + 16
     state = random_llama_state(cfg, seed=0, device=str(dev))  # identical on every rank (same seed)
     model = DecoderModel(cfg, state, dtype="bf16", max_seq_len=max_seq, batch=BATCH, tp_rank=rank, tp_world=world,
                          output="ids", use_graph=True, kv_int8=args.kv == "int8")
-    del state
-    torch.cuda.empty_cache()
-    g = torch.Generator(device=dev).manual_seed(1 + rank)
-    for t in model.k_cache + model.v_cache:  # synthetic 2048-token context
-        r = torch.randn(t[:, :, :CONTEXT].shape, generator=g, device=dev, dtype=torch.float32) * 0.5
-        t[:, :, :CONTEXT].copy_((r * 40).clamp(-127, 127).round() if model.kv_int8 else r)
-    for t in model.k_scale + model.v_scale:
-        t[:, :, :CONTEXT].fill_(1.0 / 80)
+    fill_synthetic_context(model, cfg, rank, world, dev)
     ids0 = torch.randint(0, cfg["vocab_size"], (BATCH,), device=dev, dtype=torch.int64,
                          generator=torch.Generator(device=dev).manual_seed(7))
     stream = torch.cuda.Stream(device=dev)  # a real stream handle: the library treats NULL as the model's own stream
@@ -238,63 +260,111 @@ def run_gpu_arm(args, cfg):
     # ---- device-resident throughput ----
     past = CONTEXT
     l0 = lib.mynn_b200_launch_count()
-    model.step_device(ids0, past)  # first call captures the graph
+    tok_dev = torch.zeros(BATCH, dtype=torch.int32, device=dev)
+    model.step_device(ids0, past, tok_dev)  # first call captures the graph
     launches_per_step = lib.mynn_b200_launch_count() - l0
     past += 1
-    for _ in range(warm - 1):
+    first_ids = [tok_dev.cpu().numpy().copy()]
+    for _ in range(7):  # the greedy ids of the first 8 steps: the same at every N unless a near-tie flips
+        model.step_device(None, past, tok_dev)
+        past += 1
+        first_ids.append(tok_dev.cpu().numpy().copy())
+    for _ in range(max(warm - 8, 0)):
         model.step_device(None, past)
         past += 1
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    block_ms, past0 = [], past  # every block decodes the same rows [past0, past0 + steps): equal work per block
     with ClockSampler(local) as clocks:
         torch.cuda.cudart().cudaProfilerStart()  # lets `ncu --profile-from-start off` see only the timed steps
-        e0.record(stream)
-        for _ in range(steps):
-            model.step_device(None, past)
-            past += 1
-        e1.record(stream)
-        barrier()
+        for _ in range(blocks):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            past = past0
+            e0.record(stream)
+            for _ in range(steps):
+                model.step_device(None, past)
+                past += 1
+            e1.record(stream)
+            barrier()
+            block_ms.append(max_over_ranks(e0.elapsed_time(e1)) / steps)
         torch.cuda.cudart().cudaProfilerStop()
-    ms_dev = max_over_ranks(e0.elapsed_time(e1)) / steps
+    srt = sorted(block_ms)
+    ms_dev = srt[len(srt) // 2]
 
     # ---- end to end through model(state, outputs, inputs) with host buffers ----
-    tok = model.step(ids0.cpu(), past).clone()
-    past += 1
-    for _ in range(2):
-        tok = model.step(tok, past).clone()
-        past += 1
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        tok = model.step(tok, past)  # pinned ids -> device, graph replay, token ids -> pinned host, stream sync
-        past += 1
-    barrier()
-    ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3) / steps
+    def time_e2e(m, past):
+        tok = ids0.cpu()
+        for i in range(3):
+            out = m.step(tok, past + steps - 3 + i)  # warm-up on rows the timed steps overwrite later
+            tok = out.clone() if m.output == "ids" else ids0.cpu()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            out = m.step(tok, past)  # pinned ids -> device, graph replay, result -> pinned host, stream sync
+            if m.output == "ids":
+                tok = out
+            past += 1
+        barrier()
+        return max_over_ranks((time.perf_counter() - t0) * 1e3) / steps, past
 
-    # ---- roofline of the dominant kernel, timed live over this model's own layers ----
-    roof = kernel_roofline(model, cfg, world, dev) if rank == 0 or world > 1 else None
+    ms_e2e, _ = time_e2e(model, past0)
+
+    # ---- roofline figures, timed live over this model's own layers ----
+    roof = kernel_roofline(model, cfg, world, dev)
+    gemm_all = gemm_kernel_wide(model, cfg, world, dev)
+    attn_all = attention_kernel_figure(model, cfg, world, dev)
+    weight_bytes = model.weight_bytes()
+    h2d, d2h = model.h2d_bytes_per_step, model.d2h_bytes_per_step
+    kv_int8 = model.kv_int8
+    tp_fused = model.tp_fused
+    model.close()
+    del model
+    torch.cuda.empty_cache()
+
+    # ---- the engine's own output mode: full logits to the host every step, argmax there ----
+    e2e_logits = None
+    if not args.no_logits:
+        lm = DecoderModel(cfg, state, dtype="bf16", max_seq_len=max_seq, batch=BATCH, tp_rank=rank, tp_world=world,
+                          output="logits", use_graph=True, kv_int8=args.kv == "int8")
+        fill_synthetic_context(lm, cfg, rank, world, dev)
+        ms_lg, _ = time_e2e(lm, past0)
+        e2e_logits = {"value": BATCH * 1e3 / ms_lg, "unit": UNIT, "ms_per_step": ms_lg, "h2d_bytes_per_step": lm.h2d_bytes_per_step,
+                      "d2h_bytes_per_step": lm.d2h_bytes_per_step,
+                      "what": "model(state, outputs, inputs) returning the logits [batch, vocab] to pinned host memory every step "
+                              "(the engine's graph output; the host-side argmax of its loop is not part of the timed call)"}
+        lm.close()
+        del lm
+    del state
 
     if rank == 0:
-        peak, peak_kind = measured_peak_hbm()
+        peak, _, peak_kind = measured_peaks()
+        ids = __import__("numpy").stack(first_ids)
         line = {"metric": METRIC, "value": BATCH * 1e3 / ms_dev, "unit": UNIT, "n_gpus": world, "steps": steps,
                 "warmup": warm, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": workload_name(cfg), "parallelism": f"tp{world}", "l2": "inputs larger than L2",
-                           "kv_cache": "int8 + per-token scale (quant_kv_cache option; not the headline configuration)" if model.kv_int8 else "bf16",
-                           "tp_reduce": ("nvlink peer loads fused into add+rmsnorm" if model.tp_fused else ("nccl" if world > 1 else "none"))},
+                           "kv_cache": "int8 + per-token scale (quant_kv_cache option; not the headline configuration)" if kv_int8 else "bf16",
+                           "tp_reduce": ("nvlink peer memory, fused with add + rmsnorm" if tp_fused else ("nccl" if world > 1 else "none"))},
+                "timed_blocks": {"blocks": blocks, "steps_per_block": steps, "ms_per_step_median": ms_dev,
+                                 "ms_per_step_min": srt[0], "ms_per_step_max": srt[-1]},
                 "clocks": clocks.summary(),
                 "e2e": {"value": BATCH * 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e,
-                        "h2d_bytes_per_step": model.h2d_bytes_per_step, "d2h_bytes_per_step": model.d2h_bytes_per_step},
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
                 "gpu_launches": int(launches_per_step * steps),
-                "launches_per_step": int(launches_per_step)}
-        if roof:
-            roof["peak"], roof["peak_kind"] = peak, peak_kind
-            roof["frac"] = roof["achieved"] / peak
-            line["roofline"] = roof
+                "launches_per_step": int(launches_per_step),
+                "token_ids_first_8_steps_crc32": zlib.crc32(ids.astype("<i4").tobytes()),
+                "token_ids_first_step_crc32": zlib.crc32(ids[0].astype("<i4").tobytes())}
+        if e2e_logits:
+            line["e2e_logits"] = e2e_logits
+        for key, fig in (("roofline", roof), ("gemm_kernel", gemm_all), ("attention_kernel", attn_all)):
+            if fig:
+                fig["peak"], fig["peak_kind"] = peak, peak_kind
+                fig["frac"] = fig["achieved"] / peak
+                line[key] = fig
         # algorithmic bytes of a whole step on this rank: weights once + KV once (per KV head) over HBM
-        kv_row_bytes = cfg["head_dim"] + 2 if model.kv_int8 else cfg["head_dim"] * 2
+        kv_row_bytes = cfg["head_dim"] + 2 if kv_int8 else cfg["head_dim"] * 2
         kv_bytes = 2 * cfg["num_hidden_layers"] * BATCH * (cfg["num_key_value_heads"] // world) * (CONTEXT + warm + steps // 2) * kv_row_bytes
-        step_bytes = model.weight_bytes() - cfg["vocab_size"] * cfg["hidden_size"] + kv_bytes
+        step_bytes = weight_bytes - cfg["vocab_size"] * cfg["hidden_size"] + kv_bytes
         line["step_hbm"] = {"algorithmic_bytes_per_gpu": int(step_bytes), "achieved_gbs": step_bytes / ms_dev / 1e6,
                             "frac_of_peak": step_bytes / ms_dev / 1e6 / peak}
         if world == 1 and not args.no_cpu:
@@ -308,10 +378,30 @@ def run_gpu_arm(args, cfg):
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
                                         "sample": f"failed: {e}"}
         print(json.dumps(line), flush=True)
-    model.close()
     collective.destroy_communicator()
     if world > 1:
         dist.destroy_process_group()
+
+
+def _graph_us(launch_all, n_launches, reps=3):
+    """Capture `launch_all()` (which enqueues n_launches kernels on the current stream) in one CUDA graph and return the best
+    of `reps` replays in microseconds (CUDA events on the launching stream)."""
+    import torch
+    stream = torch.cuda.current_stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        launch_all()
+    g.replay()
+    torch.cuda.synchronize()
+    best = 1e30
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e3)
+    return best
 
 
 def kernel_roofline(model, cfg, world, dev):
@@ -326,31 +416,316 @@ def kernel_roofline(model, cfg, world, dev):
     blocks = [(w, s) for w, s in zip(model._keep, model._keep[1:]) if w.dtype == torch.int8 and tuple(w.shape) == (2 * f, h)]
     act = torch.randn(BATCH, h, device=dev).bfloat16()
     out = torch.empty(BATCH, 2 * f, device=dev, dtype=torch.bfloat16)
-    stream = torch.cuda.current_stream()
     for w, s in blocks[:3]:
         ops.dequant_matmul(act, w, s, out=out)  # leaves the limbs of `act` in the workspace
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):  # one graph of all launches: removes host launch gaps from the measurement
+
+    def launch_all():
         for w, s in blocks:
             ops.dequant_matmul_same_act(act, w, s, out=out)
-    g.replay()
-    torch.cuda.synchronize()
-    e0.record(stream)
-    g.replay()
-    e1.record(stream)
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / len(blocks)
+
+    us = _graph_us(launch_all, len(blocks)) / len(blocks)
     n, k, m = 2 * f, h, BATCH
     alg = n * k + n * 2 + m * k * 2 + m * n * 2
-    # DRAM traffic of one launch from the ncu capture summarised in profiles/i8_stream_gemm_gateup_m32.md
-    # (dram__bytes_read.sum + dram__bytes_write.sum at TP1: 117,935,616 + 4,291,328 bytes); the weight stream is
-    # proportional to the shard, so it is scaled by 1/world for a tensor-parallel rank.
-    traffic = (117935616 + 4291328) // world
+    # DRAM traffic of one launch: dram__bytes_read.sum + dram__bytes_write.sum of a separate ncu capture of this kernel at
+    # this shape on one GPU (117,935,616 + 4,291,328 bytes); not measured by this run, and not available for a shard
+    traffic = 117935616 + 4291328 if world == 1 else None
     return {"kernel": "i8_stream_gemm_kernel (gate/up DequantMatMul, M=32, N=%d, K=%d; limbs written by the preceding kernel as in the step)" % (n, k),
             "bound": "hbm", "achieved": alg / us / 1e3, "unit": "GB/s", "us_per_launch": us, "algorithmic_bytes": alg,
-            "traffic": traffic}
+            "traffic": traffic,
+            "traffic_source": "separate ncu capture of one launch of this kernel at this shape (tensor parallel 1)" if traffic else None}
+
+
+def gemm_kernel_wide(model, cfg, world, dev):
+    """EVERY DequantMatMul launch of one decode step (per layer qkv, o, gate/up, down; then lm_head) over the model's own
+    weights, in step order, in one graph: weight bytes of the step / time.  The limbs of one random activation tensor per
+    reduction length are prepared before the timed region, as the step's producers do it outside these kernels."""
+    import torch
+
+    from my_nn_engine_b200 import ffi, ops
+    weights = [(w, s) for w, s in zip(model._keep, model._keep[1:]) if w.dtype == torch.int8 and w.dim() == 2][1:]  # [0] is the embedding
+    spaces, outs = {}, {}
+    for w, s in weights:
+        n, k = w.shape
+        if k not in spaces:
+            act = torch.randn(BATCH, k, device=dev).bfloat16()
+            ws = torch.zeros(ffi.lib().mynn_b200_dequant_matmul_workspace_bytes(BATCH, n, k), dtype=torch.uint8, device=dev)
+            ops.dequant_matmul(act, w, s, workspace=ws)
+            spaces[k] = (act, ws)
+        if (n, s.dtype) not in outs:
+            outs[(n, s.dtype)] = torch.empty(BATCH, n, device=dev, dtype=s.dtype)
+    torch.cuda.synchronize()
+
+    def launch_all():
+        for w, s in weights:
+            act, ws = spaces[w.shape[1]]
+            ops.dequant_matmul_same_act(act, w, s, out=outs[(w.shape[0], s.dtype)], workspace=ws)
+
+    us = _graph_us(launch_all, len(weights))
+    wbytes = sum(w.numel() for w, _ in weights)
+    alg = wbytes + sum(s.numel() * s.element_size() + BATCH * w.shape[1] * 2 + BATCH * w.shape[0] * s.element_size() for w, s in weights)
+    return {"kernel": "i8_stream_gemm_kernel, all %d launches of one step" % len(weights), "bound": "hbm", "achieved": alg / us / 1e3,
+            "unit": "GB/s", "us_per_step": us, "weight_bytes": wbytes, "algorithmic_bytes": alg, "traffic": None}
+
+
+def attention_kernel_figure(model, cfg, world, dev):
+    """The decode-attention kernel at the bench geometry over every layer's own KV cache (distinct memory per launch),
+    one graph."""
+    import torch
+
+    from my_nn_engine_b200 import ops
+    if model.kv_int8:
+        return None
+    hq, hkv, d = cfg["num_attention_heads"] // world, cfg["num_key_value_heads"] // world, cfg["head_dim"]
+    q = torch.randn(BATCH, hq, 1, d, device=dev).bfloat16()
+    out = torch.empty_like(q)
+    active = CONTEXT
+    ws = ops.attention_workspace(BATCH, hq, hkv, d, model.max_seq_len, dev)
+    ops.attention(q, model.k_cache[0], model.v_cache[0], d ** -0.5, active, out=out, workspace=ws)
+    torch.cuda.synchronize()
+
+    def launch_all():
+        for k, v in zip(model.k_cache, model.v_cache):
+            ops.attention(q, k, v, d ** -0.5, active, out=out, workspace=ws)
+
+    n = len(model.k_cache)
+    us = _graph_us(launch_all, n) / n
+    alg = 2 * BATCH * hkv * active * d * 2 + 2 * q.numel() * 2
+    return {"kernel": "attention_decode_kernel (batch %d, %d q / %d kv heads, head_dim %d, %d kv rows)" % (BATCH, hq, hkv, d, active),
+            "bound": "hbm", "achieved": alg / us / 1e3, "unit": "GB/s", "us_per_launch": us, "algorithmic_bytes": alg, "traffic": None}
+
+
+# --------------------------------------------------------------------------------------------------------
+# single-kernel cases
+# --------------------------------------------------------------------------------------------------------
+def _time_launches(fns, reps=3):
+    """fns: callables launching one kernel each; microseconds per launch, replayed from one graph on a side stream."""
+    import torch
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for f in fns[:2]:
+            f()
+        torch.cuda.synchronize()
+        return _graph_us(lambda: [f() for f in fns], len(fns), reps) / len(fns)
+
+
+def _torch_dt(name):
+    import torch
+    return {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[name]
+
+
+def case_gemm(m, n, k, dtype="bf16", ksplit=0, copies=None, kernel="tcgen05_i8", layout="nk", resident=False):
+    """One DequantMatMul shape.  resident=True replays over ONE weight copy (an L2-resident figure when it fits)."""
+    import torch
+
+    from my_nn_engine_b200 import ffi, ops
+    td = _torch_dt(dtype)
+    copies = 1 if resident else (copies or max(3, int(600e6 // (n * k)) + 1))
+    shape = (n, k) if layout == "nk" else (k, n)
+    ws = [torch.randint(-127, 128, shape, dtype=torch.int8, device="cuda") for _ in range(copies)]
+    sc = (torch.rand(n, device="cuda") * 0.018 + 0.002).to(td)
+    act = torch.randn(m, k, device="cuda").to(td)
+    out = torch.empty(m, n, device="cuda", dtype=td)
+    ffi.set_option(ffi.OPT_KSPLIT, ksplit)
+    wsp = ops.dequant_matmul_workspace(m, n, k, act.device) if kernel == "tcgen05_i8" and layout == "nk" else None
+    fns = [(lambda w=w: ops.dequant_matmul(act, w, sc, axis=0 if layout == "nk" else 1, out=out, workspace=wsp)) for w in ws]
+    if resident:
+        fns = fns * 16
+    us = _time_launches(fns)
+    ffi.set_option(ffi.OPT_KSPLIT, 0)
+    esz = act.element_size()
+    alg = n * k + n * esz + m * k * esz + m * n * esz
+    hbm, tf, kind = measured_peaks()
+    if m > 32:  # a dense contraction: tensor throughput (bf16-equivalent flops 2 M N K)
+        return {"kernel": "dequant_matmul/prefill_" + kernel, "m": m, "n": n, "k": k, "dtype": dtype, "us": us,
+                "TFLOPs_bf16_equivalent": 2.0 * m * n * k / us / 1e6, "frac_of_%s_bf16_peak" % kind: 2.0 * m * n * k / us / 1e6 / tf}
+    return {"kernel": "dequant_matmul/" + kernel, "layout": layout, "m": m, "n": n, "k": k, "dtype": dtype, "ksplit": ksplit,
+            "weights": "one copy replayed (L2-resident if it fits)" if resident else f"{copies} distinct copies (> L2)", "us": us,
+            "GBps": alg / us / 1e3, "frac_of_%s_hbm_peak" % kind: alg / us / 1e3 / hbm, "algorithmic_bytes": alg}
+
+
+def case_attention(b, hq, hkv, d, length, dtype="bf16", copies=None, kv="16bit"):
+    """Decode attention; kv="int8" times the kernel for the int8 cache (bytes: int8 rows + one scale per row)."""
+    import numpy as np
+    import torch
+
+    from my_nn_engine_b200 import ops
+    td = _torch_dt(dtype)
+    q8 = kv == "int8"
+    kv_bytes = 2 * b * hkv * length * (d + 2) if q8 else 2 * b * hkv * length * d * 2
+    copies = copies or max(3, int(600e6 // kv_bytes) + 1)
+    q = torch.randn(b, hq, 1, d, device="cuda").to(td)
+    out = torch.empty_like(q)
+    ws = ops.attention_workspace(b, hq, hkv, d, length, q.device)
+    if q8:
+        ks = [torch.randint(-127, 128, (b, hkv, length, d), device="cuda", dtype=torch.int8) for _ in range(copies)]
+        vs = [torch.randint(-127, 128, (b, hkv, length, d), device="cuda", dtype=torch.int8) for _ in range(copies)]
+        sc = [(torch.rand(b, hkv, length, device="cuda") * 0.02 + 0.005).to(td) for _ in range(copies)]
+        us = _time_launches([(lambda k=k, v=v, s=s: ops.attention_q8(q, k, v, s, s, 1 / np.sqrt(d), length, out=out, workspace=ws))
+                             for k, v, s in zip(ks, vs, sc)])
+    else:
+        ks = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(copies)]
+        vs = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(copies)]
+        us = _time_launches([(lambda k=k, v=v: ops.attention(q, k, v, 1 / np.sqrt(d), length, out=out, workspace=ws))
+                             for k, v in zip(ks, vs)])
+    alg = kv_bytes + 2 * q.numel() * 2
+    hbm, _, kind = measured_peaks()
+    return {"kernel": "attention_decode_q8" if q8 else "attention_decode", "b": b, "hq": hq, "hkv": hkv, "d": d, "len": length,
+            "dtype": dtype, "us": us, "GBps": alg / us / 1e3, "frac_of_%s_hbm_peak" % kind: alg / us / 1e3 / hbm, "algorithmic_bytes": alg}
+
+
+def case_prefill_attention(b, hq, hkv, d, length, dtype="bf16"):
+    """Causal self-attention of a whole prompt (Sq = kv length): 4 * Sq^2 / 2 * D * Hq * B flops."""
+    import numpy as np
+    import torch
+
+    from my_nn_engine_b200 import ops
+    td = _torch_dt(dtype)
+    q = torch.randn(b, hq, length, d, device="cuda").to(td)
+    ks = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(2)]
+    vs = [torch.randn(b, hkv, length, d, device="cuda").to(td) for _ in range(2)]
+    out = torch.empty_like(q)
+    us = _time_launches([(lambda k=k, v=v: ops.attention(q, k, v, 1 / np.sqrt(d), length, True, out=out)) for k, v in zip(ks, vs)])
+    ops.attention_check()
+    flops = 4.0 * length * (length + 1) / 2 * d * hq * b
+    _, tf, kind = measured_peaks()
+    return {"kernel": "attention_prefill", "b": b, "hq": hq, "hkv": hkv, "d": d, "len": length, "dtype": dtype, "us": us,
+            "TFLOPs": flops / us / 1e6, "frac_of_%s_bf16_peak" % kind: flops / us / 1e6 / tf}
+
+
+def case_prefill_model(arch="llama3-8b", batch=1, length=2048, chunk=None, layers=None, dtype="bf16", reps=3, kv_int8=False):
+    """Whole-model prefill of ``length`` prompt tokens per sequence (random int8 weights of the named architecture) in
+    chunks of ``chunk`` tokens.  Wall-clock per prompt, host call to host result (the last token's id)."""
+    import numpy as np
+    import torch
+
+    from my_nn_engine_b200 import ops
+    from my_nn_engine_b200.decoder import DecoderModel
+    from my_nn_engine_b200.quantize import random_llama_state
+    cfg = dict(LLAMA3_8B if arch == "llama3-8b" else TINYLLAMA)
+    if layers:
+        cfg["num_hidden_layers"] = layers
+    chunk = chunk or length
+    state = random_llama_state(cfg, seed=0, device="cuda")
+    model = DecoderModel(cfg, state, dtype=dtype, max_seq_len=length + 8, batch=batch, output="ids", max_prefill=chunk, kv_int8=kv_int8)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg["vocab_size"], size=(batch, length))
+    times = []
+    for _ in range(reps + 1):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for p0 in range(0, length, chunk):
+            model.prefill(prompt[:, p0:p0 + chunk], p0)
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+    ops.attention_check()
+    best = min(times[1:])
+    model.close()
+    return {"kernel": "model_prefill", "arch": arch, "layers": cfg["num_hidden_layers"], "batch": batch, "len": length, "chunk": chunk,
+            "dtype": dtype, "kv_cache": "int8" if kv_int8 else dtype, "ms": best * 1e3, "first_call_ms": times[0] * 1e3,
+            "prompt_tok_per_s": batch * length / best}
+
+
+def case_decode_model(arch="tinyllama", batch=1, context=128, steps=128, dtype="f16"):
+    """Greedy decode of a small-batch model end to end through model(state, outputs, inputs): tokens per second after a
+    prefilled prompt (the TinyLlama-1.1B-architecture configuration: batch 1, 128-token prompt, 128 greedy steps)."""
+    import numpy as np
+    import torch
+
+    from my_nn_engine_b200.decoder import DecoderModel
+    from my_nn_engine_b200.quantize import random_llama_state
+    cfg = dict(LLAMA3_8B if arch == "llama3-8b" else TINYLLAMA)
+    state = random_llama_state(cfg, seed=0, device="cuda")
+    model = DecoderModel(cfg, state, dtype=dtype, max_seq_len=context + steps + 8, batch=batch, output="ids", max_prefill=context)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg["vocab_size"], size=(batch, context))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    tok = model.prefill(prompt, 0).clone()
+    t_prefill = time.perf_counter() - t0
+    ids = [tok.numpy().copy()]
+    for i in range(3):
+        tok = model.step(tok, context + i).clone()
+        ids.append(tok.numpy().copy())
+    t0 = time.perf_counter()
+    for i in range(3, steps):
+        tok = model.step(tok, context + i)
+        ids.append(tok.numpy().copy())
+    sec = time.perf_counter() - t0
+    model.close()
+    wbytes = sum(v.numel() for k, v in state.items() if v.dtype == torch.int8 and "embed" not in k)
+    hbm, _, kind = measured_peaks()
+    ms = sec * 1e3 / (steps - 3)
+    return {"kernel": "model_decode", "arch": arch, "batch": batch, "context": context, "steps": steps, "dtype": dtype,
+            "ms_per_token": ms, "tok_per_s": batch * 1e3 / ms, "prefill_ms_first_call": t_prefill * 1e3,
+            "weight_GBps": wbytes / ms / 1e6, "frac_of_%s_hbm_peak" % kind: wbytes / ms / 1e6 / hbm,
+            "token_ids_crc32": zlib.crc32(np.stack(ids).astype("<i4").tobytes())}
+
+
+def case_w8a8(m, n, k, dtype="bf16", copies=None):
+    """QuantizedMatMul (int8 x int8) on the tcgen05 kernel; TOP/s counts 2 M N K integer operations."""
+    import torch
+
+    from my_nn_engine_b200 import ops
+    td = _torch_dt(dtype)
+    copies = copies or max(3, int(300e6 // (n * k)) + 1)
+    ws = [torch.randint(-127, 128, (n, k), device="cuda", dtype=torch.int8) for _ in range(copies)]
+    lhs = torch.randint(-127, 128, (m, k), device="cuda", dtype=torch.int8)
+    ls = (torch.rand(m, device="cuda") * 0.05 + 0.005).to(td)
+    rs = (torch.rand(n, device="cuda") * 0.018 + 0.002).to(td)
+    out = torch.empty(m, n, device="cuda", dtype=td)
+    wsp = ops.dequant_matmul_workspace(1, n, k, "cuda")
+    us = _time_launches([(lambda w=w: ops.quantized_matmul(lhs, ls, w, rs, out=out, workspace=wsp)) for w in ws])
+    ops.check_workspace(wsp)
+    alg = n * k + m * k + 2 * (m + n) + 2 * m * n
+    hbm, tf, kind = measured_peaks()
+    return {"kernel": "quantized_matmul/tcgen05_i8", "m": m, "n": n, "k": k, "dtype": dtype, "us": us, "TOPs": 2.0 * m * n * k / us / 1e6,
+            "frac_of_%s_bf16_peak" % kind: 2.0 * m * n * k / us / 1e6 / tf, "GBps": alg / us / 1e3,
+            "frac_of_%s_hbm_peak" % kind: alg / us / 1e3 / hbm, "algorithmic_bytes": alg}
+
+
+def run_case(args):
+    def emit(res):
+        print(json.dumps(res), flush=True)
+
+    c = args.case
+    prefill = c in ("prefill_gemm", "w8a8")
+    args.m = args.m or (2048 if prefill else 32)
+    args.n = args.n or (14336 if prefill else 28672)
+    args.k = args.k or 4096
+    args.b = args.b or (16 if c == "attention" else 1)
+    args.len = args.len or (4096 if c == "attention" else 2048)
+    if c == "gemv":  # the single-op GEMV configuration: f32 activation [1, 2048], W [2048, 5632] in both layouts
+        for layout in ("nk", "kn"):
+            for resident in (False, True):
+                emit(case_gemm(1, 5632, 2048, "f32", layout=layout, resident=resident))
+        emit(case_gemm(1, 5632, 2048, "bf16"))
+    elif c == "gemm":
+        emit(case_gemm(args.m, args.n, args.k, args.dtype, args.ksplit, args.copies, args.kernel, args.layout))
+    elif c == "attention":
+        emit(case_attention(args.b, args.hq, args.hkv, args.d, args.len, args.dtype, args.copies, args.kv))
+    elif c == "prefill_gemm":
+        emit(case_gemm(args.m, args.n, args.k, args.dtype, copies=args.copies or 3))
+    elif c == "prefill_attention":
+        emit(case_prefill_attention(args.b, args.hq, args.hkv, args.d, args.len, args.dtype))
+    elif c == "prefill_model":
+        emit(case_prefill_model(args.arch, args.b, args.len, args.chunk, args.layers, args.dtype, kv_int8=args.kv == "int8"))
+    elif c == "decode_model":
+        emit(case_decode_model(args.arch, args.b, dtype=args.dtype))
+    elif c == "w8a8":
+        emit(case_w8a8(args.m, args.n, args.k, args.dtype, args.copies))
+    elif c == "suite":
+        # the projections of both architectures at batch 1 and 32, the single-op GEMV, the attention shapes
+        for m in (1, 32):
+            for n, k in [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128256, 4096)]:
+                emit(case_gemm(m, n, k))
+        for n, k in [(5632, 2048), (2560, 2048), (2048, 2048), (11264, 2048), (2048, 5632), (32000, 2048)]:
+            emit(case_gemm(1, n, k))
+        emit(case_attention(16, 32, 8, 128, 4096))
+        emit(case_attention(32, 32, 8, 128, 2048))
+        emit(case_attention(1, 32, 4, 64, 256))
+    else:
+        raise SystemExit(f"unknown case {c}")
 
 
 def main():
@@ -358,12 +733,29 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--blocks", type=int, default=10, help="how often the block of --steps timed steps is repeated (median reported)")
     ap.add_argument("--impl", default="mynn_b200", choices=["mynn_b200", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="override the depth (testing only; the default is the full model)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--kv", default="bf16", choices=["bf16", "int8"],
+    ap.add_argument("--no-logits", action="store_true", help="skip the e2e_logits leg (a second model instance)")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "16bit", "int8"],
                     help="KV cache storage; the headline configuration is bf16, int8 is the engine's quant_kv_cache option")
+    ap.add_argument("--case", default="step", help="step (default) or a single-kernel case, see the module docstring")
+    for name in ("m", "n", "k", "b", "len"):  # shape of a single-kernel case; the default depends on the case
+        ap.add_argument("--" + name, type=int, default=None)
+    for name, default in (("hq", 32), ("hkv", 8), ("d", 128), ("ksplit", 0)):
+        ap.add_argument("--" + name, type=int, default=default)
+    ap.add_argument("--copies", type=int, default=None)
+    ap.add_argument("--chunk", type=int, default=None)
+    ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--kernel", default="tcgen05_i8", choices=["tcgen05_i8", "mma_sync"])
+    ap.add_argument("--layout", default="nk", choices=["nk", "kn"])
+    ap.add_argument("--arch", default="llama3-8b", choices=["llama3-8b", "tinyllama"])
     args = ap.parse_args()
+    if args.kv == "16bit":
+        args.kv = "bf16"
+    if args.case != "step":
+        return run_case(args)
     cfg = dict(LLAMA3_8B)
     if args.layers:
         cfg["num_hidden_layers"] = args.layers

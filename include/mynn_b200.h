@@ -35,6 +35,25 @@ enum { MYNN_OK = 0, MYNN_E_ARG = -1, MYNN_E_CUDA = -2, MYNN_E_UNSUPPORTED = -3, 
 enum { MYNN_W_NK = 0, MYNN_W_KN = 1 };
 
 const char *mynn_b200_last_error(void);
+/* Process-wide options.  No counterpart in the engine (its generated code has no run-time switches); they exist so that the
+ * bounded device-side waits and the kernel choices described below can be exercised by an integrator's tests.
+ *   MYNN_OPT_WAIT_BUDGET_US   time limit of every bounded device-side wait (mbarrier waits of the tcgen05 kernels, the
+ *                             cross-GPU flag wait of the fused tensor-parallel reduction), in microseconds; default
+ *                             2,000,000.  Applies to the CURRENT device.  When a wait runs out the kernel records a status
+ *                             code, finishes without the missing data and returns; the next *_check / model call reports it.
+ *   MYNN_OPT_KSPLIT           force the cluster K split of the small-batch DequantMatMul kernels: 0 automatic, else 1, 2, 4
+ *                             or 8.  The results do not depend on it (integer accumulation), which a test can verify.
+ *   MYNN_OPT_PREFILL_ATTENTION  kernels for Sq > 1: 1 (default) tcgen05 with two heads per CTA where possible; 2 / 3 tcgen05
+ *                             with one head per CTA, probabilities through shared / tensor memory; 0 the mma.sync tiled
+ *                             kernel only; -1 the row-serial kernel only.
+ *   MYNN_OPT_INJECT_STALL     test aid for the bounded waits, never set in production: 1 = the NEXT small-batch tcgen05
+ *                             DequantMatMul launch leaves out its last TMA stage, so that its MMA thread's wait runs out
+ *                             (status 2 in the workspace); 2 = the NEXT fused tensor-parallel reduction does not announce
+ *                             itself to its peers, so that their waits run out (status 21 / MYNN_E_COMM).  Nothing faults or
+ *                             hangs: the kernels return after the wait budget. */
+enum { MYNN_OPT_WAIT_BUDGET_US = 1, MYNN_OPT_KSPLIT = 2, MYNN_OPT_PREFILL_ATTENTION = 3, MYNN_OPT_INJECT_STALL = 4 };
+int mynn_b200_set_option(int option, long long value);
+
 /* Library/ABI version and the SM architecture the kernels were compiled for (100 for sm_100a). */
 int mynn_b200_abi_version(void);
 int mynn_b200_compiled_arch(void);
@@ -73,7 +92,8 @@ int mynn_b200_dequant_matmul_same_act(void *stream, void *out, const int8_t *wq,
                                       int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes);
 
 /* Synchronises the stream and reads the workspace status word: MYNN_E_CUDA if a bounded pipeline wait inside the
- * tcgen05 kernel expired (the outputs of that call are then invalid), MYNN_OK otherwise. */
+ * tcgen05 kernel expired (the outputs of that call are then invalid), MYNN_OK otherwise.  A reported expiry is cleared,
+ * so the workspace can be used again. */
 int mynn_b200_dequant_matmul_check(void *stream, const void *workspace);
 
 /* ---------------------------------------------------------------------------------------------
@@ -90,6 +110,17 @@ int mynn_b200_attention(void *stream, void *out, const void *q, const void *k, c
                         int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
                         const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
                         size_t workspace_bytes);
+/* Attention with the additive MASK operand (slot ATTENTION_MASK, src/graph/operator.rs:1027; builder
+ * crates/llm/src/builder.rs:466-515): qk = scale * (q . k) + mask before the softmax, then as mynn_b200_attention.
+ * mask (`dtype`) is addressed as the engine's launch addresses it (src/codegen/cuda.rs:1297-1325):
+ *   mask[(b * Hq + h) * mask_outer_stride + sq * mask_row_stride + kv_row],
+ * mask_row_stride = last dim of the mask (0 if its second-to-last dim is 1), mask_outer_stride = product of its last two
+ * dims (0 if all leading dims are 1).  Every shape runs on the row-serial kernel that follows the CPU recurrence
+ * (src/codegen/cpu/translator.rs:4854-4881); the Llama decoder never passes a mask (crates/llm/src/decoder.rs:351-358). */
+int mynn_b200_attention_masked(void *stream, void *out, const void *q, const void *k, const void *v, const void *mask,
+                               long long mask_outer_stride, long long mask_row_stride, float scale, int B, int Hq, int Hkv,
+                               int Sq, int D, int cache_seq_len, int active_seq_kv, const int32_t *active_seq_kv_dev,
+                               int is_causal, int dtype);
 /* Prefill chunks (Sq >= 64, D 64/128, 16-bit, 16-byte aligned tensors) run on a TMA-fed tcgen05 kernel whose pipeline
  * waits are bounded.  This call synchronises the stream and returns MYNN_E_CUDA if one of them expired in an earlier
  * attention call (the engine checks cudaGetLastError after its launches: src/codegen/cuda/cpp/common.cuh). */
@@ -234,7 +265,7 @@ int mynn_b200_comm_destroy(void);
  * (initializer[i], device pointers) and KV buffers (session_state[i], device, zeroed by the host); the library
  * owns activations, streams and graphs.  input[i] / output[i] are HOST pointers in storage dtype.
  *
- * initializer order (tp shard of each):
+ * initializer order (a tensor-parallel rank passes its shard of each: rows of q/k/v/gate/up/lm_head, columns of o/down):
  *   0 embed int8 [V,H], 1 embed scale [V], then per layer l (base 2+16*l):
  *   +0 input_layernorm [H], +1..+2 q (wq, scale), +3..+4 k, +5..+6 v, +7..+8 o, +9 post_attention_layernorm,
  *   +10..+11 gate, +12..+13 up, +14..+15 down; then final norm [H], lm_head wq, lm_head scale, cos table, sin table

@@ -162,7 +162,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
 template <typename T, int MAXE>
 __global__ void attention_generic_kernel(T *out, const T *q, const T *k, const T *v, float scale, int B, int Hq,
                                          int Hkv, int Sq, int Sk, int D, int active_host, const int32_t *active_dev,
-                                         int is_causal, int out_bshd, int ring_sink, int ring_window, int ring_start) {
+                                         int is_causal, int out_bshd, int ring_sink, int ring_window, int ring_start,
+                                         const T *mask, long long mask_outer_stride, long long mask_row_stride) {
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wid >= (long long)B * Hq * Sq) return;
@@ -194,7 +195,9 @@ __global__ void attention_generic_kernel(T *out, const T *q, const T *k, const T
             const int d = lane + 32 * e;
             if (d < D) dot += qr[e] * to_f32<T>(kp[(size_t)r * D + d]);
         }
-        const float qk = warp_sum(dot) * scale;
+        float qk = warp_sum(dot) * scale;
+        // additive mask, indexed as the engine's kernels do: (b * Hq + h) * outer stride + query row * row stride + kv row
+        if (mask != nullptr) qk += to_f32<T>(mask[bh * mask_outer_stride + sq * mask_row_stride + lr]);
         const float m_new = fmaxf(m, qk);
         const float f = expf(m - m_new), ev = expf(qk - m_new);
         s = s * f + ev;
@@ -253,13 +256,15 @@ extern "C" size_t mynn_b200_attention_workspace_bytes(int B, int Hq, int Hkv, in
 template <typename T>
 static int launch_generic(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
                           int Hq, int Hkv, int Sq, int Sk, int D, int active, const int32_t *active_dev, int causal,
-                          int out_bshd, int ring_sink = 0, int ring_window = 0, int ring_start = 0) {
+                          int out_bshd, int ring_sink = 0, int ring_window = 0, int ring_start = 0, const void *mask = nullptr,
+                          long long mask_outer_stride = 0, long long mask_row_stride = 0) {
     const long long rows = (long long)B * Hq * Sq;
     const unsigned blocks = (unsigned)((rows * 32 + 127) / 128);
 #define GEN(MAXE)                                                                                                     \
     attention_generic_kernel<T, MAXE><<<blocks, 128, 0, st>>>((T *)out, (const T *)q, (const T *)k, (const T *)v, scale, B, \
                                                              Hq, Hkv, Sq, Sk, D, active, active_dev, causal, out_bshd,   \
-                                                             ring_sink, ring_window, ring_start)
+                                                             ring_sink, ring_window, ring_start, (const T *)mask, mask_outer_stride,   \
+                                                             mask_row_stride)
     if (D <= 32) GEN(1);
     else if (D <= 64) GEN(2);
     else if (D <= 128) GEN(4);
@@ -284,6 +289,26 @@ extern "C" int mynn_b200_attention(void *stream, void *out, const void *q, const
                                    size_t workspace_bytes) {
     return mynn::launch_attention((cudaStream_t)stream, out, q, k, v, scale, B, Hq, Hkv, Sq, D, cache_seq_len,
                                   active_seq_kv, active_seq_kv_dev, is_causal, dtype, workspace, workspace_bytes, 0);
+}
+
+// Attention with the operator's additive MASK operand (src/graph/operator.rs:1027): qk = scale * q.k + mask[...] before the
+// softmax, on the row-by-row kernel that follows the CPU recurrence (src/codegen/cpu/translator.rs:4854-4881).  The mask is
+// addressed as the engine's CUDA launch addresses it (src/codegen/cuda.rs:1297-1325): element
+// (b * Hq + h) * mask_outer_stride + sq * mask_row_stride + kv_row, a stride of 0 broadcasting that dimension.
+extern "C" int mynn_b200_attention_masked(void *stream, void *out, const void *q, const void *k, const void *v, const void *mask,
+                                          long long mask_outer_stride, long long mask_row_stride, float scale, int B, int Hq,
+                                          int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
+                                          const int32_t *active_seq_kv_dev, int is_causal, int dtype) {
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || Sq < 0 || D <= 0 || cache_seq_len < 0 || active_seq_kv < 0 || Hq % Hkv)
+        return fail(MYNN_E_ARG, "attention_masked: bad shape");
+    if (!dtype_ok(dtype)) return fail(MYNN_E_ARG, "attention_masked: bad dtype %d", dtype);
+    if (mask_outer_stride < 0 || mask_row_stride < 0) return fail(MYNN_E_ARG, "attention_masked: negative mask stride");
+    if (B == 0 || Sq == 0) return MYNN_OK;
+    if (!out || !q || !k || !v || !mask) return fail(MYNN_E_ARG, "attention_masked: null pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == MYNN_F32) return launch_generic<float>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, active_seq_kv_dev, is_causal, 0, 0, 0, 0, mask, mask_outer_stride, mask_row_stride);
+    if (dtype == MYNN_BF16) return launch_generic<__nv_bfloat16>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, active_seq_kv_dev, is_causal, 0, 0, 0, 0, mask, mask_outer_stride, mask_row_stride);
+    return launch_generic<__half>(st, out, q, k, v, scale, B, Hq, Hkv, Sq, cache_seq_len, D, active_seq_kv, active_seq_kv_dev, is_causal, 0, 0, 0, 0, mask, mask_outer_stride, mask_row_stride);
 }
 
 // Attention over a sink + ring cache.  One query row: the softmax does not depend on the order of the rows, and the
@@ -337,7 +362,7 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
     const bool fast = Sq == 1 && (D == 64 || D == 128) && G <= 8 && dtype != MYNN_F32 && aligned;
     if (!fast && limbs_out) return fail(MYNN_E_UNSUPPORTED, "attention: the limb output exists only on the decode fast path");
     if (!fast) {
-        static const bool use_tiled = [] { const char *e = getenv("MYNN_PREFILL_ATTENTION"); return !e || atoi(e) != 0; }();
+        const bool use_tiled = g_prefill_attention_mode >= 0;  // -1: only the row-serial kernel
         if (use_tiled && attention_prefill_tc_supported(B, Hq, Hkv, Sq, D, cache_seq_len, dtype, q, k, v, out))
             return launch_attention_prefill_tc(st, out, q, k, v, scale, B, Hq, Hkv, Sq, D, cache_seq_len, active_seq_kv, active_seq_kv_dev,
                                                is_causal, dtype, out_bshd);

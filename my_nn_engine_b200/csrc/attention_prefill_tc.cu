@@ -51,6 +51,7 @@ constexpr uint32_t kTcSlab = 128 * 128;  // bytes of one slab: 128 rows x 64 16-
 constexpr float kTcMaxSlack = 8.0f;      // log2 units the running maximum may lag behind the true one
 
 __device__ int g_pfa_status;
+MYNN_DEFINE_WAIT_BUDGET_SETTER(attention_prefill_tc)
 
 struct TcAttnParams {
     void *out;
@@ -707,18 +708,12 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-// 0: never; 1 (default): two heads per CTA where the group size is even, else one head per CTA; 2: always one head per CTA, P
-// through shared memory; 3: the same with P through tensor memory.  MYNN_PREFILL_ATTENTION_TC overrides, and so does the debug entry below
-int g_pfa_tc_mode = [] {
-    const char *e = getenv("MYNN_PREFILL_ATTENTION_TC");
-    return e ? atoi(e) : 1;
-}();
-// Descriptor offsets of the V operand; the debug entry can override them.
-unsigned g_pfa_v_lbo = 0, g_pfa_v_sbo = 0;
-
+// g_prefill_attention_mode (MYNN_OPT_PREFILL_ATTENTION): -1 and 0 keep this file's kernels off; 1 (default): two heads per CTA
+// where the group size is even, else one head per CTA; 2: always one head per CTA, P through shared memory; 3: the same with P
+// through tensor memory.
 bool attention_prefill_tc_supported(int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len, int dtype, const void *q, const void *k,
                                     const void *v, const void *out) {
-    if (g_pfa_tc_mode == 0 || !tensor_map_api_available()) return false;
+    if (g_prefill_attention_mode <= 0 || !tensor_map_api_available()) return false;
     const bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) % 16) == 0;
     // at least one full box of rows in every tensor map, and enough query rows for a 128-row tile to pay
     return Sq >= 64 && (D == 64 || D == 128) && (dtype == MYNN_BF16 || dtype == MYNN_F16) && aligned &&
@@ -778,9 +773,9 @@ int launch_attention_prefill_tc(cudaStream_t st, void *out, const void *q, const
     p.out_bshd = out_bshd;
     // V tile in shared memory: D / 64 slabs of [128 kv rows][64 head-dim elements]: the next 64 head-dim elements are one
     // slab further (leading offset), the next 8 kv rows 8 x 128 bytes further (stride offset)
-    p.v_lbo = g_pfa_v_lbo ? g_pfa_v_lbo : kTcSlab;
-    p.v_sbo = g_pfa_v_sbo ? g_pfa_v_sbo : 1024;
-    p.p_tmem = g_pfa_tc_mode == 3;
+    p.v_lbo = kTcSlab;
+    p.v_sbo = 1024;
+    p.p_tmem = g_prefill_attention_mode == 3;
     // the maps describe the tensors as bytes: rows of D * 2 bytes, boxes of 128 bytes x 128 rows
     CUtensorMap mq, mk, mv;
     const uint64_t row_bytes = (uint64_t)D * 2;
@@ -788,7 +783,7 @@ int launch_attention_prefill_tc(cudaStream_t st, void *out, const void *q, const
     if (int rc = make_map(&mk, k, (uint64_t)B * Hkv * cache_seq_len, row_bytes, row_bytes, kTcCols)) return rc;
     if (int rc = make_map(&mv, v, (uint64_t)B * Hkv * cache_seq_len, row_bytes, row_bytes, kTcCols)) return rc;
     // an even group size can put two query heads of one kv head into every CTA (mode 4)
-    if ((Hq / Hkv) % 2 == 0 && g_pfa_tc_mode == 1) {
+    if ((Hq / Hkv) % 2 == 0 && g_prefill_attention_mode == 1) {
         if (dtype == MYNN_BF16) return D == 64 ? launch_tc2<__nv_bfloat16, 64>(st, mq, mk, mv, p, B) : launch_tc2<__nv_bfloat16, 128>(st, mq, mk, mv, p, B);
         return D == 64 ? launch_tc2<__half, 64>(st, mq, mk, mv, p, B) : launch_tc2<__half, 128>(st, mq, mk, mv, p, B);
     }
@@ -796,23 +791,26 @@ int launch_attention_prefill_tc(cudaStream_t st, void *out, const void *q, const
     return D == 64 ? launch_tc<__half, 64>(st, mq, mk, mv, p, B) : launch_tc<__half, 128>(st, mq, mk, mv, p, B);
 }
 
+// Reads and clears the status word of the tensor-core prefill kernels (the stream must be idle).
+int attention_prefill_tc_take_status(int *status) {
+    *status = 0;
+    MYNN_CUDA_OK(cudaMemcpyFromSymbol(status, g_pfa_status, sizeof *status));
+    if (*status) {
+        const int zero = 0;
+        MYNN_CUDA_OK(cudaMemcpyToSymbol(g_pfa_status, &zero, sizeof zero));
+    }
+    return MYNN_OK;
+}
+
 }  // namespace mynn
 
 using namespace mynn;
 
-// Synchronises the stream and reports whether a bounded wait inside the tensor-core prefill attention kernel ran out.
+// Synchronises the stream and reports (once) whether a bounded wait inside the tensor-core prefill attention kernel ran out.
 extern "C" int mynn_b200_attention_check(void *stream) {
     MYNN_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
     int status = 0;
-    MYNN_CUDA_OK(cudaMemcpyFromSymbol(&status, g_pfa_status, sizeof status));
+    if (int rc = attention_prefill_tc_take_status(&status)) return rc;
     if (status) return fail(MYNN_E_CUDA, "attention: pipeline wait %d timed out inside the tcgen05 prefill kernel", status);
-    return MYNN_OK;
-}
-
-// Tuning / test hook: mode as for MYNN_PREFILL_ATTENTION_TC; non-zero lbo / sbo override the V descriptor.
-extern "C" int mynn_b200_debug_prefill_attention(int mode, unsigned v_lbo, unsigned v_sbo) {
-    g_pfa_tc_mode = mode;
-    g_pfa_v_lbo = v_lbo;
-    g_pfa_v_sbo = v_sbo;
     return MYNN_OK;
 }

@@ -92,7 +92,16 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-extern int g_pdl_level;  // 0: only the GEMM overlaps its producer; 1: every decode-chain kernel; 2: GEMM also triggers early
+// Library options (mynn_b200_set_option).
+extern int g_ksplit_override;          // forced cluster K split of the DequantMatMul kernels, 0 = automatic
+extern int g_prefill_attention_mode;   // see MYNN_OPT_PREFILL_ATTENTION
+extern std::atomic<int> g_inject_stall;  // see MYNN_OPT_INJECT_STALL; consumed by the next launch it applies to
+
+// Build-time choice: 0 = only the DequantMatMul kernels carry the attribute (they overlap their limb producer); 1 = every
+// kernel launched through launch_pdl carries it.
+#ifndef MYNN_PDL_CHAIN
+#define MYNN_PDL_CHAIN 0
+#endif
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
@@ -105,7 +114,7 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_pdl_level >= 1 ? 1 : 0;
+    cfg.numAttrs = MYNN_PDL_CHAIN ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 

@@ -352,7 +352,6 @@ static int launch_stream(cudaStream_t st, OutT *out, const ActT *act, const int8
     return MYNN_OK;
 }
 
-int g_ksplit_override = 0;  // test/tuning hook, see mynn_b200_debug_set_ksplit
 
 template <typename ActT, typename OutT>
 static int dequant_matmul_typed(cudaStream_t st, OutT *out, const ActT *act, const int8_t *wq, const OutT *scale,
@@ -449,23 +448,23 @@ extern "C" int mynn_b200_dequant_matmul_check(void *stream, const void *workspac
     int status = 0;
     MYNN_CUDA_OK(cudaMemcpyAsync(&status, workspace, sizeof status, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     MYNN_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
-    if (status) return mynn::fail(MYNN_E_CUDA, "dequant_matmul: pipeline wait %d timed out inside the tcgen05 kernel", status);
+    if (status) {  // reported once: clear the word so that later calls on this workspace start clean
+        MYNN_CUDA_OK(cudaMemsetAsync(const_cast<void *>(workspace), 0, sizeof status, (cudaStream_t)stream));
+        MYNN_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+        return mynn::fail(MYNN_E_CUDA, "dequant_matmul: pipeline wait %d timed out inside the tcgen05 kernel", status);
+    }
     return MYNN_OK;
 }
 
-// Tuning hook (not part of the engine-facing ABI): force the cluster K split of the streaming kernel; 0 = automatic.
-extern "C" int mynn_b200_debug_set_ksplit(int s) {
-    if (s != 0 && s != 1 && s != 2 && s != 4 && s != 8) return mynn::fail(MYNN_E_ARG, "ksplit must be 0,1,2,4,8");
-    mynn::g_ksplit_override = s;
-    mynn::g_i8_split_override = s;
-    return MYNN_OK;
-}
-
-// Tuning hook: device buffer (8 x uint64) that CTA (0,0) of the tcgen05 GEMM fills with nanosecond timestamps of its
+#ifdef MYNN_TUNING
+// Tuning build only: device buffer (8 x uint64) that CTA (0,0) of the tcgen05 GEMM fills with nanosecond timestamps of its
 // phases (start, set-up done, predecessor complete, accumulators complete, cluster ready, outputs stored, end); NULL = off.
-extern "C" int mynn_b200_debug_set_timing_buffer(void *buf) {
+extern "C" int mynn_b200_tuning_set_timing_buffer(void *buf) {
     mynn::g_i8_timing = (unsigned long long *)buf;
     return MYNN_OK;
 }
-
-extern "C" int mynn_b200_debug_set_mode(int m) { mynn::g_i8_dbg = m; return 0; }
+extern "C" int mynn_b200_tuning_set_stages(int n) {
+    mynn::g_i8_stages_override = n;
+    return MYNN_OK;
+}
+#endif

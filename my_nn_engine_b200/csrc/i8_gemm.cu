@@ -31,6 +31,8 @@
 
 namespace mynn {
 
+MYNN_DEFINE_WAIT_BUDGET_SETTER(i8_gemm)
+
 constexpr int kTileRows = 128;   // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;     // int8 k values per pipeline stage = one 128-byte swizzle row
 constexpr int kStages = 3;      // pipeline depth when two CTAs share an SM
@@ -44,9 +46,17 @@ struct I8GemmParams {
     int M, N, K;
     int *status;          // device int, set non-zero on a timed-out wait
     int stages;           // pipeline depth: kStages or kMaxStages
-    unsigned long long *timing;  // optional: 8 timestamps (ns) of CTA (0,0) for tuning, or null
-    int dbg;
+    int skip_last_stage;  // test aid (MYNN_OPT_INJECT_STALL): the producer leaves out the last k block, so a bounded wait expires
+#ifdef MYNN_TUNING
+    unsigned long long *timing;  // 8 timestamps (ns) of CTA (0,0), or null
+#endif
 };
+
+#ifdef MYNN_TUNING
+#define MYNN_STAMP(cond, slot) do { if (p.timing != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (cond)) p.timing[slot] = global_ns(); } while (0)
+#else
+#define MYNN_STAMP(cond, slot) do { } while (0)
+#endif
 
 // grid (ceil(N/128), S), cluster (1, S, 1).  NC = activation columns (3 limbs x rows, padded to 16).
 template <typename OutT, int NC>
@@ -67,8 +77,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = gridDim.y;
-    const bool stamp = p.timing != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
-    if (stamp && threadIdx.x == 0) p.timing[0] = global_ns();
+    MYNN_STAMP(threadIdx.x == 0, 0);
     const int rank = S > 1 ? (int)cluster_ctarank() : 0;
     const int row0 = blockIdx.x * kTileRows;
     // this CTA's contiguous share of the k blocks
@@ -91,7 +100,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
-    if (stamp && threadIdx.x == 0) p.timing[1] = global_ns();  // set-up done
+    MYNN_STAMP(threadIdx.x == 0, 1);  // set-up done
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -100,16 +109,17 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             // The weights do not depend on the preceding kernel: start streaming them at once, and only then wait
             // (programmatic dependent launch) for the grid that writes the activation limbs.
-            const int pre = min(nkb, stages);
+            const int nload = nkb - (p.skip_last_stage ? 1 : 0);  // normally every k block
+            const int pre = min(nload, stages);
             for (int i = 0; i < pre; i++) {
                 mbar_expect_tx(&full_bar[i], kWBytes + kABytes);
                 tma_load_2d(smem + i * kStageBytes, &map_w, (kb_beg + i) * kBlockK, row0, &full_bar[i]);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            if (stamp) p.timing[2] = global_ns();  // predecessor grid complete
+            MYNN_STAMP(true, 2);  // predecessor grid complete
             for (int i = 0; i < pre; i++)
                 tma_load_2d(smem + i * kStageBytes + kWBytes, &map_a, (kb_beg + i) * kBlockK, 0, &full_bar[i]);
-            for (int i = pre; i < nkb; i++) {
+            for (int i = pre; i < nload; i++) {
                 const int s = i % stages, it = i / stages;
                 if (!mbar_wait_spin(&empty_bar[s], (it - 1) & 1, &abort_flag)) {
                     atomicExch(&abort_flag, 1);
@@ -186,8 +196,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         int ok_i = 1;
         if (lane == 0) ok_i = mbar_wait_spin(&accum_bar, 0, &abort_flag) ? 1 : 0;
         const bool ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
-        if (threadIdx.x == 64 && p.dbg == 2) pdl_trigger();  // main loop over: the next kernel may be scheduled during the epilogue
-        if (stamp && threadIdx.x == 64) p.timing[3] = global_ns();  // accumulators complete
+        MYNN_STAMP(threadIdx.x == 64, 3);  // accumulators complete
         if (!ok) {
             atomicExch(&abort_flag, 1);
             atomicExch(p.status, 3);
@@ -263,7 +272,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             }
         }
         cluster_sync_all();  // release/acquire: the partial sums pushed by every peer are visible
-        if (stamp && threadIdx.x == 64) p.timing[4] = global_ns();
+        MYNN_STAMP(threadIdx.x == 64, 4);
         if (warp >= 2 && n_own < p.N) {
             // a compact rolled loop: straight-line code that runs once per CTA pays an instruction-cache miss per line
             const int r_in = et % rows_per;
@@ -280,11 +289,11 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         }
     }
 
-    if (stamp && threadIdx.x == 64) p.timing[5] = global_ns();  // outputs stored
+    MYNN_STAMP(threadIdx.x == 64, 5);  // outputs stored
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
-    if (stamp && threadIdx.x == 0) p.timing[6] = global_ns();
+    MYNN_STAMP(threadIdx.x == 0, 6);
 }
 
 // ---- activation pre-pass: rows -> three int8 limbs + power-of-two row scale -----------------------------------
@@ -620,9 +629,10 @@ static int pick_split(int row_tiles, int kblocks) {
     return s;
 }
 
-int g_i8_split_override = 0;
-int g_i8_dbg = 0;
-unsigned long long *g_i8_timing = nullptr;  // tuning hook: device buffer of 8 timestamps, see I8GemmParams::timing
+#ifdef MYNN_TUNING
+unsigned long long *g_i8_timing = nullptr;  // device buffer of 8 timestamps, see I8GemmParams::timing
+int g_i8_stages_override = 0;
+#endif
 
 template <typename OutT, int NC>
 static int launch_i8(cudaStream_t st, const CUtensorMap &mw, const CUtensorMap &ma, const I8GemmParams &p, int S) {
@@ -698,16 +708,24 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
     p.N = N;
     p.K = K;
     p.status = status;
+    p.skip_last_stage = 0;
+    {
+        int want = 1;
+        if (g_inject_stall.compare_exchange_strong(want, 0)) p.skip_last_stage = 1;  // one launch only
+    }
+#ifdef MYNN_TUNING
     p.timing = g_i8_timing;
-    p.dbg = g_pdl_level >= 2 ? 2 : 0;
+#endif
     const int row_tiles = (N + kTileRows - 1) / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
-    const int S = g_i8_split_override > 0 ? g_i8_split_override : pick_split(row_tiles, kblocks);
+    const int S = g_ksplit_override > 0 ? g_ksplit_override : pick_split(row_tiles, kblocks);
     // two CTAs per SM share 227 KB: three stages with 96 limb columns (28 KB per stage), up to five with fewer columns
     // (measured at 8 and 16 rows: a fourth stage gives 2 %, a fifth nothing)
     const int stage_bytes = kTileRows * kBlockK + ((NC * kBlockK + 1023) / 1024) * 1024;
     const int shared_stages = std::max(kStages, std::min(5, (111 * 1024) / stage_bytes));
     p.stages = (long long)row_tiles * S <= 148 ? kMaxStages : shared_stages;
-    if (g_i8_dbg >= 2 && g_i8_dbg <= kMaxStages) p.stages = g_i8_dbg;  // tuning hook: pipeline depth
+#ifdef MYNN_TUNING
+    if (g_i8_stages_override >= 2 && g_i8_stages_override <= kMaxStages) p.stages = g_i8_stages_override;
+#endif
 #define GO(OT, NCV) return launch_i8<OT, NCV>(st, mw, ma, p, S)
 #define BY_NC(OT)                \
     switch (NC) {                \

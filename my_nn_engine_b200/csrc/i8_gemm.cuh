@@ -41,7 +41,8 @@ int launch_swiglu_limbs2(cudaStream_t st, int dtype, void *workspace, size_t wor
 bool i8_w8a8_supported(int M, int N, int K, const void *lhs, const void *rhs);
 int i8_w8a8_launch(cudaStream_t st, void *out, const int8_t *lhs, const void *lhs_scale, int lhs_scale_per_row, const int8_t *rhs,
                    const void *rhs_scale, int M, int N, int K, int dtype, void *workspace, size_t workspace_bytes);
-extern int g_i8_split_override;
+#ifdef MYNN_TUNING
 extern unsigned long long *g_i8_timing;
-extern int g_i8_dbg;
+extern int g_i8_stages_override;
+#endif
 }  // namespace mynn

@@ -20,6 +20,8 @@
 
 namespace mynn {
 
+MYNN_DEFINE_WAIT_BUDGET_SETTER(i8_gemm_prefill)
+
 constexpr int kPfRows = 128;      // weight rows per tile (UMMA M)
 constexpr int kPfCols = 256;      // accumulator columns per tile (UMMA N): LIMBS columns per activation row
 constexpr int kPfTokens = kPfCols / 2;  // activation rows per tile with two limbs (DequantMatMul)

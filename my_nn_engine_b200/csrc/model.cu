@@ -25,6 +25,8 @@
 #include "ops_internal.cuh"
 #include "tp_fused.cuh"
 
+extern "C" void model_destroy(void *state);
+
 namespace mynn {
 
 struct LayerW {
@@ -66,6 +68,7 @@ struct Model {
     void *k_rot = nullptr;
     void *k_deq = nullptr, *v_deq = nullptr;  // int8 cache: 16-bit copy of one layer's live rows for the tensor-core prefill attention
     cudaGraphExec_t stream_graph_exec = nullptr;
+    bool tc_attention_ran = false;  // the step just enqueued went through the tcgen05 prefill attention (its status word is checked)
     cudaStream_t stream = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
 };
@@ -136,6 +139,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
                        (size_t)std::max(H, m.ffn) * 4 <= 200 * 1024;
 
     // prefill chunks (more than 32 rows): RMSNorm and Swish*Mul write the two limbs of the prefill kernel themselves
+    if (S >= 64 && dt != MYNN_F32 && (D == 64 || D == 128)) m.tc_attention_ran = true;  // the attention launcher may pick the tcgen05 kernels
     const bool fused2 = m.gemm_ws != nullptr && M > kI8MaxRows && dt != MYNN_F32 && m.weights_aligned && tensor_map_api_available() &&
                         H % 16 == 0 && m.ffn % 16 == 0 && (size_t)std::max(H, m.ffn) * 4 <= 200 * 1024 &&
                         m.gemm_ws_bytes >= i8_prefill_workspace_bytes(M, std::max(H, m.ffn));
@@ -451,6 +455,13 @@ static int model_create(Model **out, void **initializer, void **session_state) {
         delete m;
         return fail(MYNN_E_CUDA, "model_init: stream / pinned buffer creation failed: %s", cudaGetErrorString(e));
     }
+    // the zero fills above ran on the legacy stream, the model's stream does not wait for it implicitly: finish them before the
+    // first step and before a peer can map the shared block
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        model_destroy(m);
+        return fail(MYNN_E_CUDA, "model_init: %s", cudaGetErrorString(e));
+    }
     *out = m;
     return MYNN_OK;
 }
@@ -499,6 +510,12 @@ static int copy_result_to_host(Model &m, void *dst) {
     }
     MYNN_CUDA_OK(cudaStreamSynchronize(m.stream));
     if (m.gemm_ws) RC(mynn_b200_dequant_matmul_check(m.stream, m.gemm_ws));
+    if (m.tc_attention_ran) {  // prefill chunks of 64 and more rows: the tcgen05 attention has bounded waits of its own
+        m.tc_attention_ran = false;
+        int pfa = 0;
+        RC(attention_prefill_tc_take_status(&pfa));
+        if (pfa) return fail(MYNN_E_CUDA, "model: pipeline wait %d timed out inside the tcgen05 prefill attention", pfa);
+    }
     if (m.tp_attached) {
         int st_ = 0;
         MYNN_CUDA_OK(cudaMemcpy(&st_, &m.tp.local->status, sizeof st_, cudaMemcpyDeviceToHost));
@@ -538,6 +555,7 @@ extern "C" int mynn_b200_model_configure(const mynn_b200_model_config *cfg) {
         return fail(MYNN_E_ARG, "model_configure: non-positive dimension");
     if (c.dtype != MYNN_BF16 && c.dtype != MYNN_F16 && c.dtype != MYNN_F32) return fail(MYNN_E_ARG, "model_configure: bad dtype %d", c.dtype);
     if (c.tp_world < 1 || c.tp_rank < 0 || c.tp_rank >= c.tp_world) return fail(MYNN_E_ARG, "model_configure: bad tp rank %d/%d", c.tp_rank, c.tp_world);
+    if (c.tp_world > kTpMaxRanks) return fail(MYNN_E_UNSUPPORTED, "model_configure: tp_world %d exceeds the %d ranks of one NVLink domain", c.tp_world, kTpMaxRanks);
     if (c.n_heads % c.n_kv_heads) return fail(MYNN_E_ARG, "model_configure: heads %d not a multiple of kv heads %d", c.n_heads, c.n_kv_heads);
     if (c.n_kv_heads % c.tp_world || c.ffn % c.tp_world || c.vocab % c.tp_world)
         return fail(MYNN_E_ARG, "model_configure: kv heads / ffn / vocab must divide by tp_world=%d", c.tp_world);

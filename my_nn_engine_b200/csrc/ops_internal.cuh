@@ -65,6 +65,10 @@ int launch_attention_prefill_tc(cudaStream_t st, void *out, const void *q, const
                                 int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv, const int32_t *active_seq_kv_dev,
                                 int is_causal, int dtype, int out_bshd);
 
+// Reads and clears the status word of the tcgen05 prefill attention kernels (call with the stream idle); non-zero = a bounded
+// wait expired in an earlier launch.
+int attention_prefill_tc_take_status(int *status);
+
 // Per-row (max value, last index of the maximum) of a logits shard, and the merge over tensor-parallel shards.
 int launch_argmax_pairs(cudaStream_t st, int dtype, float *pairs /*[rows][2]*/, const void *logits, int rows, int V,
                         int index_offset);

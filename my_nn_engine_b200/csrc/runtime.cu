@@ -3,6 +3,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -11,7 +12,18 @@ namespace mynn {
 static std::mutex g_err_mu;
 static char g_err[1024] = "";
 std::atomic<long long> g_launches{0};
-int g_pdl_level = [] { const char *e = getenv("MYNN_PDL_LEVEL"); return e ? atoi(e) : 0; }();
+
+// Setters of the per-translation-unit copies of the wait budget (see tcgen05.cuh).
+static std::vector<int (*)(unsigned long long)> &wait_budget_setters() {
+    static std::vector<int (*)(unsigned long long)> v;
+    return v;
+}
+void register_wait_budget_setter(int (*fn)(unsigned long long)) { wait_budget_setters().push_back(fn); }
+
+// Option state read by the launchers (defaults: automatic K split, tensor-core prefill attention, no injected stall).
+int g_ksplit_override = 0;
+int g_prefill_attention_mode = 1;
+std::atomic<int> g_inject_stall{0};
 
 void set_error(const char *fmt, ...) {
     std::lock_guard<std::mutex> lk(g_err_mu);
@@ -38,6 +50,32 @@ extern "C" int mynn_b200_compiled_arch(void) {
 #else
     return 0;
 #endif
+}
+
+extern "C" int mynn_b200_set_option(int option, long long value) {
+    using namespace mynn;
+    switch (option) {
+        case MYNN_OPT_WAIT_BUDGET_US: {
+            if (value < 1 || value > 60LL * 1000 * 1000) return fail(MYNN_E_ARG, "set_option: wait budget of %lld us outside [1, 60e6]", value);
+            for (auto fn : wait_budget_setters())
+                if (fn((unsigned long long)value * 1000ull)) return fail(MYNN_E_CUDA, "set_option: could not update the wait budget on this device");
+            return MYNN_OK;
+        }
+        case MYNN_OPT_KSPLIT:
+            if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return fail(MYNN_E_ARG, "set_option: K split must be 0, 1, 2, 4 or 8");
+            g_ksplit_override = (int)value;
+            return MYNN_OK;
+        case MYNN_OPT_PREFILL_ATTENTION:
+            if (value < -1 || value > 3) return fail(MYNN_E_ARG, "set_option: prefill attention mode %lld outside [-1, 3]", value);
+            g_prefill_attention_mode = (int)value;
+            return MYNN_OK;
+        case MYNN_OPT_INJECT_STALL:
+            if (value < 0 || value > 2) return fail(MYNN_E_ARG, "set_option: stall injection %lld outside [0, 2]", value);
+            g_inject_stall.store((int)value);
+            return MYNN_OK;
+        default:
+            return fail(MYNN_E_ARG, "set_option: unknown option %d", option);
+    }
 }
 
 extern "C" int64_t mynn_b200_launch_count(void) { return mynn::g_launches.load(); }

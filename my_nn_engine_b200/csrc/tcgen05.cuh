@@ -8,7 +8,17 @@
 
 namespace mynn {
 
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // a bounded wait gives up after 2 s
+// Time limit of every bounded wait, in nanoseconds (default 2 s).  One copy per translation unit (the library is built
+// without relocatable device code); each unit that includes this header registers a setter for its copy with
+// register_wait_budget_setter(), and mynn_b200_set_option(MYNN_OPT_WAIT_BUDGET_US) updates all of them on the current device.
+static __device__ unsigned long long d_wait_budget_ns = 2000000000ull;
+typedef int (*WaitBudgetSetter)(unsigned long long ns);
+void register_wait_budget_setter(WaitBudgetSetter fn);
+#define MYNN_DEFINE_WAIT_BUDGET_SETTER(tag)                                                                          \
+    static int set_wait_budget_##tag(unsigned long long ns) {                                                        \
+        return cudaMemcpyToSymbol(d_wait_budget_ns, &ns, sizeof ns) == cudaSuccess ? 0 : -1;                         \
+    }                                                                                                                \
+    static const int wait_budget_registered_##tag = (register_wait_budget_setter(set_wait_budget_##tag), 0);
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -42,7 +52,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const 
             if (*(volatile const int *)abort_flag) return false;
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitBudgetNs) return false;
+            else if (now - t0 > d_wait_budget_ns) return false;
         }
     }
 }
@@ -66,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t *bar, uint32_t parity, c
             if (*(volatile const int *)abort_flag) return false;
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitBudgetNs) return false;
+            else if (now - t0 > d_wait_budget_ns) return false;
         }
     }
 }

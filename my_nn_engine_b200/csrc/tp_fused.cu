@@ -18,9 +18,12 @@
 // peer; the host sees the status at its next check.
 #include "common.cuh"
 #include "i8_gemm.cuh"
+#include "tcgen05.cuh"
 #include "tp_fused.cuh"
 
 namespace mynn {
+
+MYNN_DEFINE_WAIT_BUDGET_SETTER(tp_fused)
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -58,7 +61,7 @@ tp_reduce_norm_limbs_kernel(int8_t *limbs, float *ascale, T *x, const T *w, floa
         const unsigned long long t0 = tp_now_ns();
         while ((int)(ld_acquire_sys(&loc->flags[threadIdx.x]) - target) < 0) {
             __nanosleep(100);
-            if (tp_now_ns() - t0 > 2000000000ull) {
+            if (tp_now_ns() - t0 > d_wait_budget_ns) {
                 atomicExch(&loc->status, 21);
                 break;
             }

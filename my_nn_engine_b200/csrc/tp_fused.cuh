@@ -6,10 +6,12 @@
 
 namespace mynn {
 
+constexpr int kTpMaxRanks = 8;  // ranks of one NVLink domain; sizes the flag and pointer arrays below
+
 // Header of the block of device memory every rank shares with its peers (cudaIpc); the two f32 partial-sum buffers
 // follow at the byte offsets TpPeers::part_off (identical on every rank).
 struct TpLocal {
-    uint32_t flags[8];  // flags[r] = last step number rank r has announced to this rank
+    uint32_t flags[kTpMaxRanks];  // flags[r] = last step number rank r has announced to this rank
     uint32_t epoch;     // step number of the last completed reduction on this rank
     uint32_t ticket;    // CTA arrival counter of the running reduction
     int status;         // 21 = a wait for a peer ran out of time
@@ -19,7 +21,7 @@ static_assert(sizeof(TpLocal) == 64, "TpLocal is one 64-byte header");
 
 struct TpPeers {
     TpLocal *local;       // this rank's block
-    TpLocal *remote[8];   // every rank's block as mapped into this process (remote[rank] == local)
+    TpLocal *remote[kTpMaxRanks];   // every rank's block as mapped into this process (remote[rank] == local)
     size_t part_off[2];   // byte offsets of the two partial-sum buffers inside a block
     int rank, world;
 };

@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(HERE, "libmynn_b200.so")
 F32, BF16, F16 = 0, 1, 2
 W_NK, W_KN = 0, 1
 OK, E_ARG, E_CUDA, E_UNSUPPORTED, E_COMM, E_STATE = 0, -1, -2, -3, -4, -5
+OPT_WAIT_BUDGET_US, OPT_KSPLIT, OPT_PREFILL_ATTENTION, OPT_INJECT_STALL = 1, 2, 3, 4
 
 
 class MynnError(RuntimeError):
@@ -34,6 +35,7 @@ class ModelConfig(ctypes.Structure):
 # name -> (restype, argtypes); every symbol declared in include/mynn_b200.h
 SIGNATURES = {
     "mynn_b200_last_error": (c_char_p, []),
+    "mynn_b200_set_option": (c_int, [c_int, ctypes.c_longlong]),
     "mynn_b200_abi_version": (c_int, []),
     "mynn_b200_compiled_arch": (c_int, []),
     "mynn_b200_dequant_matmul_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
@@ -44,6 +46,7 @@ SIGNATURES = {
     "mynn_b200_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "mynn_b200_attention_check": (c_int, [c_void_p]),
     "mynn_b200_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_size_t]),
+    "mynn_b200_attention_masked": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int]),
     "mynn_b200_attention_decode_noalloc_max_bytes": (c_size_t, []),
     "mynn_b200_attention_decode_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int]),
     "mynn_b200_kv_cache_update": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int]),
@@ -83,10 +86,6 @@ SIGNATURES = {
     "alloc_pinned": (c_void_p, [c_size_t]),
     "free_pinned": (None, [c_void_p]),
 }
-# tuning hooks that are not part of the engine-facing header
-_EXTRA = {"mynn_b200_debug_set_ksplit": (c_int, [c_int]), "mynn_b200_debug_set_timing_buffer": (c_int, [c_void_p]), "mynn_b200_debug_set_mode": (c_int, [c_int]),
-          "mynn_b200_debug_prefill_attention": (c_int, [c_int, ctypes.c_uint, ctypes.c_uint])}
-
 _lib = None
 
 
@@ -98,12 +97,16 @@ def lib() -> ctypes.CDLL:
             raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m my_nn_engine_b200.build` "
                                "(there is no fallback implementation)")
         handle = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
-        for name, (res, args) in {**SIGNATURES, **_EXTRA}.items():
+        for name, (res, args) in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.restype = res
             fn.argtypes = args
         _lib = handle
     return _lib
+
+
+def set_option(option: int, value: int) -> None:
+    check(lib().mynn_b200_set_option(option, value))
 
 
 def check(code: int) -> None:

@@ -125,9 +125,12 @@ def attention_workspace(b, hq, hkv, d, cache_seq_len, device):
     return ws
 
 
-def attention(q, k, v, scale: float, active_seq_kv=None, is_causal: bool = False, out=None, workspace=None):
+def attention(q, k, v, scale: float, active_seq_kv=None, is_causal: bool = False, out=None, workspace=None, mask=None):
     """``Attention{is_causal, scale}``: q [B,Hq,Sq,D]; k, v [B,Hkv,cache_seq_len,D]; ``active_seq_kv`` is an int
-    (host scalar, as the engine passes it) or an int32 CUDA tensor (read on the device); None = all rows."""
+    (host scalar, as the engine passes it) or an int32 CUDA tensor (read on the device); None = all rows.
+    ``mask``: the operator's optional additive mask, a tensor of q's dtype whose shape broadcasts against
+    [B, Hq, Sq, cache_seq_len] the way the engine's launch allows: last dim cache_seq_len, second-to-last Sq or 1, leading
+    dims either all 1 or [B, Hq]."""
     b, hq, sq, d = q.shape
     hkv, sk = k.shape[1], k.shape[2]
     if out is None:
@@ -139,6 +142,19 @@ def attention(q, k, v, scale: float, active_seq_kv=None, is_causal: bool = False
         dev_ptr = _ptr(active_seq_kv)
     elif active_seq_kv is not None:
         host_val = int(active_seq_kv)
+    if mask is not None:
+        if mask.dtype != q.dtype or mask.shape[-1] != sk:
+            raise ValueError("mask must have q's dtype and cache_seq_len as its last dim")
+        rows = mask.shape[-2] if mask.dim() >= 2 else 1
+        outer = 1
+        for n in mask.shape[:-2]:
+            outer *= n
+        if rows not in (1, sq) or outer not in (1, b * hq):
+            raise ValueError(f"mask shape {tuple(mask.shape)} does not broadcast against [{b}, {hq}, {sq}, {sk}]")
+        ffi.check(ffi.lib().mynn_b200_attention_masked(_stream(), _ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(mask),
+                                                       rows * sk if outer > 1 else 0, sk if rows > 1 else 0, float(scale), b,
+                                                       hq, hkv, sq, d, sk, host_val, dev_ptr, int(is_causal), _dt(q)))
+        return out
     if workspace is None:
         workspace = attention_workspace(b, hq, hkv, d, sk, q.device)
     ffi.check(ffi.lib().mynn_b200_attention(_stream(), _ptr(out), _ptr(q), _ptr(k), _ptr(v), float(scale), b, hq, hkv,

@@ -30,7 +30,10 @@ def quantize_per_channel(w: torch.Tensor):
     max_abs = rows.abs().amax(dim=1)
     scale = torch.where(max_abs == 0, torch.ones_like(max_abs), max_abs / 127.0)
     ratio = rows / scale[:, None]
-    rounded = torch.sign(ratio) * torch.floor(ratio.abs() + 0.5)  # f32::round: half away from zero
+    # f32::round (half away from zero) without forming |r| + 0.5, which rounds up for r = 0.5 - 2^-25: the fractional part
+    # r - trunc(r) is exact in floating point
+    t = torch.trunc(ratio)
+    rounded = t + torch.sign(ratio) * ((ratio - t).abs() >= 0.5).to(ratio.dtype)
     q = rounded.clamp_(-128, 127).to(torch.int8).reshape(w32.shape)
     return q, scale.to(torch.bfloat16)
 

@@ -75,6 +75,21 @@ def attention(q, k, v, scale, active=None, is_causal=False, parallel=False):
     return out
 
 
+def attention_q8(q, k, v, k_scale, v_scale, scale, active=None, is_causal=False, parallel=False):
+    """q f32 [B,Hq,Sq,D]; k, v int8 [B,Hkv,Sk,D]; k_scale, v_scale f32 [B,Hkv,Sk] -> f32 [B,Hq,Sq,D]."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k = np.ascontiguousarray(k, dtype=np.int8)
+    v = np.ascontiguousarray(v, dtype=np.int8)
+    ks = np.ascontiguousarray(k_scale, dtype=np.float32)
+    vs = np.ascontiguousarray(v_scale, dtype=np.float32)
+    b, hq, sq, d = q.shape
+    hkv, sk = k.shape[1], k.shape[2]
+    out = np.empty_like(q)
+    lib().orc_attention_q8(_p(out), _p(q), _p(k), _p(v), _p(ks), _p(vs), ctypes.c_float(scale), *(ctypes.c_int64(x) for x in
+                           (b, hq, hkv, sq, sk, d, sk if active is None else int(active))), int(is_causal), int(parallel))
+    return out
+
+
 def rms_norm(x, w, eps):
     x = np.ascontiguousarray(x)
     out = np.empty_like(x)

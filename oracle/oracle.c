@@ -147,6 +147,48 @@ void orc_attention(void *out, const void *q, const void *k, const void *v, float
     }
 }
 
+/* The same recurrence over an int8 KV cache with one scale per cached row (the quant_kv_cache option):
+ * qk = (q . k_int) * k_scale[r] * scale;  o = o * f + (e * v_scale[r]) * v_int
+ * (src/codegen/cpu/translator.rs:4440-5008, the k_scale / v_scale operands).  q, out, scales: f32. */
+void orc_attention_q8(float *out, const float *q, const int8_t *k, const int8_t *v, const float *k_scale,
+                      const float *v_scale, float scale, int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Sk,
+                      int64_t D, int64_t active, int is_causal, int parallel) {
+    int64_t group = Hq / Hkv;
+    int64_t past = active - Sq;
+#pragma omp parallel for schedule(static) if (parallel)
+    for (int64_t row = 0; row < B * Hq * Sq; row++) {
+        int64_t bh = row / Sq, sq = row % Sq;
+        int64_t b = bh / Hq, h = bh % Hq;
+        int64_t bhkv = b * Hkv + h / group;
+        int64_t bound = active;
+        if (is_causal) {
+            int64_t cap = past + sq + 1;
+            if (cap < bound) bound = cap;
+        }
+        if (Sk < bound) bound = Sk;
+        float *o = (float *)malloc(sizeof(float) * (size_t)D);
+        for (int64_t d = 0; d < D; d++) o[d] = 0.0f;
+        const float *qf = q + row * D;
+        float m = -INFINITY, s = 0.0f;
+        for (int64_t r = 0; r < bound; r++) {
+            int64_t base = (bhkv * Sk + r) * D;
+            float dot = 0.0f;
+            for (int64_t d = 0; d < D; d++) dot += qf[d] * (float)k[base + d];
+            float qk = dot * k_scale[bhkv * Sk + r];
+            qk = qk * scale;
+            float m_new = fmaxf(m, qk);
+            float f = expf(m - m_new);
+            float e = expf(qk - m_new);
+            s = s * f + e;
+            float ev = e * v_scale[bhkv * Sk + r];
+            for (int64_t d = 0; d < D; d++) o[d] = o[d] * f + ev * (float)v[base + d];
+            m = m_new;
+        }
+        for (int64_t d = 0; d < D; d++) out[row * D + d] = o[d] / s;
+        free(o);
+    }
+}
+
 /* cache[b,h,offset+t,:] = new[b,h,t,:], in place, no bounds check
  * (src/codegen/cpu/translator.rs:4374-4424).  elem_bytes = 2 or 4. */
 void orc_kv_cache_update(void *cache, const void *newkv, int64_t BH, int64_t cache_seq, int64_t new_seq,

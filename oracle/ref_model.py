@@ -43,7 +43,7 @@ class OracleLlama:
     whose values are already representable in the storage dtype."""
 
     def __init__(self, cfg: LlamaConfig, weights: dict, dtype: str, max_seq_len: int, batch: int = 1,
-                 kv_int8: bool = False, streaming=None):
+                 kv_int8: bool = False, streaming=None, c_attention: bool = False):
         """streaming = (sink, window): the engine's ``streaming_kv`` build option (crates/llm/src/decoder.rs:280-360): K is
         cached UNROTATED in a sink + ring layout, every step re-rotates the cached keys at their recency rank
         (``rope_fused`` with ``kv_position``) and attention walks the ring in age order.  Index math: ref_ops.streaming_state.
@@ -52,6 +52,9 @@ class OracleLlama:
         self.cfg, self.dtype, self.max_seq, self.batch = cfg, dtype, max_seq_len, batch
         self.kv_int8 = kv_int8
         self.streaming = streaming
+        # c_attention: run the attention recurrence in the C restatement (oracle.c, the same scalar loop as ref_ops.attention,
+        # row-parallel) instead of numpy; for long contexts, where the numpy form takes seconds per call
+        self.c_attention = c_attention and not streaming
         if streaming and kv_int8:
             raise ValueError("streaming with an int8 cache is not modelled")
         self.w = {}
@@ -131,12 +134,22 @@ class OracleLlama:
             if self.kv_int8:
                 R.quantizing_kv_cache_update(self.k_cache[l], self.k_scale[l], k, past_len, self.dtype)
                 R.quantizing_kv_cache_update(self.v_cache[l], self.v_scale[l], v, past_len, self.dtype)
-                a = self._st(R.attention(q, self.k_cache[l], self.v_cache[l], scale, active, is_causal=is_prefill,
-                                         k_scale=self.k_scale[l], v_scale=self.v_scale[l]))
+                if self.c_attention:
+                    from . import c_oracle
+                    a = self._st(c_oracle.attention_q8(q, self.k_cache[l], self.v_cache[l], self.k_scale[l], self.v_scale[l],
+                                                       float(scale), active, is_prefill, parallel=True))
+                else:
+                    a = self._st(R.attention(q, self.k_cache[l], self.v_cache[l], scale, active, is_causal=is_prefill,
+                                             k_scale=self.k_scale[l], v_scale=self.v_scale[l]))
             else:
                 R.kv_cache_update(self.k_cache[l], k, past_len)
                 R.kv_cache_update(self.v_cache[l], v, past_len)
-                a = self._st(R.attention(q, self.k_cache[l], self.v_cache[l], scale, active, is_causal=is_prefill))
+                if self.c_attention:
+                    from . import c_oracle
+                    a = self._st(c_oracle.attention(np.ascontiguousarray(q, dtype=np.float32), self.k_cache[l], self.v_cache[l],
+                                                    float(scale), active, is_prefill, parallel=True))
+                else:
+                    a = self._st(R.attention(q, self.k_cache[l], self.v_cache[l], scale, active, is_causal=is_prefill))
             a = a.transpose(0, 2, 1, 3).reshape(b, s, c.n_heads * c.head_dim)
             o = self._linear(a, p + "self_attn.o_proj.weight")
             x = self._st(x + o)

@@ -114,7 +114,9 @@ def dequant_matmul(act: np.ndarray, wq: np.ndarray, scale: np.ndarray) -> np.nda
 
 
 def _round_half_away(x):
-    return np.sign(x) * np.floor(np.abs(x) + np.float32(0.5))
+    """f32::round: half away from zero.  x - trunc(x) is exact, so no value just below one half rounds up."""
+    t = np.trunc(x)
+    return t + np.sign(x) * (np.abs(x - t) >= np.float32(0.5))
 
 
 def dynamic_quantize_linear(x: np.ndarray, symmetric: bool, per_row: bool, dtype: str = "bf16"):
@@ -232,14 +234,6 @@ def attention_softmax_f64(q, k, v, scale, active):
     p = np.exp(logits)
     p /= p.sum(axis=-1, keepdims=True)
     return np.einsum("bhsk,bhkd->bhsd", p, vf)
-
-
-def ring_phys_index(rank: int, ring_sink: int, ring_window: int, ring_start: int) -> int:
-    """Logical kv rank -> physical cache row for the sink+ring layout
-    (src/codegen/cuda/cpp/common.cuh:55-60).  ring_window == 0 means plain contiguous."""
-    if ring_window == 0 or rank < ring_sink:
-        return rank
-    return ring_sink + (ring_start + (rank - ring_sink)) % ring_window
 
 
 def kv_cache_update(cache: np.ndarray, new: np.ndarray, offset: int) -> np.ndarray:
@@ -398,7 +392,8 @@ def quantize_per_channel(w: np.ndarray):
     max_abs = np.abs(rows).max(axis=1)
     scale = np.where(max_abs == 0, np.float32(1.0), max_abs / np.float32(127.0)).astype(np.float32)
     ratio = rows / scale[:, None]
-    rounded = np.sign(ratio) * np.floor(np.abs(ratio) + np.float32(0.5))  # f32::round = half away from zero
+    t = np.trunc(ratio)  # f32::round = half away from zero; r - trunc(r) is exact, |r| + 0.5 is not (0.5 - 2^-25 would round up)
+    rounded = t + np.sign(ratio) * (np.abs(ratio - t) >= np.float32(0.5))
     q = np.clip(rounded, -128, 127).astype(np.int8).reshape(w.shape)
     bits = f32_to_bf16_bits_rne(scale)
     bits = np.where(np.isnan(scale), np.uint16(0x7FC0), bits)

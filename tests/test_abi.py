@@ -56,6 +56,9 @@ def test_model_configure_validation():
     assert lib.mynn_b200_model_configure(cfg) == ffi.OK
     cfg.tp_world = 2  # no communicator of that size
     assert lib.mynn_b200_model_configure(cfg) == ffi.E_STATE
+    cfg.n_heads, cfg.n_kv_heads, cfg.ffn, cfg.vocab, cfg.tp_world, cfg.tp_rank = 32, 16, 1024, 1600, 16, 3
+    assert lib.mynn_b200_model_configure(cfg) == ffi.E_UNSUPPORTED  # the peer tables of the fused reduction hold 8 ranks
+    assert "tp_world" in ffi.last_error()
     with pytest.raises(ffi.MynnError):
         ffi.check(lib.mynn_b200_model_configure(None))
 
@@ -70,3 +73,13 @@ def test_communicator_identity_world():
     assert lib.mynn_b200_comm_rank() == 0 and lib.mynn_b200_comm_world_size() == 1
     assert lib.mynn_b200_all_reduce(None, None, None, -1, ffi.F32) == ffi.E_ARG
     assert lib.mynn_b200_comm_destroy() == ffi.OK
+
+
+def test_set_option_validates_without_a_device():
+    lib = ffi.lib()
+    assert lib.mynn_b200_set_option(99, 0) == ffi.E_ARG
+    assert lib.mynn_b200_set_option(ffi.OPT_KSPLIT, 3) == ffi.E_ARG
+    assert lib.mynn_b200_set_option(ffi.OPT_KSPLIT, 4) == ffi.OK and lib.mynn_b200_set_option(ffi.OPT_KSPLIT, 0) == ffi.OK
+    assert lib.mynn_b200_set_option(ffi.OPT_PREFILL_ATTENTION, 7) == ffi.E_ARG
+    assert lib.mynn_b200_set_option(ffi.OPT_WAIT_BUDGET_US, 0) == ffi.E_ARG
+    assert lib.mynn_b200_set_option(ffi.OPT_INJECT_STALL, 5) == ffi.E_ARG

@@ -54,6 +54,22 @@ def test_quantize_single_file_known_answers(tmp_path):
     assert out[NORM].dtype == torch.float32 and out[NORM].tolist() == norm_data  # passthrough, byte for byte
 
 
+def test_quantizer_rounds_half_away_without_a_biased_addition():
+    """x / scale = 0.5 - 2^-25 must give 0 (f32::round), although f32(|r| + 0.5) == 1.0; exactly one half goes away from
+    zero.  The row maximum 127 makes the scale exactly 1, so the ratios are the inputs themselves."""
+    from my_nn_engine_b200.quantize import quantize_per_channel
+    from oracle import ref_ops as R
+    just_below = float(np.float32(0.49999997))
+    row = [127.0, just_below, -just_below, 0.5, -0.5, 1.5, -2.5, 0.0]
+    assert np.floor(np.float32(just_below) + np.float32(0.5)) == 1.0  # the trap the quantizer must not fall into
+    q, s = quantize_per_channel(torch.tensor([row], dtype=torch.float32))
+    assert q[0].tolist() == [127, 0, 0, 1, -1, 2, -3, 0] and float(s[0]) == 1.0
+    q_ref, _ = R.quantize_per_channel(np.array([row], dtype=np.float32))
+    assert q_ref[0].tolist() == q[0].tolist()
+    y, _, _ = R.dynamic_quantize_linear(np.array([row], dtype=np.float32), symmetric=True, per_row=True, dtype="f32")
+    assert y[0].tolist() == [127, 0, 0, 1, -1, 2, -3, 0]
+
+
 def test_quantize_dir_keeps_shards_and_writes_index(tmp_path):
     src_dir, dst_dir = tmp_path / "src", tmp_path / "dst"
     src_dir.mkdir()

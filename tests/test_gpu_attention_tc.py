@@ -86,9 +86,9 @@ def test_tc_and_mma_sync_prefill_kernels_agree(ops, ffi):
     scale = 1.0 / np.sqrt(128)
     a = ops.attention(q.cuda(), k.cuda(), v.cuda(), scale, 400, True)
     ops.attention_check()
-    ffi.check(ffi.lib().mynn_b200_debug_prefill_attention(0, 0, 0))
+    ffi.set_option(ffi.OPT_PREFILL_ATTENTION, 0)
     try:
         b_ = ops.attention(q.cuda(), k.cuda(), v.cuda(), scale, 400, True)
     finally:
-        ffi.lib().mynn_b200_debug_prefill_attention(1, 0, 0)
+        ffi.set_option(ffi.OPT_PREFILL_ATTENTION, 1)
     assert rel_err(a.float().cpu().numpy(), b_.float().cpu().numpy().astype(np.float64)) <= 1e-2

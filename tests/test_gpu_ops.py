@@ -114,12 +114,12 @@ def test_dequant_matmul_cluster_splits_agree(ksplit, path):
     act = torch.from_numpy(rng.standard_normal((32, 2048)).astype(np.float32)).bfloat16()
     ws = "auto" if path == "tcgen05_i8" else None
     ref1 = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda(), workspace=ws) if ksplit > 1 else None
-    ffi.check(ffi.lib().mynn_b200_debug_set_ksplit(ksplit))
+    ffi.set_option(ffi.OPT_KSPLIT, ksplit)
     try:
         a = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda(), workspace=ws)
         b = ops.dequant_matmul(act.cuda(), dev(wq), scale.cuda(), workspace=ws)
     finally:
-        ffi.lib().mynn_b200_debug_set_ksplit(0)
+        ffi.set_option(ffi.OPT_KSPLIT, 0)
     if path == "tcgen05_i8" and ref1 is not None:
         assert torch.equal(a, ref1)
     want = R.dequant_matmul(act.float().numpy(), wq, scale.float().numpy())
@@ -144,7 +144,7 @@ def test_dequant_matmul_same_activations_skip_the_conversion():
 
 
 def test_dequant_matmul_config1_both_layouts():
-    """BASELINE config 1: int8 W [2048,5632] uniform in [-127,127], f32 per-output-channel scale U(0.002,0.02),
+    """The single-op GEMV benchmark graph: int8 W [2048,5632] uniform in [-127,127], f32 per-output-channel scale U(0.002,0.02),
     f32 activation [1,2048] ~ N(0,1), seed 0 — as the literal [K,N]/axis-1 graph and as the fused [N,K]/axis-0 op."""
     rng = np.random.default_rng(0)
     w_kn = rng.integers(-127, 128, size=(2048, 5632), dtype=np.int8)
@@ -257,6 +257,27 @@ def test_attention_prefill_tiled_kernel_vs_oracle(dtype, b, hq, hkv, sq, d, cach
     assert rel_err(to_np(out), want) <= 1e-2
     out2 = ops.attention(q.cuda(), k.cuda(), v.cuda(), scale, torch.tensor([active], dtype=torch.int32, device="cuda"), causal)
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mask_shape,sq,causal", [((2, 4, 5, 24), 5, False), ((1, 1, 5, 24), 5, True), ((2, 4, 1, 24), 1, False),
+                                                  ((1, 24), 3, False), ((24,), 1, False)])
+def test_attention_mask_operand_vs_oracle(dtype, mask_shape, sq, causal):
+    """The operator's additive mask (slot 3): full [B,Hq,Sq,Sk], broadcast over batch and heads, broadcast over query rows,
+    and rank-2 / rank-1 forms, with -inf entries that remove kv rows, against the oracle's CPU recurrence."""
+    rng = np.random.default_rng(sq * 31 + len(mask_shape))
+    b, hq, hkv, d, sk, active = 2, 4, 2, 16, 24, 20
+    q = torch.from_numpy(rng.standard_normal((b, hq, sq, d)).astype(np.float32)).to(dtype)
+    k = torch.from_numpy(rng.standard_normal((b, hkv, sk, d)).astype(np.float32)).to(dtype)
+    v = torch.from_numpy(rng.standard_normal((b, hkv, sk, d)).astype(np.float32)).to(dtype)
+    m = rng.standard_normal(mask_shape).astype(np.float32)
+    m[..., 3] = -np.inf  # kv row 3 is masked out everywhere
+    mask = torch.from_numpy(m).to(dtype)
+    want = R.attention(q.float().numpy(), k.float().numpy(), v.float().numpy(), 0.25, active, is_causal=causal,
+                       mask=np.broadcast_to(mask.float().numpy(), (b, hq, sq, sk)) if len(mask_shape) > 2 else mask.float().numpy())
+    out = ops.attention(q.cuda(), k.cuda(), v.cuda(), 0.25, active, causal, mask=mask.cuda())
+    ok, md = eq_with_epsilon(to_np(out), want, 1e-4 if dtype == torch.float32 else 1e-2)
+    assert ok, md
 
 
 def test_attention_ignores_rows_past_active_even_if_nan():

@@ -257,3 +257,18 @@ def test_tiny_llama_prefill_matches_decode_only_multi_turn(tiny_llama):
     b = OracleLlama(c, weights, "f32", 32)
     got = b.generate(p1, 1, 4)[0].tolist() + b.generate(p2, 3, 4)[0].tolist()
     assert ref == got
+
+
+def test_c_oracle_int8_attention_equals_the_numpy_restatement():
+    """The C form of the attention recurrence over an int8 cache (used for long contexts) against ref_ops.attention."""
+    from oracle import c_oracle
+    rng = np.random.default_rng(1)
+    q = rng.standard_normal((2, 4, 3, 16)).astype(np.float32)
+    k = rng.integers(-127, 128, (2, 2, 20, 16), dtype=np.int8)
+    v = rng.integers(-127, 128, (2, 2, 20, 16), dtype=np.int8)
+    ks = rng.uniform(0.01, 0.02, (2, 2, 20)).astype(np.float32)
+    vs = rng.uniform(0.01, 0.02, (2, 2, 20)).astype(np.float32)
+    for causal in (False, True):
+        want = R.attention(q, k, v, 0.25, 17, is_causal=causal, k_scale=ks, v_scale=vs)
+        got = c_oracle.attention_q8(q, k, v, ks, vs, 0.25, 17, causal, parallel=True)
+        assert np.abs(got - want).max() <= 1e-6
