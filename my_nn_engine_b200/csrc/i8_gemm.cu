@@ -25,9 +25,12 @@
 // still releases TMEM and reaches every cluster barrier, and returns.
 #include <cuda.h>
 
+#include <cstring>
+
 #include "common.cuh"
 #include "i8_gemm.cuh"
 #include "tcgen05.cuh"
+#include "tp_fused.cuh"
 
 namespace mynn {
 
@@ -46,6 +49,7 @@ struct I8GemmParams {
     int M, N, K;
     int *status;          // device int, set non-zero on a timed-out wait
     int stages;           // pipeline depth: kStages or kMaxStages
+    I8Tp tp;              // tensor-parallel forms: scatter epilogue / gathered activation limbs (mode 0: neither)
     int skip_last_stage;  // test aid (MYNN_OPT_INJECT_STALL): the producer leaves out the last k block, so a bounded wait expires
 #ifdef MYNN_TUNING
     unsigned long long *timing;  // 8 timestamps (ns) of CTA (0,0), or null
@@ -117,6 +121,20 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             MYNN_STAMP(true, 2);  // predecessor grid complete
+            if (p.tp.mode == 2) {
+                // The limb rows come from the reduction kernels of ALL ranks (peer stores into this GPU's memory): hold the
+                // activation loads back, with a time limit, until the rows of every reduction this rank has completed are in.
+                const uint32_t target = *(volatile const uint32_t *)p.tp.gather_expected;
+                const unsigned long long t0 = global_ns();
+                while ((int)(ld_acquire_sys_u32(p.tp.gather_cnt) - target) < 0) {
+                    __nanosleep(40);
+                    if (global_ns() - t0 > d_wait_budget_ns) {
+                        atomicExch(p.tp.status, 22);
+                        break;
+                    }
+                }
+                asm volatile("fence.proxy.async;" ::: "memory");  // the rows were written through the generic proxy, TMA reads them
+            }
             for (int i = 0; i < pre; i++)
                 tma_load_2d(smem + i * kStageBytes + kWBytes, &map_a, (kb_beg + i) * kBlockK, 0, &full_bar[i]);
             for (int i = pre; i < nload; i++) {
@@ -184,7 +202,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     if (warp >= 2) {
         asm volatile("griddepcontrol.wait;" ::: "memory");  // row scales and the residual come from earlier grids
         // everything the finish needs from global memory is requested before waiting for the accumulators
-        if (et < 32) sh_ascale[et] = et < p.M ? p.ascale[et] : 0.f;
+        if (p.tp.mode != 2 && et < 32) sh_ascale[et] = et < p.M ? p.ascale[et] : 0.f;
         if (n_own < p.N) wscale = to_f32<OutT>(scale_p[n_own]);
         if (S == 1) {
 #pragma unroll
@@ -204,6 +222,9 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         tc_fence_after();
         // warp-uniform, because tcgen05.ld below must be executed by whole warps
         have_acc = __all_sync(0xffffffffu, ok && nkb > 0 && !*(volatile int *)&abort_flag);
+        // gathered rows: their scales were delivered with them, and the accumulators only complete after the producer has seen
+        // every row arrive, so they are read here (from L2: a peer wrote them)
+        if (p.tp.mode == 2 && et < 32) sh_ascale[et] = et < p.M ? __ldcg(&p.ascale[et]) : 0.f;
         asm volatile("bar.sync 1, 128;" ::: "memory");  // sh_ascale visible to the four epilogue warps (128 threads)
     }
     // The accumulators are read 48 columns (16 activation rows x 3 limbs) at a time to keep registers in check.
@@ -232,7 +253,13 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         // separate roundings (no fused multiply-add), so that every kernel of this operator gives the same bits
         float v = __fmul_rn(__fmul_rn((float)sum, sh_ascale[m]), wscale);
         if (resid_p) v = __fadd_rn(round_store<OutT>(v), resv);
-        out_p[(size_t)m * p.N + n_own] = from_f32<OutT>(v);
+        if (p.tp.mode == 1) {
+            // partial row m goes to the rank that owns it, into the slot of this rank (a plain store, possibly over NVLink)
+            const int owner = m % p.tp.world, local = m / p.tp.world;
+            reinterpret_cast<OutT *>(p.tp.part[owner])[((size_t)p.tp.rank * p.tp.rows_cap + local) * p.N + n_own] = from_f32<OutT>(v);
+        } else {
+            out_p[(size_t)m * p.N + n_own] = from_f32<OutT>(v);
+        }
     };
 
     if (S == 1) {
@@ -289,6 +316,14 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         }
     }
 
+    if (p.tp.mode == 1 && warp >= 2) {
+        // every store of this CTA is ordered before the counter increments: CTA barrier, then fence + release per destination
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et < p.tp.world) {
+            __threadfence_system();
+            red_release_sys_add_u32(p.tp.sig[et], 1u);
+        }
+    }
     MYNN_STAMP(threadIdx.x == 64, 5);  // outputs stored
     tc_fence_before();
     __syncthreads();
@@ -609,6 +644,8 @@ static int nc_for(int M) {
     return c <= 16 ? 16 : c <= 32 ? 32 : c <= 48 ? 48 : c <= 64 ? 64 : 96;
 }
 
+int i8_gemm_limb_rows(int M) { return nc_for(M < 1 ? 1 : (M > kI8MaxRows ? kI8MaxRows : M)); }
+
 size_t i8_gemm_workspace_bytes(int M, int K) {
     if (M <= 0 || M > kI8MaxRows || K <= 0) return 0;
     return 256 /* status word */ + 256 /* row scales */ + ((size_t)nc_for(M) * K + 255) / 256 * 256;
@@ -663,17 +700,33 @@ static int launch_i8(cudaStream_t st, const CUtensorMap &mw, const CUtensorMap &
     return MYNN_OK;
 }
 
+int i8_gemm_grid_ctas(int N, int K) {
+    const int row_tiles = (N + kTileRows - 1) / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
+    return row_tiles * (g_ksplit_override > 0 ? g_ksplit_override : pick_split(row_tiles, kblocks));
+}
+
 int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
                    int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes) {
-    const size_t need = i8_gemm_workspace_bytes(M, K);
+    return i8_gemm_launch_tp(st, out, act, wq, scale, resid, M, N, K, act_dtype, out_dtype, workspace, workspace_bytes, nullptr, nullptr,
+                             nullptr);
+}
+
+// tp: tensor-parallel form of the launch or null.  limbs_ext / ascale_ext: activation limbs that live outside the workspace
+// (the gathered rows of a tensor-parallel step); the workspace then only carries the status word.
+int i8_gemm_launch_tp(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
+                      int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes, const I8Tp *tp,
+                      const int8_t *limbs_ext, const float *ascale_ext) {
+    const size_t need = limbs_ext ? 256 : i8_gemm_workspace_bytes(M, K);
     if (!workspace || workspace_bytes < need)
         return fail(MYNN_E_ARG, "dequant_matmul: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
     if ((uintptr_t)workspace % 256) return fail(MYNN_E_ARG, "dequant_matmul: workspace must be 256-byte aligned");
+    if (limbs_ext && (act != nullptr || !ascale_ext || (uintptr_t)limbs_ext % 16))
+        return fail(MYNN_E_ARG, "dequant_matmul: external limbs need their row scales, 16-byte alignment and no activation tensor");
     const int NC = nc_for(M);
     int *status = (int *)workspace;
-    float *ascale = (float *)((char *)workspace + 256);
-    int8_t *limbs = (int8_t *)workspace + 512;  // rows 3M..NC-1 are padding: whatever they hold only reaches
-                                                 // accumulator columns that are never read
+    float *ascale = limbs_ext ? const_cast<float *>(ascale_ext) : (float *)((char *)workspace + 256);
+    int8_t *limbs = limbs_ext ? const_cast<int8_t *>(limbs_ext) : (int8_t *)workspace + 512;
+    // limb rows 3M..NC-1 are padding: whatever they hold only reaches accumulator columns that are never read
     if (act != nullptr) {  // act == nullptr: a fused producer has already left limbs and row scales in the workspace
         const bool row_kernel = K % 8 == 0 && (size_t)K * 4 <= 200 * 1024 && ((uintptr_t)act % 16) == 0;
         const size_t smem = (size_t)K * 4;
@@ -708,6 +761,8 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
     p.N = N;
     p.K = K;
     p.status = status;
+    if (tp) p.tp = *tp;
+    else memset(&p.tp, 0, sizeof p.tp);
     p.skip_last_stage = 0;
     {
         int want = 1;

@@ -9,9 +9,14 @@ namespace mynn {
 constexpr int kI8MaxRows = 32;  // activation rows per launch: 3 limbs x 32 rows = 96 accumulator columns
 // Scratch layout: [0,256) status word, [256,512) activation row scales, then the int8 limb matrix.
 size_t i8_gemm_workspace_bytes(int M, int K);
+int i8_gemm_limb_rows(int M);  // rows of the limb matrix for M activation rows (3 per row, padded to an MMA width)
 bool i8_gemm_supported(int M, int N, int K, const void *wq, int act_dtype, int out_dtype);
 int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
                    int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes);
+struct I8Tp;  // tp_fused.cuh
+int i8_gemm_launch_tp(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
+                      int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes, const I8Tp *tp,
+                      const int8_t *limbs_ext, const float *ascale_ext);
 // Fused producers: leave limbs + row scales in `workspace`; the following i8_gemm_launch is called with act == nullptr.
 // rms_norm: y = round(RMSNorm(x) * w); with part != nullptr first sum_out = round(x + round(part)) is stored and
 // normalised.  norm_out may be null.  swiglu: h = round(swish(gate) * up).

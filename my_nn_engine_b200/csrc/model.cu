@@ -55,8 +55,8 @@ struct Model {
     int32_t *tok_dev;
     char *h_in = nullptr;  // pinned mirror of the input block
     void *x, *n, *qkv, *q_rot, *attn, *gu, *h, *last_x, *logits, *logits_full;
-    float *part, *pairs, *pairs_all;  // part = partial-sum buffer 0 of the peer-shared block (tp_world > 1)
-    char *tp_block = nullptr;         // cudaMalloc'd block shared with the peers: TpLocal header + two partial-sum buffers
+    float *part, *pairs, *pairs_all;  // part = f32 partial sums of a row-parallel product (tp_world > 1, ncclAllReduce path)
+    char *tp_block = nullptr;         // cudaMalloc'd block shared with the peers (fused reduction of decode steps, tp_fused.cuh)
     size_t tp_block_bytes = 0;
     TpPeers tp = {};
     bool tp_attached = false;
@@ -134,9 +134,11 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     const size_t esz = dtype_size(dt);
     const int Nq = m.Hq * D, Nkv = m.Hkv * D;
     const float attn_scale = 1.0f / sqrtf((float)D);
-    const bool tp_fused = tp > 1 && m.tp_attached && m.gemm_ws != nullptr && M <= kI8MaxRows && H % 16 == 0 && (size_t)H * 4 <= 200 * 1024;
     const bool fused = m.gemm_ws != nullptr && M <= kI8MaxRows && H % 16 == 0 && m.ffn % 16 == 0 &&
                        (size_t)std::max(H, m.ffn) * 4 <= 200 * 1024;
+    // decode steps of a tensor-parallel model: the reduction fused with its neighbours over peer memory (tp_fused.cuh)
+    const bool tp_fused = tp > 1 && m.tp_attached && fused && S == 1 && M <= m.tp.lay.max_rows && Nq % 16 == 0 && m.weights_aligned;
+    bool gathered = false;  // the activations of the next column-parallel product are the limb rows delivered by a fused reduction
 
     // prefill chunks (more than 32 rows): RMSNorm and Swish*Mul write the two limbs of the prefill kernel themselves
     if (S >= 64 && dt != MYNN_F32 && (D == 64 || D == 128)) m.tc_attention_ran = true;  // the attention launcher may pick the tcgen05 kernels
@@ -146,8 +148,15 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     bool n_limbs2 = false;  // the last norm left two-limb rows in the workspace instead of m.n
 
     // norm(x [+ part]) feeding a DequantMatMul: either limbs in the workspace (fused) or the bf16 tensor m.n
+    auto reduce = [&](int buf, int producer_k, const void *w) -> int {  // fused reduction of the partial sums in buffer `buf`
+        int skip = 0, want = 2;
+        if (g_inject_stall.compare_exchange_strong(want, 0)) skip = 1;  // test aid: this launch delivers nothing to the peers
+        gathered = w != nullptr;
+        return launch_tp_reduce_norm_gather(st, dt, m.tp, buf, i8_gemm_grid_ctas(H, producer_k), m.x, w, c.rms_eps, M, skip);
+    };
     auto norm = [&](const void *w, const float *part, int rows, const void *src) -> int {
         n_limbs2 = false;
+        gathered = false;
         if (fused && rows <= kI8MaxRows)
             return launch_rms_norm_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, nullptr, part ? m.x : nullptr, src, part, w,
                                          c.rms_eps, rows, H);
@@ -159,6 +168,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         return mynn_b200_rms_norm(st, m.n, src, w, c.rms_eps, rows, H, dt);
     };
     auto gemm_n = [&](void *out, const int8_t *w, const void *scale, int rows, int N, int out_dtype) -> int {
+        if (gathered) return launch_tp_gemm_gathered(st, m.tp, out, w, scale, rows, N, out_dtype, m.gemm_ws, m.gemm_ws_bytes);
         if (fused && rows <= kI8MaxRows) return gemm_prequant(st, m, out, w, scale, nullptr, rows, N, H, out_dtype);
         if (n_limbs2) return gemm_prequant2(st, m, out, w, scale, nullptr, rows, N, H, out_dtype);
         return gemm(st, m, out, m.n, w, scale, nullptr, rows, N, H, out_dtype);
@@ -236,15 +246,15 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
                 RC(gemm(st, m, m.x, m.attn, L.wo, L.so, m.x, M, H, Nq, dt));
             }
             RC(norm(L.ln2, nullptr, M, m.x));
+        } else if (tp_fused) {
+            // partial rows go straight to their owners; the owners finish them and deliver the normed rows to everybody
+            RC(launch_tp_gemm_scatter(st, m.tp, 0, attn_limbs ? nullptr : m.attn, L.wo, (const float *)L.so, M, H, Nq, dt, m.gemm_ws, m.gemm_ws_bytes));
+            RC(reduce(0, Nq, L.ln2));
         } else {
             if (attn_limbs) RC(gemm_prequant(st, m, m.part, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
             else RC(gemm(st, m, m.part, m.attn, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
-            if (tp_fused) {  // peers' partial sums are read over NVLink inside the add + norm + limbs kernel
-                RC(launch_tp_reduce_norm_limbs(st, dt, m.tp, 0, m.gemm_ws, m.gemm_ws_bytes, m.x, L.ln2, c.rms_eps, M, H));
-            } else {
-                RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
-                RC(norm(L.ln2, m.part, M, m.x));  // x = round(x + round(sum of partials)), then the norm
-            }
+            RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
+            RC(norm(L.ln2, m.part, M, m.x));  // x = round(x + round(sum of partials)), then the norm
         }
         // --- MLP block ---
         const bool fuse_mlp = fused && L.gu_fused;
@@ -278,18 +288,16 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
             else if (h_limbs2) RC(gemm_prequant2(st, m, m.x, L.wd, L.sd, m.x, M, H, m.ffn, dt));
             else RC(gemm(st, m, m.x, m.h, L.wd, L.sd, m.x, M, H, m.ffn, dt));
             if (!last) RC(norm(next_norm, nullptr, M, m.x));
+        } else if (tp_fused) {
+            RC(launch_tp_gemm_scatter(st, m.tp, 1, fuse_mlp ? nullptr : m.h, L.wd, (const float *)L.sd, M, H, m.ffn, dt, m.gemm_ws, m.gemm_ws_bytes));
+            RC(reduce(1, m.ffn, last ? m.final_norm : next_norm));  // after the last layer: the final norm, whose rows feed lm_head
         } else {
-            float *pdst = tp_fused ? tp_part(m.tp.local, m.tp.part_off[1]) : m.part;
-            if (fuse_mlp) RC(gemm_prequant(st, m, pdst, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
-            else if (h_limbs2) RC(gemm_prequant2(st, m, pdst, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
-            else RC(gemm(st, m, pdst, m.h, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
-            if (tp_fused) {
-                RC(launch_tp_reduce_norm_limbs(st, dt, m.tp, 1, m.gemm_ws, m.gemm_ws_bytes, m.x, next_norm, c.rms_eps, M, H));
-            } else {
-                RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
-                if (last) RC(launch_add_f32_rms_norm(st, dt, m.x, nullptr, m.x, m.part, nullptr, c.rms_eps, M, H));
-                else RC(norm(next_norm, m.part, M, m.x));
-            }
+            if (fuse_mlp) RC(gemm_prequant(st, m, m.part, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
+            else if (h_limbs2) RC(gemm_prequant2(st, m, m.part, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
+            else RC(gemm(st, m, m.part, m.h, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
+            RC(comm_all_reduce(st, m.part, m.part, (size_t)M * H, MYNN_F32));
+            if (last) RC(launch_add_f32_rms_norm(st, dt, m.x, nullptr, m.x, m.part, nullptr, c.rms_eps, M, H));
+            else RC(norm(next_norm, m.part, M, m.x));
         }
     }
     // --- head: only the last token of each sequence is needed ---
@@ -300,7 +308,9 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         xl = m.last_x;
     }
     const bool fused_head = m.gemm_ws != nullptr && B <= kI8MaxRows && H % 16 == 0 && (size_t)H * 4 <= 200 * 1024;
-    if (fused_head) {
+    if (gathered) {  // the last fused reduction applied the final norm and delivered its rows
+        RC(launch_tp_gemm_gathered(st, m.tp, m.logits, m.lm_w, m.lm_scale, B, m.vocab_l, dt, m.gemm_ws, m.gemm_ws_bytes));
+    } else if (fused_head) {
         RC(launch_rms_norm_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, nullptr, nullptr, xl, nullptr, m.final_norm, c.rms_eps, B, H));
         RC(gemm_prequant(st, m, m.logits, m.lm_w, m.lm_scale, nullptr, B, m.vocab_l, H, dt));
     } else {
@@ -402,7 +412,7 @@ static int model_create(Model **out, void **initializer, void **session_state) {
                  o_logits = take((size_t)c.batch * m->vocab_l * esz),
                  o_full = take(tp > 1 ? (size_t)c.batch * c.vocab * esz : 0), 
                  o_pairs = take((size_t)c.batch * 8), o_pairs_all = take((size_t)c.batch * 8 * std::max(tp, 16)),
-                 o_ws = take(m->attn_ws_bytes), o_gws = take(m->gemm_ws_bytes),
+                 o_ws = take(m->attn_ws_bytes), o_gws = take(m->gemm_ws_bytes), o_part = take(tp > 1 ? R * H * 4 : 0),
                  o_kvpos = take(c.stream_window > 0 ? (size_t)c.max_seq_len * 8 : 0),
                  o_krot = take(c.stream_window > 0 ? (size_t)c.batch * m->Hkv * c.max_seq_len * D * esz : 0);
     const bool want_deq = c.kv_int8 && prefill >= 64 && c.dtype != MYNN_F32 && (D == 64 || D == 128);
@@ -430,10 +440,11 @@ static int model_create(Model **out, void **initializer, void **session_state) {
     m->k_rot = a + o_krot;
     m->k_deq = want_deq ? a + o_kdeq : nullptr;
     m->v_deq = want_deq ? a + o_vdeq : nullptr;
-    m->part = nullptr;
-    if (tp > 1) {
-        const size_t pbytes = up256(R * H * 4);
-        m->tp_block_bytes = 256 + 2 * pbytes;
+    m->part = tp > 1 ? (float *)(a + o_part) : nullptr;
+    if (tp > 1 && c.use_tensor_gemm && c.batch <= kI8MaxRows && H % 16 == 0) {
+        // the block the fused reduction of decode steps shares with the peers (tp_fused.cuh); without it the step uses NCCL
+        m->tp.lay = tp_layout(c.batch, H, tp);
+        m->tp_block_bytes = m->tp.lay.bytes;
         e = cudaMalloc(&m->tp_block, m->tp_block_bytes);
         if (e != cudaSuccess) {
             cudaFree(m->arena);
@@ -441,12 +452,9 @@ static int model_create(Model **out, void **initializer, void **session_state) {
             return fail(MYNN_E_CUDA, "model_init: cudaMalloc of the peer-shared block failed: %s", cudaGetErrorString(e));
         }
         cudaMemset(m->tp_block, 0, m->tp_block_bytes);
-        m->tp.local = (TpLocal *)m->tp_block;
-        m->tp.part_off[0] = 256;
-        m->tp.part_off[1] = 256 + pbytes;
         m->tp.rank = c.tp_rank;
         m->tp.world = tp;
-        m->part = tp_part(m->tp.local, m->tp.part_off[0]);
+        m->tp.blocks[c.tp_rank] = m->tp_block;
     }
     e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMallocHost((void **)&m->h_in, 16 + R * 8);
@@ -517,9 +525,12 @@ static int copy_result_to_host(Model &m, void *dst) {
         if (pfa) return fail(MYNN_E_CUDA, "model: pipeline wait %d timed out inside the tcgen05 prefill attention", pfa);
     }
     if (m.tp_attached) {
-        int st_ = 0;
-        MYNN_CUDA_OK(cudaMemcpy(&st_, &m.tp.local->status, sizeof st_, cudaMemcpyDeviceToHost));
-        if (st_) return fail(MYNN_E_COMM, "tensor-parallel reduction: a wait for a peer timed out (status %d)", st_);
+        int *word = &tp_header(m.tp_block)->status, st_ = 0;
+        MYNN_CUDA_OK(cudaMemcpy(&st_, word, sizeof st_, cudaMemcpyDeviceToHost));
+        if (st_) {
+            MYNN_CUDA_OK(cudaMemset(word, 0, sizeof st_));
+            return fail(MYNN_E_COMM, "tensor-parallel reduction: a wait for a peer ran out of time (status %d)", st_);
+        }
     }
     return MYNN_OK;
 }
@@ -596,7 +607,7 @@ extern "C" void model_destroy(void *state) {
     if (m->arena) cudaFree(m->arena);
     if (m->h_in) cudaFreeHost(m->h_in);
     for (int r = 0; r < m->tp.world; r++)
-        if (m->tp_attached && r != m->tp.rank && m->tp.remote[r]) cudaIpcCloseMemHandle(m->tp.remote[r]);
+        if (m->tp_attached && r != m->tp.rank && m->tp.blocks[r]) cudaIpcCloseMemHandle(m->tp.blocks[r]);
     if (m->tp_block) cudaFree(m->tp_block);
     delete m;
 }
@@ -711,7 +722,7 @@ extern "C" int mynn_b200_model_stream(void *state, const int64_t *ids_host, int 
 extern "C" int mynn_b200_model_tp_export(void *state, void *handle_out_64_bytes) {
     if (!state || !handle_out_64_bytes) return fail(MYNN_E_ARG, "model_tp_export: null pointer");
     Model &m = *(Model *)state;
-    if (!m.tp_block) return fail(MYNN_E_STATE, "model_tp_export: the model is not tensor parallel");
+    if (!m.tp_block) return fail(MYNN_E_STATE, "model_tp_export: the model has no peer-shared block (not tensor parallel, more than 32 sequences, or no tensor-core GEMM)");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
     MYNN_CUDA_OK(cudaIpcGetMemHandle((cudaIpcMemHandle_t *)handle_out_64_bytes, m.tp_block));
     return MYNN_OK;
@@ -720,19 +731,16 @@ extern "C" int mynn_b200_model_tp_export(void *state, void *handle_out_64_bytes)
 extern "C" int mynn_b200_model_tp_attach(void *state, const void *handles_world_x_64_bytes) {
     if (!state || !handles_world_x_64_bytes) return fail(MYNN_E_ARG, "model_tp_attach: null pointer");
     Model &m = *(Model *)state;
-    if (!m.tp_block) return fail(MYNN_E_STATE, "model_tp_attach: the model is not tensor parallel");
+    if (!m.tp_block) return fail(MYNN_E_STATE, "model_tp_attach: the model has no peer-shared block");
     if (m.tp_attached) return fail(MYNN_E_STATE, "model_tp_attach: already attached");
     if (m.graph_exec) return fail(MYNN_E_STATE, "model_tp_attach: call before the first step");
     for (int r = 0; r < m.tp.world; r++) {
-        if (r == m.tp.rank) {
-            m.tp.remote[r] = m.tp.local;
-            continue;
-        }
+        if (r == m.tp.rank) continue;
         cudaIpcMemHandle_t h;
         memcpy(&h, (const char *)handles_world_x_64_bytes + (size_t)r * 64, 64);
         void *p = nullptr;
         MYNN_CUDA_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
-        m.tp.remote[r] = (TpLocal *)p;
+        m.tp.blocks[r] = (char *)p;
     }
     m.tp_attached = true;
     return MYNN_OK;

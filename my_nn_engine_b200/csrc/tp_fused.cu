@@ -1,21 +1,23 @@
-// Tensor-parallel all-reduce fused with the operators that consume it, over NVLink peer memory.
+// Tensor-parallel all-reduce fused with the operators around it, over NVLink peer memory (data flow: tp_fused.cuh).
 //
 // A row-parallel DequantMatMul (o_proj, down_proj) leaves an f32 partial sum [rows, hidden] on every rank.  The engine's
 // schedule then needs: all-reduce(sum) -> round -> residual add -> RMSNorm -> (here) activation limbs for the next
-// DequantMatMul.  Instead of a collective library call followed by separate kernels, ONE kernel per rank
-//   1. tells every peer that its own partial sums are complete (a release store of the step number into the peer's
-//      flag array) and waits, with a time limit, until every peer has said the same;
-//   2. reads the partial sums of ALL ranks straight from their memory (plain peer loads over NVLink/NVSwitch, no
-//      multicast) and adds them in rank order in f32 -- every rank computes the identical sum;
-//   3. finishes the row: x = round(x + round(sum)), y = round(RMSNorm(x) * w), limbs of y.
-// The messages are small (512 KB at batch 32), so the one-shot pattern (every rank reads everything) beats a
-// reduce-scatter/all-gather pair, which would need a second cross-GPU barrier.
+// DequantMatMul on every rank (its AllReduce operator, src/graph/operator.rs, sums f32 in rank order:
+// crates/comm/src/uds.rs:106-116).  Here the reduction is a reduce-scatter by rows that the producing GEMM performs with
+// peer STORES from its epilogue, one kernel per rank that finishes the rows it owns, and an all-gather of the finished
+// limb rows, again by peer stores, that the consuming GEMM waits for while its weights are already streaming.
 //
-// Buffers: two partial-sum buffers are used alternately (attention block / MLP block).  A rank overwrites a buffer only
-// after it has passed the barrier of the following reduction, which every peer reaches only after it has finished
-// reading that buffer, so no reader can be overtaken.
-// The wait is bounded (2 s): on expiry the kernel records status 21 and carries on, so the GPU never hangs on a lost
-// peer; the host sees the status at its next check.
+// Ordering.  Data stores to a peer are followed by a CTA barrier, a system-scope fence and a release increment of a counter
+// in the peer's header; the reader polls the counter with acquire loads and only then touches the data (through L2: the
+// lines were written by another GPU).  A buffer is only rewritten after its readers are provably done: a rank delivers
+// partial sums for reduction j+1 only after its column-parallel GEMM has received the limb rows of reduction j from every
+// rank, i.e. after every rank has finished reading the partial sums of reduction j; and a rank delivers limb rows of
+// reduction j+1 to a peer only after that peer's row-parallel GEMM, which runs behind the reader of reduction j's limb rows
+// in the peer's stream, has delivered its partial sums.
+//
+// Every wait is bounded (MYNN_OPT_WAIT_BUDGET_US, default 2 s): on expiry the kernel records a status (21 here, 22 in the
+// GEMM's wait for limb rows), goes on with what it has, still delivers and signals, and returns; the host reports
+// MYNN_E_COMM at its next check.  A lost peer therefore never hangs a GPU.
 #include "common.cuh"
 #include "i8_gemm.cuh"
 #include "tcgen05.cuh"
@@ -25,164 +27,320 @@ namespace mynn {
 
 MYNN_DEFINE_WAIT_BUDGET_SETTER(tp_fused)
 
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+static size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+
+TpLayout tp_layout(int max_rows, int hidden, int world) {
+    TpLayout l;
+    l.world = world;
+    l.max_rows = max_rows;
+    l.hidden = hidden;
+    l.rows_cap = (max_rows + world - 1) / world;
+    l.nc = i8_gemm_limb_rows(max_rows);
+    size_t off = sizeof(TpHeader);
+    const size_t part = up256((size_t)world * l.rows_cap * hidden * sizeof(float));
+    l.part_off[0] = off;
+    off += part;
+    l.part_off[1] = off;
+    off += part;
+    l.limb_off = off;
+    off += up256((size_t)l.nc * hidden);
+    l.ascale_off = off;
+    off += up256((size_t)max_rows * sizeof(float));
+    l.bytes = off;
+    return l;
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ float4 ld_peer_f4(const float *p) {  // system-scope load: never served from a stale L1 line
-    float4 v;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned long long tp_now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+
+struct TpReduceParams {
+    char *blocks[kTpMaxRanks];
+    size_t part_off, limb_off, ascale_off;
+    int rank, world, rows_cap, buf, n_sig, M, D, skip_signal;
+    float eps;
+};
 
 constexpr int kTpThreads = 1024;
 
-// grid = rows.  limbs / ascale / w may be null (then only x is updated: the reduction after the last layer).
+__device__ __forceinline__ float4 ld_l2_f4(const float *p) {  // written by a peer GPU: read through L2, never from a stale L1 line
+    return __ldcg(reinterpret_cast<const float4 *>(p));
+}
+
+// grid = max(rows this rank owns, 1).  CTA j finishes row m = rank + j * world.  w may be null (then only x is updated and no
+// limbs are delivered; the counters still advance).
 template <typename T>
-__global__ void __launch_bounds__(kTpThreads)
-tp_reduce_norm_limbs_kernel(int8_t *limbs, float *ascale, T *x, const T *w, float eps, int D, int buf, const TpPeers peers) {
+__global__ void __launch_bounds__(kTpThreads) tp_reduce_norm_gather_kernel(T *x, const T *w, const TpReduceParams p) {
     extern __shared__ __align__(16) float row_s[];
     __shared__ float red[40];
-    TpLocal *loc = peers.local;
-    const uint32_t target = *(volatile uint32_t *)&loc->epoch + 1u;  // the epoch only changes when this kernel ends
-    // 1. announce and wait
-    if (blockIdx.x == 0 && threadIdx.x < peers.world)
-        st_release_sys(&peers.remote[threadIdx.x]->flags[peers.rank], target);
-    if (threadIdx.x < peers.world) {
-        const unsigned long long t0 = tp_now_ns();
-        while ((int)(ld_acquire_sys(&loc->flags[threadIdx.x]) - target) < 0) {
-            __nanosleep(100);
-            if (tp_now_ns() - t0 > d_wait_budget_ns) {
-                atomicExch(&loc->status, 21);
+    TpHeader *hdr = tp_header(p.blocks[p.rank]);
+    const int D = p.D;
+    const int m = p.rank + (int)blockIdx.x * p.world;
+    const bool have_row = m < p.M;
+    // 1. wait until every source rank has delivered all tiles of its partial sums (bounded)
+    const uint32_t part_target = *(volatile uint32_t *)&hdr->part_expected[p.buf] + (uint32_t)p.n_sig;
+    if (threadIdx.x < p.world) {
+        const unsigned long long t0 = global_ns();
+        while ((int)(ld_acquire_sys_u32(&hdr->part_cnt[p.buf][threadIdx.x]) - part_target) < 0) {
+            __nanosleep(40);
+            if (global_ns() - t0 > d_wait_budget_ns) {
+                atomicExch(&hdr->status, 21);
                 break;
             }
         }
     }
     __syncthreads();
-    // 2. sum the partial rows of all ranks in rank order, 3. residual add
-    const int m = blockIdx.x;
-    const size_t base = (size_t)m * D;
-    float ss = 0.f;
-    for (int i = 4 * threadIdx.x; i < D; i += 4 * kTpThreads) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        float4 part[8];
+    if (have_row) {
+        // 2. add the partial rows of all ranks in rank order, 3. residual add
+        const float *part = reinterpret_cast<const float *>(p.blocks[p.rank] + p.part_off) + (size_t)blockIdx.x * D;
+        const size_t slot_stride = (size_t)p.rows_cap * D;
+        T *xrow = x + (size_t)m * D;
+        float ss = 0.f;
+        for (int i = 4 * threadIdx.x; i < D; i += 4 * kTpThreads) {
+            float4 v[kTpMaxRanks];
 #pragma unroll
-        for (int r = 0; r < 8; r++)
-            if (r < peers.world) part[r] = ld_peer_f4(tp_part(peers.remote[r], peers.part_off[buf]) + base + i);
+            for (int r = 0; r < kTpMaxRanks; r++)
+                if (r < p.world) v[r] = ld_l2_f4(part + (size_t)r * slot_stride + i);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int r = 0; r < 8; r++)
-            if (r < peers.world) {
-                acc.x += part[r].x;
-                acc.y += part[r].y;
-                acc.z += part[r].z;
-                acc.w += part[r].w;
+            for (int r = 0; r < kTpMaxRanks; r++)
+                if (r < p.world) {
+                    acc.x += v[r].x;
+                    acc.y += v[r].y;
+                    acc.z += v[r].z;
+                    acc.w += v[r].w;
+                }
+            const float s4[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float t = round_store<T>(to_f32<T>(xrow[i + j]) + round_store<T>(s4[j]));
+                xrow[i + j] = from_f32<T>(t);
+                row_s[i + j] = t;
+                ss += t * t;
             }
-        const float s4[4] = {acc.x, acc.y, acc.z, acc.w};
+        }
+        if (w != nullptr) {
+            ss = warp_sum(ss);
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float tot = 0.f;
+                for (int i = 0; i < kTpThreads / 32; i++) tot += red[i];
+                red[33] = 1.0f / sqrtf(tot / (float)D + p.eps);
+            }
+            __syncthreads();
+            const float inv = red[33];
+            float mx = 0.f;
+            bool bad = false;
+            for (int i = threadIdx.x; i < D; i += kTpThreads) {
+                const float y = round_store<T>(row_s[i] * inv * to_f32<T>(w[i]));
+                row_s[i] = y;
+                bad |= !(fabsf(y) <= 3.0e38f);
+                mx = fmaxf(mx, fabsf(y));
+            }
+            // block maximum -> power-of-two limb scale (|y| * sc < 2^22), as in the other limb producers
+            mx = warp_max(mx);
+            const unsigned anybad = __syncthreads_or(bad);
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float t = 0.f;
+                for (int i = 0; i < kTpThreads / 32; i++) t = fmaxf(t, red[i]);
+                int e = 0;
+                if (t > 0.f) frexpf(t, &e);
+                const float sc = t > 0.f ? ldexpf(1.0f, 22 - e) : 1.0f;
+                red[32] = anybad ? 0.f : sc;
+                red[34] = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc;
+            }
+            __syncthreads();
+            const float sc = red[32];
+            if (!p.skip_signal) {
+                // 4. deliver the three limb rows and the row scale to every rank (peer stores; this rank's own copy too)
+                for (int gi = threadIdx.x; gi < (D >> 2); gi += kTpThreads) {
+                    uint32_t w0 = 0, w1 = 0, w2 = 0;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float v = round_store<T>(to_f32<T>(x[base + i + j]) + round_store<T>(s4[j]));
-            x[base + i + j] = from_f32<T>(v);
-            row_s[i + j] = v;
-            ss += v * v;
+                    for (int i = 0; i < 4; i++) {
+                        int A = sc == 0.f ? 0 : __float2int_rn(row_s[4 * gi + i] * sc);
+                        const int d0 = (int)(int8_t)(A & 0xFF);
+                        A = (A - d0) >> 8;
+                        const int d1 = (int)(int8_t)(A & 0xFF);
+                        A = (A - d1) >> 8;
+                        w0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
+                        w1 |= (uint32_t)(d1 & 0xFF) << (8 * i);
+                        w2 |= (uint32_t)(A & 0xFF) << (8 * i);
+                    }
+#pragma unroll
+                    for (int r = 0; r < kTpMaxRanks; r++)
+                        if (r < p.world) {
+                            uint32_t *l0 = reinterpret_cast<uint32_t *>(p.blocks[r] + p.limb_off + (size_t)(3 * m) * D);
+                            l0[gi] = w0;
+                            l0[gi + (D >> 2)] = w1;
+                            l0[gi + 2 * (D >> 2)] = w2;
+                        }
+                }
+                if (threadIdx.x < p.world)
+                    reinterpret_cast<float *>(p.blocks[threadIdx.x] + p.ascale_off)[m] = red[34];
+            }
         }
     }
-    if (w != nullptr) {
-        ss = warp_sum(ss);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float tot = 0.f;
-            for (int i = 0; i < kTpThreads / 32; i++) tot += red[i];
-            red[33] = 1.0f / sqrtf(tot / (float)D + eps);
-        }
-        __syncthreads();
-        const float inv = red[33];
-        float mx = 0.f;
-        bool bad = false;
-        for (int i = threadIdx.x; i < D; i += kTpThreads) {
-            const float y = round_store<T>(row_s[i] * inv * to_f32<T>(w[i]));
-            row_s[i] = y;
-            bad |= !(fabsf(y) <= 3.0e38f);
-            mx = fmaxf(mx, fabsf(y));
-        }
-        // block maximum -> power-of-two limb scale (|y| * sc < 2^22), as in the other limb producers
-        mx = warp_max(mx);
-        const unsigned anybad = __syncthreads_or(bad);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float t = 0.f;
-            for (int i = 0; i < kTpThreads / 32; i++) t = fmaxf(t, red[i]);
-            int e = 0;
-            if (t > 0.f) frexpf(t, &e);
-            const float sc = t > 0.f ? ldexpf(1.0f, 22 - e) : 1.0f;
-            red[32] = anybad ? 0.f : sc;
-            ascale[m] = anybad ? __int_as_float(0x7fc00000) : 1.0f / sc;
-        }
-        __syncthreads();
-        const float sc = red[32];
-        uint32_t *l0 = reinterpret_cast<uint32_t *>(limbs + (size_t)(3 * m) * D);
-        uint32_t *l1 = reinterpret_cast<uint32_t *>(limbs + (size_t)(3 * m + 1) * D);
-        uint32_t *l2 = reinterpret_cast<uint32_t *>(limbs + (size_t)(3 * m + 2) * D);
-        for (int gi = threadIdx.x; gi < (D >> 2); gi += kTpThreads) {
-            uint32_t w0 = 0, w1 = 0, w2 = 0;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                int A = sc == 0.f ? 0 : __float2int_rn(row_s[4 * gi + i] * sc);
-                const int d0 = (int)(int8_t)(A & 0xFF);
-                A = (A - d0) >> 8;
-                const int d1 = (int)(int8_t)(A & 0xFF);
-                A = (A - d1) >> 8;
-                w0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
-                w1 |= (uint32_t)(d1 & 0xFF) << (8 * i);
-                w2 |= (uint32_t)(A & 0xFF) << (8 * i);
-            }
-            l0[gi] = w0;
-            l1[gi] = w1;
-            l2[gi] = w2;
-        }
-    }
-    // the last CTA to finish advances the epoch for the next reduction
+    // every store of this CTA is ordered before the increments: CTA barrier, then fence + release per destination
     __syncthreads();
+    if (have_row && w != nullptr && !p.skip_signal && threadIdx.x < p.world) {
+        __threadfence_system();
+        red_release_sys_add_u32(&tp_header(p.blocks[threadIdx.x])->gather_cnt, 1u);
+    }
+    // the last CTA to finish records what the counters must reach for the kernels that follow
     if (threadIdx.x == 0) {
         __threadfence();
-        if (atomicAdd(&loc->ticket, 1u) == gridDim.x - 1) {
-            loc->ticket = 0u;
+        if (atomicAdd(&hdr->ticket, 1u) == gridDim.x - 1) {
+            hdr->ticket = 0u;
+            hdr->part_expected[p.buf] = part_target;
+            if (w != nullptr) hdr->gather_expected += (uint32_t)p.M;
             __threadfence();
-            *(volatile uint32_t *)&loc->epoch = target;
         }
     }
 }
 
-int launch_tp_reduce_norm_limbs(cudaStream_t st, int dtype, const TpPeers &peers, int buf, void *workspace,
-                                size_t workspace_bytes, void *x, const void *w, float eps, int rows, int D) {
-    if (rows < 1 || rows > kI8MaxRows || D % 16) return fail(MYNN_E_UNSUPPORTED, "tp reduce: rows=%d D=%d not supported", rows, D);
-    if ((size_t)D * 4 > 200 * 1024) return fail(MYNN_E_UNSUPPORTED, "tp reduce: row of %d elements exceeds shared memory", D);
-    int8_t *limbs = nullptr;
-    float *ascale = nullptr;
-    if (w != nullptr) {
-        if (!workspace || workspace_bytes < i8_gemm_workspace_bytes(rows, D) || (uintptr_t)workspace % 256)
-            return fail(MYNN_E_ARG, "tp reduce: workspace too small or misaligned");
-        ascale = (float *)((char *)workspace + 256);
-        limbs = (int8_t *)workspace + 512;
+static void fill_i8tp(I8Tp &t, const TpPeers &peers, int mode, int buf) {
+    memset(&t, 0, sizeof t);
+    t.mode = mode;
+    t.world = peers.world;
+    t.rank = peers.rank;
+    t.rows_cap = peers.lay.rows_cap;
+    for (int r = 0; r < peers.world; r++) {
+        t.part[r] = reinterpret_cast<float *>(peers.blocks[r] + peers.lay.part_off[buf]);
+        t.sig[r] = &tp_header(peers.blocks[r])->part_cnt[buf][peers.rank];
     }
+    TpHeader *own = tp_header(peers.blocks[peers.rank]);
+    t.gather_cnt = &own->gather_cnt;
+    t.gather_expected = &own->gather_expected;
+    t.status = &own->status;
+}
+
+int launch_tp_gemm_scatter(cudaStream_t st, const TpPeers &peers, int buf, const void *act, const int8_t *wq, const float *scale,
+                           int M, int N, int K, int act_dtype, void *workspace, size_t workspace_bytes) {
+    if (buf != 0 && buf != 1) return fail(MYNN_E_ARG, "tp scatter: buffer %d", buf);
+    if (M < 1 || M > peers.lay.max_rows || N != peers.lay.hidden)
+        return fail(MYNN_E_ARG, "tp scatter: M=%d N=%d do not fit a group of %d rows x %d", M, N, peers.lay.max_rows, peers.lay.hidden);
+    if (!i8_gemm_supported(M, N, K, wq, act_dtype, MYNN_F32))
+        return fail(MYNN_E_UNSUPPORTED, "tp scatter: needs the tensor-core DequantMatMul (at most %d rows, K %% 16 == 0, aligned weights)", kI8MaxRows);
+    I8Tp t;
+    fill_i8tp(t, peers, 1, buf);
+    return i8_gemm_launch_tp(st, nullptr, act, wq, scale, nullptr, M, N, K, act_dtype, MYNN_F32, workspace, workspace_bytes, &t, nullptr, nullptr);
+}
+
+int launch_tp_gemm_gathered(cudaStream_t st, const TpPeers &peers, void *out, const int8_t *wq, const void *scale, int M, int N,
+                            int out_dtype, void *workspace, size_t workspace_bytes) {
+    const int K = peers.lay.hidden;
+    if (M < 1 || M > peers.lay.max_rows) return fail(MYNN_E_ARG, "tp gathered: M=%d exceeds the group's %d rows", M, peers.lay.max_rows);
+    if (!i8_gemm_supported(M, N, K, wq, MYNN_BF16, out_dtype))
+        return fail(MYNN_E_UNSUPPORTED, "tp gathered: needs the tensor-core DequantMatMul (K %% 16 == 0, aligned weights)");
+    I8Tp t;
+    fill_i8tp(t, peers, 2, 0);
+    char *own = peers.blocks[peers.rank];
+    return i8_gemm_launch_tp(st, out, nullptr, wq, scale, nullptr, M, N, K, MYNN_BF16, out_dtype, workspace, workspace_bytes, &t,
+                             reinterpret_cast<const int8_t *>(own + peers.lay.limb_off),
+                             reinterpret_cast<const float *>(own + peers.lay.ascale_off));
+}
+
+int launch_tp_reduce_norm_gather(cudaStream_t st, int dtype, const TpPeers &peers, int buf, int n_sig, void *x, const void *w, float eps,
+                                 int M, int skip_signal) {
+    const int D = peers.lay.hidden;
+    if (buf != 0 && buf != 1) return fail(MYNN_E_ARG, "tp reduce: buffer %d", buf);
+    if (M < 1 || M > peers.lay.max_rows || D % 16) return fail(MYNN_E_UNSUPPORTED, "tp reduce: rows=%d D=%d not supported", M, D);
+    if ((size_t)D * 4 > 200 * 1024) return fail(MYNN_E_UNSUPPORTED, "tp reduce: row of %d elements exceeds shared memory", D);
+    TpReduceParams p;
+    for (int r = 0; r < kTpMaxRanks; r++) p.blocks[r] = r < peers.world ? peers.blocks[r] : nullptr;
+    p.part_off = peers.lay.part_off[buf];
+    p.limb_off = peers.lay.limb_off;
+    p.ascale_off = peers.lay.ascale_off;
+    p.rank = peers.rank;
+    p.world = peers.world;
+    p.rows_cap = peers.lay.rows_cap;
+    p.buf = buf;
+    p.n_sig = n_sig;
+    p.M = M;
+    p.D = D;
+    p.skip_signal = skip_signal;
+    p.eps = eps;
+    const int own_rows = peers.rank < M ? (M - peers.rank + peers.world - 1) / peers.world : 0;
+    const int grid = own_rows > 0 ? own_rows : 1;
     const size_t smem = (size_t)D * 4;
     MYNN_DISPATCH_DTYPE(dtype, T, {
-        auto kern = tp_reduce_norm_limbs_kernel<T>;
+        auto kern = tp_reduce_norm_gather_kernel<T>;
         if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<rows, kTpThreads, smem, st>>>(limbs, ascale, (T *)x, (const T *)w, eps, D, buf, peers);
+        kern<<<grid, kTpThreads, smem, st>>>((T *)x, (const T *)w, p);
     });
-    MYNN_LAUNCH_OK("tp_reduce_norm_limbs_kernel");
+    MYNN_LAUNCH_OK("tp_reduce_norm_gather_kernel");
+    return MYNN_OK;
+}
+
+static int group_to_peers(const mynn_b200_tp_group *g, TpPeers &peers, const char *who) {
+    if (!g) return fail(MYNN_E_ARG, "%s: null group", who);
+    if (g->world < 1 || g->world > kTpMaxRanks || g->rank < 0 || g->rank >= g->world)
+        return fail(MYNN_E_ARG, "%s: rank %d of %d (at most %d ranks)", who, g->rank, g->world, kTpMaxRanks);
+    if (g->max_rows < 1 || g->max_rows > kI8MaxRows || g->hidden < 16 || g->hidden % 16)
+        return fail(MYNN_E_ARG, "%s: a group holds 1..%d rows of a multiple of 16 elements (got %d x %d)", who, kI8MaxRows, g->max_rows, g->hidden);
+    for (int r = 0; r < g->world; r++) {
+        if (!g->blocks[r] || (uintptr_t)g->blocks[r] % 256) return fail(MYNN_E_ARG, "%s: block %d is null or not 256-byte aligned", who, r);
+        peers.blocks[r] = (char *)g->blocks[r];
+    }
+    peers.rank = g->rank;
+    peers.world = g->world;
+    peers.lay = tp_layout(g->max_rows, g->hidden, g->world);
     return MYNN_OK;
 }
 
 }  // namespace mynn
+
+using namespace mynn;
+
+extern "C" size_t mynn_b200_tp_block_bytes(int max_rows, int hidden, int world) {
+    if (max_rows < 1 || max_rows > kI8MaxRows || hidden < 16 || hidden % 16 || world < 1 || world > kTpMaxRanks) return 0;
+    return tp_layout(max_rows, hidden, world).bytes;
+}
+
+extern "C" int mynn_b200_tp_dequant_matmul_scatter(void *stream, const mynn_b200_tp_group *group, int buffer, const void *act,
+                                                   const int8_t *wq, const float *scale, int M, int K, int act_dtype,
+                                                   void *workspace, size_t workspace_bytes) {
+    TpPeers peers;
+    if (int rc = group_to_peers(group, peers, "tp_dequant_matmul_scatter")) return rc;
+    if (!act || !wq || !scale) return fail(MYNN_E_ARG, "tp_dequant_matmul_scatter: null pointer");
+    if (!dtype_ok(act_dtype)) return fail(MYNN_E_ARG, "tp_dequant_matmul_scatter: bad dtype %d", act_dtype);
+    return launch_tp_gemm_scatter((cudaStream_t)stream, peers, buffer, act, wq, scale, M, peers.lay.hidden, K, act_dtype, workspace, workspace_bytes);
+}
+
+extern "C" int mynn_b200_tp_reduce_norm_gather(void *stream, const mynn_b200_tp_group *group, int buffer, int producer_K, void *x,
+                                               const void *weight, float eps, int M, int dtype) {
+    TpPeers peers;
+    if (int rc = group_to_peers(group, peers, "tp_reduce_norm_gather")) return rc;
+    if (!x) return fail(MYNN_E_ARG, "tp_reduce_norm_gather: null pointer");
+    if (producer_K < 16) return fail(MYNN_E_ARG, "tp_reduce_norm_gather: producer_K %d", producer_K);
+    int skip = 0;
+    {
+        int want = 2;
+        if (g_inject_stall.compare_exchange_strong(want, 0)) skip = 1;
+    }
+    return launch_tp_reduce_norm_gather((cudaStream_t)stream, dtype, peers, buffer, i8_gemm_grid_ctas(peers.lay.hidden, producer_K), x, weight,
+                                        eps, M, skip);
+}
+
+extern "C" int mynn_b200_tp_dequant_matmul_gathered(void *stream, const mynn_b200_tp_group *group, void *out, const int8_t *wq,
+                                                    const void *scale, int M, int N, int out_dtype, void *workspace,
+                                                    size_t workspace_bytes) {
+    TpPeers peers;
+    if (int rc = group_to_peers(group, peers, "tp_dequant_matmul_gathered")) return rc;
+    if (!out || !wq || !scale) return fail(MYNN_E_ARG, "tp_dequant_matmul_gathered: null pointer");
+    if (!dtype_ok(out_dtype)) return fail(MYNN_E_ARG, "tp_dequant_matmul_gathered: bad dtype %d", out_dtype);
+    return launch_tp_gemm_gathered((cudaStream_t)stream, peers, out, wq, scale, M, N, out_dtype, workspace, workspace_bytes);
+}
+
+extern "C" int mynn_b200_tp_check(void *stream, const mynn_b200_tp_group *group) {
+    TpPeers peers;
+    if (int rc = group_to_peers(group, peers, "tp_check")) return rc;
+    MYNN_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+    int *word = &tp_header(peers.blocks[peers.rank])->status;
+    int status = 0;
+    MYNN_CUDA_OK(cudaMemcpy(&status, word, sizeof status, cudaMemcpyDeviceToHost));
+    if (status) {
+        MYNN_CUDA_OK(cudaMemset(word, 0, sizeof status));
+        return fail(MYNN_E_COMM, "tensor-parallel reduction: a wait for a peer ran out of time (status %d)", status);
+    }
+    return MYNN_OK;
+}

@@ -1,4 +1,18 @@
-// Internal interface of the fused tensor-parallel reduction (tp_fused.cu).
+// Internal interface of the fused tensor-parallel reduction (tp_fused.cu) and of the two DequantMatMul forms that feed it
+// and are fed by it (i8_gemm.cu).
+//
+// Data flow of one reduction over `world` ranks (rows m of the step are dealt out: row m belongs to rank m % world):
+//   1. the row-parallel DequantMatMul (o_proj, down_proj) of every rank STORES its f32 partial row m straight into slot
+//      [its own rank][m / world] of the partial buffer of the rank that owns row m (plain peer stores over NVLink, issued
+//      from the GEMM epilogue), then adds 1 to a counter in that rank's header (release at system scope);
+//   2. the owner's reduction kernel waits until every source rank has signalled all its tiles, adds the `world` partial rows
+//      in rank order from its OWN memory, finishes the row (residual add, RMSNorm, activation limbs) and stores the limbs
+//      and the row scale into the limb buffer of EVERY rank, again followed by a counter increment;
+//   3. the column-parallel DequantMatMul that follows (qkv, gate/up, lm_head) streams its weights at once and only holds
+//      its activation (limb) loads back until all rows have arrived.
+// Every rank moves rows/world of the partial sums in and 3 bytes per element of its own rows out, instead of reading
+// every rank's whole partial tensor; the transfers overlap the GEMM epilogue and the weight prefetch of the next GEMM.
+// No load ever crosses NVLink, and nothing here uses multicast.
 #pragma once
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -6,31 +20,62 @@
 
 namespace mynn {
 
-constexpr int kTpMaxRanks = 8;  // ranks of one NVLink domain; sizes the flag and pointer arrays below
+constexpr int kTpMaxRanks = 8;  // ranks of one NVLink domain; sizes the counter and pointer arrays below
 
-// Header of the block of device memory every rank shares with its peers (cudaIpc); the two f32 partial-sum buffers
-// follow at the byte offsets TpPeers::part_off (identical on every rank).
-struct TpLocal {
-    uint32_t flags[kTpMaxRanks];  // flags[r] = last step number rank r has announced to this rank
-    uint32_t epoch;     // step number of the last completed reduction on this rank
-    uint32_t ticket;    // CTA arrival counter of the running reduction
-    int status;         // 21 = a wait for a peer ran out of time
-    uint32_t pad[5];
+// Header of the block of device memory every rank shares with its peers.  All counters are monotonic (they wrap modulo
+// 2^32 and are compared by signed difference); a block must be zeroed once before its first use.
+struct TpHeader {
+    uint32_t part_cnt[2][kTpMaxRanks];  // [buffer][source rank]: tiles of partial sums that rank has delivered so far (peers add)
+    uint32_t gather_cnt;                // limb rows delivered so far by the reductions of all ranks (peers add)
+    // written by this rank only (the last CTA of each of its reduction kernels):
+    uint32_t part_expected[2];          // value part_cnt[buffer][*] has reached once every reduction launched so far is fed
+    uint32_t gather_expected;           // value gather_cnt reaches once every reduction completed so far has been delivered
+    uint32_t ticket;                    // CTA arrival counter of the running reduction kernel
+    int status;                         // 21: a wait for partial sums ran out of time; 22: a wait for limb rows did
+    uint32_t pad[64 - 2 * kTpMaxRanks - 6];
 };
-static_assert(sizeof(TpLocal) == 64, "TpLocal is one 64-byte header");
+static_assert(sizeof(TpHeader) == 256, "TpHeader is one 256-byte header");
 
+// Geometry of a block; identical on every rank.  rows_cap = rows one rank can own = ceil(max_rows / world).
+struct TpLayout {
+    int world, max_rows, hidden, rows_cap, nc;  // nc = limb rows of the gathered matrix (3 per activation row, padded)
+    size_t part_off[2], limb_off, ascale_off, bytes;
+};
+TpLayout tp_layout(int max_rows, int hidden, int world);
+
+// A rank's view of the group: its own block and every rank's block as mapped into this process (blocks[rank] == own).
 struct TpPeers {
-    TpLocal *local;       // this rank's block
-    TpLocal *remote[kTpMaxRanks];   // every rank's block as mapped into this process (remote[rank] == local)
-    size_t part_off[2];   // byte offsets of the two partial-sum buffers inside a block
+    char *blocks[kTpMaxRanks];
     int rank, world;
+    TpLayout lay;
 };
 
-__host__ __device__ inline float *tp_part(TpLocal *blk, size_t off) { return (float *)((char *)blk + off); }
+__host__ __device__ inline TpHeader *tp_header(char *blk) { return reinterpret_cast<TpHeader *>(blk); }
 
-// sum over ranks of part[buf] -> x = round(x + round(sum)); if w != null: y = round(RMSNorm(x) * w) -> limbs + row scales
-// in `workspace` (the DequantMatMul workspace).  rows <= 32.
-int launch_tp_reduce_norm_limbs(cudaStream_t st, int dtype, const TpPeers &peers, int buf, void *workspace,
-                                size_t workspace_bytes, void *x, const void *w, float eps, int rows, int D);
+// What the tcgen05 DequantMatMul kernel needs to take part (passed by value in its parameters).
+struct I8Tp {
+    int mode;                          // 0: plain; 1: scatter partial rows to their owners; 2: activation limbs are gathered rows
+    int world, rank, rows_cap;
+    float *part[kTpMaxRanks];          // mode 1: partial buffer of every rank (slot layout [source][local row][N])
+    uint32_t *sig[kTpMaxRanks];        // mode 1: &header(rank r)->part_cnt[buf][this rank]
+    const uint32_t *gather_cnt;        // mode 2: own header's counter of delivered limb rows and the value it has to reach
+    const uint32_t *gather_expected;
+    int *status;                       // own header's status word
+};
+
+// Signals one GEMM launch sends to each destination rank (= CTAs of its grid); the reduction kernel waits for that many.
+int i8_gemm_grid_ctas(int N, int K);
+
+// Row-parallel DequantMatMul with the scatter epilogue.  act == nullptr: limbs already in `workspace`.
+int launch_tp_gemm_scatter(cudaStream_t st, const TpPeers &peers, int buf, const void *act, const int8_t *wq, const float *scale,
+                           int M, int N, int K, int act_dtype, void *workspace, size_t workspace_bytes);
+// sum over ranks of the partial rows this rank owns -> x[m] = round(x[m] + round(sum)); y = round(RMSNorm(x[m]) * w) -> limbs
+// + row scale into every rank's limb buffer.  n_sig = i8_gemm_grid_ctas of the GEMM that produced the partial sums.
+// skip_signal (test aid): do everything except the deliveries to the peers.
+int launch_tp_reduce_norm_gather(cudaStream_t st, int dtype, const TpPeers &peers, int buf, int n_sig, void *x, const void *w, float eps,
+                                 int M, int skip_signal);
+// Column-parallel DequantMatMul over the gathered limb rows.  `workspace` only carries the kernel's status word.
+int launch_tp_gemm_gathered(cudaStream_t st, const TpPeers &peers, void *out, const int8_t *wq, const void *scale, int M, int N,
+                            int out_dtype, void *workspace, size_t workspace_bytes);
 
 }  // namespace mynn

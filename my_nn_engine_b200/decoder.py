@@ -183,7 +183,7 @@ class DecoderModel:
         if not self.state:
             raise RuntimeError("model_init returned no state")
         self.tp_fused = False
-        if G > 1 and tp_fused and tensor_gemm:
+        if G > 1 and tp_fused and tensor_gemm and batch <= 32 and h % 16 == 0:
             # hand every rank's partial-sum block to every other rank (64-byte IPC handles over torch.distributed)
             import torch.distributed as dist
             buf = ctypes.create_string_buffer(64)

@@ -32,6 +32,12 @@ class ModelConfig(ctypes.Structure):
                                        "use_graph", "max_prefill", "use_tensor_gemm", "stream_sink", "stream_window", "kv_int8")] + [("rms_eps", c_float)]
 
 
+class TpGroup(ctypes.Structure):
+    """Mirror of ``mynn_b200_tp_group`` (include/mynn_b200.h)."""
+
+    _fields_ = [("blocks", c_void_p * 8), ("rank", c_int32), ("world", c_int32), ("max_rows", c_int32), ("hidden", c_int32)]
+
+
 # name -> (restype, argtypes); every symbol declared in include/mynn_b200.h
 SIGNATURES = {
     "mynn_b200_last_error": (c_char_p, []),
@@ -82,6 +88,11 @@ SIGNATURES = {
     "mynn_b200_model_stream": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
     "mynn_b200_model_tp_export": (c_int, [c_void_p, c_void_p]),
     "mynn_b200_model_tp_attach": (c_int, [c_void_p, c_void_p]),
+    "mynn_b200_tp_block_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "mynn_b200_tp_dequant_matmul_scatter": (c_int, [c_void_p, POINTER(TpGroup), c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t]),
+    "mynn_b200_tp_reduce_norm_gather": (c_int, [c_void_p, POINTER(TpGroup), c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int]),
+    "mynn_b200_tp_dequant_matmul_gathered": (c_int, [c_void_p, POINTER(TpGroup), c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t]),
+    "mynn_b200_tp_check": (c_int, [c_void_p, POINTER(TpGroup)]),
     "mynn_b200_launch_count": (c_int64, []),
     "alloc_pinned": (c_void_p, [c_size_t]),
     "free_pinned": (None, [c_void_p]),

@@ -7,6 +7,8 @@ tensors and the call raises otherwise.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import ffi
@@ -346,3 +348,57 @@ def argmax_last(logits):
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     ffi.check(ffi.lib().mynn_b200_argmax_last(_stream(), _ptr(out), _ptr(logits), rows, v, _dt(logits)))
     return out
+
+
+# ---- fused tensor-parallel operators (one TpGroup per rank; see include/mynn_b200.h) ----------------------------------
+class TpGroup:
+    """One rank's view of a tensor-parallel group: ``blocks`` are the uint8 CUDA tensors of every rank's shared block as this
+    process sees them (zeroed, ``tp_block_bytes`` each; blocks[rank] is the rank's own)."""
+
+    def __init__(self, blocks, rank: int, max_rows: int, hidden: int):
+        self.blocks, self.rank, self.world, self.max_rows, self.hidden = list(blocks), rank, len(blocks), max_rows, hidden
+        self.c = ffi.TpGroup()
+        for i, b in enumerate(self.blocks):
+            self.c.blocks[i] = _ptr(b)
+        self.c.rank, self.c.world, self.c.max_rows, self.c.hidden = rank, self.world, max_rows, hidden
+
+
+def tp_block_bytes(max_rows: int, hidden: int, world: int) -> int:
+    return ffi.lib().mynn_b200_tp_block_bytes(max_rows, hidden, world)
+
+
+def tp_dequant_matmul_scatter(group: TpGroup, buffer: int, act, wq, scale, workspace="auto"):
+    """Row-parallel DequantMatMul of this rank's K shard; the f32 partial rows go to the ranks that own them."""
+    n, k = wq.shape
+    m = act.numel() // k
+    if n != group.hidden or scale.dtype != torch.float32:
+        raise ValueError("scatter: wq must have `hidden` rows and an f32 scale")
+    if isinstance(workspace, str):
+        workspace = dequant_matmul_workspace(m, n, k, act.device)
+    ffi.check(ffi.lib().mynn_b200_tp_dequant_matmul_scatter(_stream(), ctypes.byref(group.c), buffer, _ptr(act), _ptr(wq), _ptr(scale), m, k,
+                                                            _dt(act), _ptr(workspace), workspace.numel()))
+
+
+def tp_reduce_norm_gather(group: TpGroup, buffer: int, producer_k: int, x, weight, eps: float):
+    """Finish the rows this rank owns (sum of partials, residual add into ``x``, RMSNorm) and deliver them to every rank."""
+    m = x.numel() // group.hidden
+    ffi.check(ffi.lib().mynn_b200_tp_reduce_norm_gather(_stream(), ctypes.byref(group.c), buffer, producer_k, _ptr(x),
+                                                        None if weight is None else _ptr(weight), float(eps), m, _dt(x)))
+
+
+def tp_dequant_matmul_gathered(group: TpGroup, wq, scale, m: int, out=None, workspace="auto"):
+    """Column-parallel DequantMatMul over the rows delivered by the last ``tp_reduce_norm_gather``."""
+    n, k = wq.shape
+    if k != group.hidden:
+        raise ValueError("gathered: K must equal the group's hidden size")
+    if out is None:
+        out = torch.empty((m, n), dtype=scale.dtype, device=wq.device)
+    if isinstance(workspace, str):
+        workspace = dequant_matmul_workspace(m, n, k, wq.device)
+    ffi.check(ffi.lib().mynn_b200_tp_dequant_matmul_gathered(_stream(), ctypes.byref(group.c), _ptr(out), _ptr(wq), _ptr(scale), m, n,
+                                                             _dt(scale), _ptr(workspace), workspace.numel()))
+    return out
+
+
+def tp_check(group: TpGroup):
+    ffi.check(ffi.lib().mynn_b200_tp_check(_stream(), ctypes.byref(group.c)))
