@@ -15,7 +15,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmynn_b200.so")
-SOURCES = ["runtime.cu", "dequant_gemm.cu", "i8_gemm.cu", "i8_gemm_prefill.cu", "w8a8.cu", "attention.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "kv_int8.cu", "streaming_kv.cu", "glue.cu", "comm.cu", "tp_fused.cu", "model.cu"]
+SOURCES = ["runtime.cu", "dequant_gemm.cu", "i8_gemm.cu", "gemv_lean.cu", "i8_gemm_prefill.cu", "w8a8.cu", "attention.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "kv_int8.cu", "streaming_kv.cu", "glue.cu", "comm.cu", "tp_fused.cu", "model.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-DMYNN_COMPILED_ARCH=100"]
 

@@ -716,6 +716,8 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
 int i8_gemm_launch_tp(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
                       int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes, const I8Tp *tp,
                       const int8_t *limbs_ext, const float *ascale_ext) {
+    if (!tp && !limbs_ext && gemv_lean_supported(M, N, K, wq))  // a few rows over a small matrix: no tensor-core set-up to amortise
+        return gemv_lean_launch(st, out, act, wq, scale, resid, M, N, K, act_dtype, out_dtype, workspace, workspace_bytes);
     const size_t need = limbs_ext ? 256 : i8_gemm_workspace_bytes(M, K);
     if (!workspace || workspace_bytes < need)
         return fail(MYNN_E_ARG, "dequant_matmul: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);

@@ -13,6 +13,11 @@ int i8_gemm_limb_rows(int M);  // rows of the limb matrix for M activation rows 
 bool i8_gemm_supported(int M, int N, int K, const void *wq, int act_dtype, int out_dtype);
 int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
                    int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes);
+// Lean kernel for at most 4 activation rows over a small weight matrix (gemv_lean.cu): same workspace contract and
+// bit-identical results; i8_gemm_launch dispatches to it.
+bool gemv_lean_supported(int M, int N, int K, const void *wq);
+int gemv_lean_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid, int M, int N,
+                     int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes);
 struct I8Tp;  // tp_fused.cuh
 int i8_gemm_launch_tp(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
                       int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes, const I8Tp *tp,
