@@ -322,6 +322,99 @@ dequant_gemv_kn_kernel(OutT *out, const ActT *act, const int8_t *wq, const OutT 
     }
 }
 
+// [K,N] layout, the tuned form: the literal single-op graph DequantizeLinear(W [K,N], per-column scale) -> MatMul, which the
+// engine runs unfused.  A thread owns 16 adjacent columns, i.e. one 128-bit load per k row (a warp reads 512 contiguous
+// bytes); a CTA of 16 warps covers 512 columns x a k range in which every lane issues all its loads (up to 16) before it
+// waits for anything; the k dimension is split over a cluster of 8 CTAs and reduced through distributed shared memory in a
+// fixed order, so the result does not depend on timing.  int8 -> f32 is exact (byte-permute into the mantissa of 2^23,
+// one subtraction), the products accumulate in f32 as in the engine's kernels.
+// grid (ceil(N / 512), 8, M), cluster (1, 8, 1), block 512.  N % 16 == 0, wq 16-byte aligned.
+constexpr int kKnThreads = 512, kKnCols = 512, kKnSplit = 8, kKnRowsPerWarp = 16;
+
+template <typename ActT, typename OutT>
+__global__ void __launch_bounds__(kKnThreads, 1)
+dequant_gemv_kn_split_kernel(OutT *out, const ActT *act, const int8_t *wq, const OutT *scale, int N, int K) {
+    __shared__ float part[kKnThreads / 32][kKnCols + 16];  // per-warp partial sums of the CTA's 512 columns (padded rows)
+    __shared__ float cta_part[kKnCols];
+    __shared__ float act_s[kKnThreads / 32 * kKnRowsPerWarp];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m = blockIdx.z, rank = blockIdx.y;
+    const int n0 = blockIdx.x * kKnCols + lane * 16;
+    const bool col_live = n0 < N;
+    // this CTA's k range, and inside it this warp's rows
+    const int per_cta = (K + kKnSplit - 1) / kKnSplit;
+    const int k_beg = rank * per_cta, k_end = min(K, k_beg + per_cta);
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) acc[i] = 0.f;
+    for (int kb = k_beg; kb < k_end; kb += (kKnThreads / 32) * kKnRowsPerWarp) {  // one pass when K <= 8 * 256
+        const int k0 = kb + warp * kKnRowsPerWarp;
+        uint4 w[kKnRowsPerWarp];
+#pragma unroll
+        for (int r = 0; r < kKnRowsPerWarp; r++)
+            w[r] = (col_live && k0 + r < k_end) ? ld_stream_16(wq + (size_t)(k0 + r) * N + n0) : make_uint4(0u, 0u, 0u, 0u);
+        __syncthreads();  // act_s of the previous pass has been read
+        if (lane < kKnRowsPerWarp) act_s[warp * kKnRowsPerWarp + lane] = k0 + lane < k_end ? to_f32<ActT>(act[(size_t)m * K + k0 + lane]) : 0.f;
+        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < kKnRowsPerWarp; r++) {
+            const float a = act_s[warp * kKnRowsPerWarp + r];
+            const uint32_t ww[4] = {w[r].x ^ 0x80808080u, w[r].y ^ 0x80808080u, w[r].z ^ 0x80808080u, w[r].w ^ 0x80808080u};
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    // 0x4B0000bb is the float 2^23 + bb; with bb = byte + 128 the difference to 2^23 + 128 is the signed byte
+                    const float f = __uint_as_float(__byte_perm(ww[q], 0x4B000000u, 0x7650 + b)) - 8388736.0f;
+                    acc[4 * q + b] = fmaf(a, f, acc[4 * q + b]);
+                }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i += 4)
+        *reinterpret_cast<float4 *>(&part[warp][lane * 16 + i]) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+    __syncthreads();
+    {
+        float s = 0.f;
+#pragma unroll
+        for (int w_ = 0; w_ < kKnThreads / 32; w_++) s += part[w_][threadIdx.x];
+        cta_part[threadIdx.x] = s;
+    }
+    cluster.sync();
+    // rank r finishes columns [64 r, 64 r + 64) of the 512: the eight CTAs' sums in rank order, then the column scale
+    if (threadIdx.x < kKnCols / kKnSplit) {
+        const int c = rank * (kKnCols / kKnSplit) + threadIdx.x;
+        const int n = blockIdx.x * kKnCols + c;
+        float v[kKnSplit];
+#pragma unroll
+        for (int rr = 0; rr < kKnSplit; rr++) v[rr] = cluster.map_shared_rank(cta_part, rr)[c];
+        float s = 0.f;
+#pragma unroll
+        for (int rr = 0; rr < kKnSplit; rr++) s += v[rr];
+        if (n < N) out[(size_t)m * N + n] = from_f32<OutT>(s * to_f32<OutT>(scale[n]));
+    }
+    cluster.sync();  // keep shared memory alive until every peer has read it
+}
+
+template <typename ActT, typename OutT>
+static int launch_kn_split(cudaStream_t st, OutT *out, const ActT *act, const int8_t *wq, const OutT *scale, int M, int N, int K) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + kKnCols - 1) / kKnCols, kKnSplit, M);
+    cfg.blockDim = dim3(kKnThreads, 1, 1);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = kKnSplit;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MYNN_CUDA_OK(cudaLaunchKernelEx(&cfg, dequant_gemv_kn_split_kernel<ActT, OutT>, out, act, wq, scale, N, K));
+    MYNN_LAUNCH_OK("dequant_gemv_kn_split_kernel");
+    return MYNN_OK;
+}
+
 static int pick_ksplit(int row_tiles, int steps) {
     // Every CTA pays a fixed prologue and a cluster reduction, so split K only until there is about one CTA per
     // SM (148), keep at least 8 k64 steps (two stages) per CTA, and stay within the portable cluster size of 8.
@@ -364,6 +457,8 @@ static int dequant_matmul_typed(cudaStream_t st, OutT *out, const ActT *act, con
         if (cols <= 16) return launch_stream<ActT, OutT, 2>(st, out, act, wq, scale, resid, M, N, K, g_ksplit_override);
         return launch_stream<ActT, OutT, 4>(st, out, act, wq, scale, resid, M, N, K, g_ksplit_override);
     }
+    if (w_layout == MYNN_W_KN && N % 16 == 0 && ((uintptr_t)wq % 16 == 0) && resid == nullptr && M <= 4 && K >= 64)
+        return launch_kn_split<ActT, OutT>(st, out, act, wq, scale, M, N, K);
     if (w_layout == MYNN_W_KN && N % 4 == 0 && ((uintptr_t)wq % 4 == 0) && resid == nullptr) {
         dequant_gemv_kn_kernel<ActT, OutT><<<dim3((N + 127) / 128, M), 256, 0, st>>>(out, act, wq, scale, N, K);
         MYNN_LAUNCH_OK("dequant_gemv_kn_kernel");

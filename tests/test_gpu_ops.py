@@ -158,6 +158,26 @@ def test_dequant_matmul_config1_both_layouts():
     assert rel_err(to_np(ops.dequant_matmul(dev(act), w_nk, dev(scale), axis=0, workspace=None)), want) <= 1e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(1, 5632, 2048), (2, 1040, 512), (1, 16, 64), (4, 528, 4112), (1, 2048, 72), (3, 100, 50)])
+def test_dequant_matmul_kn_layout_vs_oracle(dtype, m, n, k):
+    """The [K,N] / axis-1 form (per-column scale): the cluster-split kernel for N % 16 == 0 (column groups that are partly
+    empty, k ranges that do not divide by the 8-way split, more than one pass per CTA) and the plain kernels otherwise."""
+    rng = np.random.default_rng(m + n + k)
+    w_kn = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    scale = torch.from_numpy(rng.uniform(0.002, 0.02, size=n).astype(np.float32)).to(dtype)
+    act = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype)
+    want = R.dequant_matmul_variant_a(act.float().numpy(), np.ascontiguousarray(w_kn.T), scale.float().numpy())
+    out = ops.dequant_matmul(act.cuda(), dev(w_kn), scale.cuda(), axis=1)
+    assert rel_err(to_np(out), want) <= (1e-5 if dtype == torch.float32 else 1e-2)
+    # one-hot rows read single weights back exactly: column indexing of weights and scales
+    hot = torch.zeros((1, k), dtype=dtype)
+    hot[0, k // 3] = 1.0
+    got = to_np(ops.dequant_matmul(hot.cuda(), dev(w_kn), scale.cuda(), axis=1))[0]
+    exact = R.store_round(scale.float().numpy() * w_kn[k // 3].astype(np.float32), {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}[dtype])
+    assert np.array_equal(got, exact)
+
+
 def test_weight_bytes_and_scale_indexing_bit_exact():
     """One-hot activations read single weights back: out[n] = scale[n] * wq[n,k0] must be exact in f32, for every
     row n (scale indexing) and several k0 (byte position inside the 16-byte lane loads)."""
