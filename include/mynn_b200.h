@@ -212,6 +212,20 @@ int mynn_b200_attention_ring(void *stream, void *out, const void *q, const void 
                              int ring_sink, int ring_window, int ring_start, int dtype, void *workspace,
                              size_t workspace_bytes);
 
+/* Attention with every streaming operand of the engine's Attention node (src/graph/operator.rs:1024-1042; builder
+ * `attention_streaming`, crates/llm/src/builder.rs:526-568): k/v in `dtype` (kv_int8 = 0, scales NULL) or int8 with per-row
+ * scales [B, Hkv, cache_seq_len] (kv_int8 = 1); the ring mapping of mynn_b200_attention_ring; and, when kv_position != NULL,
+ * the in-kernel key rotation of the `(streaming, quant_kv_cache)` graph branch (crates/llm/src/decoder.rs:314-326): the key
+ * of logical row r is multiplied by its scale and rotated in f32 at row kv_position[r] of the cos / sin tables
+ * ([positions, D], `dtype`), as the engine's kernels do it (cpp/attention.cuh:546-600 for one query row, :319-489 for
+ * several) -- kv_position (device int64) is indexed by the LOGICAL row.  Any Sq; with is_causal the bound of query row sq is
+ * active_seq_kv - Sq + sq + 1 logical rows.  Row-serial arithmetic as in the engine (4 warps per query row). */
+int mynn_b200_attention_streaming(void *stream, void *out, const void *q, const void *k, const void *v, const void *k_scale,
+                                  const void *v_scale, float scale, int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len,
+                                  int active_seq_kv, const int32_t *active_seq_kv_dev, int is_causal, int ring_sink,
+                                  int ring_window, int ring_start, const void *cos_table, const void *sin_table,
+                                  const int64_t *kv_position, int dtype, int kv_int8);
+
 /* RMSNorm over the last axis: y = x * rsqrt(mean(x^2) + eps) * w.  Replaces rms_norm (cpp/rms_norm.cuh:9-59). */
 int mynn_b200_rms_norm(void *stream, void *out, const void *x, const void *weight, float eps, int rows, int D,
                        int dtype);
@@ -285,7 +299,8 @@ typedef struct mynn_b200_model_config {
     int32_t use_tensor_gemm; /* 1: DequantMatMul on the tcgen05 int8 kernel (needs scratch); 0: mma.sync streaming kernel */
     int32_t stream_sink;     /* streaming (sink + ring) KV cache, the engine's `streaming_kv` option: the first stream_sink */
     int32_t stream_window;   /* tokens stay, the last stream_window tokens live in a ring; 0 = off.  Steps then go through
-                                mynn_b200_model_stream; sink + window <= max_seq_len; not combined with kv_int8 */
+                                mynn_b200_model_stream; sink + window <= max_seq_len.  With kv_int8 the keys are cached unrotated
+                                as int8 and rotated inside the attention kernel (mynn_b200_attention_streaming) */
     int32_t kv_int8;         /* 1: the engine's `quant_kv_cache` option: int8 K/V caches with one scale per cached token;
                                 session_state then holds FOUR buffers per layer: K int8, V int8, K scale, V scale */
     float rms_eps;

@@ -32,7 +32,7 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, defines: tuple = ()) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(HERE, "..", "include", "mynn_b200.h"))
     objdir = os.path.join(HERE, "build")
@@ -43,7 +43,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(objdir, src[:-3] + ".o")
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [_nvcc()] + NVCC_FLAGS + ["-D" + d for d in defines] + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             jobs.append(cmd)
 
     def run(cmd):
@@ -65,4 +65,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    # -DNAME[=value] arguments are passed to nvcc (e.g. -DMYNN_TUNING for the build with phase timestamps); use with --force
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, defines=tuple(a[2:] for a in sys.argv[1:] if a.startswith("-D"))))

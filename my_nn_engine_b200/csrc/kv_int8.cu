@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(64)
 rope_kv_append_q8_kernel(T *q_out, int8_t *k_cache, int8_t *v_cache, T *k_scale, T *v_scale, const T *q, const T *k,
                          const T *v, long long q_stride, long long k_stride, long long v_stride, const T *cos_t,
                          const T *sin_t, const int64_t *positions, int S, int Hq, int Hkv, int D, int cache_seq,
-                         const int32_t *past_len_dev, int slot0) {
+                         const int32_t *past_len_dev, int slot0, int rotate_k) {
     extern __shared__ float rowv[];  // D rotated / copied values
     __shared__ float wmax[2];
     pdl_trigger();
@@ -84,7 +84,7 @@ rope_kv_append_q8_kernel(T *q_out, int8_t *k_cache, int8_t *v_cache, T *k_scale,
     const bool is_k = slot < Hq + Hkv;
     const int h = is_k ? slot - Hq : slot - Hq - Hkv;
     float mx = 0.f;
-    if (is_k) {
+    if (is_k && rotate_k) {
         const long long pos = positions[s];
         const T *cr = cos_t + (size_t)pos * D, *sr = sin_t + (size_t)pos * D;
         const T *src = k + (size_t)row * k_stride + (size_t)h * D;
@@ -96,8 +96,8 @@ rope_kv_append_q8_kernel(T *q_out, int8_t *k_cache, int8_t *v_cache, T *k_scale,
             rowv[j + half] = hi;
             mx = fmaxf(mx, fmaxf(fabsf(lo), fabsf(hi)));
         }
-    } else {
-        const T *src = v + (size_t)row * v_stride + (size_t)h * D;
+    } else {  // V, or K of a streaming cache (cached as the projection left it, rotated when it is read)
+        const T *src = is_k ? k + (size_t)row * k_stride + (size_t)h * D : v + (size_t)row * v_stride + (size_t)h * D;
         for (int j = threadIdx.x; j < D; j += blockDim.x) {
             const float x = to_f32<T>(src[j]);
             rowv[j] = x;
@@ -119,7 +119,7 @@ int launch_rope_kv_append_q8(cudaStream_t st, int dtype, void *q_out, void *k_ca
                              void *v_scale, const void *q, const void *k, const void *v, long long q_stride,
                              long long k_stride, long long v_stride, const void *cos_t, const void *sin_t,
                              const int64_t *positions, int B, int S, int Hq, int Hkv, int D, int cache_seq,
-                             const int32_t *past_len_dev) {
+                             const int32_t *past_len_dev, int rotate_k) {
     if (B * S == 0) return MYNN_OK;
     if (D > 4096) return fail(MYNN_E_UNSUPPORTED, "rope_kv_append_q8: head dim %d too large", D);
     // prefill chunks: the q heads (most of the slots) go through the 128-bit RoPE kernel, this one keeps the k / v slots
@@ -134,7 +134,7 @@ int launch_rope_kv_append_q8(cudaStream_t st, int dtype, void *q_out, void *k_ca
         MYNN_CUDA_OK(launch_pdl(rope_kv_append_q8_kernel<T>, dim3(B * S, Hq + 2 * Hkv - slot0), dim3(64), (size_t)D * 4, st, (T *)q_out,
                                 (int8_t *)k_cache, (int8_t *)v_cache, (T *)k_scale, (T *)v_scale, (const T *)q, (const T *)k,
                                 (const T *)v, q_stride, k_stride, v_stride, (const T *)cos_t, (const T *)sin_t, positions, S,
-                                Hq, Hkv, D, cache_seq, past_len_dev, slot0));
+                                Hq, Hkv, D, cache_seq, past_len_dev, slot0, rotate_k));
     });
     MYNN_LAUNCH_OK("rope_kv_append_q8_kernel");
     return MYNN_OK;

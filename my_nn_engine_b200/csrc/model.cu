@@ -199,7 +199,17 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
             kb = k_;
             vb = v_;
         }
-        if (c.kv_int8) {
+        if (c.kv_int8 && c.stream_window > 0) {
+            // streaming int8 cache: K is quantized UNROTATED into its slot (past_dev holds the slot); the attention kernel
+            // rotates every live key in f32 at the position the per-slot table gives (the engine's in-kernel RoPE operands,
+            // crates/llm/src/decoder.rs:314-326).  The live rows are the slots [0, active): no ring remapping is needed, the
+            // softmax does not depend on the order of the rows, and a chunk never evicts, so a causal bound by slot is the bound
+            // by rank.
+            RC(launch_rope_kv_append_q8(st, dt, m.q_rot, L.kc, L.vc, L.ksc, L.vsc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
+                                        S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev, 0));
+            RC(launch_attention_streaming(st, m.attn, m.q_rot, L.kc, L.vc, L.ksc, L.vsc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
+                                          c.max_seq_len, m.active_dev, S > 1, 0, 0, 0, m.cos_t, m.sin_t, m.kvpos_dev, dt, 1, 1));
+        } else if (c.kv_int8) {
             RC(launch_rope_kv_append_q8(st, dt, m.q_rot, L.kc, L.vc, L.ksc, L.vsc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
                                         S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
             if (S >= 64 && m.k_deq &&
@@ -414,7 +424,7 @@ static int model_create(Model **out, void **initializer, void **session_state) {
                  o_pairs = take((size_t)c.batch * 8), o_pairs_all = take((size_t)c.batch * 8 * std::max(tp, 16)),
                  o_ws = take(m->attn_ws_bytes), o_gws = take(m->gemm_ws_bytes), o_part = take(tp > 1 ? R * H * 4 : 0),
                  o_kvpos = take(c.stream_window > 0 ? (size_t)c.max_seq_len * 8 : 0),
-                 o_krot = take(c.stream_window > 0 ? (size_t)c.batch * m->Hkv * c.max_seq_len * D * esz : 0);
+                 o_krot = take(c.stream_window > 0 && !c.kv_int8 ? (size_t)c.batch * m->Hkv * c.max_seq_len * D * esz : 0);
     const bool want_deq = c.kv_int8 && prefill >= 64 && c.dtype != MYNN_F32 && (D == 64 || D == 128);
     const size_t deq_bytes = want_deq ? (size_t)c.batch * m->Hkv * c.max_seq_len * D * esz : 0;
     const size_t o_kdeq = take(deq_bytes), o_vdeq = take(deq_bytes);
@@ -577,7 +587,6 @@ extern "C" int mynn_b200_model_configure(const mynn_b200_model_config *cfg) {
         return fail(MYNN_E_ARG, "model_configure: bad streaming cache (sink %d, window %d)", c.stream_sink, c.stream_window);
     if (c.stream_window > 0 && c.stream_sink + c.stream_window > c.max_seq_len)
         return fail(MYNN_E_ARG, "model_configure: sink %d + window %d exceed max_seq_len %d", c.stream_sink, c.stream_window, c.max_seq_len);
-    if (c.stream_window > 0 && c.kv_int8) return fail(MYNN_E_UNSUPPORTED, "model_configure: a streaming cache with int8 KV is not supported");
     g_cfg = c;
     g_cfg_set = true;
     return MYNN_OK;

@@ -19,13 +19,20 @@ int launch_rope_kv_append(cudaStream_t st, int dtype, void *q_out, void *k_cache
 int launch_rope_cache_rows(cudaStream_t st, int dtype, void *out, const void *x, const void *cos_t, const void *sin_t,
                            const int64_t *kv_position, int BH, int cache_seq, int D, int active_host, const int32_t *active_dev);
 
+// Attention with every streaming operand of the engine's Attention node (ring mapping, int8 cache with per-row scales, keys
+// rotated inside the kernel at kv_position[logical row]); see streaming_kv.cu.
+int launch_attention_streaming(cudaStream_t st, void *out, const void *q, const void *k, const void *v, const void *k_scale,
+                               const void *v_scale, float scale, int B, int Hq, int Hkv, int Sq, int D, int cache_seq, int active,
+                               const int32_t *active_dev, int causal, int rs, int rw, int r0, const void *cos_t, const void *sin_t,
+                               const int64_t *kv_position, int dtype, int kv_int8, int out_bshd);
+
 // The same step for an int8 KV cache: K (after RoPE and its store rounding) and V are quantized per token into
 // k_cache/v_cache int8 [B, Hkv, cache_seq, D] with their scales [B, Hkv, cache_seq] in the storage dtype.
 int launch_rope_kv_append_q8(cudaStream_t st, int dtype, void *q_out, void *k_cache, void *v_cache, void *k_scale,
                              void *v_scale, const void *q, const void *k, const void *v, long long q_stride,
                              long long k_stride, long long v_stride, const void *cos_t, const void *sin_t,
                              const int64_t *positions, int B, int S, int Hq, int Hkv, int D, int cache_seq,
-                             const int32_t *past_len_dev);
+                             const int32_t *past_len_dev, int rotate_k = 1);
 
 // Attention over an int8 KV cache (per-token scales), with the output-layout choice of launch_attention.
 int launch_attention_q8(cudaStream_t st, void *out, const void *q, const void *k, const void *v, const void *k_scale,

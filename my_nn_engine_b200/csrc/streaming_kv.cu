@@ -8,6 +8,8 @@
 // This file holds the two pieces that differ from the plain cache: the append through `ring_phys_index`
 // (src/codegen/cuda/cpp/common.cuh:55-60, kvcache_update.cuh:6-26) and the rotation of the live cache rows into a
 // scratch copy that the attention kernels then read (the ring walk itself is in attention.cu).
+#include <type_traits>
+
 #include "common.cuh"
 #include "ops_internal.cuh"
 
@@ -97,6 +99,138 @@ int launch_rope_cache_rows(cudaStream_t st, int dtype, void *out, const void *x,
     return MYNN_OK;
 }
 
+// Attention with ALL the streaming operands of the engine's Attention node (src/graph/operator.rs:1024-1042): an int8 or
+// 16/32-bit cache, per-row k/v scales, the ring mapping, and the cos / sin / kv_position operands that make the kernel rotate
+// every key on the fly: the `(streaming, quant_kv_cache)` branch of the decoder graph (crates/llm/src/decoder.rs:314-326).
+// The arithmetic follows the engine's kernels row by row (src/codegen/cuda/cpp/attention.cuh:495-606 and :319-489): the key of
+// logical row r is read from slot ring_phys_index(r), multiplied by its k_scale, rotated in f32 at table row kv_position[r]
+// (indexed by the LOGICAL row, as the engine's kernel does; never rounded), dotted with q; the softmax weight is multiplied by
+// v_scale before it meets v.  One CTA of 4 warps per query row (b, h, sq): the warps take kv rows in turn, each with its own
+// running maximum and sum, and are merged through shared memory.  D <= 32 * MAXE.
+constexpr int kStreamWarps = 4;
+
+template <typename T, typename TKV, int MAXE>
+__global__ void __launch_bounds__(kStreamWarps * 32)
+attention_streaming_kernel(T *out, const T *q, const TKV *k, const TKV *v, const T *k_scale, const T *v_scale, float scale, int Hq,
+                           int Hkv, int Sq, int D, int cache_seq, int active_host, const int32_t *active_dev, int is_causal,
+                           int ring_sink, int ring_window, int ring_start, const T *cos_t, const T *sin_t,
+                           const long long *kv_position, int out_bshd) {
+    __shared__ float sm_o[kStreamWarps][32 * MAXE];
+    __shared__ float sm_m[kStreamWarps], sm_s[kStreamWarps];
+    pdl_trigger();
+    pdl_wait();
+    const long long row = blockIdx.x;  // (b * Hq + h) * Sq + sq
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sq = (int)(row % Sq);
+    const long long bh = row / Sq;
+    const int h = (int)(bh % Hq), b = (int)(bh / Hq);
+    const int kvh = h / (Hq / Hkv), half = D >> 1;
+    const int active = min(active_dev ? *active_dev : active_host, cache_seq);
+    int bound = active;
+    if (is_causal) bound = min(bound, active - Sq + sq + 1);
+    const T *qp = q + (size_t)row * D;
+    const size_t kv_base = (size_t)(b * Hkv + kvh) * cache_seq;
+    constexpr bool QUANT = !std::is_same<T, TKV>::value;
+    float qr[MAXE], o[MAXE];
+#pragma unroll
+    for (int e = 0; e < MAXE; e++) {
+        const int d = lane + 32 * e;
+        qr[e] = d < D ? to_f32<T>(qp[d]) : 0.f;
+        o[e] = 0.f;
+    }
+    float m = -INFINITY, ssum = 0.f;
+    for (int lr = warp; lr < bound; lr += kStreamWarps) {
+        const int phys = ring_phys_index(lr, ring_sink, ring_window, ring_start);
+        const TKV *kp = k + (kv_base + phys) * D, *vp = v + (kv_base + phys) * D;
+        const float ks = QUANT ? to_f32<T>(k_scale[kv_base + phys]) : 1.0f;
+        const float vs = QUANT ? to_f32<T>(v_scale[kv_base + phys]) : 1.0f;
+        const long long pos = kv_position ? kv_position[lr] : 0;
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < MAXE; e++) {
+            const int d = lane + 32 * e;
+            if (d < D) {
+                float kv_ = (float)kp[d] * ks;
+                if (kv_position) {
+                    const int pair = d < half ? d + half : d - half;
+                    const float kpair = (float)kp[pair] * ks;
+                    const float c = to_f32<T>(cos_t[(size_t)pos * D + d]), s_ = to_f32<T>(sin_t[(size_t)pos * D + d]);
+                    kv_ = kv_ * c + (d < half ? -kpair : kpair) * s_;
+                }
+                dot += qr[e] * kv_;
+            }
+        }
+        const float qk = warp_sum(dot) * scale;
+        const float m_new = fmaxf(m, qk);
+        const float coeff = expf(m - m_new);
+        float score = expf(qk - m_new);
+        ssum = ssum * coeff + score;
+        if (QUANT) score *= vs;
+#pragma unroll
+        for (int e = 0; e < MAXE; e++) {
+            const int d = lane + 32 * e;
+            if (d < D) o[e] = o[e] * coeff + score * (float)vp[d];
+        }
+        m = m_new;
+    }
+#pragma unroll
+    for (int e = 0; e < MAXE; e++) sm_o[warp][lane + 32 * e] = o[e];
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_s[warp] = ssum;
+    }
+    __syncthreads();
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kStreamWarps; w++) mx = fmaxf(mx, sm_m[w]);
+    for (int d = threadIdx.x; d < D; d += kStreamWarps * 32) {
+        float L = 0.f, O = 0.f;
+        for (int w = 0; w < kStreamWarps; w++)
+            if (sm_m[w] > -INFINITY) {
+                const float f = expf(sm_m[w] - mx);
+                L += sm_s[w] * f;
+                O += sm_o[w][d] * f;
+            }
+        const size_t orow = out_bshd ? ((size_t)b * Sq + sq) * Hq + h : (size_t)row;  // [B, Sq, Hq, D] rows for a following o_proj
+        out[orow * D + d] = from_f32<T>(O / L);
+    }
+}
+
+template <typename T, typename TKV>
+static int launch_streaming_typed(cudaStream_t st, void *out, const void *q, const void *k, const void *v, const void *k_scale,
+                                  const void *v_scale, float scale, int B, int Hq, int Hkv, int Sq, int D, int cache_seq, int active,
+                                  const int32_t *active_dev, int causal, int rs, int rw, int r0, const void *cos_t, const void *sin_t,
+                                  const int64_t *kv_position, int out_bshd) {
+    const unsigned blocks = (unsigned)((long long)B * Hq * Sq);
+#define GEN(MAXE)                                                                                                                       \
+    MYNN_CUDA_OK(launch_pdl(attention_streaming_kernel<T, TKV, MAXE>, dim3(blocks), dim3(kStreamWarps * 32), 0, st, (T *)out, (const T *)q, \
+                            (const TKV *)k, (const TKV *)v, (const T *)k_scale, (const T *)v_scale, scale, Hq, Hkv, Sq, D, cache_seq, active, \
+                            active_dev, causal, rs, rw, r0, (const T *)cos_t, (const T *)sin_t, (const long long *)kv_position, out_bshd))
+    if (D <= 32) GEN(1);
+    else if (D <= 64) GEN(2);
+    else if (D <= 128) GEN(4);
+    else if (D <= 256) GEN(8);
+    else return fail(MYNN_E_UNSUPPORTED, "attention_streaming: head dim %d > 256", D);
+#undef GEN
+    MYNN_LAUNCH_OK("attention_streaming_kernel");
+    return MYNN_OK;
+}
+
+int launch_attention_streaming(cudaStream_t st, void *out, const void *q, const void *k, const void *v, const void *k_scale,
+                               const void *v_scale, float scale, int B, int Hq, int Hkv, int Sq, int D, int cache_seq, int active,
+                               const int32_t *active_dev, int causal, int rs, int rw, int r0, const void *cos_t, const void *sin_t,
+                               const int64_t *kv_position, int dtype, int kv_int8, int out_bshd) {
+#define GO(T)                                                                                                                          \
+    return kv_int8 ? launch_streaming_typed<T, int8_t>(st, out, q, k, v, k_scale, v_scale, scale, B, Hq, Hkv, Sq, D, cache_seq, active, \
+                                                       active_dev, causal, rs, rw, r0, cos_t, sin_t, kv_position, out_bshd)            \
+                   : launch_streaming_typed<T, T>(st, out, q, k, v, k_scale, v_scale, scale, B, Hq, Hkv, Sq, D, cache_seq, active,      \
+                                                  active_dev, causal, rs, rw, r0, cos_t, sin_t, kv_position, out_bshd)
+    if (dtype == MYNN_F32) GO(float);
+    if (dtype == MYNN_BF16) GO(__nv_bfloat16);
+    GO(__half);
+#undef GO
+}
+
 }  // namespace mynn
 
 using namespace mynn;
@@ -132,4 +266,26 @@ extern "C" int mynn_b200_rope_cache_rows(void *stream, void *out, const void *ca
     if (!out || !cache || !cos_table || !sin_table || !kv_position) return fail(MYNN_E_ARG, "rope_cache_rows: null pointer");
     return launch_rope_cache_rows((cudaStream_t)stream, dtype, out, cache, cos_table, sin_table, kv_position, BH, cache_seq_len, D,
                                   active_seq_kv, nullptr);
+}
+
+extern "C" int mynn_b200_attention_streaming(void *stream, void *out, const void *q, const void *k, const void *v, const void *k_scale,
+                                             const void *v_scale, float scale, int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len,
+                                             int active_seq_kv, const int32_t *active_seq_kv_dev, int is_causal, int ring_sink,
+                                             int ring_window, int ring_start, const void *cos_table, const void *sin_table,
+                                             const int64_t *kv_position, int dtype, int kv_int8) {
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || Sq < 0 || D <= 0 || (D & 1) || cache_seq_len < 0 || active_seq_kv < 0 || Hq % Hkv)
+        return fail(MYNN_E_ARG, "attention_streaming: bad shape");
+    if (!dtype_ok(dtype)) return fail(MYNN_E_ARG, "attention_streaming: bad dtype %d", dtype);
+    if (ring_sink < 0 || ring_window < 0 || ring_start < 0 || (ring_window > 0 && ring_start >= ring_window) ||
+        ring_sink + ring_window > cache_seq_len)
+        return fail(MYNN_E_ARG, "attention_streaming: bad ring (sink %d, window %d, start %d, cache %d)", ring_sink, ring_window, ring_start, cache_seq_len);
+    if (ring_window > 0 && active_seq_kv > ring_sink + ring_window)
+        return fail(MYNN_E_ARG, "attention_streaming: %d active rows exceed sink + window = %d", active_seq_kv, ring_sink + ring_window);
+    if (B == 0 || Sq == 0) return MYNN_OK;
+    if (!out || !q || !k || !v) return fail(MYNN_E_ARG, "attention_streaming: null pointer");
+    if (kv_int8 && (!k_scale || !v_scale)) return fail(MYNN_E_ARG, "attention_streaming: an int8 cache needs k_scale and v_scale");
+    if (kv_position && (!cos_table || !sin_table)) return fail(MYNN_E_ARG, "attention_streaming: kv_position needs the cos and sin tables");
+    return launch_attention_streaming((cudaStream_t)stream, out, q, k, v, k_scale, v_scale, scale, B, Hq, Hkv, Sq, D, cache_seq_len,
+                                      active_seq_kv, active_seq_kv_dev, is_causal, ring_sink, ring_window, ring_start, cos_table, sin_table,
+                                      kv_position, dtype, kv_int8, 0);
 }

@@ -107,13 +107,18 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_norm_gather_kernel(T *x,
                     acc.w += v[r].w;
                 }
             const float s4[4] = {acc.x, acc.y, acc.z, acc.w};
+            T xv[4];  // four residual elements with one access each way
+            if constexpr (sizeof(T) == 2) *reinterpret_cast<uint2 *>(xv) = *reinterpret_cast<const uint2 *>(xrow + i);
+            else *reinterpret_cast<float4 *>(xv) = *reinterpret_cast<const float4 *>(xrow + i);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const float t = round_store<T>(to_f32<T>(xrow[i + j]) + round_store<T>(s4[j]));
-                xrow[i + j] = from_f32<T>(t);
+                const float t = round_store<T>(to_f32<T>(xv[j]) + round_store<T>(s4[j]));
+                xv[j] = from_f32<T>(t);
                 row_s[i + j] = t;
                 ss += t * t;
             }
+            if constexpr (sizeof(T) == 2) *reinterpret_cast<uint2 *>(xrow + i) = *reinterpret_cast<const uint2 *>(xv);
+            else *reinterpret_cast<float4 *>(xrow + i) = *reinterpret_cast<const float4 *>(xv);
         }
         if (w != nullptr) {
             ss = warp_sum(ss);

@@ -350,6 +350,22 @@ def argmax_last(logits):
     return out
 
 
+def attention_streaming(q, k, v, scale: float, active_seq_kv: int, is_causal: bool = False, ring=(0, 0, 0), k_scale=None, v_scale=None,
+                        cos_table=None, sin_table=None, kv_position=None, out=None):
+    """``Attention`` with its streaming operands: ring = (sink, window, start); k/v int8 with k_scale/v_scale, or of q's dtype;
+    kv_position (int64 CUDA tensor, indexed by logical row) switches the in-kernel key rotation on."""
+    b, hq, sq, d = q.shape
+    hkv, sk = k.shape[1], k.shape[2]
+    if out is None:
+        out = torch.empty_like(q)
+    q8 = k.dtype == torch.int8
+    ffi.check(ffi.lib().mynn_b200_attention_streaming(_stream(), _ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(k_scale), _ptr(v_scale),
+                                                      float(scale), b, hq, hkv, sq, d, sk, int(active_seq_kv), None, int(is_causal),
+                                                      ring[0], ring[1], ring[2], _ptr(cos_table), _ptr(sin_table), _ptr(kv_position),
+                                                      _dt(q), int(q8)))
+    return out
+
+
 # ---- fused tensor-parallel operators (one TpGroup per rank; see include/mynn_b200.h) ----------------------------------
 class TpGroup:
     """One rank's view of a tensor-parallel group: ``blocks`` are the uint8 CUDA tensors of every rank's shared block as this

@@ -55,8 +55,8 @@ class OracleLlama:
         # c_attention: run the attention recurrence in the C restatement (oracle.c, the same scalar loop as ref_ops.attention,
         # row-parallel) instead of numpy; for long contexts, where the numpy form takes seconds per call
         self.c_attention = c_attention and not streaming
-        if streaming and kv_int8:
-            raise ValueError("streaming with an int8 cache is not modelled")
+        # streaming + kv_int8: the (streaming, quant_kv_cache) branch of the engine's graph (crates/llm/src/decoder.rs:314-326):
+        # K is quantized UNROTATED into the int8 ring and rotated inside the attention kernel, in f32, at its recency rank
         self.w = {}
         for name, arr in weights.items():
             if name.endswith(".scale"):
@@ -112,14 +112,26 @@ class OracleLlama:
             v = self._linear(n1, p + "self_attn.v_proj.weight").reshape(b, s, c.n_kv_heads, c.head_dim).transpose(0, 2, 1, 3)
             q = self._st(R.rope(q, cos_r, sin_r))
             if stream is not None:
-                for t, slot in enumerate(stream["slots"]):  # keys are cached as the projection left them
-                    self.k_cache[l][:, :, slot, :] = k[:, :, t, :]
-                    self.v_cache[l][:, :, slot, :] = v[:, :, t, :]
+                if not self.kv_int8:
+                    for t, slot in enumerate(stream["slots"]):  # keys are cached as the projection left them
+                        self.k_cache[l][:, :, slot, :] = k[:, :, t, :]
+                        self.v_cache[l][:, :, slot, :] = v[:, :, t, :]
                 kp = stream["kv_position"]
-                k_rot = self._st(R.rope(self.k_cache[l], self.cos[kp], self.sin[kp]))
                 sink, window = self.streaming
-                a = self._st(R.attention_ring(q, k_rot, self.v_cache[l], scale, stream["active"], sink, window,
-                                              stream["ring_start"], is_causal=is_prefill))
+                if self.kv_int8:
+                    # slots are written like any quantized append; the attention then walks the live slots [0, active) with
+                    # the per-slot position table and no ring remapping (the softmax does not depend on the row order, and
+                    # chunks never evict, so a causal bound by slot equals the bound by rank)
+                    for t, slot in enumerate(stream["slots"]):
+                        R.quantizing_kv_cache_update(self.k_cache[l], self.k_scale[l], k[:, :, t:t + 1, :], slot, self.dtype)
+                        R.quantizing_kv_cache_update(self.v_cache[l], self.v_scale[l], v[:, :, t:t + 1, :], slot, self.dtype)
+                    a = self._st(R.attention_streaming(q, self.k_cache[l], self.v_cache[l], scale, stream["active"], 0, 0, 0,
+                                                       is_causal=is_prefill, k_scale=self.k_scale[l], v_scale=self.v_scale[l],
+                                                       cos_table=self.cos, sin_table=self.sin, kv_position=kp))
+                else:
+                    k_rot = self._st(R.rope(self.k_cache[l], self.cos[kp], self.sin[kp]))
+                    a = self._st(R.attention_ring(q, k_rot, self.v_cache[l], scale, stream["active"], sink, window,
+                                                  stream["ring_start"], is_causal=is_prefill))
                 a = a.transpose(0, 2, 1, 3).reshape(b, s, c.n_heads * c.head_dim)
                 o = self._linear(a, p + "self_attn.o_proj.weight")
                 x = self._st(x + o)

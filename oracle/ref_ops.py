@@ -272,7 +272,7 @@ def attention_ring(q, k, v, scale, active_seq_kv, ring_sink, ring_window, ring_s
     return attention(q, kg, vg, scale, active, is_causal=is_causal)
 
 
-def streaming_state(stream_pos: int, n_new: int, sink: int, window: int, max_seq_len: int):
+def streaming_state(stream_pos: int, n_new: int, sink: int, window: int, max_seq_len: int, engine_literal: bool = False):
     """Host-side index math of a streaming (sink + ring) step that appends tokens stream_pos .. stream_pos+n_new-1.
 
     Token P lives in slot P while P < sink + window... precisely: slot(P) = P for P < sink, else sink + (P - sink) % window.
@@ -284,10 +284,32 @@ def streaming_state(stream_pos: int, n_new: int, sink: int, window: int, max_seq
     (crates/llm/src/session.rs:539-635: identity slots, ring_start 0, kv_position = slot).  After that point the
     engine's host code derives ring_start and kv_position from the position BEFORE the append and reuses ring_start for
     the write slot, which sends the new row to slot sink + 2*((P-sink) % window) % window and rotates the newest key as if
-    it were the oldest; that regime is not covered by any test of the engine.  This function follows the layout the
-    engine documents (sink rows fixed, ring holds the last ``window`` tokens in age order) consistently instead."""
+    it were the oldest; that regime is not covered by any test of the engine.  By default this function follows the layout
+    the engine documents (sink rows fixed, ring holds the last ``window`` tokens in age order) consistently instead;
+    ``engine_literal=True`` reproduces the engine's host code line by line (streaming_decode_inputs / streaming_prefill_inputs /
+    streaming_kv_position, and the write slot its KVCacheUpdate derives from them), so that the two can be compared."""
     max_active = sink + window
     after = stream_pos + n_new
+    if engine_literal:
+        if n_new == 1:  # streaming_decode_inputs (crates/llm/src/session.rs:571-598)
+            ring_start = 0 if stream_pos < max_active else (stream_pos - sink) % window
+            table_pos = stream_pos  # streaming_kv_position is called with the position BEFORE the append
+        else:           # streaming_prefill_inputs (:539-569)
+            ring_start = 0 if after <= max_active else (after - sink) % window
+            table_pos = after
+        active = min(after, max_active)
+        q_positions = np.minimum(np.arange(stream_pos, after), max_active - 1).astype(np.int64)
+        # KVCacheUpdate writes logical row offset + t = stream_pos + t through ring_phys_index with THIS ring_start
+        slots = [ring_phys_index(stream_pos + t, sink, window, ring_start) for t in range(n_new)]
+        # streaming_kv_position (:606-635)
+        rs = 0 if table_pos < max_active else (table_pos - sink) % window
+        active_in_ring = min(max(table_pos - sink, 0), window)
+        kv_position = np.arange(max_seq_len, dtype=np.int64)
+        for slot in range(sink, min(max_active, max_seq_len)):
+            rel_age = ((slot - sink) + window - rs) % window
+            if rel_age < active_in_ring:
+                kv_position[slot] = sink + rel_age
+        return dict(slots=slots, q_positions=q_positions, active=active, ring_start=ring_start, kv_position=kv_position)
     slots = [p if p < sink else sink + (p - sink) % window for p in range(stream_pos, after)]
     active = min(after, max_active)
     ring_start = 0 if after <= max_active else (after - sink) % window
@@ -300,6 +322,52 @@ def streaming_state(stream_pos: int, n_new: int, sink: int, window: int, max_seq
     if after > max_active:  # a chunk that evicts: every query row sits at the end of what it can see
         q_positions = np.minimum(q_positions, max_active - 1)
     return dict(slots=slots, q_positions=q_positions, active=active, ring_start=ring_start, kv_position=kv_position)
+
+
+def attention_streaming(q, k, v, scale, active_seq_kv, ring_sink=0, ring_window=0, ring_start=0, is_causal=False, k_scale=None,
+                        v_scale=None, cos_table=None, sin_table=None, kv_position=None):
+    """The CUDA backend's attention with all its streaming operands, restated literally (src/codegen/cuda/cpp/attention.cuh:
+    495-606 for one query row, :319-489 for several): logical rows 0..bound-1 are visited in order; row r is read from slot
+    ring_phys_index(r); with an int8 cache the row is multiplied by its k_scale first; with kv_position given the key is then
+    rotated in f32 at table row kv_position[r] -- indexed by the LOGICAL row r, as the kernel does --
+    k_rot[i] = k[i] * cos[pos, i] + sign * k[pair(i)] * sin[pos, i] (sign -1 for the first half), and never rounded; the
+    softmax weight of a row is multiplied by its v_scale before it meets v.  The only CPU-side restatement of these operands:
+    the engine's CPU backend ignores them (crates/llm/tests/run_llm.rs:76-78)."""
+    q = np.asarray(q, dtype=np.float32)
+    b, hq, sq, d = q.shape
+    hkv = k.shape[1]
+    group = hq // hkv
+    half = d // 2
+    active = int(active_seq_kv)
+    out = np.zeros_like(q)
+    for row_q in range(sq):
+        bound = min(active, active - sq + row_q + 1) if is_causal else active
+        m = np.full((b, hq), -np.inf, np.float32)
+        ssum = np.zeros((b, hq), np.float32)
+        o = np.zeros((b, hq, d), np.float32)
+        for r in range(bound):
+            phys = ring_phys_index(r, ring_sink, ring_window, ring_start)
+            kr = np.repeat(np.asarray(k[:, :, phys, :]).astype(np.float32), group, axis=1)
+            vr = np.repeat(np.asarray(v[:, :, phys, :]).astype(np.float32), group, axis=1)
+            if k_scale is not None:
+                kr = kr * np.repeat(np.asarray(k_scale[:, :, phys], dtype=np.float32), group, axis=1)[..., None]
+            if kv_position is not None:
+                pos = int(kv_position[r])
+                c, s_ = np.asarray(cos_table[pos], np.float32), np.asarray(sin_table[pos], np.float32)
+                pair = np.concatenate([-kr[..., half:], kr[..., :half]], axis=-1)
+                kr = kr * c + pair * s_
+            qk = (q[:, :, row_q, :] * kr).sum(axis=-1, dtype=np.float32) * np.float32(scale)
+            m_new = np.maximum(m, qk)
+            score = np.exp(qk - m_new).astype(np.float32)
+            coeff = np.exp(m - m_new).astype(np.float32)
+            ssum = ssum * coeff + score
+            if v_scale is not None:
+                score = score * np.repeat(np.asarray(v_scale[:, :, phys], dtype=np.float32), group, axis=1)
+            o = o * coeff[..., None] + score[..., None] * vr
+            m = m_new
+        with np.errstate(invalid="ignore", divide="ignore"):
+            out[:, :, row_q, :] = o / ssum[..., None]
+    return out
 
 
 def quantizing_kv_cache_update(cache: np.ndarray, scale: np.ndarray, new: np.ndarray, offset: int, scale_dtype: str = "bf16"):

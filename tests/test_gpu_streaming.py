@@ -125,6 +125,73 @@ def test_streaming_decoder_matches_oracle_across_eviction(dtype, batch, prefill,
     model.close()
 
 
+@pytest.mark.parametrize("dtype,batch,prefill,use_graph", [("bf16", 1, 0, True), ("f32", 2, 0, False), ("bf16", 3, 6, True), ("f16", 2, 5, True)])
+def test_streaming_decoder_with_int8_cache_matches_oracle_across_eviction(dtype, batch, prefill, use_graph):
+    """The engine's (streaming, quant_kv_cache) graph branch: keys quantized unrotated into the int8 ring and rotated inside the
+    attention kernel at their recency rank.  sink 3 + window 9, 30 tokens (one and a half wraps)."""
+    from my_nn_engine_b200.decoder import DecoderModel
+    from my_nn_engine_b200.quantize import random_llama_state
+    state = random_llama_state(MID, seed=11)
+    sink, window = 3, 9
+    oracle = OracleLlama(LlamaConfig.from_hf(MID), to_oracle_weights(state, dtype), dtype, 16, batch, streaming=(sink, window), kv_int8=True)
+    model = DecoderModel(MID, state, dtype=dtype, max_seq_len=16, batch=batch, output="logits", use_graph=use_graph,
+                         max_prefill=prefill, streaming=(sink, window), kv_int8=True)
+    rng = np.random.default_rng(batch + 7)
+    toks = rng.integers(0, MID["vocab_size"], size=(batch, 30))
+    tol = {"bf16": 3e-2, "f16": 1e-2, "f32": 2e-3}[dtype]  # f32: the int8 rows flip by one step where the inputs differ in the last bit
+    pos = 0
+    if prefill:
+        oracle.prefill(toks[:, :prefill], prefill)
+        out = model.stream(toks[:, :prefill], 0)
+        assert rel_err(out.float().numpy(), oracle.last_logits) <= tol
+        pos = prefill
+    for p in range(pos, 30):
+        oracle.decode_step(toks[:, p])
+        out = model.stream(toks[:, p], p)
+        assert rel_err(out.float().numpy(), oracle.last_logits) <= tol, p
+    kc = model.k_cache[0].cpu().numpy().astype(np.int32)  # unrotated int8 keys in their ring slots
+    assert np.abs(kc[:, :, :12] - oracle.k_cache[0][:, :, :12].astype(np.int32)).max() <= 2
+    assert not kc[:, :, 12:].any()
+    model.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("quant", [False, True])
+@pytest.mark.parametrize("b,hq,hkv,sq,d,sink,window,start,active,rope,causal", [
+    (2, 4, 2, 1, 64, 3, 9, 4, 12, True, False), (1, 8, 2, 1, 128, 0, 0, 0, 20, True, False), (2, 4, 4, 1, 8, 2, 6, 0, 5, False, False),
+    (1, 4, 2, 5, 64, 0, 0, 0, 14, True, True), (1, 2, 1, 3, 32, 4, 12, 7, 16, True, True)])
+def test_attention_streaming_operator_vs_literal_oracle(dtype, quant, b, hq, hkv, sq, d, sink, window, start, active, rope, causal):
+    """Every operand of the engine's Attention node at once: ring mapping, int8 cache with per-row scales, keys rotated inside
+    the kernel at kv_position[logical row], one and several query rows, against the literal restatement of the engine's
+    kernels."""
+    from my_nn_engine_b200 import ops
+    rng = np.random.default_rng(b * 100 + sq * 10 + d + active)
+    cache = 24
+    name = "f32" if dtype == torch.float32 else "bf16"
+    q = torch.from_numpy(rng.standard_normal((b, hq, sq, d)).astype(np.float32)).to(dtype)
+    if quant:
+        k = torch.from_numpy(rng.integers(-127, 128, (b, hkv, cache, d), dtype=np.int8))
+        v = torch.from_numpy(rng.integers(-127, 128, (b, hkv, cache, d), dtype=np.int8))
+        ks = torch.from_numpy(rng.uniform(0.005, 0.02, (b, hkv, cache)).astype(np.float32)).to(dtype)
+        vs = torch.from_numpy(rng.uniform(0.005, 0.02, (b, hkv, cache)).astype(np.float32)).to(dtype)
+    else:
+        k = torch.from_numpy(rng.standard_normal((b, hkv, cache, d)).astype(np.float32)).to(dtype)
+        v = torch.from_numpy(rng.standard_normal((b, hkv, cache, d)).astype(np.float32)).to(dtype)
+        ks = vs = None
+    cos, sin = R.rope_table(32, d, 10000.0, name)
+    kvpos = rng.permutation(32)[:cache].astype(np.int64)  # any table: the kernel must index it by logical row
+    want = R.attention_streaming(q.float().numpy(), k.numpy() if quant else k.float().numpy(), v.numpy() if quant else v.float().numpy(),
+                                 0.2, active, sink, window, start, is_causal=causal,
+                                 k_scale=None if ks is None else ks.float().numpy(), v_scale=None if vs is None else vs.float().numpy(),
+                                 cos_table=cos if rope else None, sin_table=sin if rope else None, kv_position=kvpos if rope else None)
+    out = ops.attention_streaming(q.cuda(), k.cuda(), v.cuda(), 0.2, active, causal, (sink, window, start),
+                                  None if ks is None else ks.cuda(), None if vs is None else vs.cuda(),
+                                  torch.from_numpy(cos).to(dtype).cuda() if rope else None, torch.from_numpy(sin).to(dtype).cuda() if rope else None,
+                                  torch.from_numpy(kvpos).cuda() if rope else None)
+    got = out.float().cpu().numpy()
+    assert np.abs(got - want).max() <= (1e-4 if dtype == torch.float32 else 1e-2) * max(np.abs(want).max(), 1e-6)
+
+
 def test_streaming_decoder_long_prefill_chunks_then_eviction():
     """sink 4 + window 156 = 160 live rows; two prefill chunks of 70 tokens (long enough for the tcgen05 attention over the
     rotated copy of the keys), then 40 decode steps, of which the last 20 evict."""

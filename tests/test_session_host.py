@@ -134,3 +134,32 @@ def test_streaming_chunk_shrinks_to_the_room_left():
     s = LlmSession.for_llama_streaming(model, eos_token_id=999, prefill_len=4)
     s.generate_ids([1, 2, 3, 4, 5, 1, 2], 1)
     assert [(len(t), pos) for t, pos in model.calls] == [(4, 0), (2, 4), (1, 6)]
+
+
+def test_engine_literal_streaming_index_math_and_where_it_leaves_the_documented_layout():
+    """ref_ops.streaming_state(engine_literal=True) restates the engine's host code line by line
+    (crates/llm/src/session.rs:539-635).  While nothing has been evicted it equals the layout this library keeps; from the
+    first eviction on the engine derives the ring start and the rank table from the position BEFORE the append and reuses that
+    ring start for the write slot: the new row of token P lands in slot sink + 2 * ((P - sink) % window) % window instead of
+    sink + (P - sink) % window, and the rank table lags one step behind.  An integrator who needs the engine's exact
+    post-eviction behaviour gets it from the literal mode; the library itself keeps the documented layout."""
+    import numpy as np
+    from oracle import ref_ops as R
+    sink, window, cache = 4, 8, 16
+    for p in range(sink + window):  # no eviction yet: identical in every field
+        a, b = R.streaming_state(p, 1, sink, window, cache), R.streaming_state(p, 1, sink, window, cache, engine_literal=True)
+        assert a["slots"] == b["slots"] and a["ring_start"] == b["ring_start"] == 0 and a["active"] == b["active"]
+        assert np.array_equal(a["kv_position"], b["kv_position"]) and np.array_equal(a["q_positions"], b["q_positions"])
+    for chunk in (2, 5):  # prefill chunks that do not evict: identical too
+        a, b = R.streaming_state(3, chunk, sink, window, cache), R.streaming_state(3, chunk, sink, window, cache, engine_literal=True)
+        assert a["slots"] == b["slots"] and np.array_equal(a["kv_position"], b["kv_position"])
+    for p in range(sink + window, sink + 3 * window):
+        a, b = R.streaming_state(p, 1, sink, window, cache), R.streaming_state(p, 1, sink, window, cache, engine_literal=True)
+        assert a["slots"] == [sink + (p - sink) % window]
+        assert b["slots"] == [sink + (2 * ((p - sink) % window)) % window]
+        assert b["ring_start"] == (p - sink) % window and a["ring_start"] == (p + 1 - sink) % window
+        assert a["active"] == b["active"] == sink + window
+        # documented layout: the slot just written is the newest rank; literal: the table still ranks the rows as before the append
+        assert a["kv_position"][a["slots"][0]] == sink + window - 1
+        prev = R.streaming_state(p - 1, 1, sink, window, cache)
+        assert np.array_equal(b["kv_position"], prev["kv_position"])
