@@ -85,24 +85,22 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // ---- programmatic dependent launch -----------------------------------------------------------------------------
-// Kernels of the decode chain are launched with the programmatic-stream-serialization attribute: a kernel may be
-// scheduled while its predecessor is still running, and orders itself with pdl_wait() before it touches anything an
-// earlier kernel produces (and before it writes anything an earlier kernel may still read).  pdl_trigger() lets the
-// successor be scheduled early.  Without the attribute both are no-ops.
+// Only the DequantMatMul kernels are launched with the programmatic-stream-serialization attribute: they have work that
+// does not depend on their predecessor (barrier set-up, streaming the first weight tiles) and order themselves with
+// pdl_wait() before they touch anything an earlier kernel produces.  The other kernels of the decode chain are plain
+// launches; their pdl_trigger() / pdl_wait() are no-ops there and only matter when such a kernel is the predecessor of a
+// DequantMatMul (pdl_trigger() lets that kernel be scheduled early).  Giving every kernel of the chain the attribute was
+// measured twice and rejected: without an early trigger in the GEMM it changed nothing, with one the kernels two and three
+// places ahead became resident early and took registers and shared memory from the running kernel (step 4.63 -> 5.31 ms).
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // Library options (mynn_b200_set_option).
-extern int g_ksplit_override;          // forced cluster K split of the DequantMatMul kernels, 0 = automatic
-extern int g_prefill_attention_mode;   // see MYNN_OPT_PREFILL_ATTENTION
+extern int g_ksplit_override;            // forced cluster K split of the DequantMatMul kernels, 0 = automatic
+extern int g_prefill_attention_mode;     // see MYNN_OPT_PREFILL_ATTENTION
 extern std::atomic<int> g_inject_stall;  // see MYNN_OPT_INJECT_STALL; consumed by the next launch it applies to
 
-// Build-time choice: 0 = only the DequantMatMul kernels carry the attribute (they overlap their limb producer); 1 = every
-// kernel launched through launch_pdl carries it.
-#ifndef MYNN_PDL_CHAIN
-#define MYNN_PDL_CHAIN 0
-#endif
-
+// A plain launch through cudaLaunchKernelEx (no attributes); the name says which kernels belong to the decode chain.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -110,11 +108,8 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = MYNN_PDL_CHAIN ? 1 : 0;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 

@@ -105,9 +105,6 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
     MYNN_STAMP(threadIdx.x == 0, 1);  // set-up done
-#if MYNN_PDL_CHAIN
-    pdl_trigger();  // every CTA is resident: the kernel behind this one may take the free slots and wait there
-#endif
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
