@@ -347,7 +347,7 @@ int mynn_b200_model_tp_attach(void *state, const void *handles_world_x_64_bytes)
  *             directly into the owner's block (peer stores from the GEMM epilogue), buffer 0 or 1.  N = hidden.
  *   reduce    on every rank, for the rows it owns: sum of the `world` partial rows in rank order; x[m] = round(x[m] +
  *             round(sum)); y = round(RMSNorm(x[m]) * weight); y is delivered to EVERY rank's block as the activation of
- *             the next DequantMatMul (weight NULL: only x is updated).  producer_K is the K of the scatter call that fed it.
+ *             the next DequantMatMul (weight NULL: only x is updated).
  *             x [M, hidden] in `dtype`: only the rows a rank owns are read and written.
  *   gathered  column-parallel DequantMatMul of the delivered rows: out[m, n] = scale[n] * (y[m, :] . wq[n, :]), K = hidden;
  *             its weights stream at once, its activation loads wait until all M rows have arrived.
@@ -367,8 +367,8 @@ size_t mynn_b200_tp_block_bytes(int max_rows, int hidden, int world);
 int mynn_b200_tp_dequant_matmul_scatter(void *stream, const mynn_b200_tp_group *group, int buffer, const void *act,
                                         const int8_t *wq, const float *scale, int M, int K, int act_dtype, void *workspace,
                                         size_t workspace_bytes);
-int mynn_b200_tp_reduce_norm_gather(void *stream, const mynn_b200_tp_group *group, int buffer, int producer_K, void *x,
-                                    const void *weight, float eps, int M, int dtype);
+int mynn_b200_tp_reduce_norm_gather(void *stream, const mynn_b200_tp_group *group, int buffer, void *x, const void *weight,
+                                    float eps, int M, int dtype);
 int mynn_b200_tp_dequant_matmul_gathered(void *stream, const mynn_b200_tp_group *group, void *out, const int8_t *wq,
                                          const void *scale, int M, int N, int out_dtype, void *workspace,
                                          size_t workspace_bytes);

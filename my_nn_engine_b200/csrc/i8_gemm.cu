@@ -125,12 +125,15 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 // The limb rows come from the reduction kernels of ALL ranks (peer stores into this GPU's memory): hold the
                 // activation loads back, with a time limit, until the rows of every reduction this rank has completed are in.
                 const uint32_t target = *(volatile const uint32_t *)p.tp.gather_expected;
-                const unsigned long long t0 = global_ns();
-                while ((int)(ld_acquire_sys_u32(p.tp.gather_cnt) - target) < 0) {
-                    __nanosleep(40);
-                    if (global_ns() - t0 > d_wait_budget_ns) {
-                        atomicExch(p.tp.status, 22);
-                        break;
+                unsigned long long t0 = 0;
+                for (uint32_t it = 0; (int)(ld_acquire_sys_u32(p.tp.gather_cnt) - target) < 0; it++) {
+                    if ((it & 31) == 31) {  // the clock is read rarely: the common case is a wait of a few polls
+                        const unsigned long long now = global_ns();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > d_wait_budget_ns) {
+                            atomicExch(p.tp.status, 22);
+                            break;
+                        }
                     }
                 }
                 asm volatile("fence.proxy.async;" ::: "memory");  // the rows were written through the generic proxy, TMA reads them
@@ -249,14 +252,16 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     auto combine = [](const uint32_t *a3) {
         return (long long)(int)a3[2] * 65536 + (long long)(int)a3[1] * 256 + (long long)(int)a3[0];
     };
+    const uint32_t tp_tag = p.tp.mode == 1 ? *(volatile const uint32_t *)p.tp.part_tag + 1u : 0u;  // written two reductions ago
     auto finish = [&](int m, long long sum, float resv) {
         // separate roundings (no fused multiply-add), so that every kernel of this operator gives the same bits
         float v = __fmul_rn(__fmul_rn((float)sum, sh_ascale[m]), wscale);
         if (resid_p) v = __fadd_rn(round_store<OutT>(v), resv);
         if (p.tp.mode == 1) {
-            // partial row m goes to the rank that owns it, into the slot of this rank (a plain store, possibly over NVLink)
+            // partial row m goes to the rank that owns it, into the slot of this rank: one 8-byte store {value, tag}, possibly
+            // over NVLink; the reader re-reads a word until it sees this reduction's tag, so no fence or flag follows
             const int owner = m % p.tp.world, local = m / p.tp.world;
-            reinterpret_cast<OutT *>(p.tp.part[owner])[((size_t)p.tp.rank * p.tp.rows_cap + local) * p.N + n_own] = from_f32<OutT>(v);
+            p.tp.part[owner][((size_t)p.tp.rank * p.tp.rows_cap + local) * p.N + n_own] = make_uint2(__float_as_uint(v), tp_tag);
         } else {
             out_p[(size_t)m * p.N + n_own] = from_f32<OutT>(v);
         }
@@ -316,14 +321,6 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         }
     }
 
-    if (p.tp.mode == 1 && warp >= 2) {
-        // every store of this CTA is ordered before the counter increments: CTA barrier, then fence + release per destination
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et < p.tp.world) {
-            __threadfence_system();
-            red_release_sys_add_u32(p.tp.sig[et], 1u);
-        }
-    }
     MYNN_STAMP(threadIdx.x == 64, 5);  // outputs stored
     tc_fence_before();
     __syncthreads();
@@ -698,11 +695,6 @@ static int launch_i8(cudaStream_t st, const CUtensorMap &mw, const CUtensorMap &
     MYNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mw, ma, p));
     MYNN_LAUNCH_OK("i8_stream_gemm_kernel");
     return MYNN_OK;
-}
-
-int i8_gemm_grid_ctas(int N, int K) {
-    const int row_tiles = (N + kTileRows - 1) / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
-    return row_tiles * (g_ksplit_override > 0 ? g_ksplit_override : pick_split(row_tiles, kblocks));
 }
 
 int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,

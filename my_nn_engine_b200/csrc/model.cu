@@ -148,11 +148,11 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     bool n_limbs2 = false;  // the last norm left two-limb rows in the workspace instead of m.n
 
     // norm(x [+ part]) feeding a DequantMatMul: either limbs in the workspace (fused) or the bf16 tensor m.n
-    auto reduce = [&](int buf, int producer_k, const void *w) -> int {  // fused reduction of the partial sums in buffer `buf`
+    auto reduce = [&](int buf, const void *w) -> int {  // fused reduction of the partial sums in buffer `buf`
         int skip = 0, want = 2;
         if (g_inject_stall.compare_exchange_strong(want, 0)) skip = 1;  // test aid: this launch delivers nothing to the peers
         gathered = w != nullptr;
-        return launch_tp_reduce_norm_gather(st, dt, m.tp, buf, i8_gemm_grid_ctas(H, producer_k), m.x, w, c.rms_eps, M, skip);
+        return launch_tp_reduce_norm_gather(st, dt, m.tp, buf, m.x, w, c.rms_eps, M, skip);
     };
     auto norm = [&](const void *w, const float *part, int rows, const void *src) -> int {
         n_limbs2 = false;
@@ -259,7 +259,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         } else if (tp_fused) {
             // partial rows go straight to their owners; the owners finish them and deliver the normed rows to everybody
             RC(launch_tp_gemm_scatter(st, m.tp, 0, attn_limbs ? nullptr : m.attn, L.wo, (const float *)L.so, M, H, Nq, dt, m.gemm_ws, m.gemm_ws_bytes));
-            RC(reduce(0, Nq, L.ln2));
+            RC(reduce(0, L.ln2));
         } else {
             if (attn_limbs) RC(gemm_prequant(st, m, m.part, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
             else RC(gemm(st, m, m.part, m.attn, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
@@ -300,7 +300,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
             if (!last) RC(norm(next_norm, nullptr, M, m.x));
         } else if (tp_fused) {
             RC(launch_tp_gemm_scatter(st, m.tp, 1, fuse_mlp ? nullptr : m.h, L.wd, (const float *)L.sd, M, H, m.ffn, dt, m.gemm_ws, m.gemm_ws_bytes));
-            RC(reduce(1, m.ffn, last ? m.final_norm : next_norm));  // after the last layer: the final norm, whose rows feed lm_head
+            RC(reduce(1, last ? m.final_norm : next_norm));  // after the last layer: the final norm, whose rows feed lm_head
         } else {
             if (fuse_mlp) RC(gemm_prequant(st, m, m.part, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
             else if (h_limbs2) RC(gemm_prequant2(st, m, m.part, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));

@@ -7,7 +7,7 @@
 // peer STORES from its epilogue, one kernel per rank that finishes the rows it owns, and an all-gather of the finished
 // limb rows, again by peer stores, that the consuming GEMM waits for while its weights are already streaming.
 //
-// Ordering.  Data stores to a peer are followed by a CTA barrier, a system-scope fence and a release increment of a counter
+// Ordering.  Data stores to a peer are followed by a CTA barrier, one system-scope fence and an increment of a counter
 // in the peer's header; the reader polls the counter with acquire loads and only then touches the data (through L2: the
 // lines were written by another GPU).  A buffer is only rewritten after its readers are provably done: a rank delivers
 // partial sums for reduction j+1 only after its column-parallel GEMM has received the limb rows of reduction j from every
@@ -37,7 +37,7 @@ TpLayout tp_layout(int max_rows, int hidden, int world) {
     l.rows_cap = (max_rows + world - 1) / world;
     l.nc = i8_gemm_limb_rows(max_rows);
     size_t off = sizeof(TpHeader);
-    const size_t part = up256((size_t)world * l.rows_cap * hidden * sizeof(float));
+    const size_t part = up256((size_t)world * l.rows_cap * hidden * sizeof(uint2));  // {value, tag} words
     l.part_off[0] = off;
     off += part;
     l.part_off[1] = off;
@@ -53,14 +53,17 @@ TpLayout tp_layout(int max_rows, int hidden, int world) {
 struct TpReduceParams {
     char *blocks[kTpMaxRanks];
     size_t part_off, limb_off, ascale_off;
-    int rank, world, rows_cap, buf, n_sig, M, D, skip_signal;
+    int rank, world, rows_cap, buf, M, D, skip_signal;
     float eps;
 };
 
 constexpr int kTpThreads = 1024;
 
-__device__ __forceinline__ float4 ld_l2_f4(const float *p) {  // written by a peer GPU: read through L2, never from a stale L1 line
-    return __ldcg(reinterpret_cast<const float4 *>(p));
+// 16 bytes = two {value, tag} words written by a peer GPU: a volatile load, so that every poll goes to L2
+__device__ __forceinline__ uint4 ld_volatile_u4(const uint2 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
 }
 
 // grid = max(rows this rank owns, 1).  CTA j finishes row m = rank + j * world.  w may be null (then only x is updated and no
@@ -73,30 +76,40 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_norm_gather_kernel(T *x,
     const int D = p.D;
     const int m = p.rank + (int)blockIdx.x * p.world;
     const bool have_row = m < p.M;
-    // 1. wait until every source rank has delivered all tiles of its partial sums (bounded)
-    const uint32_t part_target = *(volatile uint32_t *)&hdr->part_expected[p.buf] + (uint32_t)p.n_sig;
-    if (threadIdx.x < p.world) {
-        const unsigned long long t0 = global_ns();
-        while ((int)(ld_acquire_sys_u32(&hdr->part_cnt[p.buf][threadIdx.x]) - part_target) < 0) {
-            __nanosleep(40);
-            if (global_ns() - t0 > d_wait_budget_ns) {
-                atomicExch(&hdr->status, 21);
-                break;
-            }
-        }
-    }
-    __syncthreads();
+    // the tag the partial sums of THIS reduction carry (the previous reduction on this buffer was number part_tag)
+    const uint32_t tag = *(volatile uint32_t *)&hdr->part_tag[p.buf] + 1u;
     if (have_row) {
-        // 2. add the partial rows of all ranks in rank order, 3. residual add
-        const float *part = reinterpret_cast<const float *>(p.blocks[p.rank] + p.part_off) + (size_t)blockIdx.x * D;
+        // 1. + 2. read the partial rows of all ranks (8-byte {value, tag} words in this rank's own memory, written by the peers'
+        // GEMM epilogues), re-reading a word until it carries this reduction's tag (bounded); add them in rank order;
+        // 3. residual add
+        const uint2 *part = reinterpret_cast<const uint2 *>(p.blocks[p.rank] + p.part_off) + (size_t)blockIdx.x * D;
         const size_t slot_stride = (size_t)p.rows_cap * D;
         T *xrow = x + (size_t)m * D;
         float ss = 0.f;
+        unsigned long long t0 = 0;
+        bool gave_up = false;
         for (int i = 4 * threadIdx.x; i < D; i += 4 * kTpThreads) {
             float4 v[kTpMaxRanks];
 #pragma unroll
             for (int r = 0; r < kTpMaxRanks; r++)
-                if (r < p.world) v[r] = ld_l2_f4(part + (size_t)r * slot_stride + i);
+                if (r < p.world) {
+                    const uint2 *src = part + (size_t)r * slot_stride + i;
+                    uint4 a, b;
+                    for (uint32_t it = 0;; it++) {
+                        a = ld_volatile_u4(src);
+                        b = ld_volatile_u4(src + 2);
+                        if ((a.y == tag && a.w == tag && b.y == tag && b.w == tag) || gave_up) break;
+                        if ((it & 63) == 63) {  // the clock is read rarely: the common case is no wait at all
+                            const unsigned long long now = global_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > d_wait_budget_ns) {
+                                atomicExch(&hdr->status, 21);
+                                gave_up = true;
+                            }
+                        }
+                    }
+                    v[r] = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+                }
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int r = 0; r < kTpMaxRanks; r++)
@@ -184,18 +197,17 @@ __global__ void __launch_bounds__(kTpThreads) tp_reduce_norm_gather_kernel(T *x,
             }
         }
     }
-    // every store of this CTA is ordered before the increments: CTA barrier, then fence + release per destination
+    // every store of this CTA is ordered before the increments: CTA barrier, then a release increment per destination (the
+    // lanes of one warp in parallel: each release costs a system-scope fence)
     __syncthreads();
-    if (have_row && w != nullptr && !p.skip_signal && threadIdx.x < p.world) {
-        __threadfence_system();
+    if (have_row && w != nullptr && !p.skip_signal && threadIdx.x < p.world)
         red_release_sys_add_u32(&tp_header(p.blocks[threadIdx.x])->gather_cnt, 1u);
-    }
     // the last CTA to finish records what the counters must reach for the kernels that follow
     if (threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(&hdr->ticket, 1u) == gridDim.x - 1) {
             hdr->ticket = 0u;
-            hdr->part_expected[p.buf] = part_target;
+            hdr->part_tag[p.buf] = tag;
             if (w != nullptr) hdr->gather_expected += (uint32_t)p.M;
             __threadfence();
         }
@@ -209,10 +221,10 @@ static void fill_i8tp(I8Tp &t, const TpPeers &peers, int mode, int buf) {
     t.rank = peers.rank;
     t.rows_cap = peers.lay.rows_cap;
     for (int r = 0; r < peers.world; r++) {
-        t.part[r] = reinterpret_cast<float *>(peers.blocks[r] + peers.lay.part_off[buf]);
-        t.sig[r] = &tp_header(peers.blocks[r])->part_cnt[buf][peers.rank];
+        t.part[r] = reinterpret_cast<uint2 *>(peers.blocks[r] + peers.lay.part_off[buf]);
     }
     TpHeader *own = tp_header(peers.blocks[peers.rank]);
+    t.part_tag = &own->part_tag[buf];
     t.gather_cnt = &own->gather_cnt;
     t.gather_expected = &own->gather_expected;
     t.status = &own->status;
@@ -244,8 +256,8 @@ int launch_tp_gemm_gathered(cudaStream_t st, const TpPeers &peers, void *out, co
                              reinterpret_cast<const float *>(own + peers.lay.ascale_off));
 }
 
-int launch_tp_reduce_norm_gather(cudaStream_t st, int dtype, const TpPeers &peers, int buf, int n_sig, void *x, const void *w, float eps,
-                                 int M, int skip_signal) {
+int launch_tp_reduce_norm_gather(cudaStream_t st, int dtype, const TpPeers &peers, int buf, void *x, const void *w, float eps, int M,
+                                 int skip_signal) {
     const int D = peers.lay.hidden;
     if (buf != 0 && buf != 1) return fail(MYNN_E_ARG, "tp reduce: buffer %d", buf);
     if (M < 1 || M > peers.lay.max_rows || D % 16) return fail(MYNN_E_UNSUPPORTED, "tp reduce: rows=%d D=%d not supported", M, D);
@@ -259,7 +271,6 @@ int launch_tp_reduce_norm_gather(cudaStream_t st, int dtype, const TpPeers &peer
     p.world = peers.world;
     p.rows_cap = peers.lay.rows_cap;
     p.buf = buf;
-    p.n_sig = n_sig;
     p.M = M;
     p.D = D;
     p.skip_signal = skip_signal;
@@ -311,19 +322,17 @@ extern "C" int mynn_b200_tp_dequant_matmul_scatter(void *stream, const mynn_b200
     return launch_tp_gemm_scatter((cudaStream_t)stream, peers, buffer, act, wq, scale, M, peers.lay.hidden, K, act_dtype, workspace, workspace_bytes);
 }
 
-extern "C" int mynn_b200_tp_reduce_norm_gather(void *stream, const mynn_b200_tp_group *group, int buffer, int producer_K, void *x,
-                                               const void *weight, float eps, int M, int dtype) {
+extern "C" int mynn_b200_tp_reduce_norm_gather(void *stream, const mynn_b200_tp_group *group, int buffer, void *x, const void *weight,
+                                               float eps, int M, int dtype) {
     TpPeers peers;
     if (int rc = group_to_peers(group, peers, "tp_reduce_norm_gather")) return rc;
     if (!x) return fail(MYNN_E_ARG, "tp_reduce_norm_gather: null pointer");
-    if (producer_K < 16) return fail(MYNN_E_ARG, "tp_reduce_norm_gather: producer_K %d", producer_K);
     int skip = 0;
     {
         int want = 2;
         if (g_inject_stall.compare_exchange_strong(want, 0)) skip = 1;
     }
-    return launch_tp_reduce_norm_gather((cudaStream_t)stream, dtype, peers, buffer, i8_gemm_grid_ctas(peers.lay.hidden, producer_K), x, weight,
-                                        eps, M, skip);
+    return launch_tp_reduce_norm_gather((cudaStream_t)stream, dtype, peers, buffer, x, weight, eps, M, skip);
 }
 
 extern "C" int mynn_b200_tp_dequant_matmul_gathered(void *stream, const mynn_b200_tp_group *group, void *out, const int8_t *wq,

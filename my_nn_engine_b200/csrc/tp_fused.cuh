@@ -4,10 +4,13 @@
 // Data flow of one reduction over `world` ranks (rows m of the step are dealt out: row m belongs to rank m % world):
 //   1. the row-parallel DequantMatMul (o_proj, down_proj) of every rank STORES its f32 partial row m straight into slot
 //      [its own rank][m / world] of the partial buffer of the rank that owns row m (plain peer stores over NVLink, issued
-//      from the GEMM epilogue), then adds 1 to a counter in that rank's header (release at system scope);
-//   2. the owner's reduction kernel waits until every source rank has signalled all its tiles, adds the `world` partial rows
-//      in rank order from its OWN memory, finishes the row (residual add, RMSNorm, activation limbs) and stores the limbs
-//      and the row scale into the limb buffer of EVERY rank, again followed by a counter increment;
+//      from the GEMM epilogue).  Every value travels as an 8-byte word {value, tag} written with one store, the tag being
+//      the number of the reduction: the receiver needs no flag and the sender no fence (a system-scope release costs
+//      microseconds, and there would be one per CTA and destination);
+//   2. the owner's reduction kernel reads the `world` partial rows from its OWN memory, re-reading a word until it carries
+//      the tag of this reduction, adds them in rank order, finishes the row (residual add, RMSNorm, activation limbs) and
+//      stores the limbs and the row scale into the limb buffer of EVERY rank, followed by a release increment of a counter
+//      in that rank's header (the limbs are read by TMA, so they cannot carry tags);
 //   3. the column-parallel DequantMatMul that follows (qkv, gate/up, lm_head) streams its weights at once and only holds
 //      its activation (limb) loads back until all rows have arrived.
 // Every rank moves rows/world of the partial sums in and 3 bytes per element of its own rows out, instead of reading
@@ -25,14 +28,13 @@ constexpr int kTpMaxRanks = 8;  // ranks of one NVLink domain; sizes the counter
 // Header of the block of device memory every rank shares with its peers.  All counters are monotonic (they wrap modulo
 // 2^32 and are compared by signed difference); a block must be zeroed once before its first use.
 struct TpHeader {
-    uint32_t part_cnt[2][kTpMaxRanks];  // [buffer][source rank]: tiles of partial sums that rank has delivered so far (peers add)
     uint32_t gather_cnt;                // limb rows delivered so far by the reductions of all ranks (peers add)
     // written by this rank only (the last CTA of each of its reduction kernels):
-    uint32_t part_expected[2];          // value part_cnt[buffer][*] has reached once every reduction launched so far is fed
+    uint32_t part_tag[2];               // number of reductions run on each partial buffer = tag of the last one
     uint32_t gather_expected;           // value gather_cnt reaches once every reduction completed so far has been delivered
     uint32_t ticket;                    // CTA arrival counter of the running reduction kernel
     int status;                         // 21: a wait for partial sums ran out of time; 22: a wait for limb rows did
-    uint32_t pad[64 - 2 * kTpMaxRanks - 6];
+    uint32_t pad[64 - 6];
 };
 static_assert(sizeof(TpHeader) == 256, "TpHeader is one 256-byte header");
 
@@ -56,24 +58,20 @@ __host__ __device__ inline TpHeader *tp_header(char *blk) { return reinterpret_c
 struct I8Tp {
     int mode;                          // 0: plain; 1: scatter partial rows to their owners; 2: activation limbs are gathered rows
     int world, rank, rows_cap;
-    float *part[kTpMaxRanks];          // mode 1: partial buffer of every rank (slot layout [source][local row][N])
-    uint32_t *sig[kTpMaxRanks];        // mode 1: &header(rank r)->part_cnt[buf][this rank]
+    uint2 *part[kTpMaxRanks];          // mode 1: partial buffer of every rank, {value, tag} words, layout [source][local row][N]
+    const uint32_t *part_tag;          // mode 1: own header's count of reductions on this buffer; this product's tag is that + 1
     const uint32_t *gather_cnt;        // mode 2: own header's counter of delivered limb rows and the value it has to reach
     const uint32_t *gather_expected;
     int *status;                       // own header's status word
 };
 
-// Signals one GEMM launch sends to each destination rank (= CTAs of its grid); the reduction kernel waits for that many.
-int i8_gemm_grid_ctas(int N, int K);
-
 // Row-parallel DequantMatMul with the scatter epilogue.  act == nullptr: limbs already in `workspace`.
 int launch_tp_gemm_scatter(cudaStream_t st, const TpPeers &peers, int buf, const void *act, const int8_t *wq, const float *scale,
                            int M, int N, int K, int act_dtype, void *workspace, size_t workspace_bytes);
 // sum over ranks of the partial rows this rank owns -> x[m] = round(x[m] + round(sum)); y = round(RMSNorm(x[m]) * w) -> limbs
-// + row scale into every rank's limb buffer.  n_sig = i8_gemm_grid_ctas of the GEMM that produced the partial sums.
-// skip_signal (test aid): do everything except the deliveries to the peers.
-int launch_tp_reduce_norm_gather(cudaStream_t st, int dtype, const TpPeers &peers, int buf, int n_sig, void *x, const void *w, float eps,
-                                 int M, int skip_signal);
+// + row scale into every rank's limb buffer.  skip_signal (test aid): do everything except the deliveries to the peers.
+int launch_tp_reduce_norm_gather(cudaStream_t st, int dtype, const TpPeers &peers, int buf, void *x, const void *w, float eps, int M,
+                                 int skip_signal);
 // Column-parallel DequantMatMul over the gathered limb rows.  `workspace` only carries the kernel's status word.
 int launch_tp_gemm_gathered(cudaStream_t st, const TpPeers &peers, void *out, const int8_t *wq, const void *scale, int M, int N,
                             int out_dtype, void *workspace, size_t workspace_bytes);

@@ -395,10 +395,10 @@ def tp_dequant_matmul_scatter(group: TpGroup, buffer: int, act, wq, scale, works
                                                             _dt(act), _ptr(workspace), workspace.numel()))
 
 
-def tp_reduce_norm_gather(group: TpGroup, buffer: int, producer_k: int, x, weight, eps: float):
+def tp_reduce_norm_gather(group: TpGroup, buffer: int, x, weight, eps: float):
     """Finish the rows this rank owns (sum of partials, residual add into ``x``, RMSNorm) and deliver them to every rank."""
     m = x.numel() // group.hidden
-    ffi.check(ffi.lib().mynn_b200_tp_reduce_norm_gather(_stream(), ctypes.byref(group.c), buffer, producer_k, _ptr(x),
+    ffi.check(ffi.lib().mynn_b200_tp_reduce_norm_gather(_stream(), ctypes.byref(group.c), buffer, _ptr(x),
                                                         None if weight is None else _ptr(weight), float(eps), m, _dt(x)))
 
 

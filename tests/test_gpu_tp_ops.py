@@ -58,7 +58,7 @@ def test_lock_step_ranks_match_the_unsharded_oracle(world, m, hidden, k_total, n
         for r in range(world):
             ops.tp_dequant_matmul_scatter(groups[r], buf, act_dev[r], wr_dev[r], s_dev)
         for r in range(world):
-            ops.tp_reduce_norm_gather(groups[r], buf, ksh, xs[r], wn_dev, eps)
+            ops.tp_reduce_norm_gather(groups[r], buf, xs[r], wn_dev, eps)
         outs = [ops.tp_dequant_matmul_gathered(groups[r], wc_dev, sc_dev, m) for r in range(world)]
         for r in range(world):
             ops.tp_check(groups[r])
@@ -103,7 +103,7 @@ def test_wait_for_partial_sums_runs_out_when_a_rank_never_delivers():
     ffi.set_option(ffi.OPT_WAIT_BUDGET_US, 20000)
     try:
         ops.tp_dequant_matmul_scatter(groups[0], 0, act, w_row, s_row)
-        ops.tp_reduce_norm_gather(groups[0], 0, 256, x, w_norm, 1e-5)
+        ops.tp_reduce_norm_gather(groups[0], 0, x, w_norm, 1e-5)
         with pytest.raises(ffi.MynnError) as err:
             ops.tp_check(groups[0])
         assert err.value.code == ffi.E_COMM and "21" in str(err.value)
@@ -115,7 +115,7 @@ def test_wait_for_partial_sums_runs_out_when_a_rank_never_delivers():
         ops.tp_dequant_matmul_scatter(groups[r], 0, act, w_row, s_row)
     xs = [x.clone(), x.clone()]
     for r in range(2):
-        ops.tp_reduce_norm_gather(groups[r], 0, 256, xs[r], w_norm, 1e-5)
+        ops.tp_reduce_norm_gather(groups[r], 0, xs[r], w_norm, 1e-5)
     a = ops.tp_dequant_matmul_gathered(groups[0], w_col, s_col, 8)
     b = ops.tp_dequant_matmul_gathered(groups[1], w_col, s_col, 8)
     ops.tp_check(groups[0])
@@ -135,9 +135,9 @@ def test_wait_for_limb_rows_runs_out_when_a_rank_delivers_nothing():
         for r in range(2):
             ops.tp_dequant_matmul_scatter(groups[r], 1, act, w_row, s_row)
         xs = [x.clone(), x.clone()]
-        ops.tp_reduce_norm_gather(groups[0], 1, 256, xs[0], w_norm, 1e-5)
+        ops.tp_reduce_norm_gather(groups[0], 1, xs[0], w_norm, 1e-5)
         ffi.set_option(ffi.OPT_INJECT_STALL, 2)
-        ops.tp_reduce_norm_gather(groups[1], 1, 256, xs[1], w_norm, 1e-5)
+        ops.tp_reduce_norm_gather(groups[1], 1, xs[1], w_norm, 1e-5)
         ops.tp_dequant_matmul_gathered(groups[0], w_col, s_col, 8)
         with pytest.raises(ffi.MynnError) as err:
             ops.tp_check(groups[0])
