@@ -48,8 +48,8 @@ const char *mynn_b200_last_error(void);
  *                             kernel only; -1 the row-serial kernel only.
  *   MYNN_OPT_INJECT_STALL     test aid for the bounded waits, never set in production: 1 = the NEXT small-batch tcgen05
  *                             DequantMatMul launch leaves out its last TMA stage, so that its MMA thread's wait runs out
- *                             (status 2 in the workspace); 2 = the NEXT fused tensor-parallel reduction does not announce
- *                             itself to its peers, so that their waits run out (status 21 / MYNN_E_COMM).  Nothing faults or
+ *                             (status 2 in the workspace); 2 = the NEXT row-parallel product of a tensor-parallel step delivers
+ *                             none of its partial sums, so that the reductions' waits run out (status 21 / MYNN_E_COMM).  Nothing faults or
  *                             hangs: the kernels return after the wait budget. */
 enum { MYNN_OPT_WAIT_BUDGET_US = 1, MYNN_OPT_KSPLIT = 2, MYNN_OPT_PREFILL_ATTENTION = 3, MYNN_OPT_INJECT_STALL = 4 };
 int mynn_b200_set_option(int option, long long value);
@@ -328,35 +328,34 @@ int mynn_b200_model_step_device(void *state, void *stream, const int64_t *ids_de
 int mynn_b200_model_prefill(void *state, const int64_t *ids_host, int T, int past_len, void *out_host);
 /* Fused tensor-parallel reduction over NVLink peer memory (tp_world > 1): each rank exports a 64-byte handle of its
  * shared block; the host gathers the handles in rank order (as it distributes the communicator id) and attaches them
- * before the first step.  The per-layer all-reduce of a decode step (at most 32 rows) then runs as the three fused
+ * before the first step.  The per-layer all-reduce of a decode step (at most 32 rows) then runs as the two fused
  * operators declared below (mynn_b200_tp_*).  Without attach, and for prefill chunks, the step calls ncclAllReduce
  * instead.  No counterpart in the engine, whose AllReduce operator has no CUDA lowering (src/codegen/cuda.rs:2577-2580). */
 int mynn_b200_model_tp_export(void *state, void *handle_out_64_bytes);
 int mynn_b200_model_tp_attach(void *state, const void *handles_world_x_64_bytes);
 
 /* ---------------------------------------------------------------------------------------------
- * Fused tensor-parallel operators: the all-reduce between a row-parallel DequantMatMul (o_proj, down_proj) and the
- * column-parallel one that follows it (q/k/v, gate/up, lm_head), merged with the operators around it.  They replace the
- * sequence DequantMatMul -> AllReduce(sum, f32, rank order: crates/comm/src/uds.rs:106-116) -> Add -> RMSNorm ->
- * DequantMatMul of the engine's tensor-parallel graphs (crates/llm/src/decoder.rs:40-73).
+ * Fused tensor-parallel operators: the all-reduce behind a row-parallel DequantMatMul (o_proj, down_proj), merged with the
+ * operators around it.  They replace the sequence DequantMatMul -> AllReduce(sum, f32, rank order:
+ * crates/comm/src/uds.rs:106-116) -> Add -> RMSNorm of the engine's tensor-parallel graphs (crates/llm/src/decoder.rs:40-73)
+ * and leave the activations of the DequantMatMul that follows ready in its workspace.
  *
  * A group is `world` blocks of device memory, one per rank, each of mynn_b200_tp_block_bytes() bytes, 256-byte aligned,
  * zeroed once by its owner and mapped into every rank's process (cudaIpc*, or plain pointers when the ranks share a
- * process); blocks[r] is rank r's block as THIS process addresses it.  Row m of a step belongs to rank m % world.
- *   scatter   out-of-place row-parallel DequantMatMul: partial[m, :] = scale[:] * (act[m, :K] . wq[:, :K]^T) in f32, stored
- *             directly into the owner's block (peer stores from the GEMM epilogue), buffer 0 or 1.  N = hidden.
- *   reduce    on every rank, for the rows it owns: sum of the `world` partial rows in rank order; x[m] = round(x[m] +
- *             round(sum)); y = round(RMSNorm(x[m]) * weight); y is delivered to EVERY rank's block as the activation of
- *             the next DequantMatMul (weight NULL: only x is updated).
- *             x [M, hidden] in `dtype`: only the rows a rank owns are read and written.
- *   gathered  column-parallel DequantMatMul of the delivered rows: out[m, n] = scale[n] * (y[m, :] . wq[n, :]), K = hidden;
- *             its weights stream at once, its activation loads wait until all M rows have arrived.
- * The three calls are made in this order, with the same M, on every rank; each rank uses one stream.  Waits for peers are
- * bounded (MYNN_OPT_WAIT_BUDGET_US); mynn_b200_tp_check synchronises the stream and returns MYNN_E_COMM, once, if one ran
- * out.  All ranks of a group may also live on ONE GPU as long as their calls are issued in lock step (every scatter before
- * any reduce, every reduce before any gathered call): then no kernel ever waits for one that has not finished.
- * workspace: as for mynn_b200_dequant_matmul (scatter: mynn_b200_dequant_matmul_workspace_bytes(M, hidden, K); gathered:
- * 256 bytes suffice). */
+ * process); blocks[r] is rank r's block as THIS process addresses it.
+ *   push     row-parallel DequantMatMul of this rank's K shard: partial[m, :] = scale[:] * (act[m, :K] . wq[:, :K]^T) in f32,
+ *            N = hidden, stored from the GEMM epilogue straight into EVERY rank's block (peer stores; each value carries the
+ *            number of the reduction, so no flag, fence or collective follows), buffer 0 or 1 in turn.
+ *   reduce   on every rank: sum of the `world` partial rows in rank order (it waits, with a time limit, for values that have
+ *            not arrived yet); x[m] = round(x[m] + round(sum)); y = round(RMSNorm(x[m]) * weight), left as the activation of
+ *            the next DequantMatMul in `workspace` (call mynn_b200_dequant_matmul_same_act next; weight NULL: only x is
+ *            updated).  x [M, hidden] in `dtype`; every rank computes the identical rows.
+ * Both calls are made in this order, with the same M and buffer, on every rank; buffers alternate (0, 1, 0, ...); each rank
+ * uses one stream.  The wait is bounded (MYNN_OPT_WAIT_BUDGET_US); mynn_b200_tp_check synchronises the stream and returns
+ * MYNN_E_COMM, once, if it ran out; the ranks are in step again at the next reduction.  All ranks of a group may also live on
+ * ONE GPU as long as their calls are issued in lock step (every push before any reduce): then no kernel ever waits for one
+ * that has not finished.  workspace: as for mynn_b200_dequant_matmul (push: mynn_b200_dequant_matmul_workspace_bytes(M,
+ * hidden, K); reduce: the workspace of the product that follows, mynn_b200_dequant_matmul_workspace_bytes(M, N, hidden)). */
 typedef struct mynn_b200_tp_group {
     void *blocks[8];
     int32_t rank, world;
@@ -364,14 +363,11 @@ typedef struct mynn_b200_tp_group {
     int32_t hidden;
 } mynn_b200_tp_group;
 size_t mynn_b200_tp_block_bytes(int max_rows, int hidden, int world);
-int mynn_b200_tp_dequant_matmul_scatter(void *stream, const mynn_b200_tp_group *group, int buffer, const void *act,
-                                        const int8_t *wq, const float *scale, int M, int K, int act_dtype, void *workspace,
-                                        size_t workspace_bytes);
-int mynn_b200_tp_reduce_norm_gather(void *stream, const mynn_b200_tp_group *group, int buffer, void *x, const void *weight,
-                                    float eps, int M, int dtype);
-int mynn_b200_tp_dequant_matmul_gathered(void *stream, const mynn_b200_tp_group *group, void *out, const int8_t *wq,
-                                         const void *scale, int M, int N, int out_dtype, void *workspace,
-                                         size_t workspace_bytes);
+int mynn_b200_tp_dequant_matmul_push(void *stream, const mynn_b200_tp_group *group, int buffer, const void *act,
+                                     const int8_t *wq, const float *scale, int M, int K, int act_dtype, void *workspace,
+                                     size_t workspace_bytes);
+int mynn_b200_tp_reduce_norm(void *stream, const mynn_b200_tp_group *group, int buffer, void *x, const void *weight, float eps,
+                             int M, int dtype, void *workspace, size_t workspace_bytes);
 int mynn_b200_tp_check(void *stream, const mynn_b200_tp_group *group);
 
 /* Kernels launched by this library since load (monotonic). */

@@ -49,7 +49,7 @@ struct I8GemmParams {
     int M, N, K;
     int *status;          // device int, set non-zero on a timed-out wait
     int stages;           // pipeline depth: kStages or kMaxStages
-    I8Tp tp;              // tensor-parallel forms: scatter epilogue / gathered activation limbs (mode 0: neither)
+    I8Tp tp;              // tensor-parallel form: the outputs are delivered to every rank as tagged partial sums (mode 0: off)
     int skip_last_stage;  // test aid (MYNN_OPT_INJECT_STALL): the producer leaves out the last k block, so a bounded wait expires
 #ifdef MYNN_TUNING
     unsigned long long *timing;  // 8 timestamps (ns) of CTA (0,0), or null
@@ -121,23 +121,6 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             MYNN_STAMP(true, 2);  // predecessor grid complete
-            if (p.tp.mode == 2) {
-                // The limb rows come from the reduction kernels of ALL ranks (peer stores into this GPU's memory): hold the
-                // activation loads back, with a time limit, until the rows of every reduction this rank has completed are in.
-                const uint32_t target = *(volatile const uint32_t *)p.tp.gather_expected;
-                unsigned long long t0 = 0;
-                for (uint32_t it = 0; (int)(ld_acquire_sys_u32(p.tp.gather_cnt) - target) < 0; it++) {
-                    if ((it & 31) == 31) {  // the clock is read rarely: the common case is a wait of a few polls
-                        const unsigned long long now = global_ns();
-                        if (t0 == 0) t0 = now;
-                        else if (now - t0 > d_wait_budget_ns) {
-                            atomicExch(p.tp.status, 22);
-                            break;
-                        }
-                    }
-                }
-                asm volatile("fence.proxy.async;" ::: "memory");  // the rows were written through the generic proxy, TMA reads them
-            }
             for (int i = 0; i < pre; i++)
                 tma_load_2d(smem + i * kStageBytes + kWBytes, &map_a, (kb_beg + i) * kBlockK, 0, &full_bar[i]);
             for (int i = pre; i < nload; i++) {
@@ -205,7 +188,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     if (warp >= 2) {
         asm volatile("griddepcontrol.wait;" ::: "memory");  // row scales and the residual come from earlier grids
         // everything the finish needs from global memory is requested before waiting for the accumulators
-        if (p.tp.mode != 2 && et < 32) sh_ascale[et] = et < p.M ? p.ascale[et] : 0.f;
+        if (et < 32) sh_ascale[et] = et < p.M ? p.ascale[et] : 0.f;
         if (n_own < p.N) wscale = to_f32<OutT>(scale_p[n_own]);
         if (S == 1) {
 #pragma unroll
@@ -225,9 +208,6 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         tc_fence_after();
         // warp-uniform, because tcgen05.ld below must be executed by whole warps
         have_acc = __all_sync(0xffffffffu, ok && nkb > 0 && !*(volatile int *)&abort_flag);
-        // gathered rows: their scales were delivered with them, and the accumulators only complete after the producer has seen
-        // every row arrive, so they are read here (from L2: a peer wrote them)
-        if (p.tp.mode == 2 && et < 32) sh_ascale[et] = et < p.M ? __ldcg(&p.ascale[et]) : 0.f;
         asm volatile("bar.sync 1, 128;" ::: "memory");  // sh_ascale visible to the four epilogue warps (128 threads)
     }
     // The accumulators are read 48 columns (16 activation rows x 3 limbs) at a time to keep registers in check.
@@ -258,10 +238,14 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         float v = __fmul_rn(__fmul_rn((float)sum, sh_ascale[m]), wscale);
         if (resid_p) v = __fadd_rn(round_store<OutT>(v), resv);
         if (p.tp.mode == 1) {
-            // partial row m goes to the rank that owns it, into the slot of this rank: one 8-byte store {value, tag}, possibly
-            // over NVLink; the reader re-reads a word until it sees this reduction's tag, so no fence or flag follows
-            const int owner = m % p.tp.world, local = m / p.tp.world;
-            p.tp.part[owner][((size_t)p.tp.rank * p.tp.rows_cap + local) * p.N + n_own] = make_uint2(__float_as_uint(v), tp_tag);
+            // a partial sum goes to slot [this rank] of EVERY rank's buffer: one 8-byte store {value, tag} per destination,
+            // over NVLink for the peers; the reader re-reads a word until it sees this reduction's tag, so no fence or flag
+            // follows
+            const uint2 word = make_uint2(__float_as_uint(v), tp_tag);
+            const size_t idx = ((size_t)p.tp.rank * p.tp.max_rows + m) * p.N + n_own;
+#pragma unroll
+            for (int r = 0; r < kTpMaxRanks; r++)
+                if (r < p.tp.world && !p.tp.skip) p.tp.part[r][idx] = word;
         } else {
             out_p[(size_t)m * p.N + n_own] = from_f32<OutT>(v);
         }
@@ -704,7 +688,7 @@ int i8_gemm_launch(cudaStream_t st, void *out, const void *act, const int8_t *wq
 }
 
 // tp: tensor-parallel form of the launch or null.  limbs_ext / ascale_ext: activation limbs that live outside the workspace
-// (the gathered rows of a tensor-parallel step); the workspace then only carries the status word.
+// (the workspace then only carries the status word).
 int i8_gemm_launch_tp(cudaStream_t st, void *out, const void *act, const int8_t *wq, const void *scale, const void *resid,
                       int M, int N, int K, int act_dtype, int out_dtype, void *workspace, size_t workspace_bytes, const I8Tp *tp,
                       const int8_t *limbs_ext, const float *ascale_ext) {

@@ -138,7 +138,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
                        (size_t)std::max(H, m.ffn) * 4 <= 200 * 1024;
     // decode steps of a tensor-parallel model: the reduction fused with its neighbours over peer memory (tp_fused.cuh)
     const bool tp_fused = tp > 1 && m.tp_attached && fused && S == 1 && M <= m.tp.lay.max_rows && Nq % 16 == 0 && m.weights_aligned;
-    bool gathered = false;  // the activations of the next column-parallel product are the limb rows delivered by a fused reduction
+    bool reduced_limbs = false;  // a fused reduction left the limbs of the next product in the workspace
 
     // prefill chunks (more than 32 rows): RMSNorm and Swish*Mul write the two limbs of the prefill kernel themselves
     if (S >= 64 && dt != MYNN_F32 && (D == 64 || D == 128)) m.tc_attention_ran = true;  // the attention launcher may pick the tcgen05 kernels
@@ -148,15 +148,18 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     bool n_limbs2 = false;  // the last norm left two-limb rows in the workspace instead of m.n
 
     // norm(x [+ part]) feeding a DequantMatMul: either limbs in the workspace (fused) or the bf16 tensor m.n
-    auto reduce = [&](int buf, const void *w) -> int {  // fused reduction of the partial sums in buffer `buf`
+    auto push = [&](int buf, const void *act, const int8_t *w, const void *scale, int K) -> int {  // row-parallel product
         int skip = 0, want = 2;
-        if (g_inject_stall.compare_exchange_strong(want, 0)) skip = 1;  // test aid: this launch delivers nothing to the peers
-        gathered = w != nullptr;
-        return launch_tp_reduce_norm_gather(st, dt, m.tp, buf, m.x, w, c.rms_eps, M, skip);
+        if (g_inject_stall.compare_exchange_strong(want, 0)) skip = 1;  // test aid: this launch delivers nothing
+        return launch_tp_gemm_push(st, m.tp, buf, act, w, (const float *)scale, M, H, K, dt, m.gemm_ws, m.gemm_ws_bytes, skip);
+    };
+    auto reduce = [&](int buf, const void *w) -> int {  // fused reduction of the partial sums in buffer `buf`
+        reduced_limbs = w != nullptr;
+        return launch_tp_reduce_norm_limbs(st, dt, m.tp, buf, m.gemm_ws, m.gemm_ws_bytes, m.x, w, c.rms_eps, M);
     };
     auto norm = [&](const void *w, const float *part, int rows, const void *src) -> int {
         n_limbs2 = false;
-        gathered = false;
+        reduced_limbs = false;
         if (fused && rows <= kI8MaxRows)
             return launch_rms_norm_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, nullptr, part ? m.x : nullptr, src, part, w,
                                          c.rms_eps, rows, H);
@@ -168,7 +171,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         return mynn_b200_rms_norm(st, m.n, src, w, c.rms_eps, rows, H, dt);
     };
     auto gemm_n = [&](void *out, const int8_t *w, const void *scale, int rows, int N, int out_dtype) -> int {
-        if (gathered) return launch_tp_gemm_gathered(st, m.tp, out, w, scale, rows, N, out_dtype, m.gemm_ws, m.gemm_ws_bytes);
+        if (reduced_limbs) return gemm_prequant(st, m, out, w, scale, nullptr, rows, N, H, out_dtype);
         if (fused && rows <= kI8MaxRows) return gemm_prequant(st, m, out, w, scale, nullptr, rows, N, H, out_dtype);
         if (n_limbs2) return gemm_prequant2(st, m, out, w, scale, nullptr, rows, N, H, out_dtype);
         return gemm(st, m, out, m.n, w, scale, nullptr, rows, N, H, out_dtype);
@@ -257,8 +260,8 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
             }
             RC(norm(L.ln2, nullptr, M, m.x));
         } else if (tp_fused) {
-            // partial rows go straight to their owners; the owners finish them and deliver the normed rows to everybody
-            RC(launch_tp_gemm_scatter(st, m.tp, 0, attn_limbs ? nullptr : m.attn, L.wo, (const float *)L.so, M, H, Nq, dt, m.gemm_ws, m.gemm_ws_bytes));
+            // the partial sums go straight into every rank's memory; each rank then sums, adds, norms and writes the limbs
+            RC(push(0, attn_limbs ? nullptr : m.attn, L.wo, L.so, Nq));
             RC(reduce(0, L.ln2));
         } else {
             if (attn_limbs) RC(gemm_prequant(st, m, m.part, L.wo, L.so, nullptr, M, H, Nq, MYNN_F32));
@@ -299,7 +302,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
             else RC(gemm(st, m, m.x, m.h, L.wd, L.sd, m.x, M, H, m.ffn, dt));
             if (!last) RC(norm(next_norm, nullptr, M, m.x));
         } else if (tp_fused) {
-            RC(launch_tp_gemm_scatter(st, m.tp, 1, fuse_mlp ? nullptr : m.h, L.wd, (const float *)L.sd, M, H, m.ffn, dt, m.gemm_ws, m.gemm_ws_bytes));
+            RC(push(1, fuse_mlp ? nullptr : m.h, L.wd, L.sd, m.ffn));
             RC(reduce(1, last ? m.final_norm : next_norm));  // after the last layer: the final norm, whose rows feed lm_head
         } else {
             if (fuse_mlp) RC(gemm_prequant(st, m, m.part, L.wd, L.sd, nullptr, M, H, m.ffn, MYNN_F32));
@@ -318,8 +321,8 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
         xl = m.last_x;
     }
     const bool fused_head = m.gemm_ws != nullptr && B <= kI8MaxRows && H % 16 == 0 && (size_t)H * 4 <= 200 * 1024;
-    if (gathered) {  // the last fused reduction applied the final norm and delivered its rows
-        RC(launch_tp_gemm_gathered(st, m.tp, m.logits, m.lm_w, m.lm_scale, B, m.vocab_l, dt, m.gemm_ws, m.gemm_ws_bytes));
+    if (reduced_limbs) {  // the last fused reduction applied the final norm and left its limbs
+        RC(gemm_prequant(st, m, m.logits, m.lm_w, m.lm_scale, nullptr, B, m.vocab_l, H, dt));
     } else if (fused_head) {
         RC(launch_rms_norm_limbs(st, dt, m.gemm_ws, m.gemm_ws_bytes, nullptr, nullptr, xl, nullptr, m.final_norm, c.rms_eps, B, H));
         RC(gemm_prequant(st, m, m.logits, m.lm_w, m.lm_scale, nullptr, B, m.vocab_l, H, dt));

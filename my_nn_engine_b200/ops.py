@@ -383,37 +383,24 @@ def tp_block_bytes(max_rows: int, hidden: int, world: int) -> int:
     return ffi.lib().mynn_b200_tp_block_bytes(max_rows, hidden, world)
 
 
-def tp_dequant_matmul_scatter(group: TpGroup, buffer: int, act, wq, scale, workspace="auto"):
-    """Row-parallel DequantMatMul of this rank's K shard; the f32 partial rows go to the ranks that own them."""
+def tp_dequant_matmul_push(group: TpGroup, buffer: int, act, wq, scale, workspace="auto"):
+    """Row-parallel DequantMatMul of this rank's K shard; the f32 partial sums go into every rank's block."""
     n, k = wq.shape
     m = act.numel() // k
     if n != group.hidden or scale.dtype != torch.float32:
-        raise ValueError("scatter: wq must have `hidden` rows and an f32 scale")
+        raise ValueError("push: wq must have `hidden` rows and an f32 scale")
     if isinstance(workspace, str):
         workspace = dequant_matmul_workspace(m, n, k, act.device)
-    ffi.check(ffi.lib().mynn_b200_tp_dequant_matmul_scatter(_stream(), ctypes.byref(group.c), buffer, _ptr(act), _ptr(wq), _ptr(scale), m, k,
-                                                            _dt(act), _ptr(workspace), workspace.numel()))
+    ffi.check(ffi.lib().mynn_b200_tp_dequant_matmul_push(_stream(), ctypes.byref(group.c), buffer, _ptr(act), _ptr(wq), _ptr(scale), m, k,
+                                                         _dt(act), _ptr(workspace), workspace.numel()))
 
 
-def tp_reduce_norm_gather(group: TpGroup, buffer: int, x, weight, eps: float):
-    """Finish the rows this rank owns (sum of partials, residual add into ``x``, RMSNorm) and deliver them to every rank."""
+def tp_reduce_norm(group: TpGroup, buffer: int, x, weight, eps: float, workspace):
+    """Sum the partial rows of all ranks, add them to ``x``, RMSNorm; the result is left in ``workspace`` as the activation of
+    the DequantMatMul that follows (``dequant_matmul_same_act`` with the same workspace)."""
     m = x.numel() // group.hidden
-    ffi.check(ffi.lib().mynn_b200_tp_reduce_norm_gather(_stream(), ctypes.byref(group.c), buffer, _ptr(x),
-                                                        None if weight is None else _ptr(weight), float(eps), m, _dt(x)))
-
-
-def tp_dequant_matmul_gathered(group: TpGroup, wq, scale, m: int, out=None, workspace="auto"):
-    """Column-parallel DequantMatMul over the rows delivered by the last ``tp_reduce_norm_gather``."""
-    n, k = wq.shape
-    if k != group.hidden:
-        raise ValueError("gathered: K must equal the group's hidden size")
-    if out is None:
-        out = torch.empty((m, n), dtype=scale.dtype, device=wq.device)
-    if isinstance(workspace, str):
-        workspace = dequant_matmul_workspace(m, n, k, wq.device)
-    ffi.check(ffi.lib().mynn_b200_tp_dequant_matmul_gathered(_stream(), ctypes.byref(group.c), _ptr(out), _ptr(wq), _ptr(scale), m, n,
-                                                             _dt(scale), _ptr(workspace), workspace.numel()))
-    return out
+    ffi.check(ffi.lib().mynn_b200_tp_reduce_norm(_stream(), ctypes.byref(group.c), buffer, _ptr(x), None if weight is None else _ptr(weight),
+                                                 float(eps), m, _dt(x), _ptr(workspace), workspace.numel()))
 
 
 def tp_check(group: TpGroup):

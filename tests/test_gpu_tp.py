@@ -1,6 +1,6 @@
 """Tensor-parallel decode on 2, 4 and 8 GPUs (each case is skipped when the box has fewer): every rank's logits / greedy ids
 against the CPU ORACLE of the unsharded model, with the per-layer reduction done either by the fused peer-memory operators
-(row-parallel product scatters its partial rows, the owners reduce + add + norm, the next product gathers the rows) or by
+(the row-parallel product stores its tagged partial sums into every rank's memory, each rank reduces + adds + norms) or by
 ncclAllReduce inside the captured step.  Ranks are child processes with NVLS off; failures are made on the host (a rank
 that leaves a delivery out), no GPU fault is provoked, and every device-side wait is bounded."""
 import os
@@ -154,13 +154,14 @@ def _stall_rank_main(rank, world, port, q):
     m.step(tok, 0)  # a clean step first
     ffi.set_option(ffi.OPT_WAIT_BUDGET_US, 50000)
     if rank == 1:
-        ffi.set_option(ffi.OPT_INJECT_STALL, 2)  # this rank's next reduction delivers nothing
+        ffi.set_option(ffi.OPT_INJECT_STALL, 2)  # this rank's next row-parallel product delivers nothing
     code = 0
     try:
         m.step(tok, 1)
     except ffi.MynnError as e:
         code = e.code
-    q.put((rank, code))
+    again = m.step(tok, 1).clone()  # the ranks are in step again: this one succeeds (and overwrites the broken row)
+    q.put((rank, code, again.tolist()))
     dist.barrier()  # leave together, with nothing in flight
     m.close()
     collective.destroy_communicator()
@@ -169,13 +170,14 @@ def _stall_rank_main(rank, world, port, q):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_a_rank_that_delivers_nothing_is_reported_not_waited_for():
-    """Rank 1 leaves the deliveries of one reduction out (host-side switch).  Every rank's next product waits 50 ms for the
-    missing rows, records its status and carries on; the step returns MYNN_E_COMM on the host, and both ranks exit
-    cleanly."""
+    """Rank 1 leaves the deliveries of one row-parallel product out (host-side switch).  Every rank's reduction waits 50 ms for
+    the missing partial sums, records its status and carries on; the step returns MYNN_E_COMM on the host; the following step
+    is clean again on both ranks (the tags only count reductions); both ranks exit cleanly."""
     from my_nn_engine_b200 import ffi
     q, procs = _spawn(2, _stall_rank_main, ())
-    got = dict(q.get(timeout=300) for _ in range(2))
+    got = {r: (c, ids) for r, c, ids in (q.get(timeout=300) for _ in range(2))}
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
-    assert got[0] == ffi.E_COMM and got[1] == ffi.E_COMM
+    assert got[0][0] == ffi.E_COMM and got[1][0] == ffi.E_COMM
+    assert got[0][1] == got[1][1]

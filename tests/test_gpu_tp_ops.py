@@ -1,8 +1,8 @@
-"""The fused tensor-parallel operators (scatter DequantMatMul -> reduce + add + RMSNorm -> gathered DequantMatMul) on ONE
-GPU: all ranks of a group live in this process and their calls are issued in lock step (every scatter before any reduce,
-every reduce before any gathered product), so every cross-rank wait is already satisfied when its kernel starts and no
-kernel ever waits for one that has not run.  The results are compared with the CPU oracle of the unsharded operators.
-The two bounded waits are also made to run out, by leaving a rank's call out, with a 20 ms budget."""
+"""The fused tensor-parallel operators (row-parallel DequantMatMul that pushes its partial sums -> reduce + add + RMSNorm ->
+the next DequantMatMul) on ONE GPU: all ranks of a group live in this process and their calls are issued in lock step (every
+push before any reduce), so every cross-rank wait is already satisfied when its kernel starts and no kernel ever waits for
+one that has not run.  The results are compared with the CPU oracle of the unsharded operators.  The bounded wait is also
+made to run out, by leaving a rank's product out, with a 20 ms budget."""
 import numpy as np
 import pytest
 import torch
@@ -55,31 +55,25 @@ def test_lock_step_ranks_match_the_unsharded_oracle(world, m, hidden, k_total, n
         s_dev = torch.from_numpy(s_row).cuda()
         wn_dev = torch.from_numpy(w_norm).bfloat16().cuda()
         wc_dev, sc_dev = torch.from_numpy(w_col).cuda(), torch.from_numpy(s_col).bfloat16().cuda()
+        wss = [torch.zeros(1 << 20, dtype=torch.uint8, device="cuda") for _ in range(world)]  # each rank's GEMM workspace
         for r in range(world):
-            ops.tp_dequant_matmul_scatter(groups[r], buf, act_dev[r], wr_dev[r], s_dev)
+            ops.tp_dequant_matmul_push(groups[r], buf, act_dev[r], wr_dev[r], s_dev, workspace=wss[r])
+        outs = []
         for r in range(world):
-            ops.tp_reduce_norm_gather(groups[r], buf, xs[r], wn_dev, eps)
-        outs = [ops.tp_dequant_matmul_gathered(groups[r], wc_dev, sc_dev, m) for r in range(world)]
+            ops.tp_reduce_norm(groups[r], buf, xs[r], wn_dev, eps, wss[r])
+            outs.append(ops.dequant_matmul_same_act(xs[r], wc_dev, sc_dev, workspace=wss[r]))
         for r in range(world):
             ops.tp_check(groups[r])
         x_ref, y_ref = oracle_reduction(act, w_row, s_row, x_ref, w_norm, world, eps)
         want = R.dequant_matmul(y_ref, w_col, s_col)
         ulp = 2.0 ** -7
         for r in range(world):
-            own = list(range(r, m, world))  # empty for a rank beyond the last row
-            got_x = xs[r].float().cpu().numpy()[own]
-            assert not own or np.abs(got_x - x_ref[own]).max() <= 2 * ulp * np.abs(x_ref).max(), (it, r)
+            got_x = xs[r].float().cpu().numpy()
+            assert np.abs(got_x - x_ref).max() <= 2 * ulp * np.abs(x_ref).max(), (it, r)
             got = outs[r].float().cpu().numpy()
             assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max(), (it, r)
-            assert torch.equal(outs[r], outs[0])  # every rank received identical rows
-        # carry the device's own residual rows forward (each row from its owner), as the oracle carries x_ref
-        merged = np.zeros_like(x0)
-        for r in range(world):
-            own = list(range(r, m, world))
-            merged[own] = xs[r].float().cpu().numpy()[own]
-        x_ref = merged
-        for r in range(world):
-            xs[r].copy_(torch.from_numpy(merged).bfloat16())
+            assert torch.equal(outs[r], outs[0]) and torch.equal(xs[r], xs[0])  # every rank computes identical rows
+        x_ref = xs[0].float().cpu().numpy()  # carry the device's own residual rows forward, as the oracle carries x_ref
 
 
 def _small_problem(rng, hidden=256, k_total=512, m=8):
@@ -94,57 +88,46 @@ def _small_problem(rng, hidden=256, k_total=512, m=8):
 
 
 def test_wait_for_partial_sums_runs_out_when_a_rank_never_delivers():
-    """Two ranks; only rank 0 runs its scatter.  Rank 0's reduction waits 20 ms for rank 1's tiles, records status 21, finishes
-    and returns; tp_check reports MYNN_E_COMM once; a fresh group then works."""
+    """Two ranks; only rank 0 runs its product.  Rank 0's reduction waits 20 ms for rank 1's partial sums, records status 21,
+    finishes and returns; tp_check reports MYNN_E_COMM once.  The tags only count reductions, so the SAME group works again at
+    the next reduction, and so does a product whose deliveries were switched off by MYNN_OPT_INJECT_STALL = 2."""
     from my_nn_engine_b200 import ffi, ops
     rng = np.random.default_rng(1)
     w_row, s_row, act, x, w_norm, w_col, s_col = _small_problem(rng)
     groups = make_groups(2, 32, 256)
+    wss = [torch.zeros(1 << 18, dtype=torch.uint8, device="cuda") for _ in range(2)]
     ffi.set_option(ffi.OPT_WAIT_BUDGET_US, 20000)
     try:
-        ops.tp_dequant_matmul_scatter(groups[0], 0, act, w_row, s_row)
-        ops.tp_reduce_norm_gather(groups[0], 0, x, w_norm, 1e-5)
+        ops.tp_dequant_matmul_push(groups[0], 0, act, w_row, s_row, workspace=wss[0])
+        ops.tp_reduce_norm(groups[0], 0, x.clone(), w_norm, 1e-5, wss[0])
         with pytest.raises(ffi.MynnError) as err:
             ops.tp_check(groups[0])
         assert err.value.code == ffi.E_COMM and "21" in str(err.value)
         ops.tp_check(groups[0])  # reported once
-    finally:
-        ffi.set_option(ffi.OPT_WAIT_BUDGET_US, 2000000)
-    groups = make_groups(2, 32, 256)
-    for r in range(2):
-        ops.tp_dequant_matmul_scatter(groups[r], 0, act, w_row, s_row)
-    xs = [x.clone(), x.clone()]
-    for r in range(2):
-        ops.tp_reduce_norm_gather(groups[r], 0, xs[r], w_norm, 1e-5)
-    a = ops.tp_dequant_matmul_gathered(groups[0], w_col, s_col, 8)
-    b = ops.tp_dequant_matmul_gathered(groups[1], w_col, s_col, 8)
-    ops.tp_check(groups[0])
-    ops.tp_check(groups[1])
-    assert torch.equal(a, b) and torch.isfinite(a.float()).all()
-
-
-def test_wait_for_limb_rows_runs_out_when_a_rank_delivers_nothing():
-    """Both ranks scatter, but rank 1's reduction is told (MYNN_OPT_INJECT_STALL = 2) to deliver nothing: rank 0's gathered
-    product waits 20 ms for rank 1's rows, records status 22 and returns."""
-    from my_nn_engine_b200 import ffi, ops
-    rng = np.random.default_rng(2)
-    w_row, s_row, act, x, w_norm, w_col, s_col = _small_problem(rng)
-    groups = make_groups(2, 32, 256)
-    ffi.set_option(ffi.OPT_WAIT_BUDGET_US, 20000)
-    try:
-        for r in range(2):
-            ops.tp_dequant_matmul_scatter(groups[r], 1, act, w_row, s_row)
-        xs = [x.clone(), x.clone()]
-        ops.tp_reduce_norm_gather(groups[0], 1, xs[0], w_norm, 1e-5)
+        # rank 1 catches up with the reduction it missed (nobody delivers to it: it times out as well)
+        ops.tp_reduce_norm(groups[1], 0, x.clone(), w_norm, 1e-5, wss[1])
+        with pytest.raises(ffi.MynnError):
+            ops.tp_check(groups[1])
+        # next reduction, on the other buffer, with rank 1's deliveries switched off: both time out
+        ops.tp_dequant_matmul_push(groups[0], 1, act, w_row, s_row, workspace=wss[0])
         ffi.set_option(ffi.OPT_INJECT_STALL, 2)
-        ops.tp_reduce_norm_gather(groups[1], 1, xs[1], w_norm, 1e-5)
-        ops.tp_dequant_matmul_gathered(groups[0], w_col, s_col, 8)
-        with pytest.raises(ffi.MynnError) as err:
-            ops.tp_check(groups[0])
-        assert err.value.code == ffi.E_COMM and "22" in str(err.value)
+        ops.tp_dequant_matmul_push(groups[1], 1, act, w_row, s_row, workspace=wss[1])
+        for r in range(2):
+            ops.tp_reduce_norm(groups[r], 1, x.clone(), w_norm, 1e-5, wss[r])
+            with pytest.raises(ffi.MynnError):
+                ops.tp_check(groups[r])
     finally:
         ffi.set_option(ffi.OPT_INJECT_STALL, 0)
         ffi.set_option(ffi.OPT_WAIT_BUDGET_US, 2000000)
-    # the context is intact: an ordinary product still runs
-    out = ops.dequant_matmul(act, w_row, s_row.bfloat16())
-    assert torch.isfinite(out.float()).all()
+    # the same group, in step again: a complete reduction on buffer 0
+    for r in range(2):
+        ops.tp_dequant_matmul_push(groups[r], 0, act, w_row, s_row, workspace=wss[r])
+    xs, outs = [x.clone(), x.clone()], []
+    for r in range(2):
+        ops.tp_reduce_norm(groups[r], 0, xs[r], w_norm, 1e-5, wss[r])
+        outs.append(ops.dequant_matmul_same_act(xs[r], w_col, s_col, workspace=wss[r]))
+        ops.tp_check(groups[r])
+    assert torch.equal(outs[0], outs[1]) and torch.isfinite(outs[0].float()).all()
+    part = R.dequant_matmul(act.float().cpu().numpy(), w_row.cpu().numpy(), s_row.cpu().numpy())
+    want_x = R.round_bf16(x.float().cpu().numpy() + R.round_bf16(part + part))
+    assert np.abs(xs[0].float().cpu().numpy() - want_x).max() <= 2.0 ** -6 * np.abs(want_x).max()
