@@ -353,7 +353,11 @@ def run_gpu_arm(args, cfg):
                 "gpu_launches": int(launches_per_step * steps),
                 "launches_per_step": int(launches_per_step),
                 "token_ids_first_8_steps_crc32": zlib.crc32(ids.astype("<i4").tobytes()),
-                "token_ids_first_step_crc32": zlib.crc32(ids[0].astype("<i4").tobytes())}
+                "token_ids_first_step_crc32": zlib.crc32(ids[0].astype("<i4").tobytes()),
+                # the ids themselves, so that runs at different N can be compared pick by pick: the logits of a random-init model
+                # are nearly uniform, and a top-2 gap below the bf16 resolution may fall either way when the f32 summation order
+                # changes with the number of ranks
+                "token_ids_first_step": [int(t) for t in ids[0]]}
         if e2e_logits:
             line["e2e_logits"] = e2e_logits
         for key, fig in (("roofline", roof), ("gemm_kernel", gemm_all), ("attention_kernel", attn_all)):
