@@ -50,8 +50,13 @@ const char *mynn_b200_last_error(void);
  *                             DequantMatMul launch leaves out its last TMA stage, so that its MMA thread's wait runs out
  *                             (status 2 in the workspace); 2 = the NEXT row-parallel product of a tensor-parallel step delivers
  *                             none of its partial sums, so that the reductions' waits run out (status 21 / MYNN_E_COMM).  Nothing faults or
- *                             hangs: the kernels return after the wait budget. */
-enum { MYNN_OPT_WAIT_BUDGET_US = 1, MYNN_OPT_KSPLIT = 2, MYNN_OPT_PREFILL_ATTENTION = 3, MYNN_OPT_INJECT_STALL = 4 };
+ *                             hangs: the kernels return after the wait budget.
+ *   MYNN_OPT_FUSE_ROPE        1 (default): in a decode step of the model entry points the attention kernel rotates q and the
+ *                             new key itself and appends the new key / value rows to the cache (one launch less per layer);
+ *                             0: RoPE + append run as a kernel of their own in front of it.  Read when a model's step is
+ *                             recorded.  The rotated rows have the same bits either way; the softmax takes the new row in a tile of its own,
+ *                             so outputs agree to rounding of the f32 sums, not to the bit. */
+enum { MYNN_OPT_WAIT_BUDGET_US = 1, MYNN_OPT_KSPLIT = 2, MYNN_OPT_PREFILL_ATTENTION = 3, MYNN_OPT_INJECT_STALL = 4, MYNN_OPT_FUSE_ROPE = 5 };
 int mynn_b200_set_option(int option, long long value);
 
 /* Library/ABI version and the SM architecture the kernels were compiled for (100 for sm_100a). */

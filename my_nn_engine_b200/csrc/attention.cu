@@ -49,14 +49,39 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
     const T *kbase = reinterpret_cast<const T *>(p.k) + (size_t)(b * p.Hkv + kvh) * p.cache_seq * D;
     const T *vbase = reinterpret_cast<const T *>(p.v) + (size_t)(b * p.Hkv + kvh) * p.cache_seq * D;
 
+    const bool fused = p.fused_k != nullptr;  // RoPE + KV append happen here instead of in a kernel of their own
+    const int new_row = fused ? *p.fused_row : -1;
+    const size_t tab = fused ? (size_t)(*p.fused_pos) * D : 0;
+    const T *cos_t = reinterpret_cast<const T *>(p.cos_t), *sin_t = reinterpret_cast<const T *>(p.sin_t);
+    // x rotated against its partner xp (the element half a head away): low half x c - xp s, high half x c + xp s, rounded to
+    // the storage type as the stand-alone RoPE kernel rounds it
+    auto rot4 = [&](uint2 x, uint2 xp, int d0, bool low) {
+        const uint2 c = *reinterpret_cast<const uint2 *>(cos_t + tab + d0), sn = *reinterpret_cast<const uint2 *>(sin_t + tab + d0);
+        const T *xe = reinterpret_cast<const T *>(&x), *pe = reinterpret_cast<const T *>(&xp);
+        const T *ce = reinterpret_cast<const T *>(&c), *se = reinterpret_cast<const T *>(&sn);
+        uint2 r;
+        T *re = reinterpret_cast<T *>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float a = to_f32<T>(xe[e]), b_ = to_f32<T>(pe[e]);
+            re[e] = from_f32<T>(low ? rope_low(a, b_, to_f32<T>(ce[e]), to_f32<T>(se[e])) : rope_high(b_, a, to_f32<T>(ce[e]), to_f32<T>(se[e])));
+        }
+        return r;
+    };
+
     // Q fragments of head g (zero for padding rows g >= G)
     uint32_t qa0[KS], qa2[KS];
     {
-        const T *qrow = reinterpret_cast<const T *>(p.q) + (size_t)(b * p.Hq + kvh * G + min(g, G - 1)) * D;
+        const T *qrow = fused ? reinterpret_cast<const T *>(p.q) + (size_t)b * p.qkv_stride + (size_t)(kvh * G + min(g, G - 1)) * D
+                              : reinterpret_cast<const T *>(p.q) + (size_t)(b * p.Hq + kvh * G + min(g, G - 1)) * D;
+        uint2 raw[KS];
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) raw[ks] = *reinterpret_cast<const uint2 *>(qrow + 8 * (t + 4 * (ks >> 1)) + 4 * (ks & 1));
 #pragma unroll
         for (int ks = 0; ks < KS; ks++) {
+            // the partner of elements d0 .. d0+3 lies half a head away: fragment ks ^ (KS / 2) of this same lane
             const int d0 = 8 * (t + 4 * (ks >> 1)) + 4 * (ks & 1);
-            uint2 w = *reinterpret_cast<const uint2 *>(qrow + d0);
+            const uint2 w = fused ? rot4(raw[ks], raw[ks ^ (KS / 2)], d0, d0 < D / 2) : raw[ks];
             qa0[ks] = g < G ? w.x : 0u;
             qa2[ks] = g < G ? w.y : 0u;
         }
@@ -70,24 +95,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
 #pragma unroll
         for (int i = 0; i < 4; i++) o[j][i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
-    const int last = row_end - 1;
 
-    for (int base = row_beg + 16 * warp; base < row_end; base += 16 * kAttnWarps) {
-        // ---- issue all loads of this tile (rows past the end are clamped to a valid row and masked below) ----
-        uint4 kr[2][KCH], vr[4][VH];
-#pragma unroll
-        for (int nt = 0; nt < 2; nt++) {
-            const T *kp = kbase + (size_t)min(base + 8 * nt + g, last) * D + 8 * t;
-#pragma unroll
-            for (int i = 0; i < KCH; i++) kr[nt][i] = ldg_16(kp + 32 * i);
-        }
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const int row = base + 2 * t + (r & 1) + 8 * (r >> 1);
-            const T *vp = vbase + (size_t)min(row, last) * D + 8 * g;
-#pragma unroll
-            for (int h = 0; h < VH; h++) vr[r][h] = ldg_16(vp + 64 * h);
-        }
+    // One 16-row tile whose K / V fragments are in registers: rows base .. base+15, of which those below `end` count.
+    auto tile = [&](const uint4 (&kr)[2][KCH], const uint4 (&vr)[4][VH], int base, int end) {
         // ---- S = Q K^T: s[nt][e] = S[head g][kv row base + 8nt + 2t + e] ----
         float s[2][4];
 #pragma unroll
@@ -107,7 +117,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
 #pragma unroll
             for (int e = 0; e < 2; e++) {
                 const int row = base + 8 * nt + 2 * t + e;
-                pv[nt][e] = row < row_end ? s[nt][e] * p.scale : -INFINITY;
+                pv[nt][e] = row < end ? s[nt][e] * p.scale : -INFINITY;
                 tmax = fmaxf(tmax, pv[nt][e]);
             }
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
@@ -152,6 +162,67 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
                 mma_kv<T>(acc, a0, a1, a2, a3, pb0l, pb1l);
             }
         }
+    };
+
+    // the rows this CTA reads from the cache: with the fused append the new row is not there yet
+    const int cache_end = fused ? min(row_end, new_row) : row_end;
+    const int last = cache_end - 1;
+    for (int base = row_beg + 16 * warp; base < cache_end; base += 16 * kAttnWarps) {
+        // ---- issue all loads of this tile (rows past the end are clamped to a valid row and masked in the tile) ----
+        uint4 kr[2][KCH], vr[4][VH];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            const T *kp = kbase + (size_t)min(base + 8 * nt + g, last) * D + 8 * t;
+#pragma unroll
+            for (int i = 0; i < KCH; i++) kr[nt][i] = ldg_16(kp + 32 * i);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int row = base + 2 * t + (r & 1) + 8 * (r >> 1);
+            const T *vp = vbase + (size_t)min(row, last) * D + 8 * g;
+#pragma unroll
+            for (int h = 0; h < VH; h++) vr[r][h] = ldg_16(vp + 64 * h);
+        }
+        tile(kr, vr, base, cache_end);
+    }
+    if (fused && warp == 0 && new_row >= row_beg && new_row < row_end) {
+        // The new row of this (batch, kv head): rotate the key, store key and value into the cache for the steps to come, and
+        // run them through one more tile in which only row 0 counts.  K row 0 of the tile lives in lanes g == 0 (chunks
+        // 8t + 32i), V row 0 in lanes t == 0 (chunks 8g + 64h); everything else is zero.
+        uint4 kr[2][KCH], vr[4][VH];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int i = 0; i < KCH; i++) kr[nt][i] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+            for (int h = 0; h < VH; h++) vr[r][h] = make_uint4(0u, 0u, 0u, 0u);
+        T *kcache = const_cast<T *>(kbase) + (size_t)new_row * D, *vcache = const_cast<T *>(vbase) + (size_t)new_row * D;
+        if (g == 0) {
+            const T *kraw = reinterpret_cast<const T *>(p.fused_k) + (size_t)b * p.qkv_stride + (size_t)kvh * D;
+            uint4 raw[KCH];
+#pragma unroll
+            for (int i = 0; i < KCH; i++) raw[i] = *reinterpret_cast<const uint4 *>(kraw + 8 * t + 32 * i);
+#pragma unroll
+            for (int i = 0; i < KCH; i++) {
+                const int d0 = 8 * t + 32 * i;
+                const uint4 x = raw[i], xp = raw[i ^ (KCH / 2)];
+                const uint2 lo = rot4(make_uint2(x.x, x.y), make_uint2(xp.x, xp.y), d0, d0 < D / 2);
+                const uint2 hi = rot4(make_uint2(x.z, x.w), make_uint2(xp.z, xp.w), d0 + 4, d0 < D / 2);
+                kr[0][i] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                *reinterpret_cast<uint4 *>(kcache + d0) = kr[0][i];
+            }
+        }
+        if (t == 0) {
+            const T *vraw = reinterpret_cast<const T *>(p.fused_v) + (size_t)b * p.qkv_stride + (size_t)kvh * D;
+#pragma unroll
+            for (int h = 0; h < VH; h++) {
+                vr[0][h] = *reinterpret_cast<const uint4 *>(vraw + 8 * g + 64 * h);
+                *reinterpret_cast<uint4 *>(vcache + 8 * g + 64 * h) = vr[0][h];
+            }
+        }
+        tile(kr, vr, new_row, new_row + 1);
     }
 
     decode_tail<T, D, VH * 4, Map16>(p, o, m_run, l_run);
@@ -350,7 +421,7 @@ bool mynn::attention_decode_fast_path(int Sq, int D, int Hq, int Hkv, int dtype,
 int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
                            int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
                            const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
-                           size_t workspace_bytes, int out_bshd, int8_t *limbs_out, float *ascale_out) {
+                           size_t workspace_bytes, int out_bshd, int8_t *limbs_out, float *ascale_out, const AttentionFuse *fuse) {
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Sq < 0 || D <= 0 || cache_seq_len < 0 || active_seq_kv < 0)
         return fail(MYNN_E_ARG, "attention: bad shape");
     if (Hq % Hkv != 0) return fail(MYNN_E_ARG, "attention: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
@@ -360,7 +431,7 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
     const int G = Hq / Hkv;
     const bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % 16) == 0;
     const bool fast = Sq == 1 && (D == 64 || D == 128) && G <= 8 && dtype != MYNN_F32 && aligned;
-    if (!fast && limbs_out) return fail(MYNN_E_UNSUPPORTED, "attention: the limb output exists only on the decode fast path");
+    if (!fast && (limbs_out || fuse)) return fail(MYNN_E_UNSUPPORTED, "attention: the limb output and the fused RoPE + append exist only on the decode fast path");
     if (!fast) {
         const bool use_tiled = g_prefill_attention_mode >= 0;  // -1: only the row-serial kernel
         if (use_tiled && attention_prefill_tc_supported(B, Hq, Hkv, Sq, D, cache_seq_len, dtype, q, k, v, out))
@@ -392,6 +463,18 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
     p.v_scale = nullptr;
     p.limbs = limbs_out;
     p.ascale = ascale_out;
+    if (fuse) {
+        if (!fuse->k_new || !fuse->v_new || !fuse->cos_t || !fuse->sin_t || !fuse->pos || !fuse->row || fuse->qkv_stride % 8 ||
+            (((uintptr_t)fuse->k_new | (uintptr_t)fuse->v_new | (uintptr_t)fuse->cos_t | (uintptr_t)fuse->sin_t) % 16))
+            return fail(MYNN_E_ARG, "attention: fused RoPE + append needs 16-byte aligned rows, tables and device scalars");
+        p.fused_k = fuse->k_new;
+        p.fused_v = fuse->v_new;
+        p.qkv_stride = fuse->qkv_stride;
+        p.cos_t = fuse->cos_t;
+        p.sin_t = fuse->sin_t;
+        p.fused_pos = fuse->pos;
+        p.fused_row = fuse->row;
+    }
     if (int rc = decode_bind_workspace(p, B, D, workspace, workspace_bytes)) return rc;
     if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B) : launch_decode<__nv_bfloat16, 128>(st, p, B);
     return D == 64 ? launch_decode<__half, 64>(st, p, B) : launch_decode<__half, 128>(st, p, B);

@@ -64,6 +64,15 @@ struct DecodeParams {
     int8_t *limbs;        // [3 B][Hq * D] limb rows (3 b + l), or null
     float *ascale;        // [B] row scales
     unsigned *row_ticket; // [B], zero before first use; re-zeroed by the CTA that converts the row
+    // Optional (16-bit decode kernel): RoPE and the KV append fused in.  q then points at the UNROTATED projection output
+    // (row b at q + b * qkv_stride elements, heads contiguous), fused_k / fused_v at the new key / value of (row b, kv head h)
+    // = fused_k + b * qkv_stride + h * D; the new row is rotated (k) at table row *fused_pos, written to cache row
+    // *fused_row, and takes part in the attention as row *fused_row; the cache is read for the rows before it.
+    const void *fused_k = nullptr, *fused_v = nullptr;
+    long long qkv_stride = 0;
+    const void *cos_t = nullptr, *sin_t = nullptr;
+    const int64_t *fused_pos = nullptr;
+    const int32_t *fused_row = nullptr;
 };
 
 // Called by every CTA that has stored final outputs of (batch b, one kv head): the last of the Hkv to arrive converts the

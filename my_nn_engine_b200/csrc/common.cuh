@@ -69,6 +69,12 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { retu
 template <>
 __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
+// One RoPE pair (xl, xh = the elements half a head apart) with the roundings of the engine's CPU kernel: two products and
+// one sum, each rounded to f32, never contracted into a fused multiply-add.  Every kernel that rotates uses these, so the
+// stand-alone RoPE kernel and the rotation inside the decode attention kernel give the same bits.
+__device__ __forceinline__ float rope_low(float xl, float xh, float c, float s) { return __fsub_rn(__fmul_rn(xl, c), __fmul_rn(xh, s)); }
+__device__ __forceinline__ float rope_high(float xl, float xh, float c, float s) { return __fadd_rn(__fmul_rn(xh, c), __fmul_rn(xl, s)); }
+
 // One store point: round to storage dtype and come back to f32.
 template <typename T>
 __device__ __forceinline__ float round_store(float v) { return to_f32<T>(from_f32<T>(v)); }
@@ -98,6 +104,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // Library options (mynn_b200_set_option).
 extern int g_ksplit_override;            // forced cluster K split of the DequantMatMul kernels, 0 = automatic
 extern int g_prefill_attention_mode;     // see MYNN_OPT_PREFILL_ATTENTION
+extern int g_fuse_rope;                  // see MYNN_OPT_FUSE_ROPE
 extern std::atomic<int> g_inject_stall;  // see MYNN_OPT_INJECT_STALL; consumed by the next launch it applies to
 
 // A plain launch through cudaLaunchKernelEx (no attributes); the name says which kernels belong to the decode chain.

@@ -94,8 +94,8 @@ __global__ void rope_kernel(T *out, const T *x, const T *cos_t, const T *sin_t, 
     const long long pos = position[row % S];
     const size_t ro = (size_t)row * D, to = (size_t)pos * D;
     const float xl = to_f32<T>(x[ro + j]), xh = to_f32<T>(x[ro + j + half]);
-    out[ro + j] = from_f32<T>(xl * to_f32<T>(cos_t[to + j]) - xh * to_f32<T>(sin_t[to + j]));
-    out[ro + j + half] = from_f32<T>(xh * to_f32<T>(cos_t[to + j + half]) + xl * to_f32<T>(sin_t[to + j + half]));
+    out[ro + j] = from_f32<T>(rope_low(xl, xh, to_f32<T>(cos_t[to + j]), to_f32<T>(sin_t[to + j])));
+    out[ro + j + half] = from_f32<T>(rope_high(xl, xh, to_f32<T>(cos_t[to + j + half]), to_f32<T>(sin_t[to + j + half])));
 }
 
 // ---- elementwise --------------------------------------------------------------------------------------
@@ -235,8 +235,8 @@ __global__ void rope_kv_append_kernel(T *q_out, T *k_cache, T *v_cache, const T 
         T *dst = is_q ? q_out + (((size_t)b * Hq + h) * S + s) * D : k_cache + (((size_t)b * Hkv + h) * cache_seq + cache_row) * D;
         for (int j = threadIdx.x; j < half; j += blockDim.x) {
             const float xl = to_f32<T>(src[j]), xh = to_f32<T>(src[j + half]);
-            dst[j] = from_f32<T>(xl * to_f32<T>(cr[j]) - xh * to_f32<T>(sr[j]));
-            dst[j + half] = from_f32<T>(xh * to_f32<T>(cr[j + half]) + xl * to_f32<T>(sr[j + half]));
+            dst[j] = from_f32<T>(rope_low(xl, xh, to_f32<T>(cr[j]), to_f32<T>(sr[j])));
+            dst[j + half] = from_f32<T>(rope_high(xl, xh, to_f32<T>(cr[j + half]), to_f32<T>(sr[j + half])));
         }
     } else {
         if (!in_cache) return;
@@ -288,8 +288,8 @@ rope_kv_append_vec_kernel(T *q_out, T *k_cache, T *v_cache, const T *q, const T 
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const float a = to_f32<T>(xl[i]), c = to_f32<T>(xh[i]);
-        ol[i] = from_f32<T>(a * to_f32<T>(cl[i]) - c * to_f32<T>(sl[i]));
-        oh[i] = from_f32<T>(c * to_f32<T>(ch[i]) + a * to_f32<T>(sh[i]));
+        ol[i] = from_f32<T>(rope_low(a, c, to_f32<T>(cl[i]), to_f32<T>(sl[i])));
+        oh[i] = from_f32<T>(rope_high(a, c, to_f32<T>(ch[i]), to_f32<T>(sh[i])));
     }
     *reinterpret_cast<uint4 *>(dst + j0) = *reinterpret_cast<const uint4 *>(ol);
     *reinterpret_cast<uint4 *>(dst + j0 + half) = *reinterpret_cast<const uint4 *>(oh);

@@ -75,8 +75,8 @@ rope_kv_append_q8_kernel(T *q_out, int8_t *k_cache, int8_t *v_cache, T *k_scale,
         T *dst = q_out + (((size_t)b * Hq + slot) * S + s) * D;
         for (int j = threadIdx.x; j < half; j += blockDim.x) {
             const float xl = to_f32<T>(src[j]), xh = to_f32<T>(src[j + half]);
-            dst[j] = from_f32<T>(xl * to_f32<T>(cr[j]) - xh * to_f32<T>(sr[j]));
-            dst[j + half] = from_f32<T>(xh * to_f32<T>(cr[j + half]) + xl * to_f32<T>(sr[j + half]));
+            dst[j] = from_f32<T>(rope_low(xl, xh, to_f32<T>(cr[j]), to_f32<T>(sr[j])));
+            dst[j + half] = from_f32<T>(rope_high(xl, xh, to_f32<T>(cr[j + half]), to_f32<T>(sr[j + half])));
         }
         return;
     }
@@ -90,8 +90,8 @@ rope_kv_append_q8_kernel(T *q_out, int8_t *k_cache, int8_t *v_cache, T *k_scale,
         const T *src = k + (size_t)row * k_stride + (size_t)h * D;
         for (int j = threadIdx.x; j < half; j += blockDim.x) {
             const float xl = to_f32<T>(src[j]), xh = to_f32<T>(src[j + half]);
-            const float lo = round_store<T>(xl * to_f32<T>(cr[j]) - xh * to_f32<T>(sr[j]));
-            const float hi = round_store<T>(xh * to_f32<T>(cr[j + half]) + xl * to_f32<T>(sr[j + half]));
+            const float lo = round_store<T>(rope_low(xl, xh, to_f32<T>(cr[j]), to_f32<T>(sr[j])));
+            const float hi = round_store<T>(rope_high(xl, xh, to_f32<T>(cr[j + half]), to_f32<T>(sr[j + half])));
             rowv[j] = lo;
             rowv[j + half] = hi;
             mx = fmaxf(mx, fmaxf(fabsf(lo), fabsf(hi)));

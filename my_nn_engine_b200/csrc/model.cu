@@ -236,14 +236,26 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
             RC(launch_attention(st, m.attn, m.q_rot, m.k_rot, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
                                 c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1));
         } else {
-            RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
-                                     S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
             // decode: the attention kernel also leaves its output rows as the activation limbs of o_proj
             attn_limbs = fused && S == 1 && Nq % 16 == 0 && (size_t)Nq * 4 <= 200 * 1024 &&
-                         attention_decode_fast_path(S, D, m.Hq, m.Hkv, dt, m.q_rot, L.kc, L.vc);
-            RC(launch_attention(st, m.attn, m.q_rot, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
-                                c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1,
-                                attn_limbs ? (int8_t *)m.gemm_ws + 512 : nullptr, attn_limbs ? (float *)((char *)m.gemm_ws + 256) : nullptr));
+                         attention_decode_fast_path(S, D, m.Hq, m.Hkv, dt, qb, L.kc, L.vc);
+            // ... and rotates q and the new key and appends the new key / value rows itself (one launch less per layer), when
+            // the projection output is one block whose rows and heads are 16-byte aligned
+            const bool fuse_rope = g_fuse_rope && attn_limbs && L.qkv_fused && qs % 8 == 0 && D % 32 == 0 &&
+                                   (((uintptr_t)kb | (uintptr_t)vb) % 16) == 0;
+            if (fuse_rope) {
+                const AttentionFuse fz = {kb, vb, qs, m.cos_t, m.sin_t, m.pos0_dev, m.past_dev};
+                RC(launch_attention(st, m.attn, qb, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len, c.max_seq_len,
+                                    m.active_dev, 0, dt, m.attn_ws, m.attn_ws_bytes, 1, (int8_t *)m.gemm_ws + 512,
+                                    (float *)((char *)m.gemm_ws + 256), &fz));
+            } else {
+                RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
+                                         S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
+                attn_limbs = attn_limbs && attention_decode_fast_path(S, D, m.Hq, m.Hkv, dt, m.q_rot, L.kc, L.vc);
+                RC(launch_attention(st, m.attn, m.q_rot, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
+                                    c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1,
+                                    attn_limbs ? (int8_t *)m.gemm_ws + 512 : nullptr, attn_limbs ? (float *)((char *)m.gemm_ws + 256) : nullptr));
+            }
         }
         if (tp == 1) {
             // x = round(x + round(o))

@@ -51,10 +51,21 @@ int launch_add_f32_rms_norm(cudaStream_t st, int dtype, void *sum_out, void *nor
 // Attention with a choice of output layout: out_bshd != 0 writes [B, Sq, Hq, D] instead of [B, Hq, Sq, D].
 // limbs_out / ascale_out (decode fast path only, see attention_decode_fast_path): the output rows are also left as
 // activation limbs [3 B][Hq * D] + row scales [B] for the DequantMatMul that follows; needs the workspace.
+// fuse (decode fast path only): RoPE and the KV append happen inside the attention kernel.  q is then the UNROTATED projection
+// output (row b at q + b * qkv_stride elements), k_new / v_new the new key / value rows with the same row stride; the new row
+// is rotated at table row *pos, stored to cache row *row, and attended to as that row (active_seq_kv must be *row + 1).
+struct AttentionFuse {
+    const void *k_new, *v_new;
+    long long qkv_stride;
+    const void *cos_t, *sin_t;
+    const int64_t *pos;
+    const int32_t *row;
+};
 int launch_attention(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
                      int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
                      const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
-                     size_t workspace_bytes, int out_bshd, int8_t *limbs_out = nullptr, float *ascale_out = nullptr);
+                     size_t workspace_bytes, int out_bshd, int8_t *limbs_out = nullptr, float *ascale_out = nullptr,
+                     const AttentionFuse *fuse = nullptr);
 bool attention_decode_fast_path(int Sq, int D, int Hq, int Hkv, int dtype, const void *q, const void *k, const void *v);
 
 // Tiled tensor-core attention for several query rows (prefill chunks); see attention_prefill.cu.

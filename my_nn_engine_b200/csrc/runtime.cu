@@ -23,6 +23,7 @@ void register_wait_budget_setter(int (*fn)(unsigned long long)) { wait_budget_se
 // Option state read by the launchers (defaults: automatic K split, tensor-core prefill attention, no injected stall).
 int g_ksplit_override = 0;
 int g_prefill_attention_mode = 1;
+int g_fuse_rope = 1;
 std::atomic<int> g_inject_stall{0};
 
 void set_error(const char *fmt, ...) {
@@ -72,6 +73,10 @@ extern "C" int mynn_b200_set_option(int option, long long value) {
         case MYNN_OPT_INJECT_STALL:
             if (value < 0 || value > 2) return fail(MYNN_E_ARG, "set_option: stall injection %lld outside [0, 2]", value);
             g_inject_stall.store((int)value);
+            return MYNN_OK;
+        case MYNN_OPT_FUSE_ROPE:
+            if (value != 0 && value != 1) return fail(MYNN_E_ARG, "set_option: fused RoPE must be 0 or 1");
+            g_fuse_rope = (int)value;
             return MYNN_OK;
         default:
             return fail(MYNN_E_ARG, "set_option: unknown option %d", option);

@@ -73,8 +73,8 @@ __global__ void rope_cache_rows_plain_kernel(T *out, const T *x, const T *cos_t,
     const int s = (int)(idx / half), j = (int)(idx - (long long)s * half);
     const size_t ro = ((size_t)blockIdx.y * cache_seq + s) * D, to = (size_t)kv_position[s] * D;
     const float a = to_f32<T>(x[ro + j]), b = to_f32<T>(x[ro + j + half]);
-    out[ro + j] = from_f32<T>(a * to_f32<T>(cos_t[to + j]) - b * to_f32<T>(sin_t[to + j]));
-    out[ro + j + half] = from_f32<T>(b * to_f32<T>(cos_t[to + j + half]) + a * to_f32<T>(sin_t[to + j + half]));
+    out[ro + j] = from_f32<T>(rope_low(a, b, to_f32<T>(cos_t[to + j]), to_f32<T>(sin_t[to + j])));
+    out[ro + j + half] = from_f32<T>(rope_high(a, b, to_f32<T>(cos_t[to + j + half]), to_f32<T>(sin_t[to + j + half])));
 }
 
 int launch_rope_cache_rows(cudaStream_t st, int dtype, void *out, const void *x, const void *cos_t, const void *sin_t,

@@ -83,3 +83,4 @@ def test_set_option_validates_without_a_device():
     assert lib.mynn_b200_set_option(ffi.OPT_PREFILL_ATTENTION, 7) == ffi.E_ARG
     assert lib.mynn_b200_set_option(ffi.OPT_WAIT_BUDGET_US, 0) == ffi.E_ARG
     assert lib.mynn_b200_set_option(ffi.OPT_INJECT_STALL, 5) == ffi.E_ARG
+    assert lib.mynn_b200_set_option(ffi.OPT_FUSE_ROPE, 2) == ffi.E_ARG and lib.mynn_b200_set_option(ffi.OPT_FUSE_ROPE, 1) == ffi.OK

