@@ -96,8 +96,10 @@ __device__ __forceinline__ float warp_max(float v) {
 // pdl_wait() before they touch anything an earlier kernel produces.  The other kernels of the decode chain are plain
 // launches; their pdl_trigger() / pdl_wait() are no-ops there and only matter when such a kernel is the predecessor of a
 // DequantMatMul (pdl_trigger() lets that kernel be scheduled early).  Giving every kernel of the chain the attribute was
-// measured twice and rejected: without an early trigger in the GEMM it changed nothing, with one the kernels two and three
-// places ahead became resident early and took registers and shared memory from the running kernel (step 4.63 -> 5.31 ms).
+// measured three times and rejected: without an early trigger in the GEMM it changed nothing; with a trigger at the GEMM's start
+// the kernels two and three places ahead became resident early and took registers and shared memory from the running kernel
+// (step 4.63 -> 5.31 ms); with a trigger after the GEMM's main loop the gaps stayed as they were (the glue kernels' own run
+// time, not their launch, fills them) and the o_proj CTAs that became resident under the attention kernel slowed it by 5-40 %.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -554,8 +554,10 @@ extern "C" int mynn_b200_dequant_matmul_check(void *stream, const void *workspac
 #ifdef MYNN_TUNING
 // Tuning build only: device buffer (8 x uint64) that CTA (0,0) of the tcgen05 GEMM fills with nanosecond timestamps of its
 // phases (start, set-up done, predecessor complete, accumulators complete, cluster ready, outputs stored, end); NULL = off.
-extern "C" int mynn_b200_tuning_set_timing_buffer(void *buf) {
+extern "C" int mynn_b200_tuning_set_timing_buffer(void *buf, int slots) {
     mynn::g_i8_timing = (unsigned long long *)buf;
+    mynn::g_i8_timing_slots = slots > 0 ? slots : 1;
+    mynn::g_i8_timing_next = 0;
     return MYNN_OK;
 }
 extern "C" int mynn_b200_tuning_set_stages(int n) {

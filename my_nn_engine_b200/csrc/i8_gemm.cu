@@ -40,7 +40,7 @@ constexpr int kTileRows = 128;   // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 128;     // int8 k values per pipeline stage = one 128-byte swizzle row
 constexpr int kStages = 3;      // pipeline depth when two CTAs share an SM
 constexpr int kMaxStages = 7;   // depth when the grid has at most one CTA per SM (196 KB of tiles in flight)
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, eight epilogue warps
 
 struct I8GemmParams {
     void *out;
@@ -70,7 +70,8 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     constexpr uint32_t kWBytes = kTileRows * kBlockK, kABytes = NC * kBlockK;
     constexpr uint32_t kStageBytes = kWBytes + ((kABytes + 1023) / 1024) * 1024;
     constexpr uint32_t kTmemCols = NC <= 32 ? 32 : (NC <= 64 ? 64 : 128);
-    static_assert(kStages * kStageBytes >= NC * kTileRows * 4, "reduction buffer aliases the stage buffers");
+    static_assert(kStages * kStageBytes >= (NC / 3) * kTileRows * 8 + ((NC / 3 + 3) / 4) * (kGemmThreads - 64) * 4,
+                  "the reduction buffer and the residual staging area alias the stage buffers");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzled tiles need 1024-byte alignment
     __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], accum_bar;
@@ -113,7 +114,7 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             // The weights do not depend on the preceding kernel: start streaming them at once, and only then wait
             // (programmatic dependent launch) for the grid that writes the activation limbs.
-            const int nload = nkb - (p.skip_last_stage ? 1 : 0);  // normally every k block
+            const int nload = nkb - ((p.skip_last_stage & 1) ? 1 : 0);  // normally every k block
             const int pre = min(nload, stages);
             for (int i = 0; i < pre; i++) {
                 mbar_expect_tx(&full_bar[i], kWBytes + kABytes);
@@ -164,26 +165,38 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         __syncwarp();
     }
 
-    // ---------------- epilogue: warps 2..5 own TMEM lane quadrants (warp & 3) ----------------
-    // S == 1: thread t finishes weight row t of the tile for every activation row m.
+    // ---------------- epilogue: warps 2..9; a warp may read the TMEM lane quadrant (warp & 3) ----------------
+    // Eight warps, two per lane quadrant: warps 2..5 take the first chunk of accumulator columns (48 = 16 activation rows
+    // x 3 limbs), warps 6..9 the second.  The finish of an output is a chain of dependent instructions and every epilogue
+    // warp sits alone on its scheduler, so the epilogue's length is the chain length times the outputs per thread: twice
+    // the warps halve it.
+    // S == 1: thread (quadrant, lane) finishes weight row quad * 32 + lane of the tile for the activation rows of its chunk.
     // S  > 1: every CTA first pushes its int64 partial sums (limbs already combined, still exact) into the shared
     //         memory of the CTA that owns the row (rows are dealt out in S contiguous groups), with remote stores
     //         that need no round trip; after a cluster barrier each CTA adds what it received and finishes its rows.
     //         The receive buffer aliases the stage buffers, so a first cluster barrier makes sure every CTA of the
     //         cluster is past its main loop before anybody writes into a peer.
+    constexpr int kEpiThreads = kGemmThreads - 64;
     const int quad = warp & 3;
     const int r_local = quad * 32 + lane;
     const OutT *scale_p = reinterpret_cast<const OutT *>(p.scale);
     const OutT *resid_p = reinterpret_cast<const OutT *>(p.resid);
     OutT *out_p = reinterpret_cast<OutT *>(p.out);
-    constexpr int MR = NC / 3;                       // activation rows this instantiation can hold
-    const int rows_per = kTileRows / S, mstep = S;   // S > 1: this thread finishes row r_own for m = m_own + j * S
-    const int et = threadIdx.x - 64;                 // epilogue thread index 0..127 (warps >= 2)
+    constexpr int MR = NC / 3;                        // activation rows this instantiation can hold
+    constexpr int kChunk = NC < 48 ? NC : 48;         // accumulator columns per warp
+    constexpr int RPC = kChunk / 3;                   // activation rows per chunk
+    constexpr int kOwnMax = (MR + 3) / 4;             // outputs per thread with a K split (S >= 2)
+    const int c0 = warp >= 6 ? kChunk : 0, m0 = warp >= 6 ? RPC : 0;  // this warp's chunk
+    const bool has_chunk = warp >= 2 && c0 < NC;
+    const int rows_per = kTileRows / S, mstep = kEpiThreads / rows_per;  // S > 1: this thread finishes row r_own for m = m_own + j * mstep
+    const int et = threadIdx.x - 64;                  // epilogue thread index 0..255 (warps >= 2)
     const int r_own = S == 1 ? r_local : rank * rows_per + (et % rows_per);
     const int m_own = S == 1 ? 0 : et / rows_per;
     const int n_own = row0 + r_own;
-    constexpr int kMaxOut = MR;                      // outputs per thread: MR for S == 1, ceil(MR / S) otherwise
-    float wscale = 0.f, res[kMaxOut];
+    // The residuals are requested before the main loop ends and wait in registers with compile-time indices (a load per
+    // output inside the finish loop cost 200-400 ns each): S == 1 those of this warp's chunk, S > 1 those of this thread's
+    // outputs m_own + j * mstep.
+    float wscale = 0.f, res_r[RPC > kOwnMax ? RPC : kOwnMax];  // one array: the two forms never run together
     bool have_acc = false;
     if (warp >= 2) {
         asm volatile("griddepcontrol.wait;" ::: "memory");  // row scales and the residual come from earlier grids
@@ -192,10 +205,18 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if (n_own < p.N) wscale = to_f32<OutT>(scale_p[n_own]);
         if (S == 1) {
 #pragma unroll
-            for (int m = 0; m < kMaxOut; m++)
-                res[m] = (resid_p && n_own < p.N && m < p.M) ? to_f32<OutT>(resid_p[(size_t)m * p.N + n_own]) : 0.f;
+            for (int i = 0; i < RPC; i++) {
+                const int m = m0 + i;
+                res_r[i] = (resid_p && n_own < p.N && m < MR && m < p.M) ? to_f32<OutT>(resid_p[(size_t)m * p.N + n_own]) : 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < kOwnMax; j++) {
+                const int m = m_own + j * mstep;
+                res_r[j] = (resid_p && n_own < p.N && m < p.M) ? to_f32<OutT>(resid_p[(size_t)m * p.N + n_own]) : 0.f;
+            }
         }
-        // one lane per warp polls the barrier (128 spinning threads would flood the shared-memory pipe that the
+        // one lane per warp polls the barrier (spinning threads would flood the shared-memory pipe that the
         // co-resident CTA needs); the outcome is broadcast to the warp
         int ok_i = 1;
         if (lane == 0) ok_i = mbar_wait_spin(&accum_bar, 0, &abort_flag) ? 1 : 0;
@@ -208,75 +229,91 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         tc_fence_after();
         // warp-uniform, because tcgen05.ld below must be executed by whole warps
         have_acc = __all_sync(0xffffffffu, ok && nkb > 0 && !*(volatile int *)&abort_flag);
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // sh_ascale visible to the four epilogue warps (128 threads)
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // sh_ascale visible to the epilogue warps
+        MYNN_STAMP(threadIdx.x == 64, 7);
     }
-    // The accumulators are read 48 columns (16 activation rows x 3 limbs) at a time to keep registers in check.
-    constexpr int kChunk = NC < 48 ? NC : 48;
-    auto load_chunk = [&](int c0, int ncols, uint32_t (&acc)[kChunk]) {
-        if (have_acc) {
+    // A warp reads its chunk in pieces of kSub columns (24 = 8 activation rows when the chunk has 48) to keep registers in check.
+    constexpr int kSub = kChunk == 48 ? 24 : kChunk, kSubs = kChunk / kSub, RS = kSub / 3;
+    auto load_sub = [&](int h, uint32_t (&acc)[kSub]) {
+        const int cb = c0 + h * kSub;  // first column; columns at and past NC do not exist
+        if (have_acc && cb < NC) {
+            uint32_t v[16];
+            tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + cb, v);
 #pragma unroll
-            for (int c = 0; c < kChunk / 16; c++) {
-                if (c * 16 < ncols) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0 + c * 16, v);
+            for (int j = 0; j < 16; j++) acc[j] = v[j];
+            if (kSub == 24) {
+                if (cb + 16 < NC) tmem_ld8(tmem_base + ((uint32_t)(quad * 32) << 16) + cb + 16, &acc[16]);
+            } else if (kSub == 32) {
+                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + cb + 16, v);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) acc[c * 16 + j] = v[j];
-                }
+                for (int j = 0; j < 16; j++) acc[16 + j] = v[j];
             }
             tmem_ld_wait();
         } else {
 #pragma unroll
-            for (int c = 0; c < kChunk; c++) acc[c] = 0u;
+            for (int c = 0; c < kSub; c++) acc[c] = 0u;
         }
     };
     auto combine = [](const uint32_t *a3) {
         return (long long)(int)a3[2] * 65536 + (long long)(int)a3[1] * 256 + (long long)(int)a3[0];
     };
     const uint32_t tp_tag = p.tp.mode == 1 ? *(volatile const uint32_t *)p.tp.part_tag + 1u : 0u;  // written two reductions ago
-    auto finish = [&](int m, long long sum, float resv) {
+    // An output in two steps, so that a caller can compute several values before it stores any: a store through the generic
+    // `out` pointer may alias anything as far as the compiler knows, which would otherwise pin every finish behind the
+    // previous one's store and expose its whole dependent chain (conversions, two products, the rounding) once per output.
+    auto value = [&](long long sum, float asc, float resv) {
         // separate roundings (no fused multiply-add), so that every kernel of this operator gives the same bits
-        float v = __fmul_rn(__fmul_rn((float)sum, sh_ascale[m]), wscale);
+        float v = __fmul_rn(__fmul_rn((float)sum, asc), wscale);
         if (resid_p) v = __fadd_rn(round_store<OutT>(v), resv);
+        return v;
+    };
+    auto deliver = [&](int m, float v) {
         if (p.tp.mode == 1) {
             // a partial sum goes to slot [this rank] of EVERY rank's buffer: one 8-byte store {value, tag} per destination,
             // over NVLink for the peers; the reader re-reads a word until it sees this reduction's tag, so no fence or flag
             // follows
             const uint2 word = make_uint2(__float_as_uint(v), tp_tag);
             const size_t idx = ((size_t)p.tp.rank * p.tp.max_rows + m) * p.N + n_own;
-#pragma unroll
-            for (int r = 0; r < kTpMaxRanks; r++)
-                if (r < p.tp.world && !p.tp.skip) p.tp.part[r][idx] = word;
+            const int nr = p.tp.skip ? 0 : p.tp.world;
+#pragma unroll 1
+            for (int r = 0; r < nr; r++) p.tp.part[r][idx] = word;
         } else {
             out_p[(size_t)m * p.N + n_own] = from_f32<OutT>(v);
         }
     };
 
     if (S == 1) {
-        if (warp >= 2) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < NC; c0 += kChunk) {  // rolled: keeps the once-per-CTA epilogue code small
-                uint32_t acc[kChunk];
-                load_chunk(c0, NC - c0 < kChunk ? NC - c0 : kChunk, acc);
+        if (has_chunk) {
 #pragma unroll
-                for (int i = 0; i < kChunk / 3; i++) {
-                    const int m = c0 / 3 + i;
-                    if (m < MR && m < p.M && n_own < p.N) finish(m, combine(&acc[3 * i]), res[m]);
+            for (int h = 0; h < kSubs; h++) {
+                uint32_t acc[kSub];
+                load_sub(h, acc);
+                MYNN_STAMP(threadIdx.x == 64 && h == 0, 4);
+                float asc[RS], vv[RS];
+#pragma unroll
+                for (int i = 0; i < RS; i++) asc[i] = sh_ascale[min(m0 + h * RS + i, 31)];
+#pragma unroll
+                for (int i = 0; i < RS; i++) vv[i] = value(combine(&acc[3 * i]), asc[i], res_r[h * RS + i]);
+#pragma unroll
+                for (int i = 0; i < RS; i++) {
+                    const int m = m0 + h * RS + i;
+                    if (m < MR && m < p.M && n_own < p.N) deliver(m, vv[i]);
                 }
             }
         }
     } else {
         long long *recv = reinterpret_cast<long long *>(smem);  // [S source ranks][MR][rows_per] int64 <= 32 KB
         cluster_sync_all();  // every CTA of the cluster is past its main loop: stage buffers are free everywhere
-        if (warp >= 2) {
+        if (has_chunk) {
             const uint32_t owner = (uint32_t)(r_local / rows_per);
             const int r_in = r_local % rows_per;
-#pragma unroll 1
-            for (int c0 = 0; c0 < NC; c0 += kChunk) {  // rolled: keeps the once-per-CTA epilogue code small
-                uint32_t acc[kChunk];
-                load_chunk(c0, NC - c0 < kChunk ? NC - c0 : kChunk, acc);
 #pragma unroll
-                for (int i = 0; i < kChunk / 3; i++) {
-                    const int m = c0 / 3 + i;
+            for (int h = 0; h < kSubs; h++) {
+                uint32_t acc[kSub];
+                load_sub(h, acc);
+#pragma unroll
+                for (int i = 0; i < RS; i++) {
+                    const int m = m0 + h * RS + i;
                     if (m < MR && m < p.M) {
                         const long long v = combine(&acc[3 * i]);
                         const uint32_t local = smem_u32(&recv[((size_t)rank * MR + m) * rows_per + r_in]);
@@ -287,20 +324,28 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 }
             }
         }
+        // the rolled loop below takes its residuals from this thread's own column of a staging area behind the receive
+        // buffer (nobody else touches it)
+        float *res_stage = reinterpret_cast<float *>(smem + (size_t)MR * kTileRows * 8) + et;
+        if (warp >= 2 && resid_p) {
+#pragma unroll
+            for (int j = 0; j < kOwnMax; j++) res_stage[j * kEpiThreads] = res_r[j];
+        }
         cluster_sync_all();  // release/acquire: the partial sums pushed by every peer are visible
         MYNN_STAMP(threadIdx.x == 64, 4);
         if (warp >= 2 && n_own < p.N) {
             // a compact rolled loop: straight-line code that runs once per CTA pays an instruction-cache miss per line
             const int r_in = et % rows_per;
+            int j = 0;
 #pragma unroll 1
-            for (int m = m_own; m < p.M; m += mstep) {
-                const float resv = resid_p ? to_f32<OutT>(resid_p[(size_t)m * p.N + n_own]) : 0.f;
+            for (int m = m_own; m < p.M; m += mstep, j++) {
+                const float resv = resid_p ? res_stage[j * kEpiThreads] : 0.f;
                 const long long *src = recv + (size_t)m * rows_per + r_in;
                 long long sum = 0;
 #pragma unroll
                 for (int rr = 0; rr < 8; rr++)
                     if (rr < S) sum += src[(size_t)rr * MR * rows_per];
-                finish(m, sum, resv);
+                deliver(m, value(sum, sh_ascale[m], resv));
             }
         }
     }
@@ -648,7 +693,8 @@ static int pick_split(int row_tiles, int kblocks) {
 }
 
 #ifdef MYNN_TUNING
-unsigned long long *g_i8_timing = nullptr;  // device buffer of 8 timestamps, see I8GemmParams::timing
+unsigned long long *g_i8_timing = nullptr;  // device buffer of 8 timestamps per slot, see I8GemmParams::timing
+int g_i8_timing_slots = 1, g_i8_timing_next = 0;  // consecutive launches write consecutive slots (a captured graph keeps its slots)
 int g_i8_stages_override = 0;
 #endif
 
@@ -747,7 +793,7 @@ int i8_gemm_launch_tp(cudaStream_t st, void *out, const void *act, const int8_t 
         if (g_inject_stall.compare_exchange_strong(want, 0)) p.skip_last_stage = 1;  // one launch only
     }
 #ifdef MYNN_TUNING
-    p.timing = g_i8_timing;
+    p.timing = g_i8_timing ? g_i8_timing + 32 * (size_t)(g_i8_timing_next++ % g_i8_timing_slots) : nullptr;
 #endif
     const int row_tiles = (N + kTileRows - 1) / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
     const int S = g_ksplit_override > 0 ? g_ksplit_override : pick_split(row_tiles, kblocks);

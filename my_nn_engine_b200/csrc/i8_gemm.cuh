@@ -53,6 +53,6 @@ int i8_w8a8_launch(cudaStream_t st, void *out, const int8_t *lhs, const void *lh
                    const void *rhs_scale, int M, int N, int K, int dtype, void *workspace, size_t workspace_bytes);
 #ifdef MYNN_TUNING
 extern unsigned long long *g_i8_timing;
-extern int g_i8_stages_override;
+extern int g_i8_stages_override, g_i8_timing_slots, g_i8_timing_next;
 #endif
 }  // namespace mynn
