@@ -755,9 +755,16 @@ def main():
     ap.add_argument("--kernel", default="tcgen05_i8", choices=["tcgen05_i8", "mma_sync"])
     ap.add_argument("--layout", default="nk", choices=["nk", "kn"])
     ap.add_argument("--arch", default="llama3-8b", choices=["llama3-8b", "tinyllama"])
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="library option set before the run (mynn_b200_set_option), e.g. decode_ring=0, fuse_rope=0, ksplit=4")
     args = ap.parse_args()
     if args.kv == "16bit":
         args.kv = "bf16"
+    if args.option and args.impl != "reference":
+        from my_nn_engine_b200 import ffi
+        for item in args.option:
+            name, _, value = item.partition("=")
+            ffi.set_option(getattr(ffi, "OPT_" + name.upper()), int(value))
     if args.case != "step":
         return run_case(args)
     cfg = dict(LLAMA3_8B)

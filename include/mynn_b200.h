@@ -55,8 +55,16 @@ const char *mynn_b200_last_error(void);
  *                             new key itself and appends the new key / value rows to the cache (one launch less per layer);
  *                             0: RoPE + append run as a kernel of their own in front of it.  Read when a model's step is
  *                             recorded.  The rotated rows have the same bits either way; the softmax takes the new row in a tile of its own,
- *                             so outputs agree to rounding of the f32 sums, not to the bit. */
-enum { MYNN_OPT_WAIT_BUDGET_US = 1, MYNN_OPT_KSPLIT = 2, MYNN_OPT_PREFILL_ATTENTION = 3, MYNN_OPT_INJECT_STALL = 4, MYNN_OPT_FUSE_ROPE = 5 };
+ *                             so outputs agree to rounding of the f32 sums, not to the bit.
+ *   MYNN_OPT_DECODE_RING      1 (default): the 16-bit decode attention kernel takes its K / V tiles from per-warp rings in
+ *                             shared memory that the TMA engine fills; 0: every thread loads its fragments from global
+ *                             memory itself.  Same arithmetic on the same fragments: the outputs are bit-identical whenever
+ *                             both forms use the same number of splits, which a test verifies.  Read at launch (a model
+ *                             reads it when its step is recorded). */
+enum {
+    MYNN_OPT_WAIT_BUDGET_US = 1, MYNN_OPT_KSPLIT = 2, MYNN_OPT_PREFILL_ATTENTION = 3, MYNN_OPT_INJECT_STALL = 4,
+    MYNN_OPT_FUSE_ROPE = 5, MYNN_OPT_DECODE_RING = 6
+};
 int mynn_b200_set_option(int option, long long value);
 
 /* Library/ABI version and the SM architecture the kernels were compiled for (100 for sm_100a). */

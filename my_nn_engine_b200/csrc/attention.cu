@@ -17,11 +17,14 @@
 // Everything else (f32 tensors, head dims other than 64/128, groups larger than 8, more than one query row,
 // causal masks) goes to a generic one-warp-per-query-row kernel that follows the CPU recurrence literally.
 #include <atomic>
+#include <cstring>
 #include <type_traits>
 
 #include "attention_internal.cuh"
 #include "common.cuh"
+#include "i8_gemm.cuh"
 #include "ops_internal.cuh"
+#include "tcgen05.cuh"
 
 namespace mynn {
 
@@ -30,8 +33,18 @@ struct Map16 {  // accumulator tile i = 4h + j of the 16-bit kernel holds head-d
 };
 
 // grid (splits, Hkv, B), block 128.
-template <typename T, int D>
-__global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(const DecodeParams p) {
+// RING: the K / V rows do not go from global memory into the registers of the thread that needs them; every warp keeps a
+// ring of kRingDepth 16-row tiles in shared memory that the TMA engine fills (cp.async.bulk.tensor over 2-D maps of the two
+// caches, 16 rows x 128 bytes per box, 128-byte swizzle; tensor maps of this GPU's own memory, no multicast), and takes its
+// fragments from there with 16-byte shared loads.  The loads of the next kRingDepth - 1 tiles are in flight while a tile
+// is computed, without holding registers.  Each warp owns its ring and its barriers: the lane that issues the copies is
+// lane 0 of the consuming warp, after the warp has copied a tile into registers, so no second barrier is needed.
+constexpr int kRingDepth = 3;
+__device__ int g_ring_status;  // 31: a wait for a tile ran out of time (read and cleared by mynn_b200_attention_check)
+
+template <typename T, int D, bool RING>
+__global__ void __launch_bounds__(kAttnWarps * 32, RING ? 2 : 4)
+attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
     constexpr int KS = D / 16;   // k16 steps of QK^T
     constexpr int KCH = D / 32;  // 16-byte K chunks per lane per row
     constexpr int VH = D / 64;   // 16-byte V chunks per lane per row
@@ -167,6 +180,79 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
     // the rows this CTA reads from the cache: with the fused append the new row is not there yet
     const int cache_end = fused ? min(row_end, new_row) : row_end;
     const int last = cache_end - 1;
+    extern __shared__ __align__(1024) uint8_t ring_raw[];
+    constexpr int NB = D / 64;                      // 128-byte boxes per K (and per V) row
+    constexpr uint32_t kBox = 16 * 128;             // one box: 16 rows x 128 bytes
+    constexpr uint32_t kTile = 2 * NB * kBox;       // K boxes, then V boxes
+    if constexpr (RING) {
+        __shared__ uint64_t full[kAttnWarps][kRingDepth];
+        __shared__ int abort_flag;
+        uint8_t *ring = ring_raw + (size_t)warp * kRingDepth * kTile;
+        const int first = row_beg + 16 * warp;
+        const int ntile = first < cache_end ? (cache_end - first + 16 * kAttnWarps - 1) / (16 * kAttnWarps) : 0;
+        const int y0 = (b * p.Hkv + kvh) * p.cache_seq + first;  // tensor row of this warp's first tile
+        if (threadIdx.x == 0) abort_flag = 0;
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < kRingDepth; s++) mbar_init(&full[warp][s], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+        auto issue = [&](int j) {  // lane 0: tile j of this warp into stage j % depth
+            const int s = j % kRingDepth;
+            uint8_t *st = ring + (size_t)s * kTile;
+            const int y = y0 + 16 * kAttnWarps * j;
+            mbar_expect_tx(&full[warp][s], kTile);
+#pragma unroll
+            for (int hf = 0; hf < NB; hf++) {
+                tma_load_2d(st + hf * kBox, &map_k, 128 * hf, y, &full[warp][s]);  // byte maps: x counts bytes
+                tma_load_2d(st + (NB + hf) * kBox, &map_v, 128 * hf, y, &full[warp][s]);
+            }
+        };
+        if (lane == 0)
+            for (int j = 0; j < min(ntile, kRingDepth); j++) issue(j);
+        for (int j = 0; j < ntile; j++) {
+            const int s = j % kRingDepth;
+            const int base = first + 16 * kAttnWarps * j;
+            int ok_i = 1;
+            if (lane == 0) ok_i = mbar_wait_spin(&full[warp][s], (j / kRingDepth) & 1, &abort_flag) ? 1 : 0;
+            if (!__shfl_sync(0xffffffffu, ok_i, 0)) {  // the copy never arrived: report it, leave the rows out
+                if (lane == 0) {
+                    atomicExch(&abort_flag, 1);
+                    atomicExch(p.status ? p.status : &g_ring_status, 31);
+                }
+                break;
+            }
+            const uint8_t *st = ring + (size_t)s * kTile;
+            uint4 kr[2][KCH], vr[4][VH];
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+                const int row = 8 * nt + g;  // row & 7 == g
+#pragma unroll
+                for (int i = 0; i < KCH; i++) {
+                    // element 8t + 32i of the row = box i / 2, 16-byte chunk t + 4 (i % 2), stored at chunk ^ (row % 8)
+                    const int c = (t + 4 * (i & 1)) ^ g;
+                    kr[nt][i] = *reinterpret_cast<const uint4 *>(st + (i >> 1) * kBox + row * 128 + (c << 4));
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const int row = 2 * t + (r & 1) + 8 * (r >> 1);
+                const bool live = base + row < cache_end;  // rows past the end may hold anything: keep them out of P V
+#pragma unroll
+                for (int h = 0; h < VH; h++) {
+                    const uint4 w = *reinterpret_cast<const uint4 *>(st + (NB + h) * kBox + row * 128 + ((g ^ (row & 7)) << 4));
+                    vr[r][h] = live ? w : make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            __syncwarp();  // every lane has its fragments: the stage may be refilled
+            if (lane == 0 && j + kRingDepth < ntile) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue(j + kRingDepth);
+            }
+            tile(kr, vr, base, cache_end);
+        }
+    } else {
     for (int base = row_beg + 16 * warp; base < cache_end; base += 16 * kAttnWarps) {
         // ---- issue all loads of this tile (rows past the end are clamped to a valid row and masked in the tile) ----
         uint4 kr[2][KCH], vr[4][VH];
@@ -184,6 +270,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
             for (int h = 0; h < VH; h++) vr[r][h] = ldg_16(vp + 64 * h);
         }
         tile(kr, vr, base, cache_end);
+    }
     }
     if (fused && warp == 0 && new_row >= row_beg && new_row < row_end) {
         // The new row of this (batch, kv head): rotate the key, store key and value into the cache for the steps to come, and
@@ -225,7 +312,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_kernel(co
         tile(kr, vr, new_row, new_row + 1);
     }
 
-    decode_tail<T, D, VH * 4, Map16>(p, o, m_run, l_run);
+    if constexpr (RING) {
+        // the warps' staging rows for the merge reuse each warp's own ring (all of its copies have landed and been read)
+        __syncwarp();
+        decode_tail<T, D, VH * 4, Map16, true>(p, o, m_run, l_run, reinterpret_cast<float *>(ring_raw), (int)(kRingDepth * kTile / 4));
+    } else {
+        decode_tail<T, D, VH * 4, Map16>(p, o, m_run, l_run);
+    }
 }
 
 // Generic attention: one warp per (b, h, sq) query row, the CPU kernel's recurrence row by row
@@ -347,10 +440,46 @@ static int launch_generic(cudaStream_t st, void *out, const void *q, const void 
     return MYNN_OK;
 }
 
+// The ring form needs the driver's tensor-map encoder and tensor rows that fit a 32-bit coordinate.
+static bool decode_ring_possible(int B, int Hkv, int cache_seq) {
+    return g_decode_ring && tensor_map_api_available() && (long long)B * Hkv * cache_seq < (1ll << 31);
+}
+// resident CTAs per SM of the decode kernel: the ring form at head_dim 128 holds 96 KB of tiles per CTA
+static int decode_ctas_per_sm(bool ring, int D) { return ring && D == 128 ? 2 : kAttnCtasPerSm; }
+
 template <typename T, int D>
-static int launch_decode(cudaStream_t st, const DecodeParams &p, int B) {
-    MYNN_CUDA_OK(launch_pdl(attention_decode_kernel<T, D>, dim3(p.splits, p.Hkv, B), dim3(kAttnWarps * 32), 0, st, p));
+static int launch_decode(cudaStream_t st, const DecodeParams &p, int B, bool ring) {
+    CUtensorMap mk, mv;
+    memset(&mk, 0, sizeof mk);
+    memset(&mv, 0, sizeof mv);
+    if (ring) {
+        // the caches as [B * Hkv * cache_seq rows][D * 2 bytes]: boxes of 16 rows x 128 bytes, 128-byte swizzle
+        const uint64_t rows = (uint64_t)B * p.Hkv * p.cache_seq, row_bytes = (uint64_t)D * sizeof(T);
+        if (int rc = make_map(&mk, p.k, rows, row_bytes, row_bytes, 16)) return rc;
+        if (int rc = make_map(&mv, p.v, rows, row_bytes, row_bytes, 16)) return rc;
+        constexpr size_t smem = (size_t)kAttnWarps * kRingDepth * 2 * (D / 64) * 16 * 128;
+        auto kern = attention_decode_kernel<T, D, true>;
+        static bool attr_set = false;
+        if (!attr_set) {  // with the kernel's static shared memory every head_dim is past the 48 KB that need no opt-in
+            MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set = true;
+        }
+        MYNN_CUDA_OK(launch_pdl(kern, dim3(p.splits, p.Hkv, B), dim3(kAttnWarps * 32), smem, st, mk, mv, p));
+    } else {
+        MYNN_CUDA_OK(launch_pdl(attention_decode_kernel<T, D, false>, dim3(p.splits, p.Hkv, B), dim3(kAttnWarps * 32), 0, st, mk, mv, p));
+    }
     MYNN_LAUNCH_OK("attention_decode_kernel");
+    return MYNN_OK;
+}
+
+// Reads and clears the library's own status word of the ring kernel (the stream must be idle).
+int mynn::attention_decode_take_status(int *status) {
+    *status = 0;
+    MYNN_CUDA_OK(cudaMemcpyFromSymbol(status, g_ring_status, sizeof *status));
+    if (*status) {
+        const int zero = 0;
+        MYNN_CUDA_OK(cudaMemcpyToSymbol(g_ring_status, &zero, sizeof zero));
+    }
     return MYNN_OK;
 }
 
@@ -421,7 +550,7 @@ bool mynn::attention_decode_fast_path(int Sq, int D, int Hq, int Hkv, int dtype,
 int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void *k, const void *v, float scale, int B,
                            int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
                            const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
-                           size_t workspace_bytes, int out_bshd, int8_t *limbs_out, float *ascale_out, const AttentionFuse *fuse) {
+                           size_t workspace_bytes, int out_bshd, int8_t *limbs_out, float *ascale_out, const AttentionFuse *fuse, int *status_word) {
     if (B < 0 || Hq <= 0 || Hkv <= 0 || Sq < 0 || D <= 0 || cache_seq_len < 0 || active_seq_kv < 0)
         return fail(MYNN_E_ARG, "attention: bad shape");
     if (Hq % Hkv != 0) return fail(MYNN_E_ARG, "attention: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
@@ -458,11 +587,13 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
     p.active_host = active_seq_kv;
     p.active_dev = active_seq_kv_dev;
     const int rows_bound = active_seq_kv_dev ? cache_seq_len : (active_seq_kv < cache_seq_len ? active_seq_kv : cache_seq_len);
-    p.splits = decode_splits(B, Hkv, rows_bound);
+    const bool ring = decode_ring_possible(B, Hkv, cache_seq_len);
+    p.splits = decode_splits(B, Hkv, rows_bound, 16, decode_ctas_per_sm(ring, D));
     p.k_scale = nullptr;
     p.v_scale = nullptr;
     p.limbs = limbs_out;
     p.ascale = ascale_out;
+    p.status = status_word;
     if (fuse) {
         if (!fuse->k_new || !fuse->v_new || !fuse->cos_t || !fuse->sin_t || !fuse->pos || !fuse->row || fuse->qkv_stride % 8 ||
             (((uintptr_t)fuse->k_new | (uintptr_t)fuse->v_new | (uintptr_t)fuse->cos_t | (uintptr_t)fuse->sin_t) % 16))
@@ -476,8 +607,8 @@ int mynn::launch_attention(cudaStream_t st, void *out, const void *q, const void
         p.fused_row = fuse->row;
     }
     if (int rc = decode_bind_workspace(p, B, D, workspace, workspace_bytes)) return rc;
-    if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B) : launch_decode<__nv_bfloat16, 128>(st, p, B);
-    return D == 64 ? launch_decode<__half, 64>(st, p, B) : launch_decode<__half, 128>(st, p, B);
+    if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B, ring) : launch_decode<__nv_bfloat16, 128>(st, p, B, ring);
+    return D == 64 ? launch_decode<__half, 64>(st, p, B, ring) : launch_decode<__half, 128>(st, p, B, ring);
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -580,6 +711,6 @@ extern "C" int mynn_b200_attention_decode_noalloc(void *stream, void *out, const
         p.ws_ml = (float *)(base + tickets);
         p.ws_o = (float *)(base + tickets + ml);
     }
-    if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B) : launch_decode<__nv_bfloat16, 128>(st, p, B);
-    return D == 64 ? launch_decode<__half, 64>(st, p, B) : launch_decode<__half, 128>(st, p, B);
+    if (dtype == MYNN_BF16) return D == 64 ? launch_decode<__nv_bfloat16, 64>(st, p, B, false) : launch_decode<__nv_bfloat16, 128>(st, p, B, false);
+    return D == 64 ? launch_decode<__half, 64>(st, p, B, false) : launch_decode<__half, 128>(st, p, B, false);
 }

@@ -73,6 +73,7 @@ struct DecodeParams {
     const void *cos_t = nullptr, *sin_t = nullptr;
     const int64_t *fused_pos = nullptr;
     const int32_t *fused_row = nullptr;
+    int *status = nullptr;  // ring kernel: where a timed-out wait is recorded (null: the library's own word, see attention_check)
 };
 
 // Called by every CTA that has stored final outputs of (batch b, one kv head): the last of the Hkv to arrive converts the
@@ -159,9 +160,21 @@ __device__ __forceinline__ void decode_row_limbs(const DecodeParams &p, int b, u
 // (head 2t, d), (head 2t+1, d), (head 2t, d+1), (head 2t+1, d+1) with d = DMap::d(i, g).  The warps are merged through
 // shared memory; with more than one split the partial result goes to the workspace and the last CTA of the
 // (batch, kv head) pair to arrive (atomic ticket, no spinning) combines the splits and writes the output.
-template <typename T, int D, int NACC, typename DMap>
-__device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (&o)[NACC][4], float m_run, float l_run) {
-    __shared__ float sm_o[kAttnWarps][8][D];
+// ext != nullptr: the per-warp output staging rows live in caller-provided shared memory, warp w's [8][D] floats at
+// ext + w * ext_stride (the ring kernel hands every warp a piece of its own, by then idle, ring).
+template <typename T, int D, int NACC, typename DMap, bool EXT = false>
+__device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (&o)[NACC][4], float m_run, float l_run,
+                                            float *ext = nullptr, int ext_stride = 0) {
+    float *so_base;
+    int so_stride;
+    if constexpr (EXT) {
+        so_base = ext;
+        so_stride = ext_stride;
+    } else {
+        __shared__ float sm_o[kAttnWarps][8][D];
+        so_base = &sm_o[0][0][0];
+        so_stride = 8 * D;
+    }
     __shared__ float sm_m[kAttnWarps][8], sm_l[kAttnWarps][8];
     __shared__ unsigned sm_last, sm_row_last;
     __shared__ float sm_red[kAttnWarps];
@@ -178,10 +191,11 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (
 #pragma unroll
     for (int i = 0; i < NACC; i++) {
         const int d = DMap::d(i, g);
-        sm_o[warp][2 * t][d] = o[i][0];
-        sm_o[warp][2 * t + 1][d] = o[i][1];
-        sm_o[warp][2 * t][d + 1] = o[i][2];
-        sm_o[warp][2 * t + 1][d + 1] = o[i][3];
+        float *so = so_base + (size_t)warp * so_stride;
+        so[(2 * t) * D + d] = o[i][0];
+        so[(2 * t + 1) * D + d] = o[i][1];
+        so[(2 * t) * D + d + 1] = o[i][2];
+        so[(2 * t + 1) * D + d + 1] = o[i][3];
     }
     __syncthreads();
 
@@ -198,7 +212,7 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (
             for (int w = 0; w < kAttnWarps; w++) {
                 const float f = __expf(sm_m[w][hd] - mx);
                 L += sm_l[w][hd] * f;
-                O += sm_o[w][hd][d] * f;
+                O += so_base[(size_t)w * so_stride + hd * D + d] * f;
             }
         }
         if (p.splits == 1) {
@@ -225,16 +239,34 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (
     __threadfence();
     for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
         const int hd = idx / D, d = idx - hd * D;
-        float mx = -INFINITY;
-        for (int sp = 0; sp < p.splits; sp++) mx = fmaxf(mx, __ldcg(&p.ws_ml[((pair * p.splits + sp) * 8 + hd) * 2]));
-        float L = 0.f, O = 0.f;
-        for (int sp = 0; sp < p.splits; sp++) {
-            const size_t slot = (pair * p.splits + sp) * 8 + hd;
-            const float ms = __ldcg(&p.ws_ml[slot * 2]);
-            if (ms == -INFINITY) continue;
-            const float f = __expf(ms - mx);
-            L += __ldcg(&p.ws_ml[slot * 2 + 1]) * f;
-            O += __ldcg(&p.ws_o[slot * D + d]) * f;
+        // eight splits at a time, all of their loads issued before any is used: the combine costs one L2 round trip per
+        // eight splits instead of four dependent ones per split
+        float mx = -INFINITY, L = 0.f, O = 0.f;
+        for (int s0 = 0; s0 < p.splits; s0 += 8) {
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const bool in = s0 + j < p.splits;
+                const size_t slot = (pair * p.splits + (in ? s0 + j : s0)) * 8 + hd;
+                ms[j] = in ? __ldcg(&p.ws_ml[slot * 2]) : -INFINITY;
+                ls[j] = in ? __ldcg(&p.ws_ml[slot * 2 + 1]) : 0.f;
+                os[j] = in ? __ldcg(&p.ws_o[slot * D + d]) : 0.f;
+            }
+            float cm = mx;
+#pragma unroll
+            for (int j = 0; j < 8; j++) cm = fmaxf(cm, ms[j]);
+            if (cm == -INFINITY) continue;  // nothing but empty splits so far
+            const float f0 = __expf(mx - cm);  // 0 while mx is still -inf
+            L *= f0;
+            O *= f0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (ms[j] == -INFINITY) continue;
+                const float f = __expf(ms[j] - cm);
+                L += ls[j] * f;
+                O += os[j] * f;
+            }
+            mx = cm;
         }
         outp[(size_t)hd * D + d] = from_f32<T>(O / L);
     }
@@ -244,9 +276,9 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (
 
 // All CTAs of a launch last equally long, so the grid should fit in ONE wave of resident CTAs (148 SMs): a partly
 // filled second wave would cost as much time as a full one.
-inline int decode_splits(int B, int Hkv, int rows_bound, int tile_rows = 16) {
+inline int decode_splits(int B, int Hkv, int rows_bound, int tile_rows = 16, int ctas_per_sm = kAttnCtasPerSm) {
     const int pairs = B * Hkv;
-    int s = (kAttnCtasPerSm * 148) / pairs;
+    int s = (ctas_per_sm * 148) / pairs;
     const int cap = rows_bound / (tile_rows * kAttnWarps);  // at least one tile per warp and split
     if (s > cap) s = cap;
     if (s < 1) s = 1;

@@ -812,5 +812,7 @@ extern "C" int mynn_b200_attention_check(void *stream) {
     int status = 0;
     if (int rc = attention_prefill_tc_take_status(&status)) return rc;
     if (status) return fail(MYNN_E_CUDA, "attention: pipeline wait %d timed out inside the tcgen05 prefill kernel", status);
+    if (int rc = attention_decode_take_status(&status)) return rc;
+    if (status) return fail(MYNN_E_CUDA, "attention: wait %d for a K/V tile timed out inside the decode kernel", status);
     return MYNN_OK;
 }

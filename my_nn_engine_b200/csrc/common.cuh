@@ -107,6 +107,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 extern int g_ksplit_override;            // forced cluster K split of the DequantMatMul kernels, 0 = automatic
 extern int g_prefill_attention_mode;     // see MYNN_OPT_PREFILL_ATTENTION
 extern int g_fuse_rope;                  // see MYNN_OPT_FUSE_ROPE
+extern int g_decode_ring;                // see MYNN_OPT_DECODE_RING
 extern std::atomic<int> g_inject_stall;  // see MYNN_OPT_INJECT_STALL; consumed by the next launch it applies to
 
 // A plain launch through cudaLaunchKernelEx (no attributes); the name says which kernels belong to the decode chain.

@@ -546,7 +546,7 @@ extern "C" int mynn_b200_dequant_matmul_check(void *stream, const void *workspac
     if (status) {  // reported once: clear the word so that later calls on this workspace start clean
         MYNN_CUDA_OK(cudaMemsetAsync(const_cast<void *>(workspace), 0, sizeof status, (cudaStream_t)stream));
         MYNN_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
-        return mynn::fail(MYNN_E_CUDA, "dequant_matmul: pipeline wait %d timed out inside the tcgen05 kernel", status);
+        return mynn::fail(MYNN_E_CUDA, "dequant_matmul: pipeline wait %d timed out inside a kernel that uses this workspace (1-3: the tcgen05 DequantMatMul, 31: decode attention waiting for a K/V tile)", status);
     }
     return MYNN_OK;
 }

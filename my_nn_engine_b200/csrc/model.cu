@@ -247,14 +247,15 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
                 const AttentionFuse fz = {kb, vb, qs, m.cos_t, m.sin_t, m.pos0_dev, m.past_dev};
                 RC(launch_attention(st, m.attn, qb, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len, c.max_seq_len,
                                     m.active_dev, 0, dt, m.attn_ws, m.attn_ws_bytes, 1, (int8_t *)m.gemm_ws + 512,
-                                    (float *)((char *)m.gemm_ws + 256), &fz));
+                                    (float *)((char *)m.gemm_ws + 256), &fz, (int *)m.gemm_ws));
             } else {
                 RC(launch_rope_kv_append(st, dt, m.q_rot, L.kc, L.vc, qb, kb, vb, qs, ks, vs, m.cos_t, m.sin_t,
                                          S == 1 ? m.pos0_dev : m.pos_dev, B, S, m.Hq, m.Hkv, D, c.max_seq_len, m.past_dev));
                 attn_limbs = attn_limbs && attention_decode_fast_path(S, D, m.Hq, m.Hkv, dt, m.q_rot, L.kc, L.vc);
                 RC(launch_attention(st, m.attn, m.q_rot, L.kc, L.vc, attn_scale, B, m.Hq, m.Hkv, S, D, c.max_seq_len,
                                     c.max_seq_len, m.active_dev, S > 1, dt, m.attn_ws, m.attn_ws_bytes, 1,
-                                    attn_limbs ? (int8_t *)m.gemm_ws + 512 : nullptr, attn_limbs ? (float *)((char *)m.gemm_ws + 256) : nullptr));
+                                    attn_limbs ? (int8_t *)m.gemm_ws + 512 : nullptr, attn_limbs ? (float *)((char *)m.gemm_ws + 256) : nullptr,
+                                    nullptr, (int *)m.gemm_ws));
             }
         }
         if (tp == 1) {

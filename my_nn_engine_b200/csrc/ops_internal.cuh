@@ -65,7 +65,9 @@ int launch_attention(cudaStream_t st, void *out, const void *q, const void *k, c
                      int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
                      const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,
                      size_t workspace_bytes, int out_bshd, int8_t *limbs_out = nullptr, float *ascale_out = nullptr,
-                     const AttentionFuse *fuse = nullptr);
+                     const AttentionFuse *fuse = nullptr, int *status_word = nullptr);
+// status_word: where the ring form of the decode kernel records a timed-out wait (null: the library's own word)
+int attention_decode_take_status(int *status);
 bool attention_decode_fast_path(int Sq, int D, int Hq, int Hkv, int dtype, const void *q, const void *k, const void *v);
 
 // Tiled tensor-core attention for several query rows (prefill chunks); see attention_prefill.cu.

@@ -24,6 +24,7 @@ void register_wait_budget_setter(int (*fn)(unsigned long long)) { wait_budget_se
 int g_ksplit_override = 0;
 int g_prefill_attention_mode = 1;
 int g_fuse_rope = 1;
+int g_decode_ring = 1;
 std::atomic<int> g_inject_stall{0};
 
 void set_error(const char *fmt, ...) {
@@ -77,6 +78,10 @@ extern "C" int mynn_b200_set_option(int option, long long value) {
         case MYNN_OPT_FUSE_ROPE:
             if (value != 0 && value != 1) return fail(MYNN_E_ARG, "set_option: fused RoPE must be 0 or 1");
             g_fuse_rope = (int)value;
+            return MYNN_OK;
+        case MYNN_OPT_DECODE_RING:
+            if (value != 0 && value != 1) return fail(MYNN_E_ARG, "set_option: decode ring must be 0 or 1");
+            g_decode_ring = (int)value;
             return MYNN_OK;
         default:
             return fail(MYNN_E_ARG, "set_option: unknown option %d", option);

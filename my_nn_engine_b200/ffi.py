@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(HERE, "libmynn_b200.so")
 F32, BF16, F16 = 0, 1, 2
 W_NK, W_KN = 0, 1
 OK, E_ARG, E_CUDA, E_UNSUPPORTED, E_COMM, E_STATE = 0, -1, -2, -3, -4, -5
-OPT_WAIT_BUDGET_US, OPT_KSPLIT, OPT_PREFILL_ATTENTION, OPT_INJECT_STALL, OPT_FUSE_ROPE = 1, 2, 3, 4, 5
+OPT_WAIT_BUDGET_US, OPT_KSPLIT, OPT_PREFILL_ATTENTION, OPT_INJECT_STALL, OPT_FUSE_ROPE, OPT_DECODE_RING = 1, 2, 3, 4, 5, 6
 
 
 class MynnError(RuntimeError):

@@ -373,3 +373,42 @@ def test_glue_ops_vs_oracle(dtype):
     logits[2, 0] = 70.0
     got = ops.argmax_last(logits.cuda()).cpu().numpy().tolist()
     assert got == [R.argmax_last(r) for r in logits.float().numpy()] == [90000, 128255, 0]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,hq,hkv,d,sk,active", [(2, 8, 2, 64, 700, 613), (1, 32, 8, 64, 2048, 2048), (3, 4, 4, 128, 130, 97),
+                                                  (8, 32, 8, 128, 4096, 4096), (2, 16, 2, 128, 96, 17), (1, 8, 8, 128, 64, 1)])
+def test_attention_decode_ring_and_direct_loads_agree(dtype, b, hq, hkv, d, sk, active):
+    """MYNN_OPT_DECODE_RING: K / V tiles through the TMA-fed shared-memory rings against fragments loaded from global memory by
+    the threads themselves.  Same fragments, same arithmetic: bit-identical outputs when the split count is the same (head_dim
+    64, and short contexts at head_dim 128); otherwise only the order of the final merge differs.  Rows past active_seq_kv
+    hold NaN (the ring copies whole 16-row boxes: they must not leak into the result), and the last row of the tensor is the
+    last row of a tile (zero fill past the end)."""
+    from my_nn_engine_b200 import ffi
+    rng = np.random.default_rng(b + hq + sk + active)
+    q = torch.from_numpy(rng.standard_normal((b, hq, 1, d)).astype(np.float32)).to(dtype).cuda()
+    k = torch.from_numpy(rng.standard_normal((b, hkv, sk, d)).astype(np.float32)).to(dtype).cuda()
+    v = torch.from_numpy(rng.standard_normal((b, hkv, sk, d)).astype(np.float32)).to(dtype).cuda()
+    k[:, :, active:] = float("nan")
+    v[:, :, active:] = float("nan")
+    scale = 1.0 / np.sqrt(d)
+    outs = []
+    try:
+        for ring in (0, 1):
+            ffi.set_option(ffi.OPT_DECODE_RING, ring)
+            outs.append(ops.attention(q, k, v, scale, active).clone())
+            act_dev = torch.tensor([active], dtype=torch.int32, device="cuda")
+            outs.append(ops.attention(q, k, v, scale, act_dev).clone())
+    finally:
+        ffi.set_option(ffi.OPT_DECODE_RING, 1)
+    ops.attention_check()
+    want = R.attention_softmax_f64(q.float().cpu().numpy(), k.float().cpu().numpy()[:, :, :active], v.float().cpu().numpy()[:, :, :active], scale, active)
+    for o in outs:
+        assert torch.isfinite(o.float()).all()
+        assert rel_err(to_np(o), want) <= 1e-2
+    same_splits = d == 64 or sk <= 130
+    if same_splits:
+        assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])
+    else:
+        ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+        assert (outs[0].float() - outs[2].float()).abs().max() <= 2 * ulp * outs[0].float().abs().max()
