@@ -560,6 +560,8 @@ extern "C" int mynn_b200_tuning_set_timing_buffer(void *buf, int slots) {
     mynn::g_i8_timing_next = 0;
     return MYNN_OK;
 }
+namespace mynn { int glue_timing_read(unsigned long long *out, unsigned *n); }
+extern "C" int mynn_b200_tuning_read_glue(unsigned long long *out, unsigned *n) { return mynn::glue_timing_read(out, n); }
 extern "C" int mynn_b200_tuning_set_stages(int n) {
     mynn::g_i8_stages_override = n;
     return MYNN_OK;

@@ -61,6 +61,22 @@ struct I8GemmParams {
 #else
 #define MYNN_STAMP(cond, slot) do { } while (0)
 #endif
+#ifdef MYNN_TUNING
+// Tuning build: CTA 0 of a limb-producer kernel records {start, end, kernel id} in a ring (read with cudaMemcpyFromSymbol).
+__device__ unsigned long long g_glue_t[3 * 1024];
+__device__ unsigned g_glue_n;
+#define MYNN_GLUE_BEGIN(id)                                                  \
+    unsigned glue_slot = 0;                                                  \
+    if (blockIdx.x == 0 && threadIdx.x == 0) {                               \
+        glue_slot = atomicAdd(&g_glue_n, 1u) % 1024u;                        \
+        g_glue_t[3 * glue_slot] = global_ns();                               \
+        g_glue_t[3 * glue_slot + 2] = (id);                                  \
+    }
+#define MYNN_GLUE_END() do { if (blockIdx.x == 0 && threadIdx.x == 0) g_glue_t[3 * glue_slot + 1] = global_ns(); } while (0)
+#else
+#define MYNN_GLUE_BEGIN(id) do { } while (0)
+#define MYNN_GLUE_END() do { } while (0)
+#endif
 
 // grid (ceil(N/128), S), cluster (1, S, 1).  NC = activation columns (3 limbs x rows, padded to 16).
 template <typename OutT, int NC>
@@ -528,6 +544,7 @@ rms_norm_limbs_kernel(int8_t *limbs, float *ascale, T *norm_out, T *sum_out, con
                       float eps, int D) {
     extern __shared__ __align__(16) float row_s[];
     __shared__ float red[40];
+    MYNN_GLUE_BEGIN(1);
     pdl_trigger();
     pdl_wait();
     const int m = blockIdx.x;
@@ -575,6 +592,7 @@ rms_norm_limbs_kernel(int8_t *limbs, float *ascale, T *norm_out, T *sum_out, con
     }
     const float sc = block_limb_scale(mx, bad, ascale + m, red);  // its barriers also publish row_s
     smem_row_to_limbs(row_s, D, limbs + (size_t)(3 * m) * D, sc);
+    MYNN_GLUE_END();
 }
 
 // h = round(swish(gate) * up) -> limbs; gate/up rows are in_stride elements apart.  F % 8 == 0, 16-byte aligned rows.
@@ -583,6 +601,7 @@ __global__ void __launch_bounds__(kRowThreads)
 swiglu_limbs_kernel(int8_t *limbs, float *ascale, const T *gate, const T *up, int F, long long in_stride) {
     extern __shared__ __align__(16) float row_s[];
     __shared__ float red[40];
+    MYNN_GLUE_BEGIN(2);
     pdl_trigger();
     pdl_wait();
     const int m = blockIdx.x;
@@ -602,6 +621,7 @@ swiglu_limbs_kernel(int8_t *limbs, float *ascale, const T *gate, const T *up, in
     }
     const float sc = block_limb_scale(mx, bad, ascale + m, red);
     smem_row_to_limbs(row_s, F, limbs + (size_t)(3 * m) * F, sc);
+    MYNN_GLUE_END();
 }
 
 // Plain pre-pass in the same style (one 1024-thread CTA per row, 16-byte loads): act -> limbs.  K % 8 == 0.
@@ -693,6 +713,11 @@ static int pick_split(int row_tiles, int kblocks) {
 }
 
 #ifdef MYNN_TUNING
+int glue_timing_read(unsigned long long *out, unsigned *n) {
+    MYNN_CUDA_OK(cudaMemcpyFromSymbol(out, g_glue_t, sizeof(unsigned long long) * 3 * 1024));
+    MYNN_CUDA_OK(cudaMemcpyFromSymbol(n, g_glue_n, sizeof(unsigned)));
+    return MYNN_OK;
+}
 unsigned long long *g_i8_timing = nullptr;  // device buffer of 8 timestamps per slot, see I8GemmParams::timing
 int g_i8_timing_slots = 1, g_i8_timing_next = 0;  // consecutive launches write consecutive slots (a captured graph keeps its slots)
 int g_i8_stages_override = 0;
