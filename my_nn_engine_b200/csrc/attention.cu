@@ -41,6 +41,7 @@ struct Map16 {  // accumulator tile i = 4h + j of the 16-bit kernel holds head-d
 // lane 0 of the consuming warp, after the warp has copied a tile into registers, so no second barrier is needed.
 constexpr int kRingDepth = 3;
 __device__ int g_ring_status;  // 31: a wait for a tile ran out of time (read and cleared by mynn_b200_attention_check)
+MYNN_DEFINE_WAIT_BUDGET_SETTER(attention_decode)
 
 template <typename T, int D, bool RING>
 __global__ void __launch_bounds__(kAttnWarps * 32, RING ? 2 : 4)

@@ -814,5 +814,7 @@ extern "C" int mynn_b200_attention_check(void *stream) {
     if (status) return fail(MYNN_E_CUDA, "attention: pipeline wait %d timed out inside the tcgen05 prefill kernel", status);
     if (int rc = attention_decode_take_status(&status)) return rc;
     if (status) return fail(MYNN_E_CUDA, "attention: wait %d for a K/V tile timed out inside the decode kernel", status);
+    if (int rc = attention_decode_q8_take_status(&status)) return rc;
+    if (status) return fail(MYNN_E_CUDA, "attention: wait %d for a K/V tile timed out inside the int8-cache decode kernel", status);
     return MYNN_OK;
 }

@@ -73,7 +73,17 @@ __device__ unsigned g_glue_n;
         g_glue_t[3 * glue_slot + 2] = (id);                                  \
     }
 #define MYNN_GLUE_END() do { if (blockIdx.x == 0 && threadIdx.x == 0) g_glue_t[3 * glue_slot + 1] = global_ns(); } while (0)
+#define MYNN_GLUE_BEGIN_C(id)                                                \
+    unsigned glue_slot = 0;                                                  \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {            \
+        glue_slot = atomicAdd(&g_glue_n, 1u) % 1024u;                        \
+        g_glue_t[3 * glue_slot] = global_ns();                               \
+        g_glue_t[3 * glue_slot + 2] = (id);                                  \
+    }
+#define MYNN_GLUE_END_C() do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_glue_t[3 * glue_slot + 1] = global_ns(); } while (0)
 #else
+#define MYNN_GLUE_BEGIN_C(id) do { } while (0)
+#define MYNN_GLUE_END_C() do { } while (0)
 #define MYNN_GLUE_BEGIN(id) do { } while (0)
 #define MYNN_GLUE_END() do { } while (0)
 #endif
@@ -510,10 +520,11 @@ __device__ __forceinline__ float block_limb_scale(float mx, bool bad, float *asc
     return red[32];
 }
 
-__device__ __forceinline__ void smem_row_to_limbs(const float *row_s, int K, int8_t *limb_row0, float sc) {
+// K elements of a row whose limb rows are `stride` bytes apart (stride == K for a whole row).
+__device__ __forceinline__ void smem_row_to_limbs(const float *row_s, int K, int8_t *limb_row0, float sc, size_t stride) {
     uint32_t *l0 = reinterpret_cast<uint32_t *>(limb_row0);
-    uint32_t *l1 = reinterpret_cast<uint32_t *>(limb_row0 + K);
-    uint32_t *l2 = reinterpret_cast<uint32_t *>(limb_row0 + 2 * (size_t)K);
+    uint32_t *l1 = reinterpret_cast<uint32_t *>(limb_row0 + stride);
+    uint32_t *l2 = reinterpret_cast<uint32_t *>(limb_row0 + 2 * stride);
     for (int gi = threadIdx.x; gi < (K >> 2); gi += blockDim.x) {
         const float4 x4 = reinterpret_cast<const float4 *>(row_s)[gi];
         const float x[4] = {x4.x, x4.y, x4.z, x4.w};
@@ -591,7 +602,7 @@ rms_norm_limbs_kernel(int8_t *limbs, float *ascale, T *norm_out, T *sum_out, con
         if (norm_out != nullptr) store8<T>(norm_out + base + i, y);
     }
     const float sc = block_limb_scale(mx, bad, ascale + m, red);  // its barriers also publish row_s
-    smem_row_to_limbs(row_s, D, limbs + (size_t)(3 * m) * D, sc);
+    smem_row_to_limbs(row_s, D, limbs + (size_t)(3 * m) * D, sc, D);
     MYNN_GLUE_END();
 }
 
@@ -620,8 +631,65 @@ swiglu_limbs_kernel(int8_t *limbs, float *ascale, const T *gate, const T *up, in
         }
     }
     const float sc = block_limb_scale(mx, bad, ascale + m, red);
-    smem_row_to_limbs(row_s, F, limbs + (size_t)(3 * m) * F, sc);
+    smem_row_to_limbs(row_s, F, limbs + (size_t)(3 * m) * F, sc, F);
     MYNN_GLUE_END();
+}
+
+// The same with a row dealt out to a cluster of C CTAs (grid (C, rows), cluster (C, 1, 1), F % (8 C) == 0).  One SM needs
+// about 2.5 us for the 14336 exponentials and divisions of a Llama-3-8B row; a quarter row per SM takes the operator off
+// the step's critical path.  Every CTA pushes the maximum of its part into the shared memory of all CTAs of its cluster
+// (remote stores, one cluster barrier), so each derives the same row scale and converts its own part.
+constexpr int kSegThreads = 512;
+template <typename T>
+__global__ void __launch_bounds__(kSegThreads)
+swiglu_limbs_cluster_kernel(int8_t *limbs, float *ascale, const T *gate, const T *up, int F, long long in_stride) {
+    extern __shared__ __align__(16) float row_s[];
+    __shared__ float red[40];
+    __shared__ float peer_max[8];  // slot r: maximum of cluster rank r's part, negative when that part held a non-finite value
+    MYNN_GLUE_BEGIN_C(2);
+    pdl_trigger();
+    pdl_wait();
+    const int C = gridDim.x, rank = (int)cluster_ctarank(), m = blockIdx.y;
+    const int seg = F / C, f0 = rank * seg;
+    float mx = 0.f;
+    bool bad = false;
+    for (int i = 8 * threadIdx.x; i < seg; i += 8 * kSegThreads) {
+        float g[8], u[8];
+        load8<T>(gate + (size_t)m * in_stride + f0 + i, g);
+        load8<T>(up + (size_t)m * in_stride + f0 + i, u);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float h = round_store<T>((g[j] / (1.0f + expf(-g[j]))) * u[j]);
+            row_s[i + j] = h;
+            bad |= !(fabsf(h) <= 3.0e38f);
+            mx = fmaxf(mx, fabsf(h));
+        }
+    }
+    mx = warp_max(mx);
+    const unsigned anybad = __syncthreads_or(bad);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x < C) {  // thread r delivers this CTA's maximum to cluster rank r
+        float t = 0.f;
+        for (int i = 0; i < kSegThreads / 32; i++) t = fmaxf(t, red[i]);
+        if (anybad) t = -1.f;
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&peer_max[rank])), "r"((uint32_t)threadIdx.x));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(t) : "memory");
+    }
+    cluster_sync_all();  // release / acquire: every part's maximum has arrived; also publishes row_s to the whole CTA
+    float t = 0.f;
+    bool rowbad = false;
+    for (int r = 0; r < C; r++) {
+        rowbad |= peer_max[r] < 0.f;
+        t = fmaxf(t, peer_max[r]);
+    }
+    int e = 0;
+    if (t > 0.f) frexpf(t, &e);
+    const float sc1 = t > 0.f ? ldexpf(1.0f, 22 - e) : 1.0f;
+    if (rank == 0 && threadIdx.x == 0) ascale[m] = rowbad ? __int_as_float(0x7fc00000) : 1.0f / sc1;  // non-finite input -> NaN outputs
+    smem_row_to_limbs(row_s, seg, limbs + (size_t)(3 * m) * F + f0, rowbad ? 0.f : sc1, (size_t)F);
+    MYNN_GLUE_END_C();
 }
 
 // Plain pre-pass in the same style (one 1024-thread CTA per row, 16-byte loads): act -> limbs.  K % 8 == 0.
@@ -645,7 +713,7 @@ __global__ void __launch_bounds__(kRowThreads) act_limbs_row_kernel(int8_t *limb
         }
     }
     const float sc = block_limb_scale(mx, bad, ascale + m, red);
-    smem_row_to_limbs(row_s, K, limbs + (size_t)(3 * m) * K, sc);
+    smem_row_to_limbs(row_s, K, limbs + (size_t)(3 * m) * K, sc, K);
 }
 
 // ---- host side --------------------------------------------------------------------------------------------------
@@ -878,6 +946,35 @@ int launch_swiglu_limbs(cudaStream_t st, int dtype, void *workspace, size_t work
     float *ascale;
     int rc = fused_ws(workspace, workspace_bytes, rows, F, &limbs, &ascale);
     if (rc) return rc;
+    // a cluster of C CTAs per row when the row is long enough to be worth a cluster barrier and the grid stays within one wave
+    int C = 1;
+    for (int c = 8; c >= 2; c >>= 1)
+        if (F % (8 * c) == 0 && F / c >= 1024 && rows * c <= 148) {
+            C = c;
+            break;
+        }
+    if (C > 1) {
+        const size_t smem = (size_t)(F / C) * 4;
+        MYNN_DISPATCH_DTYPE(dtype, T, {
+            auto kern = swiglu_limbs_cluster_kernel<T>;
+            if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(C, rows, 1);
+            cfg.blockDim = dim3(kSegThreads, 1, 1);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = C;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            MYNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, limbs, ascale, (const T *)gate, (const T *)up, F, in_stride));
+        });
+        MYNN_LAUNCH_OK("swiglu_limbs_cluster_kernel");
+        return MYNN_OK;
+    }
     const size_t smem = (size_t)F * 4;
     MYNN_DISPATCH_DTYPE(dtype, T, {
         auto kern = swiglu_limbs_kernel<T>;

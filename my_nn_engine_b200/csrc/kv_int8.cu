@@ -16,7 +16,9 @@
 //     only ever see exact small integers on the cache side.
 #include "attention_internal.cuh"
 #include "i8_cvt.cuh"
+#include "i8_gemm.cuh"
 #include "ops_internal.cuh"
+#include "tcgen05.cuh"
 
 namespace mynn {
 
@@ -181,8 +183,18 @@ __device__ __forceinline__ uint32_t load_scale_pair(const T *sc, int row, int la
 // QK^T runs on the int8 tensor-core path with no conversion of K at all: the query row of each head enters as two
 // signed 8-bit limbs of a 15-bit fixed-point value (per-head power-of-two scale, error <= 2^-15 of the row maximum, far
 // below the rounding of the 16-bit output), S = (Q0 . K + 256 Q1 . K) / sc exactly in int32.
-template <typename T, int D>
-__global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_q8_kernel(const DecodeParams p) {
+//
+// RING (head_dim 128): as in the 16-bit kernel, every warp owns a ring of kQ8RingDepth tiles in shared memory that the TMA
+// engine fills: one 32-row x 128-byte box of K and one of V per tile (2-D maps of the caches, 128-byte swizzle) plus the 32
+// row scales of each by an untiled bulk copy; the fragments and scales are then taken from shared memory.  Lane 0 of the
+// consuming warp issues the copies of tile j + depth once the warp has tile j in registers.
+constexpr int kQ8RingDepth = 3;
+__device__ int g_q8_ring_status;  // 32: a wait for a tile ran out of time
+MYNN_DEFINE_WAIT_BUDGET_SETTER(kv_int8)
+
+template <typename T, int D, bool RING>
+__global__ void __launch_bounds__(kAttnWarps * 32, RING ? 2 : 4)
+attention_decode_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
     constexpr bool F16 = std::is_same<T, __half>::value;
     constexpr int KCH = D / 64;  // 16-byte K chunks per lane per row
     constexpr int VB = D / 8;    // V bytes per lane per row
@@ -262,11 +274,80 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_q8_kernel
     float m_run = -INFINITY, l_run = 0.f;
     const int last = row_end - 1;
 
-    for (int base = row_beg + 32 * warp; base < row_end; base += 32 * kAttnWarps) {
-        // ---- issue all loads of this tile (rows past the end are clamped to a valid row and masked below) ----
+    // ring state (RING only)
+    extern __shared__ __align__(1024) uint8_t ring_raw[];
+    constexpr uint32_t kBox = 32 * 128, kTile = 2 * kBox;
+    __shared__ uint64_t full[RING ? kAttnWarps : 1][kQ8RingDepth];
+    __shared__ __align__(16) T sm_sc[RING ? kAttnWarps : 1][kQ8RingDepth][2][32];
+    __shared__ int abort_flag;
+    uint8_t *ring = ring_raw + (size_t)warp * kQ8RingDepth * kTile;
+    const int first = row_beg + 32 * warp;
+    const int ntile = first < row_end ? (row_end - first + 32 * kAttnWarps - 1) / (32 * kAttnWarps) : 0;
+    auto issue = [&](int j) {  // lane 0: tile j of this warp into stage j % depth
+        if constexpr (RING) {
+            const int s = j % kQ8RingDepth, base = first + 32 * kAttnWarps * j;
+            uint8_t *st = ring + (size_t)s * kTile;
+            const uint32_t sc_bytes = (uint32_t)min(32, p.cache_seq - base) * (uint32_t)sizeof(T);  // a multiple of 16
+            mbar_expect_tx(&full[warp][s], kTile + 2 * sc_bytes);
+            tma_load_2d(st, &map_k, 0, (int)head + base, &full[warp][s]);
+            tma_load_2d(st + kBox, &map_v, 0, (int)head + base, &full[warp][s]);
+            bulk_load_1d(&sm_sc[warp][s][0][0], ksc + base, sc_bytes, &full[warp][s]);
+            bulk_load_1d(&sm_sc[warp][s][1][0], vsc + base, sc_bytes, &full[warp][s]);
+        }
+    };
+    if constexpr (RING) {
+        if (threadIdx.x == 0) abort_flag = 0;
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < kQ8RingDepth; s++) mbar_init(&full[warp][s], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+        if (lane == 0)
+            for (int j = 0; j < min(ntile, kQ8RingDepth); j++) issue(j);
+    }
+
+    for (int base = first, j = 0; base < row_end; base += 32 * kAttnWarps, j++) {
         uint4 kr[2][2][KCH];
         uint32_t vr[2][4][VW];
         uint32_t ksr[2][2], vsr[2][2];
+        if constexpr (RING) {
+            const int s = j % kQ8RingDepth;
+            int ok_i = 1;
+            if (lane == 0) ok_i = mbar_wait_spin(&full[warp][s], (j / kQ8RingDepth) & 1, &abort_flag) ? 1 : 0;
+            if (!__shfl_sync(0xffffffffu, ok_i, 0)) {  // the copy never arrived: report it, leave the rows out
+                if (lane == 0) {
+                    atomicExch(&abort_flag, 1);
+                    atomicExch(p.status ? p.status : &g_q8_ring_status, 32);
+                }
+                break;
+            }
+            const uint8_t *st = ring + (size_t)s * kTile;
+#pragma unroll
+            for (int u = 0; u < 2; u++)
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++) {
+                    const int row = 16 * u + 8 * nt + g;  // row % 8 == g
+#pragma unroll
+                    for (int i = 0; i < KCH; i++) kr[u][nt][i] = *reinterpret_cast<const uint4 *>(st + row * 128 + (((t + 4 * i) ^ g) << 4));
+                    ksr[u][nt] = *reinterpret_cast<const uint32_t *>(&sm_sc[warp][s][0][16 * u + 8 * nt + 2 * t]);
+                    vsr[u][nt] = *reinterpret_cast<const uint32_t *>(&sm_sc[warp][s][1][16 * u + 8 * nt + 2 * t]);
+                }
+#pragma unroll
+            for (int u = 0; u < 2; u++)
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    const int row = 16 * u + 2 * t + (r & 1) + 8 * (r >> 1);
+                    const uint4 w = *reinterpret_cast<const uint4 *>(st + kBox + row * 128 + ((g ^ (row & 7)) << 4));
+                    vr[u][r][0] = w.x, vr[u][r][1] = w.y, vr[u][r][2] = w.z, vr[u][r][3] = w.w;
+                }
+            __syncwarp();  // every lane has its fragments: the stage may be refilled
+            if (lane == 0 && j + kQ8RingDepth < ntile) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue(j + kQ8RingDepth);
+            }
+        } else {
+        // ---- issue all loads of this tile (rows past the end are clamped to a valid row and masked below) ----
 #pragma unroll
         for (int u = 0; u < 2; u++)
 #pragma unroll
@@ -296,6 +377,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_q8_kernel
                 ksr[u][nt] = load_scale_pair<T>(ksc, base + 16 * u + 8 * nt + 2 * t, last, packed_scales);
                 vsr[u][nt] = load_scale_pair<T>(vsc, base + 16 * u + 8 * nt + 2 * t, last, packed_scales);
             }
+        }
         // ---- S = Q K^T in int32: k32 step (i, jj) pairs words (2jj, 2jj+1) of K chunk i with the same words of Q ----
         int s0[2][2][4], s1[2][2][4];
 #pragma unroll
@@ -350,7 +432,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_q8_kernel
                 for (int e = 0; e < 2; e++) {
                     const float pe = __expf(pv[u][nt][e] - m_new);
                     psum += pe;
-                    pv[u][nt][e] = pe * vv[e];  // the V scale of the row rides on P
+                    const bool live = base + 16 * u + 8 * nt + 2 * t + e < row_end;  // past the end the ring holds no scale
+                    pv[u][nt][e] = live ? pe * vv[e] : 0.f;  // the V scale of the row rides on P
                 }
             }
         l_run = l_run * alpha + psum;
@@ -381,7 +464,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 4) attention_decode_q8_kernel
             }
         }
     }
-    decode_tail<T, D, NACC, MapQ8<VB>>(p, o, m_run, l_run);
+    if constexpr (RING) {
+        __syncwarp();
+        decode_tail<T, D, NACC, MapQ8<VB>, true>(p, o, m_run, l_run, reinterpret_cast<float *>(ring_raw), (int)(kQ8RingDepth * kTile / 4));
+    } else {
+        decode_tail<T, D, NACC, MapQ8<VB>>(p, o, m_run, l_run);
+    }
 }
 
 // Generic form: one warp per (b, h, sq) query row, the CPU kernel's recurrence row by row with the two scales.
@@ -459,9 +547,47 @@ static int launch_q8_generic(cudaStream_t st, void *out, const void *q, const vo
     return MYNN_OK;
 }
 
+// Reads and clears the status word of the ring form (the stream must be idle).
+int attention_decode_q8_take_status(int *status) {
+    *status = 0;
+    MYNN_CUDA_OK(cudaMemcpyFromSymbol(status, g_q8_ring_status, sizeof *status));
+    if (*status) {
+        const int zero = 0;
+        MYNN_CUDA_OK(cudaMemcpyToSymbol(g_q8_ring_status, &zero, sizeof zero));
+    }
+    return MYNN_OK;
+}
+
+// The ring form: head_dim 128 (a row is one 128-byte box line), scale rows that a 16-byte bulk copy can address, the
+// driver's tensor-map encoder, and tensor rows that fit a 32-bit coordinate.
+static bool q8_ring_possible(const DecodeParams &p, int B, int D) {
+    return g_decode_ring && D == 128 && p.cache_seq % 8 == 0 && tensor_map_api_available() &&
+           (((uintptr_t)p.k_scale | (uintptr_t)p.v_scale) % 16) == 0 && (long long)B * p.Hkv * p.cache_seq < (1ll << 31);
+}
+
 template <typename T, int D>
-static int launch_decode_q8(cudaStream_t st, const DecodeParams &p, int B) {
-    MYNN_CUDA_OK(launch_pdl(attention_decode_q8_kernel<T, D>, dim3(p.splits, p.Hkv, B), dim3(kAttnWarps * 32), 0, st, p));
+static int launch_decode_q8(cudaStream_t st, const DecodeParams &p, int B, bool ring) {
+    CUtensorMap mk, mv;
+    memset(&mk, 0, sizeof mk);
+    memset(&mv, 0, sizeof mv);
+    if constexpr (D == 128) {
+        if (ring) {
+            const uint64_t rows = (uint64_t)B * p.Hkv * p.cache_seq;
+            if (int rc = make_map(&mk, p.k, rows, D, D, 32)) return rc;
+            if (int rc = make_map(&mv, p.v, rows, D, D, 32)) return rc;
+            constexpr size_t smem = (size_t)kAttnWarps * kQ8RingDepth * 2 * 32 * 128;
+            auto kern = attention_decode_q8_kernel<T, D, true>;
+            static bool attr_set = false;
+            if (!attr_set) {
+                MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                attr_set = true;
+            }
+            MYNN_CUDA_OK(launch_pdl(kern, dim3(p.splits, p.Hkv, B), dim3(kAttnWarps * 32), smem, st, mk, mv, p));
+            MYNN_LAUNCH_OK("attention_decode_q8_kernel");
+            return MYNN_OK;
+        }
+    }
+    MYNN_CUDA_OK(launch_pdl(attention_decode_q8_kernel<T, D, false>, dim3(p.splits, p.Hkv, B), dim3(kAttnWarps * 32), 0, st, mk, mv, p));
     MYNN_LAUNCH_OK("attention_decode_q8_kernel");
     return MYNN_OK;
 }
@@ -540,10 +666,11 @@ int launch_attention_q8(cudaStream_t st, void *out, const void *q, const void *k
     p.active_host = active_seq_kv;
     p.active_dev = active_seq_kv_dev;
     const int rows_bound = active_seq_kv_dev ? cache_seq_len : (active_seq_kv < cache_seq_len ? active_seq_kv : cache_seq_len);
-    p.splits = decode_splits(B, Hkv, rows_bound, 32);
+    const bool ring = q8_ring_possible(p, B, D);
+    p.splits = decode_splits(B, Hkv, rows_bound, 32, ring ? 2 : kAttnCtasPerSm);
     if (int rc = decode_bind_workspace(p, B, D, workspace, workspace_bytes)) return rc;
-    if (dtype == MYNN_BF16) return D == 64 ? launch_decode_q8<__nv_bfloat16, 64>(st, p, B) : launch_decode_q8<__nv_bfloat16, 128>(st, p, B);
-    return D == 64 ? launch_decode_q8<__half, 64>(st, p, B) : launch_decode_q8<__half, 128>(st, p, B);
+    if (dtype == MYNN_BF16) return D == 64 ? launch_decode_q8<__nv_bfloat16, 64>(st, p, B, ring) : launch_decode_q8<__nv_bfloat16, 128>(st, p, B, ring);
+    return D == 64 ? launch_decode_q8<__half, 64>(st, p, B, ring) : launch_decode_q8<__half, 128>(st, p, B, ring);
 }
 
 }  // namespace mynn

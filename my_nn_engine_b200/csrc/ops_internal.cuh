@@ -68,6 +68,7 @@ int launch_attention(cudaStream_t st, void *out, const void *q, const void *k, c
                      const AttentionFuse *fuse = nullptr, int *status_word = nullptr);
 // status_word: where the ring form of the decode kernel records a timed-out wait (null: the library's own word)
 int attention_decode_take_status(int *status);
+int attention_decode_q8_take_status(int *status);
 bool attention_decode_fast_path(int Sq, int D, int Hq, int Hkv, int dtype, const void *q, const void *k, const void *v);
 
 // Tiled tensor-core attention for several query rows (prefill chunks); see attention_prefill.cu.

@@ -157,3 +157,43 @@ def test_attention_q8_ignores_rows_past_active():
     out = ops.attention_q8(q.cuda(), torch.from_numpy(kc).cuda(), torch.from_numpy(vc).cuda(),
                            torch.from_numpy(ks).bfloat16().cuda(), torch.from_numpy(vs).bfloat16().cuda(), 0.1, active)
     assert rel_err(out.float().cpu().numpy(), want) <= 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,hq,hkv,sk,active", [(2, 8, 2, 704, 613), (3, 32, 8, 136, 97), (4, 32, 8, 4096, 4096), (1, 8, 8, 64, 1),
+                                                (2, 16, 2, 200, 200), (2, 8, 2, 129, 129)])
+def test_attention_q8_ring_and_direct_loads_agree(dtype, b, hq, hkv, sk, active):
+    """MYNN_OPT_DECODE_RING on the int8-cache decode kernel (head_dim 128): K / V boxes and the row scales through the TMA-fed
+    rings against loads issued by the threads.  Rows past active_seq_kv hold the extreme byte and NaN scales (whole boxes are
+    copied: they must not leak); a cache length that is not a multiple of 8 keeps the direct form (scale rows could not be
+    addressed by a 16-byte bulk copy); the last tile of the last head runs into the end of the tensor."""
+    from my_nn_engine_b200 import ffi
+    d = 128
+    rng = np.random.default_rng(b + hq + sk + active)
+    q = torch.from_numpy(rng.standard_normal((b, hq, 1, d)).astype(np.float32)).to(dtype)
+    kc, ks, vc, vs = _quantized_cache(rng, b, hkv, sk, d, dtype)
+    scale = 1.0 / np.sqrt(d)
+    want = R.attention(q.float().numpy(), kc, vc, scale, active, k_scale=ks, v_scale=vs)
+    kc, vc, ks, vs = kc.copy(), vc.copy(), ks.copy(), vs.copy()
+    kc[:, :, active:] = -128
+    vc[:, :, active:] = -128
+    ks[:, :, active:] = np.nan
+    vs[:, :, active:] = np.nan
+    args = (q.cuda(), torch.from_numpy(kc).cuda(), torch.from_numpy(vc).cuda(), torch.from_numpy(ks).to(dtype).cuda(),
+            torch.from_numpy(vs).to(dtype).cuda(), scale)
+    outs = []
+    try:
+        for ring in (0, 1):
+            ffi.set_option(ffi.OPT_DECODE_RING, ring)
+            outs.append(ops.attention_q8(*args, active).clone())
+            outs.append(ops.attention_q8(*args, torch.tensor([active], dtype=torch.int32, device="cuda")).clone())
+    finally:
+        ffi.set_option(ffi.OPT_DECODE_RING, 1)
+    ops.attention_check()
+    for o in outs:
+        assert torch.isfinite(o.float()).all()
+        assert rel_err(o.float().cpu().numpy(), want) <= 1e-2
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    assert (outs[0].float() - outs[2].float()).abs().max() <= 2 * ulp * outs[0].float().abs().max()
+    if sk <= 200:  # same number of splits in both forms: same sums in the same order
+        assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])
