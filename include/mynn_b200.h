@@ -354,18 +354,21 @@ int mynn_b200_model_tp_attach(void *state, const void *handles_world_x_64_bytes)
  * and leave the activations of the DequantMatMul that follows ready in its workspace.
  *
  * A group is `world` blocks of device memory, one per rank, each of mynn_b200_tp_block_bytes() bytes, 256-byte aligned,
- * zeroed once by its owner and mapped into every rank's process (cudaIpc*, or plain pointers when the ranks share a
- * process); blocks[r] is rank r's block as THIS process addresses it.
+ * initialised once by its owner with mynn_b200_tp_block_init (before any rank's first push) and mapped into every rank's
+ * process (cudaIpc*, or plain pointers when the ranks share a process); blocks[r] is rank r's block as THIS process
+ * addresses it.
  *   push     row-parallel DequantMatMul of this rank's K shard: partial[m, :] = scale[:] * (act[m, :K] . wq[:, :K]^T) in f32,
- *            N = hidden, stored from the GEMM epilogue straight into EVERY rank's block (peer stores; each value carries the
- *            number of the reduction, so no flag, fence or collective follows), buffer 0 or 1 in turn.
+ *            N = hidden, stored from the GEMM epilogue straight into EVERY rank's block (4-byte peer stores; a slot without a
+ *            value holds a reserved NaN pattern, so the value itself says that it has arrived and no flag, fence or
+ *            collective follows), buffer 0 or 1 in turn.
  *   reduce   on every rank: sum of the `world` partial rows in rank order (it waits, with a time limit, for values that have
- *            not arrived yet); x[m] = round(x[m] + round(sum)); y = round(RMSNorm(x[m]) * weight), left as the activation of
- *            the next DequantMatMul in `workspace` (call mynn_b200_dequant_matmul_same_act next; weight NULL: only x is
- *            updated).  x [M, hidden] in `dtype`; every rank computes the identical rows.
+ *            not arrived yet, and marks the slots empty again); x[m] = round(x[m] + round(sum)); y = round(RMSNorm(x[m]) *
+ *            weight), left as the activation of the next DequantMatMul in `workspace` (call mynn_b200_dequant_matmul_same_act
+ *            next; weight NULL: only x is updated).  x [M, hidden] in `dtype`; every rank computes the identical rows.
  * Both calls are made in this order, with the same M and buffer, on every rank; buffers alternate (0, 1, 0, ...); each rank
  * uses one stream.  The wait is bounded (MYNN_OPT_WAIT_BUDGET_US); mynn_b200_tp_check synchronises the stream and returns
- * MYNN_E_COMM, once, if it ran out; the ranks are in step again at the next reduction.  All ranks of a group may also live on
+ * MYNN_E_COMM, once, if it ran out.  After a rank that delivered nothing the ranks are in step again at the next reduction;
+ * if a rank may have delivered late, re-initialise the blocks with all ranks idle before going on.  All ranks of a group may also live on
  * ONE GPU as long as their calls are issued in lock step (every push before any reduce): then no kernel ever waits for one
  * that has not finished.  workspace: as for mynn_b200_dequant_matmul (push: mynn_b200_dequant_matmul_workspace_bytes(M,
  * hidden, K); reduce: the workspace of the product that follows, mynn_b200_dequant_matmul_workspace_bytes(M, N, hidden)). */
@@ -376,6 +379,7 @@ typedef struct mynn_b200_tp_group {
     int32_t hidden;
 } mynn_b200_tp_group;
 size_t mynn_b200_tp_block_bytes(int max_rows, int hidden, int world);
+int mynn_b200_tp_block_init(void *stream, void *block, int max_rows, int hidden, int world);
 int mynn_b200_tp_dequant_matmul_push(void *stream, const mynn_b200_tp_group *group, int buffer, const void *act,
                                      const int8_t *wq, const float *scale, int M, int K, int act_dtype, void *workspace,
                                      size_t workspace_bytes);

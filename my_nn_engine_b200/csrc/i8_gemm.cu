@@ -49,7 +49,7 @@ struct I8GemmParams {
     int M, N, K;
     int *status;          // device int, set non-zero on a timed-out wait
     int stages;           // pipeline depth: kStages or kMaxStages
-    I8Tp tp;              // tensor-parallel form: the outputs are delivered to every rank as tagged partial sums (mode 0: off)
+    I8Tp tp;              // tensor-parallel form: the outputs are delivered to every rank as partial sums (mode 0: off)
     int skip_last_stage;  // test aid (MYNN_OPT_INJECT_STALL): the producer leaves out the last k block, so a bounded wait expires
 #ifdef MYNN_TUNING
     unsigned long long *timing;  // 8 timestamps (ns) of CTA (0,0), or null
@@ -283,7 +283,6 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     auto combine = [](const uint32_t *a3) {
         return (long long)(int)a3[2] * 65536 + (long long)(int)a3[1] * 256 + (long long)(int)a3[0];
     };
-    const uint32_t tp_tag = p.tp.mode == 1 ? *(volatile const uint32_t *)p.tp.part_tag + 1u : 0u;  // written two reductions ago
     // An output in two steps, so that a caller can compute several values before it stores any: a store through the generic
     // `out` pointer may alias anything as far as the compiler knows, which would otherwise pin every finish behind the
     // previous one's store and expose its whole dependent chain (conversions, two products, the rounding) once per output.
@@ -295,10 +294,10 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     };
     auto deliver = [&](int m, float v) {
         if (p.tp.mode == 1) {
-            // a partial sum goes to slot [this rank] of EVERY rank's buffer: one 8-byte store {value, tag} per destination,
-            // over NVLink for the peers; the reader re-reads a word until it sees this reduction's tag, so no fence or flag
-            // follows
-            const uint2 word = make_uint2(__float_as_uint(v), tp_tag);
+            // a partial sum goes to slot [this rank] of EVERY rank's buffer: one 4-byte store per destination, over NVLink
+            // for the peers; the reader re-reads a word while it is EMPTY, so no fence or flag follows.  A NaN travels as the
+            // canonical NaN, which is not the EMPTY pattern.
+            const uint32_t word = v != v ? 0x7fc00000u : __float_as_uint(v);
             const size_t idx = ((size_t)p.tp.rank * p.tp.max_rows + m) * p.N + n_own;
             const int nr = p.tp.skip ? 0 : p.tp.world;
 #pragma unroll 1

@@ -477,7 +477,7 @@ static int model_create(Model **out, void **initializer, void **session_state) {
             delete m;
             return fail(MYNN_E_CUDA, "model_init: cudaMalloc of the peer-shared block failed: %s", cudaGetErrorString(e));
         }
-        cudaMemset(m->tp_block, 0, m->tp_block_bytes);
+        tp_block_init(nullptr, m->tp_block, m->tp_block_bytes);  // header zero, partial sums EMPTY; ordered by the synchronise below
         m->tp.rank = c.tp_rank;
         m->tp.world = tp;
         m->tp.blocks[c.tp_rank] = m->tp_block;

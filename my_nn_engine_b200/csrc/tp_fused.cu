@@ -7,17 +7,19 @@
 // epilogue, and ONE kernel per rank sums the `world` partial rows it finds in its own memory, in rank order, and finishes
 // the row: residual add, RMSNorm, limbs.
 //
-// Ordering without fences.  A partial sum is an 8-byte word {f32 value, u32 tag}, written with a single 8-byte store (such a
-// store is never torn).  The tag is the number of the reduction on that buffer, which every rank counts for itself (they all
-// run the same sequence of reductions).  The reader polls the word until its tag is the current one; a word with the
-// right tag carries the right value because both arrived in one store.  A buffer is rewritten by the reduction after the
-// next one on the other buffer; by then every rank has read it: a rank can only deliver partial sums of reduction j+2 after
-// it has finished its own reduction j+1, which needed every rank's partial sums of j+1, which those ranks computed after
-// their reduction j.
+// Ordering without fences.  A partial sum is one 4-byte word; a slot that holds no value holds the EMPTY word (kTpEmpty, a
+// NaN pattern that is never delivered).  The reader polls a 16-byte piece until none of its four words is EMPTY; a word that
+// is not EMPTY is the value, because a 4-byte store is never torn.  Having read a piece, the reader stores EMPTY back, so the
+// buffer is ready for its next use.  That next use is the reduction after the next one on the other buffer, and no value of
+// it can arrive before the reader has put EMPTY back: a rank can only deliver partial sums of reduction j+2 after it has
+// finished its own reduction j+1, which needed THIS rank's partial sums of j+1, which this rank computed after its reduction
+// j, the kernel that put EMPTY back.
 //
 // The wait is bounded (MYNN_OPT_WAIT_BUDGET_US, default 2 s): on expiry the kernel records status 21, goes on with what it
-// has and returns; the host reports MYNN_E_COMM at its next check.  A lost peer therefore never hangs a GPU, and because the
-// tags only count reductions, the ranks are in step again at the next reduction.
+// has (EMPTY reads as NaN), still puts EMPTY back and returns; the host reports MYNN_E_COMM at its next check.  A lost peer
+// therefore never hangs a GPU.  After a rank that delivered NOTHING the group is in step again at the next reduction; after
+// a rank that delivered LATE (past the budget) its stale values could be taken for those of a later reduction, so a caller
+// that has seen MYNN_E_COMM and wants to go on re-initialises the blocks (mynn_b200_tp_block_init) with all ranks idle.
 #include <cstring>
 
 #include "common.cuh"
@@ -37,7 +39,7 @@ TpLayout tp_layout(int max_rows, int hidden, int world) {
     l.max_rows = max_rows;
     l.hidden = hidden;
     size_t off = sizeof(TpHeader);
-    const size_t part = up256((size_t)world * max_rows * hidden * sizeof(uint2));  // {value, tag} words
+    const size_t part = up256((size_t)world * max_rows * hidden * sizeof(uint32_t));
     l.part_off[0] = off;
     off += part;
     l.part_off[1] = off;
@@ -46,10 +48,17 @@ TpLayout tp_layout(int max_rows, int hidden, int world) {
     return l;
 }
 
+// header zero, every partial-sum word EMPTY
+int tp_block_init(cudaStream_t st, char *block, size_t bytes) {
+    MYNN_CUDA_OK(cudaMemsetAsync(block, 0, sizeof(TpHeader), st));
+    MYNN_CUDA_OK(cudaMemsetAsync(block + sizeof(TpHeader), 0xFF, bytes - sizeof(TpHeader), st));
+    return MYNN_OK;
+}
+
 constexpr int kTpThreads = 1024;
 
-// 16 bytes = two {value, tag} words written by a peer GPU: a volatile load, so that every poll goes to L2
-__device__ __forceinline__ uint4 ld_volatile_u4(const uint2 *p) {
+// 16 bytes = four partial sums written by peer GPUs: a volatile load, so that every poll goes to L2
+__device__ __forceinline__ uint4 ld_volatile_u4(const uint32_t *p) {
     uint4 v;
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
@@ -58,17 +67,15 @@ __device__ __forceinline__ uint4 ld_volatile_u4(const uint2 *p) {
 // grid = rows.  limbs / ascale / w may be null (then only x is updated).  part = this rank's partial buffer `buf`.
 template <typename T>
 __global__ void __launch_bounds__(kTpThreads)
-tp_reduce_norm_limbs_kernel(int8_t *limbs, float *ascale, T *x, const T *w, float eps, int D, int buf, TpHeader *hdr, const uint2 *part,
-                            int world, int max_rows) {
+tp_reduce_norm_limbs_kernel(int8_t *limbs, float *ascale, T *x, const T *w, float eps, int D, TpHeader *hdr, uint32_t *part, int world,
+                            int max_rows) {
     extern __shared__ __align__(16) float row_s[];
     __shared__ float red[40];
     const int m = blockIdx.x;
-    // the tag the partial sums of THIS reduction carry (the previous reduction on this buffer was number part_tag)
-    const uint32_t tag = *(volatile uint32_t *)&hdr->part_tag[buf] + 1u;
-    // 1. read the partial rows of all ranks, re-reading a word until it carries this reduction's tag (bounded); 2. add them
-    // in rank order; 3. residual add
+    // 1. read the partial rows of all ranks, re-reading a piece while any of its words is EMPTY (bounded), and put EMPTY back;
+    // 2. add them in rank order; 3. residual add
     const size_t slot_stride = (size_t)max_rows * D;
-    const uint2 *prow = part + (size_t)m * D;
+    uint32_t *prow = part + (size_t)m * D;
     T *xrow = x + (size_t)m * D;
     float ss = 0.f;
     unsigned long long t0 = 0;
@@ -78,12 +85,11 @@ tp_reduce_norm_limbs_kernel(int8_t *limbs, float *ascale, T *x, const T *w, floa
 #pragma unroll
         for (int r = 0; r < kTpMaxRanks; r++)
             if (r < world) {
-                const uint2 *src = prow + (size_t)r * slot_stride + i;
-                uint4 a, b;
+                uint32_t *src = prow + (size_t)r * slot_stride + i;
+                uint4 a;
                 for (uint32_t it = 0;; it++) {
                     a = ld_volatile_u4(src);
-                    b = ld_volatile_u4(src + 2);
-                    if ((a.y == tag && a.w == tag && b.y == tag && b.w == tag) || gave_up) break;
+                    if ((a.x != kTpEmpty && a.y != kTpEmpty && a.z != kTpEmpty && a.w != kTpEmpty) || gave_up) break;
                     if ((it & 63) == 63) {  // the clock is read rarely: the common case is no wait at all
                         const unsigned long long now = global_ns();
                         if (t0 == 0) t0 = now;
@@ -93,7 +99,8 @@ tp_reduce_norm_limbs_kernel(int8_t *limbs, float *ascale, T *x, const T *w, floa
                         }
                     }
                 }
-                v[r] = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+                *reinterpret_cast<uint4 *>(src) = make_uint4(kTpEmpty, kTpEmpty, kTpEmpty, kTpEmpty);  // ready for the next use
+                v[r] = make_float4(__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w));
             }
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -172,16 +179,6 @@ tp_reduce_norm_limbs_kernel(int8_t *limbs, float *ascale, T *x, const T *w, floa
             l0[gi + 2 * (D >> 2)] = w2;
         }
     }
-    // the last CTA to finish advances the tag of this buffer for the next reduction on it
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(&hdr->ticket, 1u) == gridDim.x - 1) {
-            hdr->ticket = 0u;
-            hdr->part_tag[buf] = tag;
-            __threadfence();
-        }
-    }
 }
 
 int launch_tp_gemm_push(cudaStream_t st, const TpPeers &peers, int buf, const void *act, const int8_t *wq, const float *scale, int M,
@@ -197,8 +194,7 @@ int launch_tp_gemm_push(cudaStream_t st, const TpPeers &peers, int buf, const vo
     t.world = peers.world;
     t.rank = peers.rank;
     t.max_rows = peers.lay.max_rows;
-    for (int r = 0; r < peers.world; r++) t.part[r] = reinterpret_cast<uint2 *>(peers.blocks[r] + peers.lay.part_off[buf]);
-    t.part_tag = &tp_header(peers.blocks[peers.rank])->part_tag[buf];
+    for (int r = 0; r < peers.world; r++) t.part[r] = reinterpret_cast<uint32_t *>(peers.blocks[r] + peers.lay.part_off[buf]);
     t.skip = skip_delivery;
     return i8_gemm_launch_tp(st, nullptr, act, wq, scale, nullptr, M, N, K, act_dtype, MYNN_F32, workspace, workspace_bytes, &t, nullptr, nullptr);
 }
@@ -222,8 +218,8 @@ int launch_tp_reduce_norm_limbs(cudaStream_t st, int dtype, const TpPeers &peers
     MYNN_DISPATCH_DTYPE(dtype, T, {
         auto kern = tp_reduce_norm_limbs_kernel<T>;
         if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<M, kTpThreads, smem, st>>>(limbs, ascale, (T *)x, (const T *)w, eps, D, buf, tp_header(own),
-                                          reinterpret_cast<const uint2 *>(own + peers.lay.part_off[buf]), peers.world, peers.lay.max_rows);
+        kern<<<M, kTpThreads, smem, st>>>(limbs, ascale, (T *)x, (const T *)w, eps, D, tp_header(own),
+                                          reinterpret_cast<uint32_t *>(own + peers.lay.part_off[buf]), peers.world, peers.lay.max_rows);
     });
     MYNN_LAUNCH_OK("tp_reduce_norm_limbs_kernel");
     return MYNN_OK;
@@ -252,6 +248,13 @@ using namespace mynn;
 extern "C" size_t mynn_b200_tp_block_bytes(int max_rows, int hidden, int world) {
     if (max_rows < 1 || max_rows > kI8MaxRows || hidden < 16 || hidden % 16 || world < 1 || world > kTpMaxRanks) return 0;
     return tp_layout(max_rows, hidden, world).bytes;
+}
+
+extern "C" int mynn_b200_tp_block_init(void *stream, void *block, int max_rows, int hidden, int world) {
+    const size_t bytes = mynn_b200_tp_block_bytes(max_rows, hidden, world);
+    if (!bytes) return fail(MYNN_E_ARG, "tp_block_init: bad geometry (%d rows x %d, %d ranks)", max_rows, hidden, world);
+    if (!block || (uintptr_t)block % 256) return fail(MYNN_E_ARG, "tp_block_init: block is null or not 256-byte aligned");
+    return tp_block_init((cudaStream_t)stream, (char *)block, bytes);
 }
 
 extern "C" int mynn_b200_tp_dequant_matmul_push(void *stream, const mynn_b200_tp_group *group, int buffer, const void *act,

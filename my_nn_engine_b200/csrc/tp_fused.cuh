@@ -3,17 +3,19 @@
 //
 // Data flow of one reduction over `world` ranks:
 //   1. the row-parallel DequantMatMul (o_proj, down_proj) of every rank STORES its f32 partial sums straight into slot
-//      [its own rank] of the partial buffer of EVERY rank (plain peer stores over NVLink, issued from the GEMM epilogue).
-//      Every value travels as an 8-byte word {value, tag} written with one store, the tag being the number of the reduction:
-//      the receiver needs no flag and the sender no fence (a system-scope release costs microseconds, and there would be
-//      one per CTA and destination);
-//   2. one kernel per rank reads the `world` partial rows from its OWN memory, re-reading a word until it carries the tag of
-//      this reduction, adds them in rank order (every rank computes the identical sum), and finishes the row: residual add,
-//      RMSNorm, activation limbs of the next DequantMatMul in the local workspace.
-// One NVLink hop per reduction, no load ever crosses NVLink, no fence, no collective call, and nothing here uses multicast.
-// (Measured against it on the same step: reading the peers' partial sums with peer loads behind a flag barrier, 3.89 ms per
-// step at 2 ranks; a reduce-scatter by rows plus an all-gather of the finished limb rows, which moves 1/world of the bytes
-// but needs two hops and a system-scope release per hop, 4.24 ms.)
+//      [its own rank] of the partial buffer of EVERY rank (plain 4-byte peer stores over NVLink, issued from the GEMM
+//      epilogue, 128 contiguous bytes per warp).  A slot that holds no value yet holds the EMPTY word 0xFFFFFFFF, a NaN
+//      pattern no product ever stores (a NaN result is delivered as the canonical NaN), so the value itself tells the
+//      receiver that it has arrived: no flag, no tag, and no fence on the sender (a system-scope release costs microseconds,
+//      and there would be one per CTA and destination);
+//   2. one kernel per rank reads the `world` partial rows from its OWN memory, re-reading a 16-byte piece until none of its
+//      words is EMPTY, puts EMPTY back, adds the values in rank order (every rank computes the identical sum), and finishes
+//      the row: residual add, RMSNorm, activation limbs of the next DequantMatMul in the local workspace.
+// One NVLink hop per reduction, 4 bytes per value, no load ever crosses NVLink, no collective call, nothing uses multicast.
+// (Measured against it on the same step: every value as an 8-byte {value, number of the reduction} word, which needs no
+// EMPTY words but moves twice the bytes over NVLink and through the reducing kernel; reading the peers' partial sums with
+// peer loads behind a flag barrier, 3.89 ms per step at 2 ranks against 3.69; a reduce-scatter by rows plus an all-gather of
+// the finished limb rows, which moves 1/world of the bytes but needs two hops and a system-scope release per hop, 4.24 ms.)
 #pragma once
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -23,21 +25,23 @@ namespace mynn {
 
 constexpr int kTpMaxRanks = 8;  // ranks of one NVLink domain; sizes the pointer arrays below
 
-// Header of the block of device memory every rank shares with its peers; a block must be zeroed once before its first use.
+constexpr uint32_t kTpEmpty = 0xFFFFFFFFu;  // "no value yet" in a partial buffer
+
+// Header of the block of device memory every rank shares with its peers.  Before its first use a block's header is zeroed
+// and every byte behind it set to 0xFF (mynn_b200_tp_block_init).
 struct TpHeader {
-    uint32_t part_tag[2];  // number of reductions run on each partial buffer = tag of the last one (written by this rank only)
-    uint32_t ticket;       // CTA arrival counter of the running reduction kernel
-    int status;            // 21: a wait for partial sums ran out of time
-    uint32_t pad[60];
+    int status;  // 21: a wait for partial sums ran out of time
+    uint32_t pad[63];
 };
 static_assert(sizeof(TpHeader) == 256, "TpHeader is one 256-byte header");
 
 // Geometry of a block; identical on every rank.
 struct TpLayout {
     int world, max_rows, hidden;
-    size_t part_off[2], bytes;  // each partial buffer: [source rank][row][hidden] words of {value, tag}
+    size_t part_off[2], bytes;  // each partial buffer: [source rank][row][hidden] f32 words (kTpEmpty: not there yet)
 };
 TpLayout tp_layout(int max_rows, int hidden, int world);
+int tp_block_init(cudaStream_t st, char *block, size_t bytes);  // header zero, every partial-sum word EMPTY
 
 // A rank's view of the group: its own block and every rank's block as mapped into this process (blocks[rank] == own).
 struct TpPeers {
@@ -48,16 +52,15 @@ struct TpPeers {
 
 __host__ __device__ inline TpHeader *tp_header(char *blk) { return reinterpret_cast<TpHeader *>(blk); }
 
-// What the tcgen05 DequantMatMul kernel needs to deliver its outputs as tagged partial sums (passed by value in its parameters).
+// What the tcgen05 DequantMatMul kernel needs to deliver its outputs as partial sums (passed by value in its parameters).
 struct I8Tp {
     int mode;                   // 0: plain output; 1: the outputs go to slot [rank] of every rank's partial buffer
     int world, rank, max_rows;
-    uint2 *part[kTpMaxRanks];   // partial buffer of every rank
-    const uint32_t *part_tag;   // own header's count of reductions on this buffer; this product's tag is that + 1
+    uint32_t *part[kTpMaxRanks];  // partial buffer of every rank
     int skip;                   // test aid: deliver nothing
 };
 
-// Row-parallel DequantMatMul whose f32 outputs go to every rank as tagged partial sums.  act == nullptr: limbs already in
+// Row-parallel DequantMatMul whose f32 outputs go to every rank as partial sums.  act == nullptr: limbs already in
 // `workspace`.  skip_delivery (test aid): run the product but deliver nothing.
 int launch_tp_gemm_push(cudaStream_t st, const TpPeers &peers, int buf, const void *act, const int8_t *wq, const float *scale, int M,
                         int N, int K, int act_dtype, void *workspace, size_t workspace_bytes, int skip_delivery);

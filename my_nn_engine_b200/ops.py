@@ -369,7 +369,7 @@ def attention_streaming(q, k, v, scale: float, active_seq_kv: int, is_causal: bo
 # ---- fused tensor-parallel operators (one TpGroup per rank; see include/mynn_b200.h) ----------------------------------
 class TpGroup:
     """One rank's view of a tensor-parallel group: ``blocks`` are the uint8 CUDA tensors of every rank's shared block as this
-    process sees them (zeroed, ``tp_block_bytes`` each; blocks[rank] is the rank's own)."""
+    process sees them (``tp_block_bytes`` each, initialised by their owner with ``tp_block_init``; blocks[rank] is the rank's own)."""
 
     def __init__(self, blocks, rank: int, max_rows: int, hidden: int):
         self.blocks, self.rank, self.world, self.max_rows, self.hidden = list(blocks), rank, len(blocks), max_rows, hidden
@@ -381,6 +381,12 @@ class TpGroup:
 
 def tp_block_bytes(max_rows: int, hidden: int, world: int) -> int:
     return ffi.lib().mynn_b200_tp_block_bytes(max_rows, hidden, world)
+
+
+def tp_block_init(block, max_rows: int, hidden: int, world: int) -> None:
+    """Header zero, every partial-sum slot empty; once per block, before any rank's first push (and again, with all ranks
+    idle, after a reduction that timed out on a late peer)."""
+    ffi.check(ffi.lib().mynn_b200_tp_block_init(_stream(), _ptr(block), max_rows, hidden, world))
 
 
 def tp_dequant_matmul_push(group: TpGroup, buffer: int, act, wq, scale, workspace="auto"):

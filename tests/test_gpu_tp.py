@@ -1,6 +1,6 @@
 """Tensor-parallel decode on 2, 4 and 8 GPUs (each case is skipped when the box has fewer): every rank's logits / greedy ids
 against the CPU ORACLE of the unsharded model, with the per-layer reduction done either by the fused peer-memory operators
-(the row-parallel product stores its tagged partial sums into every rank's memory, each rank reduces + adds + norms) or by
+(the row-parallel product stores its partial sums into every rank's memory, each rank reduces + adds + norms) or by
 ncclAllReduce inside the captured step.  Ranks are child processes with NVLS off; failures are made on the host (a rank
 that leaves a delivery out), no GPU fault is provoked, and every device-side wait is bounded."""
 import os
@@ -172,7 +172,7 @@ def _stall_rank_main(rank, world, port, q):
 def test_a_rank_that_delivers_nothing_is_reported_not_waited_for():
     """Rank 1 leaves the deliveries of one row-parallel product out (host-side switch).  Every rank's reduction waits 50 ms for
     the missing partial sums, records its status and carries on; the step returns MYNN_E_COMM on the host; the following step
-    is clean again on both ranks (the tags only count reductions); both ranks exit cleanly."""
+    is clean again on both ranks (every reduction leaves the slots it read empty again); both ranks exit cleanly."""
     from my_nn_engine_b200 import ffi
     q, procs = _spawn(2, _stall_rank_main, ())
     got = {r: (c, ids) for r, c, ids in (q.get(timeout=300) for _ in range(2))}

@@ -16,7 +16,9 @@ def make_groups(world, max_rows, hidden):
     from my_nn_engine_b200 import ops
     nbytes = ops.tp_block_bytes(max_rows, hidden, world)
     assert nbytes > 0
-    blocks = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    blocks = [torch.empty(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    for b in blocks:
+        ops.tp_block_init(b, max_rows, hidden, world)
     return [ops.TpGroup(blocks, r, max_rows, hidden) for r in range(world)]
 
 
@@ -42,7 +44,7 @@ def test_lock_step_ranks_match_the_unsharded_oracle(world, m, hidden, k_total, n
     xs = [torch.from_numpy(x0).bfloat16().cuda() for _ in range(world)]  # every rank's copy of the residual stream
     x_ref = x0
     ksh = k_total // world
-    for it in range(3):  # three reductions on alternating buffers: the counters and their expected values advance
+    for it in range(3):  # three reductions on alternating buffers: every slot is emptied by the reduction that read it
         buf = it & 1
         w_row = rng.integers(-127, 128, size=(hidden, k_total), dtype=np.int8)
         s_row = rng.uniform(0.0002, 0.002, hidden).astype(np.float32)
@@ -89,8 +91,9 @@ def _small_problem(rng, hidden=256, k_total=512, m=8):
 
 def test_wait_for_partial_sums_runs_out_when_a_rank_never_delivers():
     """Two ranks; only rank 0 runs its product.  Rank 0's reduction waits 20 ms for rank 1's partial sums, records status 21,
-    finishes and returns; tp_check reports MYNN_E_COMM once.  The tags only count reductions, so the SAME group works again at
-    the next reduction, and so does a product whose deliveries were switched off by MYNN_OPT_INJECT_STALL = 2."""
+    finishes and returns; tp_check reports MYNN_E_COMM once.  The reduction leaves every slot it read empty again, so after a
+    rank that delivered NOTHING the same group works again at the next reduction, and so does a product whose deliveries were
+    switched off by MYNN_OPT_INJECT_STALL = 2."""
     from my_nn_engine_b200 import ffi, ops
     rng = np.random.default_rng(1)
     w_row, s_row, act, x, w_norm, w_col, s_col = _small_problem(rng)
