@@ -4,14 +4,15 @@
 //   * assigns one CTA to (kv-row split, kv head, batch) so that all query heads of a GQA group share a single
 //     pass over their KV head (the engine's kernel re-reads the KV head once per query head and walks the rows
 //     serially, src/codegen/cuda/cpp/attention.cuh:495-606);
-//   * lets each of its 4 warps take 16-row tiles whose K and V bytes every lane pulls straight from global memory
-//     into registers with 128-bit loads, laid out as mma.m16n8k16 operand fragments: the head-dim index (for
-//     QK^T) and the kv-row pairing (for PV) are permuted so that no shared-memory transpose is needed;
+//   * lets each of its 4 warps take 16-row tiles laid out as mma.m16n8k16 operand fragments: the head-dim index (for
+//     QK^T) and the kv-row pairing (for PV) are permuted so that a 16-byte piece of a row IS a fragment and no transpose
+//     is needed.  The pieces come out of per-warp rings in shared memory that the TMA engine fills three tiles ahead
+//     (default), or straight from global memory with 128-bit loads (MYNN_OPT_DECODE_RING = 0: 128 registers, 4 CTAs per SM);
 //   * computes S = Q K^T (A = Q, padded to 16 heads) and O^T = V^T P^T (A = V^T, B = P^T, so the 8-column B tile is
 //     the head group and no accumulator register is wasted) on the tensor cores with f32 accumulation and an
 //     online softmax in f32; P enters as a high 16-bit part plus its rounding remainder (~16 significant bits);
-//   * stays within 128 registers and 17 KB of shared memory so that 16 warps per SM hide the latency of the
-//     dependent load -> MMA chain -> softmax -> MMA sequence;
+//   * in the decoder step also rotates q and the new key and appends the new key / value rows (RoPE + KVCacheUpdate),
+//     and leaves a finished output row as the activation limbs of the o_proj DequantMatMul;
 //   * merges the warps through shared memory, and the splits through a small global workspace where the last
 //     CTA to arrive (atomic ticket, no spinning) combines the partial results and writes the output.
 // Everything else (f32 tensors, head dims other than 64/128, groups larger than 8, more than one query row,
