@@ -71,6 +71,7 @@ tp_reduce_norm_limbs_kernel(int8_t *limbs, float *ascale, T *x, const T *w, floa
                             int max_rows) {
     extern __shared__ __align__(16) float row_s[];
     __shared__ float red[40];
+    pdl_trigger();  // the DequantMatMul that follows may set up and stream its first weight tiles while this kernel waits and sums
     const int m = blockIdx.x;
     // 1. read the partial rows of all ranks, re-reading a piece while any of its words is EMPTY (bounded), and put EMPTY back;
     // 2. add them in rank order; 3. residual add
