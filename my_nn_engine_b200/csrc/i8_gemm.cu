@@ -248,6 +248,10 @@ i8_stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if (lane == 0) ok_i = mbar_wait_spin(&accum_bar, 0, &abort_flag) ? 1 : 0;
         const bool ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
         MYNN_STAMP(threadIdx.x == 64, 3);  // accumulators complete
+        // Delivering form: the kernel that sums the partial sums polls for them word by word and touches nothing else this
+        // kernel still reads, so it may become resident now (if it was launched as a programmatic dependent) instead of
+        // after this grid's slowest CTA has left.
+        if (p.tp.mode == 1 && threadIdx.x == 64) pdl_trigger();
         if (!ok) {
             atomicExch(&abort_flag, 1);
             atomicExch(p.status, 3);

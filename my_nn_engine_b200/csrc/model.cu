@@ -155,7 +155,7 @@ static int enqueue_forward(Model &m, cudaStream_t st, int S) {
     };
     auto reduce = [&](int buf, const void *w) -> int {  // fused reduction of the partial sums in buffer `buf`
         reduced_limbs = w != nullptr;
-        return launch_tp_reduce_norm_limbs(st, dt, m.tp, buf, m.gemm_ws, m.gemm_ws_bytes, m.x, w, c.rms_eps, M);
+        return launch_tp_reduce_norm_limbs(st, dt, m.tp, buf, m.gemm_ws, m.gemm_ws_bytes, m.x, w, c.rms_eps, M, true);  // always right behind its push
     };
     auto norm = [&](const void *w, const float *part, int rows, const void *src) -> int {
         n_limbs2 = false;

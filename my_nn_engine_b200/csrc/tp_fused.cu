@@ -201,7 +201,7 @@ int launch_tp_gemm_push(cudaStream_t st, const TpPeers &peers, int buf, const vo
 }
 
 int launch_tp_reduce_norm_limbs(cudaStream_t st, int dtype, const TpPeers &peers, int buf, void *workspace, size_t workspace_bytes,
-                                void *x, const void *w, float eps, int M) {
+                                void *x, const void *w, float eps, int M, bool after_push) {
     const int D = peers.lay.hidden;
     if (buf != 0 && buf != 1) return fail(MYNN_E_ARG, "tp reduce: buffer %d", buf);
     if (M < 1 || M > peers.lay.max_rows || D % 16) return fail(MYNN_E_UNSUPPORTED, "tp reduce: rows=%d D=%d not supported", M, D);
@@ -219,8 +219,23 @@ int launch_tp_reduce_norm_limbs(cudaStream_t st, int dtype, const TpPeers &peers
     MYNN_DISPATCH_DTYPE(dtype, T, {
         auto kern = tp_reduce_norm_limbs_kernel<T>;
         if (smem > 48 * 1024) MYNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<M, kTpThreads, smem, st>>>(limbs, ascale, (T *)x, (const T *)w, eps, D, tp_header(own),
-                                          reinterpret_cast<uint32_t *>(own + peers.lay.part_off[buf]), peers.world, peers.lay.max_rows);
+        // after_push (the caller guarantees that the kernel in front of this one on the stream is the delivering DequantMatMul
+        // of the same reduction): launched as a programmatic dependent of that grid, which triggers once its main loop is
+        // over.  This kernel contains no griddepcontrol.wait because every value it needs from that grid is polled for, and
+        // what else it reads (x) and writes (x, the limb workspace) that grid no longer touches by the time a row's values
+        // are complete: a row is complete only when every CTA of the grid has finished its main loop and reached its epilogue.
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(M, 1, 1);
+        cfg.blockDim = dim3(kTpThreads, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = after_push ? 1 : 0;
+        MYNN_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, limbs, ascale, (T *)x, (const T *)w, eps, D, tp_header(own),
+                                        reinterpret_cast<uint32_t *>(own + peers.lay.part_off[buf]), (int)peers.world, (int)peers.lay.max_rows));
     });
     MYNN_LAUNCH_OK("tp_reduce_norm_limbs_kernel");
     return MYNN_OK;
@@ -275,7 +290,7 @@ extern "C" int mynn_b200_tp_reduce_norm(void *stream, const mynn_b200_tp_group *
     TpPeers peers;
     if (int rc = group_to_peers(group, peers, "tp_reduce_norm")) return rc;
     if (!x) return fail(MYNN_E_ARG, "tp_reduce_norm: null pointer");
-    return launch_tp_reduce_norm_limbs((cudaStream_t)stream, dtype, peers, buffer, workspace, workspace_bytes, x, weight, eps, M);
+    return launch_tp_reduce_norm_limbs((cudaStream_t)stream, dtype, peers, buffer, workspace, workspace_bytes, x, weight, eps, M, false);
 }
 
 extern "C" int mynn_b200_tp_check(void *stream, const mynn_b200_tp_group *group) {

@@ -65,8 +65,9 @@ struct I8Tp {
 int launch_tp_gemm_push(cudaStream_t st, const TpPeers &peers, int buf, const void *act, const int8_t *wq, const float *scale, int M,
                         int N, int K, int act_dtype, void *workspace, size_t workspace_bytes, int skip_delivery);
 // sum over ranks of the partial rows -> x = round(x + round(sum)); if w != null: y = round(RMSNorm(x) * w) -> limbs + row
-// scales in `workspace` (the DequantMatMul workspace of the product that follows).
+// scales in `workspace` (the DequantMatMul workspace of the product that follows).  after_push: the kernel in front of this
+// one on the stream is the delivering DequantMatMul of the same reduction (the two may then overlap).
 int launch_tp_reduce_norm_limbs(cudaStream_t st, int dtype, const TpPeers &peers, int buf, void *workspace, size_t workspace_bytes,
-                                void *x, const void *w, float eps, int M);
+                                void *x, const void *w, float eps, int M, bool after_push);
 
 }  // namespace mynn
