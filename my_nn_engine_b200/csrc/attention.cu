@@ -57,7 +57,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int G = p.G;
     int active = p.active_dev ? *p.active_dev : p.active_host;
     active = max(0, min(active, p.cache_seq));
-    const int rows_per_split = (((active + p.splits - 1) / p.splits) + 15) & ~15;
+    // whole rounds of the CTA's four warps (64 rows): a split that ends inside a round leaves some warps a tile short
+    const int rows_per_split = (((active + p.splits - 1) / p.splits) + 16 * kAttnWarps - 1) / (16 * kAttnWarps) * (16 * kAttnWarps);
     const int row_beg = split * rows_per_split;
     const int row_end = min(row_beg + rows_per_split, active);
 
@@ -68,6 +69,44 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int new_row = fused ? *p.fused_row : -1;
     const size_t tab = fused ? (size_t)(*p.fused_pos) * D : 0;
     const T *cos_t = reinterpret_cast<const T *>(p.cos_t), *sin_t = reinterpret_cast<const T *>(p.sin_t);
+    // the rows this CTA reads from the cache: with the fused append the new row is not there yet
+    const int cache_end = fused ? min(row_end, new_row) : row_end;
+
+    // Ring set-up and the copies of the first tiles come first: they travel while the query fragments are built.
+    extern __shared__ __align__(1024) uint8_t ring_raw[];
+    constexpr int NB = D / 64;                      // 128-byte boxes per K (and per V) row
+    constexpr uint32_t kBox = 16 * 128;             // one box: 16 rows x 128 bytes
+    constexpr uint32_t kTile = 2 * NB * kBox;       // K boxes, then V boxes
+    __shared__ uint64_t full[RING ? kAttnWarps : 1][kRingDepth];
+    __shared__ int abort_flag;
+    uint8_t *ring = ring_raw + (size_t)warp * kRingDepth * kTile;
+    const int first = row_beg + 16 * warp;
+    const int ntile = first < cache_end ? (cache_end - first + 16 * kAttnWarps - 1) / (16 * kAttnWarps) : 0;
+    const int y0 = (b * p.Hkv + kvh) * p.cache_seq + first;  // tensor row of this warp's first tile
+    auto issue = [&](int j) {  // lane 0: tile j of this warp into stage j % depth
+        if constexpr (RING) {
+            const int s = j % kRingDepth;
+            uint8_t *st = ring + (size_t)s * kTile;
+            const int y = y0 + 16 * kAttnWarps * j;
+            mbar_expect_tx(&full[warp][s], kTile);
+#pragma unroll
+            for (int hf = 0; hf < NB; hf++) {
+                tma_load_2d(st + hf * kBox, &map_k, 128 * hf, y, &full[warp][s]);  // byte maps: x counts bytes
+                tma_load_2d(st + (NB + hf) * kBox, &map_v, 128 * hf, y, &full[warp][s]);
+            }
+        }
+    };
+    if constexpr (RING) {
+        if (threadIdx.x == 0) abort_flag = 0;
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < kRingDepth; s++) mbar_init(&full[warp][s], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+        if (lane == 0)
+            for (int j = 0; j < min(ntile, kRingDepth); j++) issue(j);
+    }
     // x rotated against its partner xp (the element half a head away): low half x c - xp s, high half x c + xp s, rounded to
     // the storage type as the stand-alone RoPE kernel rounds it
     auto rot4 = [&](uint2 x, uint2 xp, int d0, bool low) {
@@ -179,40 +218,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
     };
 
-    // the rows this CTA reads from the cache: with the fused append the new row is not there yet
-    const int cache_end = fused ? min(row_end, new_row) : row_end;
     const int last = cache_end - 1;
-    extern __shared__ __align__(1024) uint8_t ring_raw[];
-    constexpr int NB = D / 64;                      // 128-byte boxes per K (and per V) row
-    constexpr uint32_t kBox = 16 * 128;             // one box: 16 rows x 128 bytes
-    constexpr uint32_t kTile = 2 * NB * kBox;       // K boxes, then V boxes
     if constexpr (RING) {
-        __shared__ uint64_t full[kAttnWarps][kRingDepth];
-        __shared__ int abort_flag;
-        uint8_t *ring = ring_raw + (size_t)warp * kRingDepth * kTile;
-        const int first = row_beg + 16 * warp;
-        const int ntile = first < cache_end ? (cache_end - first + 16 * kAttnWarps - 1) / (16 * kAttnWarps) : 0;
-        const int y0 = (b * p.Hkv + kvh) * p.cache_seq + first;  // tensor row of this warp's first tile
-        if (threadIdx.x == 0) abort_flag = 0;
-        if (lane == 0) {
-#pragma unroll
-            for (int s = 0; s < kRingDepth; s++) mbar_init(&full[warp][s], 1);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        }
-        __syncthreads();
-        auto issue = [&](int j) {  // lane 0: tile j of this warp into stage j % depth
-            const int s = j % kRingDepth;
-            uint8_t *st = ring + (size_t)s * kTile;
-            const int y = y0 + 16 * kAttnWarps * j;
-            mbar_expect_tx(&full[warp][s], kTile);
-#pragma unroll
-            for (int hf = 0; hf < NB; hf++) {
-                tma_load_2d(st + hf * kBox, &map_k, 128 * hf, y, &full[warp][s]);  // byte maps: x counts bytes
-                tma_load_2d(st + (NB + hf) * kBox, &map_v, 128 * hf, y, &full[warp][s]);
-            }
-        };
-        if (lane == 0)
-            for (int j = 0; j < min(ntile, kRingDepth); j++) issue(j);
         for (int j = 0; j < ntile; j++) {
             const int s = j % kRingDepth;
             const int base = first + 16 * kAttnWarps * j;

@@ -283,6 +283,7 @@ inline int decode_splits(int B, int Hkv, int rows_bound, int tile_rows = 16, int
     if (s > cap) s = cap;
     if (s < 1) s = 1;
     if (s > kMaxSplits) s = kMaxSplits;
+    if (s > 8) s &= ~7;  // the merge takes the splits eight at a time: a ninth costs a round trip for an eighth of the rows
     return s;
 }
 

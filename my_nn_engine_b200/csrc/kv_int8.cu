@@ -211,7 +211,8 @@ attention_decode_q8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     const int G = p.G;
     int active = p.active_dev ? *p.active_dev : p.active_host;
     active = max(0, min(active, p.cache_seq));
-    const int rows_per_split = (((active + p.splits - 1) / p.splits) + 15) & ~15;
+    // whole rounds of the CTA's four warps (128 rows): a split that ends inside a round leaves some warps a tile short
+    const int rows_per_split = (((active + p.splits - 1) / p.splits) + 32 * kAttnWarps - 1) / (32 * kAttnWarps) * (32 * kAttnWarps);
     const int row_beg = split * rows_per_split;
     const int row_end = min(row_beg + rows_per_split, active);
 
