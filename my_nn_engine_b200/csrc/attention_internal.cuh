@@ -274,16 +274,27 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, const float (
     decode_row_limbs<T, D>(p, b, &sm_row_last, sm_red);
 }
 
-// All CTAs of a launch last equally long, so the grid should fit in ONE wave of resident CTAs (148 SMs): a partly
-// filled second wave would cost as much time as a full one.
+// How many CTAs share the rows of one (batch, kv head) pair.  All CTAs of a launch last equally long, so the grid should fit
+// in ONE wave of resident CTAs (148 SMs): a partly filled second wave would cost as much time as a full one.  A split is not
+// free either: its partial result goes through the merge (a round trip through L2 per eight splits, plus the tail of one
+// more CTA), so a split gets at least four tiles per warp, and more than eight splits are only used when a split would
+// otherwise be longer than 32 tiles per warp.  (Measured, 2048 rows, 32 pairs: 1 / 2 / 4 / 8 / 16 / 32 splits = 30 / 21 / 15 /
+// 16 / 22 / 33 us; 256 rows, 4 pairs: 1 / 2 / 4 splits = 4.8 / 7.4 / 7.2 us.)
 inline int decode_splits(int B, int Hkv, int rows_bound, int tile_rows = 16, int ctas_per_sm = kAttnCtasPerSm) {
     const int pairs = B * Hkv;
+    const int round = tile_rows * kAttnWarps;  // rows the four warps of a CTA take at a time
     int s = (ctas_per_sm * 148) / pairs;
-    const int cap = rows_bound / (tile_rows * kAttnWarps);  // at least one tile per warp and split
+    int cap = rows_bound / (4 * round);
+    if (cap < 1) cap = 1;
     if (s > cap) s = cap;
     if (s < 1) s = 1;
+    if (s > 8) {
+        const int long_rows = rows_bound / (32 * round);
+        s = s < long_rows ? s : long_rows;
+        if (s < 8) s = 8;
+        s &= ~7;  // the merge takes the splits eight at a time
+    }
     if (s > kMaxSplits) s = kMaxSplits;
-    if (s > 8) s &= ~7;  // the merge takes the splits eight at a time: a ninth costs a round trip for an eighth of the rows
     return s;
 }
 
