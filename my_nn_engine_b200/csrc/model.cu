@@ -54,6 +54,7 @@ struct Model {
     int64_t *pos_dev;  // positions of a prefill chunk
     int32_t *tok_dev;
     char *h_in = nullptr;  // pinned mirror of the input block
+    int *h_status = nullptr;  // pinned: status words of the GEMM workspace and of the tensor-parallel block, fetched with the result
     void *x, *n, *qkv, *q_rot, *attn, *gu, *h, *last_x, *logits, *logits_full;
     float *part, *pairs, *pairs_all;  // part = f32 partial sums of a row-parallel product (tp_world > 1, ncclAllReduce path)
     char *tp_block = nullptr;         // cudaMalloc'd block shared with the peers (fused reduction of decode steps, tp_fused.cuh)
@@ -484,6 +485,7 @@ static int model_create(Model **out, void **initializer, void **session_state) {
     }
     e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMallocHost((void **)&m->h_in, 16 + R * 8);
+    if (e == cudaSuccess) e = cudaMallocHost((void **)&m->h_status, 2 * sizeof(int));
     if (e != cudaSuccess) {
         cudaFree(m->arena);
         delete m;
@@ -542,18 +544,24 @@ static int copy_result_to_host(Model &m, void *dst) {
     } else {
         MYNN_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, m.stream));
     }
+    // the status words of the bounded waits travel with the result: one synchronisation per step, not one per word
+    int *hs = m.h_status;
+    hs[0] = hs[1] = 0;
+    if (m.gemm_ws) MYNN_CUDA_OK(cudaMemcpyAsync(&hs[0], m.gemm_ws, sizeof(int), cudaMemcpyDeviceToHost, m.stream));
+    if (m.tp_attached)
+        MYNN_CUDA_OK(cudaMemcpyAsync(&hs[1], &tp_header(m.tp_block)->status, sizeof(int), cudaMemcpyDeviceToHost, m.stream));
     MYNN_CUDA_OK(cudaStreamSynchronize(m.stream));
-    if (m.gemm_ws) RC(mynn_b200_dequant_matmul_check(m.stream, m.gemm_ws));
+    if (hs[0]) RC(mynn_b200_dequant_matmul_check(m.stream, m.gemm_ws));  // reports the code and clears the word
     if (m.tc_attention_ran) {  // prefill chunks of 64 and more rows: the tcgen05 attention has bounded waits of its own
         m.tc_attention_ran = false;
         int pfa = 0;
         RC(attention_prefill_tc_take_status(&pfa));
         if (pfa) return fail(MYNN_E_CUDA, "model: pipeline wait %d timed out inside the tcgen05 prefill attention", pfa);
     }
-    if (m.tp_attached) {
-        int *word = &tp_header(m.tp_block)->status, st_ = 0;
-        MYNN_CUDA_OK(cudaMemcpy(&st_, word, sizeof st_, cudaMemcpyDeviceToHost));
-        if (st_) {
+    if (hs[1]) {
+        int *word = &tp_header(m.tp_block)->status;
+        const int st_ = hs[1];
+        {
             MYNN_CUDA_OK(cudaMemset(word, 0, sizeof st_));
             return fail(MYNN_E_COMM, "tensor-parallel reduction: a wait for a peer ran out of time (status %d)", st_);
         }
@@ -631,6 +639,7 @@ extern "C" void model_destroy(void *state) {
     if (m->stream) cudaStreamDestroy(m->stream);
     if (m->arena) cudaFree(m->arena);
     if (m->h_in) cudaFreeHost(m->h_in);
+    if (m->h_status) cudaFreeHost(m->h_status);
     for (int r = 0; r < m->tp.world; r++)
         if (m->tp_attached && r != m->tp.rank && m->tp.blocks[r]) cudaIpcCloseMemHandle(m->tp.blocks[r]);
     if (m->tp_block) cudaFree(m->tp_block);

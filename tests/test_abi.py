@@ -84,3 +84,4 @@ def test_set_option_validates_without_a_device():
     assert lib.mynn_b200_set_option(ffi.OPT_WAIT_BUDGET_US, 0) == ffi.E_ARG
     assert lib.mynn_b200_set_option(ffi.OPT_INJECT_STALL, 5) == ffi.E_ARG
     assert lib.mynn_b200_set_option(ffi.OPT_FUSE_ROPE, 2) == ffi.E_ARG and lib.mynn_b200_set_option(ffi.OPT_FUSE_ROPE, 1) == ffi.OK
+    assert lib.mynn_b200_set_option(ffi.OPT_DECODE_RING, -1) == ffi.E_ARG and lib.mynn_b200_set_option(ffi.OPT_DECODE_RING, 1) == ffi.OK
