@@ -387,6 +387,11 @@ int mynn_b200_tp_reduce_norm(void *stream, const mynn_b200_tp_group *group, int 
                              int M, int dtype, void *workspace, size_t workspace_bytes);
 int mynn_b200_tp_check(void *stream, const mynn_b200_tp_group *group);
 
+/* How many CTAs the 16-bit decode attention kernel lets share the kv rows of one (batch, kv head) pair, given an upper bound
+ * of the rows and the number of CTAs of that kernel an SM holds (2 for the ring form at head_dim 128, else 4).  Pure host
+ * arithmetic, exported so that an integrator can see what mynn_b200_attention_workspace_bytes is sized for. */
+int mynn_b200_attention_decode_splits(int B, int Hkv, int rows_bound, int ctas_per_sm);
+
 /* Kernels launched by this library since load (monotonic). */
 int64_t mynn_b200_launch_count(void);
 

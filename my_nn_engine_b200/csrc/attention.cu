@@ -492,6 +492,11 @@ int mynn::attention_decode_take_status(int *status) {
     return MYNN_OK;
 }
 
+extern "C" int mynn_b200_attention_decode_splits(int B, int Hkv, int rows_bound, int ctas_per_sm) {
+    if (B < 1 || Hkv < 1 || rows_bound < 0 || ctas_per_sm < 1) return 0;
+    return mynn::decode_splits(B, Hkv, rows_bound, 16, ctas_per_sm);
+}
+
 extern "C" int mynn_b200_attention(void *stream, void *out, const void *q, const void *k, const void *v, float scale,
                                    int B, int Hq, int Hkv, int Sq, int D, int cache_seq_len, int active_seq_kv,
                                    const int32_t *active_seq_kv_dev, int is_causal, int dtype, void *workspace,

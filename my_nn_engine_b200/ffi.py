@@ -89,6 +89,7 @@ SIGNATURES = {
     "mynn_b200_model_stream": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
     "mynn_b200_model_tp_export": (c_int, [c_void_p, c_void_p]),
     "mynn_b200_model_tp_attach": (c_int, [c_void_p, c_void_p]),
+    "mynn_b200_attention_decode_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "mynn_b200_tp_block_bytes": (c_size_t, [c_int, c_int, c_int]),
     "mynn_b200_tp_block_init": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int]),
     "mynn_b200_tp_dequant_matmul_push": (c_int, [c_void_p, POINTER(TpGroup), c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t]),

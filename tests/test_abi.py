@@ -85,3 +85,24 @@ def test_set_option_validates_without_a_device():
     assert lib.mynn_b200_set_option(ffi.OPT_INJECT_STALL, 5) == ffi.E_ARG
     assert lib.mynn_b200_set_option(ffi.OPT_FUSE_ROPE, 2) == ffi.E_ARG and lib.mynn_b200_set_option(ffi.OPT_FUSE_ROPE, 1) == ffi.OK
     assert lib.mynn_b200_set_option(ffi.OPT_DECODE_RING, -1) == ffi.E_ARG and lib.mynn_b200_set_option(ffi.OPT_DECODE_RING, 1) == ffi.OK
+
+
+def test_decode_attention_split_rule():
+    """Host arithmetic of the kv-row split: one wave of CTAs, at least four tiles per warp and split, at most eight splits
+    unless a split would exceed 2048 rows, and then full chunks of eight."""
+    lib = ffi.lib()
+    f = lib.mynn_b200_attention_decode_splits
+    assert f(32, 8, 2112, 2) == 1          # the benchmark step: 256 pairs fill the wave
+    assert f(16, 8, 4096, 2) == 2          # config 3
+    assert f(32, 2, 2112, 2) == 4 and f(32, 1, 2112, 2) == 8   # tensor-parallel shards
+    assert f(1, 4, 264, 4) == 1            # a short context is not split
+    assert f(1, 4, 1024, 4) == 4
+    assert f(1, 8, 8192, 2) == 8 and f(1, 8, 32768, 2) == 16 and f(1, 8, 1 << 20, 2) == 32
+    assert f(0, 8, 100, 2) == 0
+    for pairs in (1, 3, 8, 40, 300):
+        last = 1
+        for rows in (16, 255, 256, 1000, 5000, 70000):
+            s = f(pairs, 1, rows, 2)
+            assert 1 <= s <= 64 and s * pairs <= max(296, pairs) and (s <= 8 or s % 8 == 0)
+            assert s >= last  # more rows never mean fewer splits
+            last = s
