@@ -237,13 +237,37 @@ def run_gpu_arm(args, cfg):
     steps, warm, blocks = args.steps, max(args.warmup, 8), max(args.blocks, 1)  # the first 8 steps are always run (their ids are reported)
     max_seq = CONTEXT + warm + steps + 16
     state = random_llama_state(cfg, seed=0, device=str(dev))  # identical on every rank (same seed)
-    model = DecoderModel(cfg, state, dtype="bf16", max_seq_len=max_seq, batch=BATCH, tp_rank=rank, tp_world=world,
-                         output="ids", use_graph=True, kv_int8=args.kv == "int8")
-    fill_synthetic_context(model, cfg, rank, world, dev)
+    def build_model(output, fused):
+        m = DecoderModel(cfg, state, dtype="bf16", max_seq_len=max_seq, batch=BATCH, tp_rank=rank, tp_world=world,
+                         output=output, use_graph=True, kv_int8=args.kv == "int8", tp_fused=fused)
+        fill_synthetic_context(m, cfg, rank, world, dev)
+        return m
+
+    model = build_model("ids", True)
     ids0 = torch.randint(0, cfg["vocab_size"], (BATCH,), device=dev, dtype=torch.int64,
                          generator=torch.Generator(device=dev).manual_seed(7))
     stream = torch.cuda.Stream(device=dev)  # a real stream handle: the library treats NULL as the model's own stream
     torch.cuda.set_stream(stream)
+    # Several GPUs: one step through the host entry first, which reads the status words of the bounded waits.  If the
+    # peer-memory reduction reports a wait that ran out (a width this build could not be tried on), every rank switches to
+    # the NCCL all-reduce together, and the line says so, instead of spending the whole run in timed-out waits.
+    tp_note = None
+    if world > 1 and model.tp_fused:
+        ok = 1
+        ffi.set_option(ffi.OPT_WAIT_BUDGET_US, 300000)
+        try:
+            model.step(ids0.cpu(), CONTEXT)
+        except ffi.MynnError as exc:
+            ok, tp_note = 0, str(exc)
+        ffi.set_option(ffi.OPT_WAIT_BUDGET_US, 2000000)
+        agreed = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            dist.barrier()
+            torch.cuda.synchronize()
+            model.close()
+            model = build_model("ids", False)
+            tp_note = "nccl all-reduce: the peer-memory reduction reported a timed-out wait at this width (%s)" % (tp_note or "on another rank")
 
     def barrier():
         if world > 1:
@@ -324,9 +348,7 @@ def run_gpu_arm(args, cfg):
     # ---- the engine's own output mode: full logits to the host every step, argmax there ----
     e2e_logits = None
     if not args.no_logits:
-        lm = DecoderModel(cfg, state, dtype="bf16", max_seq_len=max_seq, batch=BATCH, tp_rank=rank, tp_world=world,
-                          output="logits", use_graph=True, kv_int8=args.kv == "int8")
-        fill_synthetic_context(lm, cfg, rank, world, dev)
+        lm = build_model("logits", tp_fused or world == 1)
         ms_lg, _ = time_e2e(lm, past0)
         e2e_logits = {"value": BATCH * 1e3 / ms_lg, "unit": UNIT, "ms_per_step": ms_lg, "h2d_bytes_per_step": lm.h2d_bytes_per_step,
                       "d2h_bytes_per_step": lm.d2h_bytes_per_step,
@@ -344,7 +366,7 @@ def run_gpu_arm(args, cfg):
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": workload_name(cfg), "parallelism": f"tp{world}", "l2": "inputs larger than L2",
                            "kv_cache": "int8 + per-token scale (quant_kv_cache option; not the headline configuration)" if kv_int8 else "bf16",
-                           "tp_reduce": ("nvlink peer memory, fused with add + rmsnorm" if tp_fused else ("nccl" if world > 1 else "none"))},
+                           "tp_reduce": ("nvlink peer memory, fused with add + rmsnorm" if tp_fused else ((tp_note or "nccl") if world > 1 else "none"))},
                 "timed_blocks": {"blocks": blocks, "steps_per_block": steps, "ms_per_step_median": ms_dev,
                                  "ms_per_step_min": srt[0], "ms_per_step_max": srt[-1]},
                 "clocks": clocks.summary(),
