@@ -106,3 +106,26 @@ def test_decode_attention_split_rule():
             assert 1 <= s <= 64 and s * pairs <= max(296, pairs) and (s <= 8 or s % 8 == 0)
             assert s >= last  # more rows never mean fewer splits
             last = s
+
+
+def test_tensor_parallel_block_geometry_and_argument_checks():
+    """Host-side checks of the fused tensor-parallel operators: block size = 256-byte header + two buffers of
+    world x max_rows x hidden f32 words (each rounded up to 256 bytes); bad geometry, null or misaligned blocks and bad ranks
+    are refused before anything touches a device."""
+    import ctypes
+    lib = ffi.lib()
+    assert lib.mynn_b200_tp_block_bytes(32, 4096, 8) == 256 + 2 * 8 * 32 * 4096 * 4
+    assert lib.mynn_b200_tp_block_bytes(5, 48, 3) == 256 + 2 * ((3 * 5 * 48 * 4 + 255) // 256 * 256)
+    for bad in ((0, 4096, 2), (33, 4096, 2), (32, 4100, 2), (32, 8, 2), (32, 4096, 0), (32, 4096, 9)):
+        assert lib.mynn_b200_tp_block_bytes(*bad) == 0
+        assert lib.mynn_b200_tp_block_init(None, ctypes.c_void_p(4096), *bad) == ffi.E_ARG
+    assert lib.mynn_b200_tp_block_init(None, None, 32, 4096, 2) == ffi.E_ARG
+    assert lib.mynn_b200_tp_block_init(None, ctypes.c_void_p(4096 + 16), 32, 4096, 2) == ffi.E_ARG  # not 256-byte aligned
+    g = ffi.TpGroup()
+    g.rank, g.world, g.max_rows, g.hidden = 2, 2, 32, 4096  # rank outside the group
+    assert lib.mynn_b200_tp_check(None, ctypes.byref(g)) == ffi.E_ARG
+    g.rank, g.world = 0, 9
+    assert lib.mynn_b200_tp_reduce_norm(None, ctypes.byref(g), 0, ctypes.c_void_p(256), None, 1e-5, 1, ffi.BF16, None, 0) == ffi.E_ARG
+    g.world = 2  # blocks are null
+    assert lib.mynn_b200_tp_dequant_matmul_push(None, ctypes.byref(g), 0, ctypes.c_void_p(256), ctypes.c_void_p(256), ctypes.c_void_p(256),
+                                                1, 64, ffi.BF16, None, 0) == ffi.E_ARG
