@@ -454,7 +454,7 @@ def kernel_roofline(model, cfg, world, dev):
     n, k, m = 2 * f, h, BATCH
     alg = n * k + n * 2 + m * k * 2 + m * n * 2
     # DRAM traffic of one launch: dram__bytes_read.sum + dram__bytes_write.sum of a separate ncu capture of this kernel at
-    # this shape on one GPU (117,935,616 + 4,291,328 bytes); not measured by this run, and not available for a shard
+    # this shape on one GPU (117,945,856 + 3,616,256 bytes); not measured by this run, and not available for a shard
     traffic = 117945856 + 3616256 if world == 1 else None
     return {"kernel": "i8_stream_gemm_kernel (gate/up DequantMatMul, M=32, N=%d, K=%d; limbs written by the preceding kernel as in the step)" % (n, k),
             "bound": "hbm", "achieved": alg / us / 1e3, "unit": "GB/s", "us_per_launch": us, "algorithmic_bytes": alg,
