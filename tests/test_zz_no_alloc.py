@@ -4,10 +4,13 @@ Some hosts of this library cannot give an operator scratch memory: the engine's 
 operand and its planner has already spent the device-memory budget when a step runs.  For them the library keeps the
 split-KV partial results in a 4 MiB array of its own.  The test drives that entry point through the C ABI twice in a
 row (the array is shared and keeps the last call's contents, so the second call proves it is reusable) and compares
-with the regular entry point, which gets a caller-owned workspace, to the tolerance of the other attention tests."""
+with the CPU oracle (two-pass softmax attention in float64) and with the regular entry point, which gets a caller-owned
+workspace, to the tolerance of the other attention tests."""
 import numpy as np
 import pytest
 import torch
+
+from oracle import ref_ops as R
 
 pytestmark = pytest.mark.gpu
 
@@ -33,12 +36,15 @@ def test_noalloc_decode_attention_matches_workspace_entry_point_twice(dtype):
         v = torch.randn(b, hkv, sk, d, device="cuda", generator=g).to(dtype)
         scale = 1.0 / np.sqrt(d)
         want = ops.attention(q, k, v, scale, active).float()
+        oracle = R.attention_softmax_f64(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), scale, active)
         for call in range(2):  # second call reuses the array as the first left it
             out = torch.full_like(q, float("nan"))
             ffi.check(_call_noalloc(ffi, q, k, v, scale, active, out))
             torch.cuda.synchronize()
             err = (out.float() - want).abs().max().item() / want.abs().max().item()
             assert err <= 1e-2, (call, err)
+            got = out.float().cpu().numpy()
+            assert np.abs(got - oracle).max() / np.abs(oracle).max() <= 1e-2, call
         # device-side active length, as a replayed step would pass it
         act_dev = torch.tensor([active], dtype=torch.int32, device="cuda")
         out = torch.full_like(q, float("nan"))
