@@ -95,6 +95,23 @@ def _oracle_run(case):
     return np.stack(logits)
 
 
+def _collect(q, procs, world, timeout=600.0):
+    """One result per rank from the queue; gives up at once (instead of waiting out the timeout) when a rank has died."""
+    import queue
+    import time
+    got, t0 = [], time.time()
+    while len(got) < world:
+        try:
+            got.append(q.get(timeout=2.0))
+            continue
+        except queue.Empty:
+            pass
+        dead = [(i, p.exitcode) for i, p in enumerate(procs) if p.exitcode not in (None, 0)]
+        assert not dead, f"rank processes died (rank, exit code): {dead}"
+        assert time.time() - t0 < timeout, f"only {len(got)} of {world} ranks answered within {timeout:.0f} s"
+    return got
+
+
 def _spawn(world, target, args):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -113,7 +130,7 @@ def test_tensor_parallel_matches_the_oracle(world, case):
     modes = ("logits", "ids", "logits_nccl") if case == "mid" else ("logits", "ids")
     q, procs = _spawn(world, _rank_main, (case, modes))
     want = _oracle_run(case)  # the unsharded model on the CPU, while the ranks run
-    got = dict(q.get(timeout=600) for _ in range(world))
+    got = dict(_collect(q, procs, world))
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
@@ -175,7 +192,7 @@ def test_a_rank_that_delivers_nothing_is_reported_not_waited_for():
     is clean again on both ranks (every reduction leaves the slots it read empty again); both ranks exit cleanly."""
     from my_nn_engine_b200 import ffi
     q, procs = _spawn(2, _stall_rank_main, ())
-    got = {r: (c, ids) for r, c, ids in (q.get(timeout=300) for _ in range(2))}
+    got = {r: (c, ids) for r, c, ids in _collect(q, procs, 2, timeout=300.0)}
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
