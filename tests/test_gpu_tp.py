@@ -116,7 +116,7 @@ def _spawn(world, target, args):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=target, args=(r, world, port, q) + args) for r in range(world)]
+    procs = [ctx.Process(target=target, args=(r, world, port, q) + args, daemon=True) for r in range(world)]  # never outlive the test run
     for p in procs:
         p.start()
     return q, procs
